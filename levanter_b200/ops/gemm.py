@@ -1,0 +1,176 @@
+"""bf16 GEMM on tcgen05 tensor cores (see ``csrc/gemm_bf16.cu``) and the ``linear`` autograd op on top of it.
+
+Replaces the dense projections that the reference lowers through ``hnn.Linear`` /
+``hax.dot`` (src/levanter/layers/attention.py:1606-1635, src/levanter/models/llama.py:273-280).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import lib
+
+F_OUT_F32 = 1
+F_ACCUMULATE = 2
+F_BIAS = 4
+F_RESIDUAL = 8
+F_BIAS_F32 = 16
+
+_gemm_fn = None
+
+
+def _fn():
+    global _gemm_fn
+    if _gemm_fn is None:
+        c = lib
+        _gemm_fn = lib.fn(
+            "lvb_gemm_bf16",
+            [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+             c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p],
+        )
+    return _gemm_fn
+
+
+def _rowmajor_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError(f"expected a 2-D tensor, got {tuple(t.shape)}")
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, accumulate=False,
+                   bias=None, residual=None, alpha=1.0):
+    """PyTorch fp32 statement of :func:`gemm` (used on CPU and as the test oracle)."""
+    af = (a.t() if a_mn else a).float()
+    bf = (b if b_mn else b.t()).float()
+    c = alpha * (af @ bf)
+    if bias is not None:
+        c = c + bias.float()
+    if residual is not None:
+        c = c + residual.float()
+    if out is not None:
+        if accumulate:
+            c = c + out.float()
+        out.copy_(c.to(out.dtype))
+        return out
+    return c.to(out_dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    alpha: float = 1.0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+residual) (+C)``.
+
+    ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]`` or ``[K,N]``.
+    Inputs are bf16; the accumulator is fp32; ``out`` may be bf16 or fp32.
+    """
+    if not (a.is_cuda and lib.available()):
+        return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
+                              bias=bias, residual=residual, alpha=alpha)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm expects bf16 operands")
+    a = _rowmajor_2d(a)
+    b = _rowmajor_2d(b)
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"reduction dims differ: {K} vs {Kb}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        if accumulate:
+            raise ValueError("accumulate=True needs out=")
+    else:
+        if out.shape != (M, N) or out.stride(1) != 1:
+            raise ValueError("out has the wrong shape or is not row-major")
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= F_OUT_F32
+    elif out.dtype != torch.bfloat16:
+        raise TypeError("out must be bf16 or fp32")
+    if accumulate:
+        flags |= F_ACCUMULATE
+    if bias is not None:
+        flags |= F_BIAS
+        if bias.dtype == torch.float32:
+            flags |= F_BIAS_F32
+        bias = bias.contiguous()
+    ldr = 0
+    if residual is not None:
+        flags |= F_RESIDUAL
+        if residual.dtype != torch.bfloat16 or residual.stride(-1) != 1:
+            residual = residual.to(torch.bfloat16).contiguous()
+        residual = residual.view(M, N) if residual.dim() != 2 else residual
+        ldr = residual.stride(0)
+    rc = _fn()(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr, int(max_ctas),
+        lib.status_buffer().data_ptr(), lib.stream_ptr(),
+    )
+    lib.check_rc(rc, "lvb_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T (+ b).  ``weight`` is ``[out, in]``.
+
+    If ``weight`` carries a ``main_grad`` attribute (an fp32 buffer of the same shape, owned by the
+    sharded-gradient engine) the weight gradient is accumulated straight into it by the GEMM
+    epilogue and autograd sees no dense weight gradient.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = gemm(x2, weight, bias=bias)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = shp
+        ctx.weight_ref = weight
+        return y.view(*shp[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(ctx.weight_ref, "main_grad", None)
+            if main_grad is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype if weight.dtype in (torch.bfloat16, torch.float32) else torch.float32)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Linear layer on the tcgen05 GEMM when running bf16 on a B200; ``F.linear`` otherwise."""
+    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,101 @@
+"""ctypes binding to the in-tree sm_100a kernel library.
+
+The library is loaded lazily the first time a kernel is needed.  On a machine
+with a CUDA device a missing or unloadable library is an error (never a silent
+fallback to eager PyTorch); on a CPU-only machine :func:`available` is False and
+callers use their PyTorch reference implementations.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+_status: dict[int, torch.Tensor] = {}
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_longlong = ctypes.c_longlong
+
+
+def cuda_ok() -> bool:
+    return torch.cuda.is_available()
+
+
+def available() -> bool:
+    """True when the native kernels can run here (a CUDA device of compute capability 10.x)."""
+    if not cuda_ok():
+        return False
+    major, _ = torch.cuda.get_device_capability()
+    return major == 10
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.lib_path()
+            if not path.exists():
+                path = _build.build()
+            _lib = ctypes.CDLL(str(path))
+    return _lib
+
+
+def fn(name: str, argtypes: list, restype=c_int):
+    f = getattr(load(), name)
+    f.argtypes = argtypes
+    f.restype = restype
+    return f
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def status_buffer() -> torch.Tensor:
+    """Per-device int32[8] word that kernels write a timeout / bounds code into."""
+    dev = torch.cuda.current_device()
+    buf = _status.get(dev)
+    if buf is None:
+        buf = torch.zeros(8, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = buf
+    return buf
+
+
+class KernelStatusError(RuntimeError):
+    pass
+
+
+def check_status(reset: bool = True) -> None:
+    """Read the status word (device->host sync) and raise if a kernel recorded a failure."""
+    if not _status:
+        return
+    for dev, buf in _status.items():
+        vals = buf.tolist()
+        if vals[0] != 0:
+            if reset:
+                buf.zero_()
+            names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument", 4: "bounds check"}
+            raise KernelStatusError(
+                f"kernel status on cuda:{dev}: {names.get(vals[0], vals[0])} "
+                f"(cta={vals[1]}, site={vals[2]}, extra={vals[3]})"
+            )
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        names = {-1: "bad argument", -2: "CUDA launch error", -3: "tensor-map encode failed", -4: "size beyond limit"}
+        raise RuntimeError(f"{what}: {names.get(rc, rc)}")

@@ -1,0 +1,79 @@
+"""tcgen05 GEMM against a PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+from levanter_b200.ops import gemm as G
+from levanter_b200.ops import lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * 0.5).to(torch.bfloat16)
+
+
+def _check(c, ref, K):
+    err = (c.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item() + 1e-6
+    assert err / scale < 2e-2, f"rel err {err/scale}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 264, 200), (1000, 136, 72), (77, 96, 512), (2048, 4096, 1024)])
+def test_gemm_matches_fp32(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    if a_mn and (M % 8):
+        pytest.skip("MN-major A needs M % 8 == 0 (row stride multiple of 16 bytes)")
+    if b_mn and (N % 8):
+        pytest.skip("MN-major B needs N % 8 == 0")
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    c = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    lib.check_status()
+    ref = G.gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _check(c, ref, K)
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 300, 520, 328
+    a, b = _rand(M, K), _rand(N, K)
+    bias = _rand(N)
+    res = _rand(M, N)
+    c = G.gemm(a, b, bias=bias, residual=res, alpha=0.5)
+    ref = G.gemm_reference(a, b, bias=bias, residual=res, alpha=0.5, out_dtype=torch.float32)
+    _check(c, ref, K)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    acc0 = acc.clone()
+    G.gemm(a, b, out=acc, accumulate=True)
+    ref = acc0 + a.float() @ b.float().t()
+    _check(acc, ref, K)
+    lib.check_status()
+
+
+def test_linear_autograd():
+    torch.manual_seed(2)
+    x = _rand(4, 96, 256).requires_grad_()
+    w = _rand(384, 256).requires_grad_()
+    bias = _rand(384).requires_grad_()
+    y = G.linear(x, w, bias)
+    g = _rand(4, 96, 384)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    br = bias.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    _check(y, yr, 256)
+    _check(x.grad, xr.grad, 384)
+    _check(w.grad, wr.grad, 384)
+    _check(bias.grad, br.grad, 384)
+    lib.check_status()
+
+
+def test_gemm_deterministic():
+    a, b = _rand(512, 512), _rand(768, 512)
+    c1 = G.gemm(a, b).clone()
+    c2 = G.gemm(a, b)
+    assert torch.equal(c1, c2)
