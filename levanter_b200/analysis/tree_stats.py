@@ -1,0 +1,39 @@
+"""Per-parameter norms and histograms of a parameter-shaped tree (src/levanter/analysis/tree_stats.py:17-102)."""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..optim.config import levanter_path
+from ..tracker.histogram import Histogram
+
+
+def summary_statistics_for_tree(prefix: str, tree: Dict[str, Optional[torch.Tensor]], split_scan_layers: bool = True,
+                                include_histogram: bool = False, include_norms: bool = True,
+                                include_per_parameter_norms: bool = True, group=None, sharded: bool = False) -> Dict[str, Any]:
+    """Metrics ``<prefix>/norm/<path>``, ``<prefix>/norm/total`` and ``<prefix>/hist/<path>``.  With
+    ``split_scan_layers`` every layer gets its own entry (``.../layers/3/...``); otherwise layers are aggregated under
+    the stacked path.  ``sharded`` trees hold local slices: squared norms and histogram counts are summed over ``group``."""
+    out: Dict[str, Any] = {}
+    names = [k for k, v in tree.items() if v is not None]
+    if not names:
+        return out
+    if include_norms:
+        sq = torch.stack([(tree[k].float() ** 2).sum() for k in names])
+        if sharded and dist.is_initialized():
+            dist.all_reduce(sq, group=group)
+        keyed: Dict[str, torch.Tensor] = {}
+        for k, v in zip(names, sq):
+            key = k if split_scan_layers else levanter_path(k)
+            keyed[key] = keyed.get(key, 0) + v
+        if include_per_parameter_norms:
+            for key, v in keyed.items():
+                out[f"{prefix}/norm/{key.replace('.', '/')}"] = torch.sqrt(v)
+        out[f"{prefix}/norm/total"] = torch.sqrt(sq.sum())
+    if include_histogram:
+        for k in names:
+            key = k if split_scan_layers else levanter_path(k)
+            out[f"{prefix}/hist/{key.replace('.', '/')}"] = Histogram.from_array(tree[k], group=group, sharded=sharded)
+    return out

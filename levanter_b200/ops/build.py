@@ -43,7 +43,7 @@ def _nvcc() -> str:
 
 
 def _sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
 
 
 def _digest(paths: list[Path]) -> str:
@@ -78,7 +78,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(src: Path) -> Path:
         obj = LIBDIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        flags = NVCC_FLAGS if src.suffix == ".cu" else ["-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+        cmd = [nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         logs[src.name] = r.stderr + r.stdout
         if r.returncode != 0:
@@ -88,7 +89,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
     out = lib_path()
-    cmd = [nvcc, "-shared", "-o", str(out), *[str(o) for o in objs], "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", str(out), *[str(o) for o in objs], "-gencode", "arch=compute_100a,code=sm_100a", "-ldl", "-lpthread"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stderr}")

@@ -1,0 +1,139 @@
+// Optimizer kernels over flat parameter shards.
+//
+//  * sumsq: deterministic two-stage sum of squares (global gradient norm; the cross-rank part is a
+//    tiny all-reduce done by the caller)
+//  * clip_coef: min(1, max_norm / (norm + 1e-6)) kept on the device so no host sync is needed
+//  * adamw: clip -> Adam moments -> bias correction -> decoupled weight decay -> -lr, in the order
+//    of the reference's optax chain (src/levanter/optim/config.py:458-494), writing the fp32 master
+//    weights and the bf16 compute copy in one pass.
+#include "common.cuh"
+
+namespace lvb {
+namespace optim {
+
+constexpr int kBlock = 256;
+constexpr int kMaxParts = 1024;
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock) sumsq_partial_kernel(const T* __restrict__ x, long long n,
+                                                               float* __restrict__ partial) {
+  float acc = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    float v = ldf<T>(x, i);
+    acc += v * v;
+  }
+  acc = warp_sum(acc);
+  __shared__ float sm[kBlock / 32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < kBlock / 32; ++w) s += sm[w];
+    partial[blockIdx.x] = s;
+  }
+}
+
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out,
+                                   int accumulate) {
+  // single warp, fixed order: deterministic
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 32) acc += partial[i];
+  acc = warp_sum(acc);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + acc : acc;
+}
+
+__global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm, float* __restrict__ coef,
+                                 float* __restrict__ norm_out) {
+  const float norm = sqrtf(sumsq[0]);
+  if (norm_out != nullptr) norm_out[0] = norm;
+  coef[0] = (max_norm > 0.f && norm > max_norm) ? max_norm / (norm + 1e-6f) : 1.f;
+}
+
+template <typename G>
+__global__ void __launch_bounds__(kBlock)
+adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, const G* __restrict__ g,
+             __nv_bfloat16* __restrict__ p_bf16, long long n, float lr, float b1, float b2, float eps, float wd,
+             float bc1, float bc2, const float* __restrict__ grad_scale, float grad_mul, int nesterov) {
+  const float gs = (grad_scale != nullptr ? grad_scale[0] : 1.f) * grad_mul;
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    const float gi = ldf<G>(g, i) * gs;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    // optax scale_by_adam: nesterov uses b1 * m_hat(t+1 correction) + (1 - b1) * g / bc1
+    float mhat = mi / bc1;
+    if (nesterov) mhat = b1 * (mi / (1.f - (1.f - bc1) * b1)) + (1.f - b1) * gi / bc1;
+    const float vhat = vi / bc2;
+    float u = mhat / (sqrtf(vhat) + eps);
+    const float pi = p[i];
+    u += wd * pi;
+    const float np = pi - lr * u;
+    p[i] = np;
+    if (p_bf16 != nullptr) p_bf16[i] = __float2bfloat16(np);
+  }
+}
+
+inline int grid_for(long long n) {
+  long long g = (n + kBlock - 1) / kBlock;
+  long long cap = static_cast<long long>(num_sms()) * 8;
+  if (cap > kMaxParts) cap = kMaxParts;
+  return static_cast<int>(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace optim
+}  // namespace lvb
+
+// out[0] (+)= sum(x^2).  x is fp32 (is_bf16 = 0) or bf16.  scratch: fp32 [1024].
+extern "C" int lvb_sumsq(const void* x, long long n, int is_bf16, float* scratch, float* out, int accumulate,
+                         void* stream) {
+  using namespace lvb;
+  using namespace lvb::optim;
+  if (n <= 0) return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n);
+  if (is_bf16)
+    sumsq_partial_kernel<__nv_bfloat16><<<grid, kBlock, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), n, scratch);
+  else
+    sumsq_partial_kernel<float><<<grid, kBlock, 0, s>>>(reinterpret_cast<const float*>(x), n, scratch);
+  sumsq_final_kernel<<<1, 32, 0, s>>>(scratch, grid, out, accumulate);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+extern "C" int lvb_clip_coef(const float* sumsq, float max_norm, float* coef, float* norm_out, void* stream) {
+  lvb::optim::clip_coef_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, coef, norm_out);
+  return cudaGetLastError() == cudaSuccess ? lvb::kErrOk : lvb::kErrCuda;
+}
+
+// Fused AdamW over a flat shard.  p/m/v fp32 [n]; g fp32 or bf16 [n]; p_bf16 optional bf16 [n].
+// grad_scale: optional device scalar (clip coefficient); grad_mul: host scalar (e.g. 1/accum_steps).
+// bc1 = 1 - b1^t, bc2 = 1 - b2^t.
+extern "C" int lvb_adamw(float* p, float* m, float* v, const void* g, int g_is_bf16, void* p_bf16, long long n, float lr,
+                         float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+                         float grad_mul, int nesterov, void* stream) {
+  using namespace lvb;
+  using namespace lvb::optim;
+  if (n <= 0) return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  long long gl = (n + kBlock - 1) / kBlock;
+  long long cap = static_cast<long long>(num_sms()) * 16;
+  const int grid = static_cast<int>(gl < cap ? gl : cap);
+  if (g_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid, kBlock, 0, s>>>(p, m, v, reinterpret_cast<const __nv_bfloat16*>(g),
+                                                        reinterpret_cast<__nv_bfloat16*>(p_bf16), n, lr, b1, b2, eps, wd,
+                                                        bc1, bc2, grad_scale, grad_mul, nesterov);
+  else
+    adamw_kernel<float><<<grid, kBlock, 0, s>>>(p, m, v, reinterpret_cast<const float*>(g),
+                                                reinterpret_cast<__nv_bfloat16*>(p_bf16), n, lr, b1, b2, eps, wd, bc1,
+                                                bc2, grad_scale, grad_mul, nesterov);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}

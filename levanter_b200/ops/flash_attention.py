@@ -1,0 +1,49 @@
+"""Causal flash attention on tcgen05 tensor cores (``csrc/flash_attn.cu``): GQA, sliding window, segment ids.
+
+Replaces the reference's fused-attention call sites (TransformerEngine/cuDNN on GPU, src/levanter/layers/attention.py:
+533-544; pure-JAX flash attention, src/levanter/models/flash_attention.py:143-385)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import lib
+
+
+def kernel_built() -> bool:
+    try:
+        return hasattr(lib.load(), "lvb_flash_attn_fwd")
+    except Exception:
+        return False
+
+
+def supported(q, k, v, mask, bias, no_dropout: bool, attention_dtype) -> bool:
+    from ..layers.attention import AttentionMask, _structured_only
+
+    if not (q.is_cuda and lib.available() and kernel_built()):
+        return False
+    if bias is not None or not no_dropout:
+        return False
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        return False
+    if attention_dtype is not None and attention_dtype not in (torch.float32, torch.bfloat16):
+        return False
+    if q.shape[-1] != 128 or v.shape[-1] != 128:
+        return False
+    if q.shape[1] != k.shape[1] or q.shape[1] % 128 != 0:
+        return False
+    if mask is not None and not isinstance(mask, AttentionMask):
+        return False
+    if isinstance(mask, AttentionMask) and not mask.is_causal:
+        return False
+    if mask is None:
+        return False
+    return _structured_only(mask)
+
+
+def flash_attention(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
+    from ._flash_impl import flash_attention_cuda
+
+    return flash_attention_cuda(q, k, v, mask, logits_soft_cap=logits_soft_cap, scaling_factor=scaling_factor)

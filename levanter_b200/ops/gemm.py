@@ -138,12 +138,14 @@ class _LinearFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight, bias):
+    def forward(ctx, x, weight, bias, residual=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        y = gemm(x2, weight, bias=bias)
+        r2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
+        y = gemm(x2, weight, bias=bias, residual=r2)
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
         ctx.x_shape = shp
         ctx.weight_ref = weight
         return y.view(*shp[:-1], weight.shape[0])
@@ -166,11 +168,24 @@ class _LinearFn(torch.autograd.Function):
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype if weight.dtype in (torch.bfloat16, torch.float32) else torch.float32)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0)
-        return dx, dw, db
+        dres = dy if ctx.has_res else None
+        return dx, dw, db, dres
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Linear layer on the tcgen05 GEMM when running bf16 on a B200; ``F.linear`` otherwise."""
     if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
-        return _LinearFn.apply(x, weight, bias)
+        return _LinearFn.apply(x, weight, bias, None)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], residual: Optional[torch.Tensor]) -> torch.Tensor:
+    """``x W^T + b + residual`` with the residual added in the GEMM epilogue (one pass over the output)."""
+    if residual is None:
+        return linear(x, weight, bias)
+    if weight.dtype != x.dtype:
+        weight = weight.to(x.dtype)
+        bias = bias.to(x.dtype) if bias is not None else None
+    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, weight, bias, residual)
+    return torch.nn.functional.linear(x, weight, bias) + residual

@@ -50,11 +50,25 @@ def load() -> ctypes.CDLL:
     return _lib
 
 
-def fn(name: str, argtypes: list, restype=c_int):
+launch_count = 0  # kernels launched through this binding since import (see count_launches)
+
+
+def fn(name: str, argtypes: list, restype=c_int, launches: int = 1):
+    """Bind an ``extern "C"`` launcher.  ``launches`` is how many kernels one call puts on the stream; the running total
+    is kept in ``launch_count`` so benchmarks can report how many of this library's kernels ran in a timed region."""
     f = getattr(load(), name)
     f.argtypes = argtypes
     f.restype = restype
-    return f
+    if launches <= 0:
+        return f
+
+    def counted(*args):
+        global launch_count
+        launch_count += launches
+        return f(*args)
+
+    counted.__name__ = name
+    return counted
 
 
 def stream_ptr() -> int:

@@ -1,0 +1,301 @@
+"""Write / read a state tree as one zarr array per leaf, at ``<path>/<key path with '.' -> '/'>``
+(src/levanter/tensorstore_serialization.py:36-215).
+
+Key paths follow the reference's ``leaf_key_paths``: dataclass / NamedTuple field names, tuple and list indices, dict keys.
+Model parameters and the optimizer moments that mirror them are converted to the reference's layout on the way out:
+per-layer tensors ``transformer.layers.<i>.x`` are stacked under ``transformer/layers/stacked/x`` with a leading layer
+axis, 2-D ``[out, in]`` Linear weights are reshaped to their articulated axes (and transposed for ``out_first=False``
+modules).  Loading inverts this, accepts arbitrary chunk grids, and reshards to whatever mesh is running.
+
+Leaves may be ``DeferredLeaf`` objects (sharded tensors gathered only while they are being written); every rank resolves
+every leaf in the same order (the gathers are collectives) and leaf ``i`` is written by rank ``i mod world``."""
+from __future__ import annotations
+
+import json
+import logging
+import re
+import threading
+from concurrent.futures import Future, ThreadPoolExecutor
+from dataclasses import dataclass, fields, is_dataclass
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .store.zarr_array import ZarrArray, default_chunks
+from .utils import fsspec_utils
+
+logger = logging.getLogger(__name__)
+_LAYER_RE = re.compile(r"^(.*?\.)?(layers|blocks|h)\.(\d+)\.(.*)$")
+
+
+class DeferredLeaf:
+    """A tensor produced on demand (e.g. an all-gather of optimizer-state shards)."""
+
+    def __init__(self, fn: Callable[[], torch.Tensor], shape: Tuple[int, ...], dtype: torch.dtype):
+        self.fn = fn
+        self.shape = tuple(shape)
+        self.dtype = dtype
+
+    def resolve(self) -> torch.Tensor:
+        return self.fn()
+
+
+@dataclass
+class ParamLayout:
+    """How one torch parameter maps to the reference's array: articulated shape and whether it is stored transposed."""
+
+    lev_shape: Tuple[int, ...]
+    transposed: bool = False
+
+
+def layouts_of(model: torch.nn.Module) -> Dict[str, ParamLayout]:
+    out = {}
+    for name, p in model.named_parameters():
+        shape = tuple(getattr(p, "lev_shape", tuple(p.shape)))
+        out[name] = ParamLayout(shape, bool(getattr(p, "lev_transposed", False)))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ key paths
+def leaf_key_paths(tree: Any, prefix: str = "") -> List[Tuple[str, Any]]:
+    """Flatten ``tree`` into ``(dotted key path, leaf)`` pairs; ``None`` leaves are skipped
+    (src/levanter/utils/jax_utils.py:150-223)."""
+    out: List[Tuple[str, Any]] = []
+
+    def join(p, k):
+        return f"{p}.{k}" if p else str(k)
+
+    def rec(x, p):
+        if x is None:
+            return
+        if isinstance(x, (torch.Tensor, np.ndarray, DeferredLeaf, int, float, bool, np.generic)):
+            out.append((p, x))
+        elif isinstance(x, tuple) and hasattr(x, "_fields"):
+            for f in x._fields:
+                rec(getattr(x, f), join(p, f))
+        elif is_dataclass(x) and not isinstance(x, type):
+            for f in fields(x):
+                rec(getattr(x, f.name), join(p, f.name))
+        elif isinstance(x, dict):
+            for k, v in x.items():
+                rec(v, join(p, k))
+        elif isinstance(x, (list, tuple)):
+            for i, v in enumerate(x):
+                rec(v, join(p, i))
+        # anything else (callables, strings) is static configuration, not state
+
+    rec(tree, prefix)
+    return out
+
+
+def _fs_path(base: str, key_path: str) -> str:
+    return fsspec_utils.join_path(base, key_path.replace(".", "/")) if key_path else base
+
+
+# ------------------------------------------------------------------------------------------------ layout conversion
+def _is_param_dict(d) -> bool:
+    return isinstance(d, dict) and len(d) > 0 and all(isinstance(k, str) for k in d) and \
+        all(v is None or isinstance(v, (torch.Tensor, DeferredLeaf)) for v in d.values()) and \
+        any(k.endswith((".weight", ".bias")) or k in ("weight", "bias") or "." in k for k in d)
+
+
+def to_reference_layout(params: Dict[str, Any], layouts: Optional[Dict[str, ParamLayout]]) -> Dict[str, Any]:
+    """torch-named flat dict -> nested dict in the reference's layout (stacked layers, articulated axes)."""
+    groups: Dict[str, Dict[int, Tuple[str, Any]]] = {}
+    singles: Dict[str, Any] = {}
+    for name, t in params.items():
+        if t is None:
+            continue
+        m = _LAYER_RE.match(name)
+        if m:
+            pre, coll, idx, rest = m.group(1) or "", m.group(2), int(m.group(3)), m.group(4)
+            groups.setdefault(f"{pre}{coll}.stacked.{rest}", {})[idx] = (name, t)
+        else:
+            singles[name] = t
+
+    def articulate(name, t):
+        lay = layouts.get(name) if layouts else None
+
+        def conv(x: torch.Tensor) -> torch.Tensor:
+            if lay is None:
+                return x
+            if lay.transposed and x.dim() == 2:
+                x = x.t()
+            return x.reshape(lay.lev_shape)
+
+        if isinstance(t, DeferredLeaf):
+            shape = lay.lev_shape if lay is not None else t.shape
+            return DeferredLeaf(lambda t=t: conv(t.resolve()), shape, t.dtype)
+        return conv(t)
+
+    flat: Dict[str, Any] = {}
+    for name, t in singles.items():
+        flat[name] = articulate(name, t)
+    for key, members in groups.items():
+        idxs = sorted(members)
+        items = [articulate(*members[i]) for i in idxs]
+        shape = (len(items),) + tuple(items[0].shape)
+        dtype = items[0].dtype
+
+        def stack(items=items):
+            return torch.stack([(x.resolve() if isinstance(x, DeferredLeaf) else x) for x in items])
+
+        flat[key] = DeferredLeaf(stack, shape, dtype)
+    return _nest(flat)
+
+
+def _nest(flat: Dict[str, Any]) -> Dict[str, Any]:
+    root: Dict[str, Any] = {}
+    for k, v in flat.items():
+        cur = root
+        parts = k.split(".")
+        for p in parts[:-1]:
+            cur = cur.setdefault(p, {})
+        cur[parts[-1]] = v
+    return root
+
+
+def convert_state_for_save(state: Any, layouts: Optional[Dict[str, ParamLayout]]) -> Any:
+    """Apply :func:`to_reference_layout` to every parameter-shaped dict inside ``state``."""
+    if _is_param_dict(state):
+        return to_reference_layout(state, layouts)
+    if isinstance(state, tuple) and hasattr(state, "_fields"):
+        return type(state)(*[convert_state_for_save(v, layouts) for v in state])
+    if isinstance(state, tuple):
+        return tuple(convert_state_for_save(v, layouts) for v in state)
+    if isinstance(state, list):
+        return [convert_state_for_save(v, layouts) for v in state]
+    if isinstance(state, dict):
+        return {k: convert_state_for_save(v, layouts) for k, v in state.items()}
+    return state
+
+
+def reference_key_for(name: str) -> Tuple[str, Optional[int]]:
+    """torch parameter name -> (reference key path, layer index or None)."""
+    m = _LAYER_RE.match(name)
+    if m:
+        pre, coll, idx, rest = m.group(1) or "", m.group(2), int(m.group(3)), m.group(4)
+        return f"{pre}{coll}.stacked.{rest}", idx
+    return name, None
+
+
+# ------------------------------------------------------------------------------------------------ save
+class AsyncSerializer:
+    """Background writer: ``serialize`` returns once every leaf has been copied to host memory; chunk compression and
+    file writes proceed on a thread pool; ``wait_until_finished`` joins them and runs commit callbacks."""
+
+    def __init__(self, max_workers: int = 8):
+        self._pool = ThreadPoolExecutor(max_workers=max_workers)
+        self._pending: List[Tuple[List[Future], Optional[Callable[[], None]]]] = []
+        self._lock = threading.Lock()
+
+    def serialize(self, leaves: Sequence[Tuple[str, Any]], on_commit: Optional[Callable[[], None]] = None) -> None:
+        rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
+        world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        futures: List[Future] = []
+        for i, (path, leaf) in enumerate(leaves):
+            t = leaf.resolve() if isinstance(leaf, DeferredLeaf) else leaf
+            if i % world != rank:
+                continue
+            if isinstance(t, (int, float, bool, np.generic)):
+                t = torch.tensor(t)
+            elif isinstance(t, np.ndarray):
+                t = torch.from_numpy(np.ascontiguousarray(t))
+            host = t.detach().to("cpu", copy=True) if t.device.type != "cpu" else t.detach().clone()
+            futures.append(self._pool.submit(_write_leaf, path, host))
+        with self._lock:
+            self._pending.append((futures, on_commit))
+
+    def wait_until_finished(self) -> None:
+        with self._lock:
+            pending, self._pending = self._pending, []
+        for futures, cb in pending:
+            for f in futures:
+                f.result()
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                dist.barrier()
+            if cb is not None:
+                cb()
+
+
+def _write_leaf(path: str, t: torch.Tensor) -> None:
+    itemsize = t.element_size()
+    arr = ZarrArray.create(path, list(t.shape), default_chunks(list(t.shape), itemsize), t.dtype)
+    arr.write_tensor(t)
+
+
+def tree_serialize_leaves_tensorstore(checkpoint_dir: str, tree: Any, manager: Optional[AsyncSerializer] = None, *,
+                                      commit_callback: Optional[Callable[[], None]] = None,
+                                      layouts: Optional[Dict[str, ParamLayout]] = None) -> None:
+    own = manager is None
+    manager = manager or AsyncSerializer()
+    tree = convert_state_for_save(tree, layouts)
+    leaves = [(_fs_path(checkpoint_dir, kp), leaf) for kp, leaf in leaf_key_paths(tree)]
+    manager.serialize(leaves, on_commit=commit_callback)
+    if own:
+        manager.wait_until_finished()
+
+
+# ------------------------------------------------------------------------------------------------ load
+def read_leaf(checkpoint_dir: str, key_path: str) -> Optional[torch.Tensor]:
+    p = _fs_path(checkpoint_dir, key_path)
+    if not ZarrArray.exists(p):
+        return None
+    return ZarrArray.open(p).read_tensor()
+
+
+def read_param(checkpoint_dir: str, prefix: str, name: str, layout: Optional[ParamLayout], shape: Tuple[int, ...]) -> Optional[torch.Tensor]:
+    """Read torch parameter ``name`` from a reference-layout checkpoint under ``prefix`` (e.g. ``model``): picks the
+    layer row of a stacked array and undoes the articulated reshape / transpose."""
+    key, layer = reference_key_for(name)
+    p = _fs_path(checkpoint_dir, f"{prefix}.{key}" if prefix else key)
+    if not ZarrArray.exists(p):
+        return None
+    arr = ZarrArray.open(p)
+    if layer is not None:
+        lo = [layer] + [0] * (len(arr.shape) - 1)
+        hi = [layer + 1] + list(arr.shape[1:])
+        t = arr.read_tensor(lo, hi)[0]
+    else:
+        t = arr.read_tensor()
+    if layout is not None and layout.transposed and len(shape) == 2:
+        t = t.reshape(shape[1], shape[0]).t()
+    return t.reshape(shape)
+
+
+def tree_deserialize_leaves_tensorstore(checkpoint_dir: str, tree: Any, *, allow_missing: bool = False) -> Any:
+    """Read every leaf of ``tree`` (used as a structure exemplar) from ``checkpoint_dir``; with ``allow_missing`` leaves
+    absent on disk keep their exemplar value (src/levanter/tensorstore_serialization.py:119-215)."""
+
+    def rec(x, p):
+        if x is None:
+            return None
+        if isinstance(x, (torch.Tensor, np.ndarray, int, float, bool, np.generic)):
+            t = read_leaf(checkpoint_dir, p)
+            if t is None:
+                if allow_missing:
+                    return x
+                raise FileNotFoundError(f"Missing checkpoint leaf {p} in {checkpoint_dir}")
+            if isinstance(x, bool):
+                return bool(t.item())
+            if isinstance(x, int):
+                return int(t.item())
+            if isinstance(x, float):
+                return float(t.item())
+            if isinstance(x, torch.Tensor):
+                return t.to(dtype=x.dtype).reshape(x.shape).to(x.device)
+            return t.numpy()
+        j = (lambda k: f"{p}.{k}" if p else str(k))
+        if isinstance(x, tuple) and hasattr(x, "_fields"):
+            return type(x)(*[rec(getattr(x, f), j(f)) for f in x._fields])
+        if isinstance(x, dict):
+            return {k: rec(v, j(k)) for k, v in x.items()}
+        if isinstance(x, tuple):
+            return tuple(rec(v, j(i)) for i, v in enumerate(x))
+        if isinstance(x, list):
+            return [rec(v, j(i)) for i, v in enumerate(x)]
+        return x
+
+    return rec(tree, "")

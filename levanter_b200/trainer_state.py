@@ -1,0 +1,94 @@
+"""Training state (src/levanter/trainer_state.py:43-291).
+
+``TrainerState`` bundles the step counter, the model (compute-dtype parameters, views into the engine's flat buffer),
+the sharded parameter/optimizer engine, the RNG key and the optional model average.  ``saveable_state`` is the tree the
+checkpointer writes: ``step``, ``model`` (trainable parameters in param dtype), ``opt_state``, ``training_key``,
+``model_averaging`` (:229-240)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Optional
+
+import torch
+import torch.nn as nn
+
+from .config import Policy
+from .parallel.engine import ShardedEngine
+
+
+@dataclass
+class TrainerState:
+    step: int
+    model: nn.Module
+    engine: ShardedEngine
+    training_key: torch.Tensor  # uint32[2]-style key material (seed, counter)
+    mp: Policy
+    model_averaging: Optional[Any] = None
+    is_trainable: Optional[Callable[[str], bool]] = None
+
+    @property
+    def opt_state(self):
+        return self.engine.optimizer_state_tree()
+
+    @property
+    def optimizer(self):
+        return self.engine.opt
+
+    @property
+    def trainable_model(self) -> Dict[str, torch.Tensor]:
+        return self.engine.master_tree()
+
+    @property
+    def eval_model(self) -> nn.Module:
+        """The model to evaluate: the averaged weights when model averaging is on (copied into a shadow module)."""
+        if self.model_averaging is None:
+            return self.model
+        full = self.engine._gather_leaf_tree(self.model_averaging.model_params)
+        return _shadow_with(self.model, full, self.mp)
+
+    @property
+    def saveable_state(self) -> Dict[str, Any]:
+        out = {
+            "step": self.step,
+            "model": self.engine.deferred_named(self.engine.master),
+            "opt_state": self.engine.optimizer_state_tree(deferred=True),
+            "training_key": self.training_key,
+        }
+        if self.model_averaging is not None:
+            out["model_averaging"] = {"model": self.engine._deferred_leaf_tree(self.model_averaging.model_params)}
+            for k in ("beta", "tot_weight"):
+                if hasattr(self.model_averaging, k):
+                    out["model_averaging"][k] = getattr(self.model_averaging, k)
+        return out
+
+    def next_key(self) -> int:
+        """Split the training key: returns a per-step seed and advances the stored key."""
+        k = self.training_key
+        seed = int(k[0].item()) * 1000003 + int(k[1].item())
+        self.training_key = torch.stack([k[0], k[1] + 1])
+        return seed & 0x7FFFFFFF
+
+
+_shadow_cache: Dict[int, nn.Module] = {}
+
+
+def _shadow_with(model: nn.Module, params: Dict[str, torch.Tensor], mp: Policy) -> nn.Module:
+    import copy
+
+    key = id(model)
+    shadow = _shadow_cache.get(key)
+    if shadow is None:
+        shadow = copy.deepcopy(model)
+        for p in shadow.parameters():
+            p.requires_grad_(False)
+        _shadow_cache[key] = shadow
+    with torch.no_grad():
+        sd = dict(shadow.named_parameters())
+        for k, v in params.items():
+            if k in sd:
+                sd[k].copy_(v.to(sd[k].dtype).view(sd[k].shape))
+    return shadow
+
+
+def make_training_key(seed: int) -> torch.Tensor:
+    return torch.tensor([seed & 0xFFFFFFFF, 0], dtype=torch.int64)
