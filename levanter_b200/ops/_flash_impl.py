@@ -1,0 +1,88 @@
+"""Autograd binding of the tcgen05 flash-attention kernels (``csrc/flash_attn.cu``)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import lib
+
+_f = {}
+_FORCE_ONE_TILE = False  # tests flip this to exercise the one-tile forward kernel on every shape
+
+
+def _fwd():
+    if "f" not in _f:
+        c = lib
+        _f["f"] = lib.fn("lvb_flash_attn_fwd", [c.c_void_p] * 7 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+    return _f["f"]
+
+
+def _fwd2():
+    if "f2" not in _f:
+        c = lib
+        _f["f2"] = lib.fn("lvb_flash_attn_fwd2", [c.c_void_p] * 7 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+    return _f["f2"]
+
+
+def _bwd():
+    if "b" not in _f:
+        c = lib
+        _f["b"] = lib.fn("lvb_flash_attn_bwd", [c.c_void_p] * 12 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p],
+                         launches=2)
+    return _f["b"]
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window):
+        B, S, Hq, D = q.shape
+        Hkv = k.shape[2]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+        # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
+        fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
+        rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+                    B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(),
+                    lib.stream_ptr())
+        lib.check_rc(rc, "lvb_flash_attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse2, q_seg, k_seg)
+        ctx.args = (scale, soft_cap, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse2, q_seg, k_seg = ctx.saved_tensors
+        scale, soft_cap, window = ctx.args
+        B, S, Hq, D = q.shape
+        Hkv = k.shape[2]
+        do = do.contiguous()
+        if do.dtype != torch.bfloat16:
+            do = do.to(torch.bfloat16)
+        dq32 = torch.zeros(B, S, Hq, D, dtype=torch.float32, device=q.device)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+        rc = _bwd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
+                    dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
+                    float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_flash_attn_bwd")
+        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None
+
+
+def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
+    """``q[B,S,Hq,128]``, ``k/v[B,S,Hkv,128]`` bf16; ``mask`` is a causal ``AttentionMask`` (optionally with a sliding
+    window and segment ids)."""
+    scale = scaling_factor if scaling_factor is not None else 1.0 / math.sqrt(q.shape[-1])
+    q_seg = k_seg = None
+    window = 0
+    if mask is not None:
+        window = mask.sliding_window or 0
+        if mask.segment_ids is not None:
+            q_seg, k_seg = mask.segment_ids
+            B, S = q.shape[0], q.shape[1]
+            q_seg = q_seg.to(torch.int32).expand(B, S).contiguous()
+            k_seg = k_seg.to(torch.int32).expand(B, S).contiguous()
+    return _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window)

@@ -1,0 +1,85 @@
+"""tcgen05 flash attention (forward and backward) against a PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from levanter_b200.layers.attention import AttentionMask, simple_attention_with_dropout
+from levanter_b200.ops import lib
+from levanter_b200.ops._flash_impl import flash_attention_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    scale = b.abs().max().item() + 1e-6
+    assert err / scale < tol, f"rel err {err / scale}"
+
+
+def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0):
+    torch.manual_seed(seed)
+    q = torch.randn(B, S, Hq, 128, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    o = flash_attention_cuda(q, k, v, mask, logits_soft_cap=soft_cap)
+    g = torch.randn_like(o)
+    o.backward(g)
+    torch.cuda.synchronize()
+    lib.check_status()
+    qr, kr, vr = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    orf = simple_attention_with_dropout(qr, kr, vr, mask, attention_dtype=torch.float32, logits_soft_cap=soft_cap)
+    orf.backward(g.float())
+    _close(o, orf, 2e-2)
+    _close(q.grad, qr.grad, 4e-2)
+    _close(k.grad, kr.grad, 4e-2)
+    _close(v.grad, vr.grad, 4e-2)
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 2, 2), (1, 512, 4, 1), (2, 384, 4, 2)])
+def test_causal(B, S, Hq, Hkv):
+    _run(B, S, Hq, Hkv, AttentionMask.causal())
+
+
+def test_sliding_window():
+    _run(1, 640, 2, 2, AttentionMask.causal(sliding_window=200))
+    _run(1, 512, 2, 1, AttentionMask.causal(sliding_window=128))
+
+
+def test_segment_ids():
+    S = 384
+    seg = torch.zeros(2, S, dtype=torch.int32, device="cuda")
+    seg[0, 100:] = 1
+    seg[0, 300:] = 2
+    seg[1, 129:] = 1
+    _run(2, S, 2, 2, AttentionMask.causal().with_segment_ids(seg))
+
+
+def test_soft_cap():
+    _run(1, 256, 2, 2, AttentionMask.causal(), soft_cap=20.0)
+
+
+def test_one_tile_kernel_matches():
+    from levanter_b200.ops import _flash_impl
+
+    _flash_impl._FORCE_ONE_TILE = True
+    try:
+        _run(2, 512, 2, 2, AttentionMask.causal())
+        _run(1, 512, 2, 1, AttentionMask.causal(sliding_window=128))
+    finally:
+        _flash_impl._FORCE_ONE_TILE = False
+
+
+def test_long_sequence():
+    _run(1, 2048, 2, 2, AttentionMask.causal(), seed=7)
+
+
+def test_deterministic_forward():
+    torch.manual_seed(3)
+    q = torch.randn(1, 512, 2, 128, device="cuda").bfloat16()
+    k = torch.randn(1, 512, 2, 128, device="cuda").bfloat16()
+    v = torch.randn(1, 512, 2, 128, device="cuda").bfloat16()
+    a = flash_attention_cuda(q, k, v, AttentionMask.causal()).clone()
+    b = flash_attention_cuda(q, k, v, AttentionMask.causal())
+    assert torch.equal(a, b)
