@@ -175,3 +175,32 @@ class YarnRotaryEmbeddingsConfig(RotaryEmbeddingsConfig):
     def to_hf_config(self):
         return self.theta, {"type": "yarn", "factor": self.factor, "beta_fast": self.beta_fast, "beta_slow": self.beta_slow,
                             "original_max_position_embeddings": self.original_max_position_embeddings, "mscale": self.mscale}
+
+
+def rope_config_from_hf(get, default_theta: float = 10000.0) -> RotaryEmbeddingsConfig:
+    """RoPE config from an HF config accessor ``get(key, default)``: understands both the legacy ``rope_theta`` +
+    ``rope_scaling`` keys and the merged ``rope_parameters`` dict of newer ``transformers`` releases."""
+    params = get("rope_parameters", None)
+    theta = get("rope_theta", None)
+    scaling = get("rope_scaling", None)
+    if isinstance(params, dict):
+        if "rope_theta" not in params and any(isinstance(v, dict) for v in params.values()):
+            # per-layer-type parameters (e.g. full_attention / sliding_attention): take the global one
+            params = params.get("full_attention") or next(v for v in params.values() if isinstance(v, dict))
+        theta = params.get("rope_theta", theta)
+        if params.get("rope_type", params.get("type", "default")) != "default":
+            scaling = {k: v for k, v in params.items() if k != "rope_theta"}
+    if theta is None:
+        theta = default_theta
+    return RotaryEmbeddingsConfig.from_hf_config(float(theta), scaling)
+
+
+def rope_to_hf_dict(rope: RotaryEmbeddingsConfig) -> dict:
+    """Keys to merge into an HF config for ``rope``: legacy (``rope_theta``, ``rope_scaling``) and ``rope_parameters``."""
+    theta, scaling = rope.to_hf_config()
+    params = {"rope_theta": theta, "rope_type": "default"}
+    if scaling:
+        params.update(scaling)
+        params["rope_type"] = scaling.get("rope_type", scaling.get("type", "default"))
+        params.pop("type", None)
+    return {"rope_theta": theta, "rope_scaling": scaling, "rope_parameters": params}

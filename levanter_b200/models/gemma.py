@@ -20,7 +20,7 @@ from torch.utils.checkpoint import checkpoint
 from ..compat.hf_checkpoints import HFCheckpointConverter, HFCompatConfig
 from ..layers.attention import Attention, AttentionBackend, AttentionConfig
 from ..layers.normalization import LayerNormConfigBase
-from ..layers.rotary import DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
+from ..layers.rotary import rope_config_from_hf, rope_to_hf_dict, DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
 from ..nn import Linear
 from ..ops.norm import fused_norm
 from ..utils.activation import ActivationFunctionEnum, from_hf_name
@@ -102,7 +102,7 @@ class GemmaConfig(HFCompatConfig):
                     head_dim=g("head_dim", 256), activation_function=from_hf_name(act) if act in ("gelu_pytorch_tanh",) else ActivationFunctionEnum(act),
                     initializer_range=g("initializer_range", 0.02), layer_norm_epsilon=g("rms_norm_eps", 1e-6),
                     tie_word_embeddings=bool(g("tie_word_embeddings", True)),
-                    rope=RotaryEmbeddingsConfig.from_hf_config(g("rope_theta", 10000.0), g("rope_scaling", None)))
+                    rope=rope_config_from_hf(g, 10000.0))
 
     @classmethod
     def from_hf_config(cls, hf_config):
@@ -119,6 +119,7 @@ class GemmaConfig(HFCompatConfig):
 
     def to_hf_config(self, vocab_size: int, config_overrides: Optional[Dict] = None) -> dict:
         cfg = dict(model_type=self.hf_model_type, architectures=[self.hf_architecture], **self._common_to_hf(vocab_size))
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 
@@ -273,6 +274,7 @@ class Gemma2Config(GemmaConfig):
                    query_pre_attn_scalar=self.query_pre_attn_scalar or self.head_dim,
                    final_logit_softcapping=self.final_logit_softcapping, attn_logit_softcapping=self.attn_logit_softcapping,
                    sliding_window=self.sliding_window if self.sliding_window is not None else self.seq_len)
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 
@@ -321,6 +323,7 @@ class Gemma3Config(Gemma2Config):
         cfg.update(use_qk_norm=self.use_qk_norm, rope_local_base_freq=self.rope_local_base_freq,
                    sliding_window_pattern=self.sliding_window_pattern if self.sliding_window_pattern is not None else 1,
                    attention_dropout=0.0, use_cache=True)
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 

@@ -20,7 +20,7 @@ from torch.utils.checkpoint import checkpoint
 from ..compat.hf_checkpoints import HFCheckpointConverter, HFCompatConfig
 from ..layers.attention import Attention, AttentionBackend, AttentionConfig, AttentionMask, KvPageCache
 from ..layers.normalization import LayerNormConfigBase, RmsNormConfig
-from ..layers.rotary import DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
+from ..layers.rotary import rope_config_from_hf, rope_to_hf_dict, DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
 from ..nn import Embedding, Linear
 from ..ops.gemm import linear_residual
 from ..ops.glu import gated_activation
@@ -76,7 +76,7 @@ class LlamaConfig(HFCompatConfig):
     @classmethod
     def from_hf_config(cls, hf_config) -> "LlamaConfig":
         g = _getter(hf_config)
-        rope = RotaryEmbeddingsConfig.from_hf_config(g("rope_theta", 10000.0), g("rope_scaling", None))
+        rope = rope_config_from_hf(g, 10000.0)
         return cls(
             seq_len=g("max_position_embeddings"), hidden_dim=g("hidden_size"), intermediate_dim=g("intermediate_size"),
             num_layers=g("num_hidden_layers"), num_heads=g("num_attention_heads"),
@@ -101,6 +101,7 @@ class LlamaConfig(HFCompatConfig):
         )
         if self.head_dim is not None:
             cfg["head_dim"] = self.head_dim
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 

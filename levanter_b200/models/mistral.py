@@ -12,7 +12,7 @@ from typing import Dict, Optional, Type
 
 from ..compat.hf_checkpoints import HFCheckpointConverter
 from ..layers.attention import AttentionBackend, AttentionConfig
-from ..layers.rotary import DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
+from ..layers.rotary import rope_config_from_hf, rope_to_hf_dict, DefaultRotaryEmbeddingsConfig, RotaryEmbeddingsConfig
 from ..utils.activation import ActivationFunctionEnum
 from ..utils.flop_utils import lm_flops_per_token
 from .llama import LlamaConfig, LlamaLMHeadModel, _getter
@@ -50,7 +50,7 @@ class MistralConfig(LlamaConfig):
                    activation_function=ActivationFunctionEnum(g("hidden_act", "silu")),
                    initializer_range=g("initializer_range", 0.02), layer_norm_epsilon=g("rms_norm_eps", 1e-6),
                    sliding_window=g("sliding_window", 4096) or 4096,
-                   rope=RotaryEmbeddingsConfig.from_hf_config(g("rope_theta", 10000.0), g("rope_scaling", None)))
+                   rope=rope_config_from_hf(g, 10000.0))
 
     def to_hf_config(self, vocab_size: int, config_overrides: Optional[Dict] = None) -> dict:
         theta, _ = self.rope.to_hf_config()
@@ -60,6 +60,7 @@ class MistralConfig(LlamaConfig):
                    hidden_act=self.activation_function.name, initializer_range=self.initializer_range,
                    rms_norm_eps=self.layer_norm_epsilon, sliding_window=self.sliding_window, vocab_size=vocab_size,
                    rope_theta=theta, tie_word_embeddings=False)
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 

@@ -10,7 +10,7 @@ from dataclasses import dataclass
 from typing import Dict, Optional, Type
 
 from ..layers.attention import Attention, AttentionConfig
-from ..layers.rotary import RotaryEmbeddingsConfig
+from ..layers.rotary import rope_config_from_hf, rope_to_hf_dict, RotaryEmbeddingsConfig
 from ..utils.activation import ActivationFunctionEnum
 from .llama import LlamaConfig, LlamaDecoderLayer, LlamaLMHeadModel, _getter
 from .lm_model import LmConfig
@@ -41,7 +41,7 @@ class QwenConfig(LlamaConfig):
                    activation_function=ActivationFunctionEnum(g("hidden_act", "silu")),
                    initializer_range=g("initializer_range", 0.02), layer_norm_epsilon=g("rms_norm_eps", 1e-6),
                    tie_word_embeddings=bool(g("tie_word_embeddings", False)),
-                   rope=RotaryEmbeddingsConfig.from_hf_config(g("rope_theta", 10000.0), g("rope_scaling", None)))
+                   rope=rope_config_from_hf(g, 10000.0))
 
     def to_hf_config(self, vocab_size: int, config_overrides: Optional[Dict] = None) -> dict:
         theta, scaling = self.rope.to_hf_config()
@@ -52,6 +52,7 @@ class QwenConfig(LlamaConfig):
                    max_window_layers=self.max_window_layers, hidden_act=self.activation_function.name,
                    initializer_range=self.initializer_range, rms_norm_eps=self.layer_norm_epsilon,
                    tie_word_embeddings=self.tie_word_embeddings, vocab_size=vocab_size, rope_theta=theta, rope_scaling=scaling)
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 
@@ -102,6 +103,7 @@ class Qwen3Config(LlamaConfig):
                    initializer_range=self.initializer_range, rms_norm_eps=self.layer_norm_epsilon,
                    tie_word_embeddings=self.tie_word_embeddings, vocab_size=vocab_size, rope_theta=theta, rope_scaling=scaling,
                    attention_bias=self.use_bias, head_dim=self.head_dim or self.hidden_dim // self.num_heads)
+        cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
         cfg.update(config_overrides or {})
         return cfg
 
@@ -114,7 +116,7 @@ class Qwen3Config(LlamaConfig):
                    activation_function=ActivationFunctionEnum(g("hidden_act", "silu")),
                    initializer_range=g("initializer_range", 0.02), layer_norm_epsilon=g("rms_norm_eps", 1e-6),
                    tie_word_embeddings=bool(g("tie_word_embeddings", False)),
-                   rope=RotaryEmbeddingsConfig.from_hf_config(g("rope_theta", 10000.0), g("rope_scaling", None)),
+                   rope=rope_config_from_hf(g, 10000.0),
                    use_bias=bool(g("attention_bias", False)), head_dim=g("head_dim", None))
 
     def attention_config(self) -> AttentionConfig:

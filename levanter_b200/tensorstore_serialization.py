@@ -48,13 +48,14 @@ class ParamLayout:
 
     lev_shape: Tuple[int, ...]
     transposed: bool = False
+    permute: Optional[Tuple[int, ...]] = None  # reference array = param.permute(permute).reshape(lev_shape)
 
 
 def layouts_of(model: torch.nn.Module) -> Dict[str, ParamLayout]:
     out = {}
     for name, p in model.named_parameters():
         shape = tuple(getattr(p, "lev_shape", tuple(p.shape)))
-        out[name] = ParamLayout(shape, bool(getattr(p, "lev_transposed", False)))
+        out[name] = ParamLayout(shape, bool(getattr(p, "lev_transposed", False)), getattr(p, "lev_permute", None))
     return out
 
 
@@ -121,7 +122,9 @@ def to_reference_layout(params: Dict[str, Any], layouts: Optional[Dict[str, Para
         def conv(x: torch.Tensor) -> torch.Tensor:
             if lay is None:
                 return x
-            if lay.transposed and x.dim() == 2:
+            if lay.permute is not None:
+                x = x.permute(*lay.permute)
+            elif lay.transposed and x.dim() == 2:
                 x = x.t()
             return x.reshape(lay.lev_shape)
 
@@ -260,6 +263,11 @@ def read_param(checkpoint_dir: str, prefix: str, name: str, layout: Optional[Par
         t = arr.read_tensor(lo, hi)[0]
     else:
         t = arr.read_tensor()
+    if layout is not None and layout.permute is not None:
+        perm = layout.permute
+        permuted_shape = [shape[i] for i in perm]
+        inv = [perm.index(i) for i in range(len(perm))]
+        return t.reshape(permuted_shape).permute(*inv).contiguous()
     if layout is not None and layout.transposed and len(shape) == 2:
         t = t.reshape(shape[1], shape[0]).t()
     return t.reshape(shape)
