@@ -138,6 +138,7 @@ class ParamInfo:
         self.class_paths: Dict[str, str] = {}
         self.shapes: Dict[str, tuple] = {}
         self.module_types: Dict[str, str] = {}
+        self.lev_shapes: Dict[str, tuple] = {}
         if model is not None:
             for mod_name, mod in model.named_modules():
                 for pname, p in mod.named_parameters(recurse=False):
@@ -145,6 +146,8 @@ class ParamInfo:
                     self.class_paths[full] = f"{type(mod).__name__}.{pname}"
                     self.shapes[full] = tuple(p.shape)
                     self.module_types[full] = type(mod).__name__
+                    if hasattr(p, "lev_shape"):
+                        self.lev_shapes[full] = tuple(p.lev_shape)
 
     def class_path(self, name: str) -> Optional[str]:
         return self.class_paths.get(name)

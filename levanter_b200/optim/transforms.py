@@ -103,6 +103,8 @@ def chain(*transforms: GradientTransformation) -> GradientTransformation:
 def scale(factor: float) -> GradientTransformation:
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         torch._foreach_mul_(_leaves(updates, keys), factor)
         return updates, state
 
@@ -117,6 +119,8 @@ def scale_by_schedule(fn: Schedule) -> GradientTransformation:
     def update(updates, state, params=None, **extra):
         f = float(fn(state.count))
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         torch._foreach_mul_(_leaves(updates, keys), f)
         return updates, ScaleByScheduleState(state.count + 1)
 
@@ -136,6 +140,8 @@ def clip_by_global_norm(max_norm: float) -> GradientTransformation:
         # optax: where(g < max_norm, u, u / g * max_norm)
         coef = torch.where(g < max_norm, torch.ones_like(g), max_norm / g.clamp_min(1e-30))
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         torch._foreach_mul_(_leaves(updates, keys), coef.to(updates[keys[0]].device) if keys else coef)
         return updates, state
 
@@ -177,6 +183,8 @@ def scale_by_adam(b1: float = 0.9, b2: float = 0.999, eps: float = 1e-8, eps_roo
 
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         g = _leaves(updates, keys)
         mu = _leaves(state.mu, keys)
         nu = _leaves(state.nu, keys)
@@ -217,6 +225,8 @@ def trace(decay: float, nesterov: bool = False) -> GradientTransformation:
 
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         g = _leaves(updates, keys)
         t = _leaves(state.trace, keys)
         torch._foreach_mul_(t, decay)
@@ -247,6 +257,8 @@ def ema(decay: float, debias: bool = False) -> GradientTransformation:
 
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         e = _leaves(state.ema, keys)
         torch._foreach_mul_(e, decay)
         torch._foreach_add_(e, _leaves(updates, keys), alpha=1 - decay)
@@ -271,6 +283,8 @@ def scale_by_lion(b1: float = 0.9, b2: float = 0.99) -> GradientTransformation:
 
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         g = _leaves(updates, keys)
         mu = _leaves(state.mu, keys)
         direction = torch._foreach_mul(mu, b1)
@@ -301,6 +315,8 @@ def scale_by_rms(decay: float = 0.9, eps: float = 1e-8, initial_scale: float = 0
 
     def update(updates, state, params=None, **extra):
         keys = tree_keys(updates)
+        if not keys:
+            return updates, state
         g = _leaves(updates, keys)
         nu = _leaves(state.nu, keys)
         torch._foreach_mul_(nu, decay)

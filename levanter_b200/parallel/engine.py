@@ -155,6 +155,7 @@ class ShardedEngine:
             self.shard_numel, dtype=torch.float32, device=self.device)
         # (param name -> list of (local offset, flat offset, length)) for the owned part of each parameter
         self.segments: Dict[str, Tuple[int, int, int]] = {}
+        self._shapes: Dict[str, Tuple[int, ...]] = {s.name: s.shape for s in self.slots}
         local = 0
         self._bucket_local_start: List[int] = []
         for b in self.buckets:
@@ -195,11 +196,19 @@ class ShardedEngine:
                 self.master[lo:lo + n].copy_(src[a:a + n].to(self.master.dtype))
 
     # ------------------------------------------------------------------------------------------ trees
+    def _shaped(self, name: str, flat: torch.Tensor) -> torch.Tensor:
+        """A segment that covers its whole parameter is presented in the parameter's shape (matrix optimizers need it)."""
+        shape = self._shapes.get(name)
+        if shape is not None and flat.numel() == math.prod(shape):
+            return flat.view(shape)
+        return flat
+
     def master_tree(self) -> Dict[str, torch.Tensor]:
-        return {name: self.master[lo:lo + n] for name, (lo, fo, n) in self.segments.items()}
+        return {name: self._shaped(name, self.master[lo:lo + n]) for name, (lo, fo, n) in self.segments.items()}
 
     def grad_tree(self) -> Dict[str, torch.Tensor]:
-        return {name: self.grad_shard[lo:lo + n] if self.grad_shard is not self.grad_flat else self.grad_flat[fo:fo + n]
+        return {name: self._shaped(name, self.grad_shard[lo:lo + n] if self.grad_shard is not self.grad_flat
+                                   else self.grad_flat[fo:fo + n])
                 for name, (lo, fo, n) in self.segments.items()}
 
     def param_names(self) -> List[str]:
