@@ -419,9 +419,11 @@ class Attention(nn.Module):
             attn = attn.squeeze(0)
         attn = attn.reshape(*x.shape[:-1], self.local_heads * c.head_size).to(x.dtype)
         if residual is not None:
-            from ..ops.gemm import linear_residual
+            if type(self.o_proj) is Linear:
+                from ..ops.gemm import linear_residual
 
-            return linear_residual(attn, self.o_proj.weight, None if skip_out_bias else self.o_proj.bias, residual)
+                return linear_residual(attn, self.o_proj.weight, None if skip_out_bias else self.o_proj.bias, residual)
+            return self.o_proj(attn, skip_bias=skip_out_bias) + residual  # wrapped projections (LoRA, fp8) add it themselves
         return self.o_proj(attn, skip_bias=skip_out_bias)
 
     def forward_with_residual(self, x, mask, pos_ids, residual):

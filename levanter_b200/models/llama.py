@@ -171,7 +171,10 @@ class LlamaMlp(nn.Module):
             if self.down_proj.bias is not None:
                 out = out + self.down_proj.bias
             return out if residual is None else out + residual
-        return linear_residual(h, self.down_proj.weight, self.down_proj.bias, residual)
+        if type(self.down_proj) is Linear:
+            return linear_residual(h, self.down_proj.weight, self.down_proj.bias, residual)
+        out = self.down_proj(h)
+        return out if residual is None else out + residual
 
 
 class LlamaDecoderLayer(nn.Module):
