@@ -242,3 +242,20 @@ def broadcast_one_to_all(obj, src: int = 0):
     box = [obj]
     dist.broadcast_object_list(box, src=src)
     return box[0]
+
+
+def process_index() -> int:
+    """Rank of this process in the job (0 when ``torch.distributed`` is not initialised and no launcher variable is set)."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank()
+    return int(os.environ.get("RANK", os.environ.get("SLURM_PROCID", "0")))
+
+
+def process_count() -> int:
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size()
+    return int(os.environ.get("WORLD_SIZE", os.environ.get("SLURM_NTASKS", "1")))
