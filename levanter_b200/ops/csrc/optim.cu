@@ -137,3 +137,93 @@ extern "C" int lvb_adamw(float* p, float* m, float* v, const void* g, int g_is_b
                                                 bc2, grad_scale, grad_mul, nesterov);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Sum of squares without any allocation.
+//
+// lvb_sumsq takes its 4 KB of partial-sum scratch from the caller, which in practice means from an allocator.  Some hosts
+// cannot go to one at the moment they need a gradient norm:
+//   * a plain C/C++ host has no caching allocator, and the driver's own allocate/free calls synchronise the whole device,
+//     which would stall a step whose collectives and copies are in flight on other streams;
+//   * a health-check or watchdog thread that samples the gradient norm while the training thread is inside the framework's
+//     allocator must not take that lock or change the memory plan that was sized for the step.
+// For them the scratch lives in the library image itself: a file-scope device array, whose address is looked up once per
+// device.  Nothing is allocated, freed or resized here, by this code or by a library routine.
+//
+// Limits and rules:
+//   * n <= kNoAllocMaxElems (2^31 elements); beyond that the call is rejected with kErrTooLarge and a message.
+//   * The first call on a device does the address look-up (cudaGetSymbolAddress, with that device current); it should be
+//     made before any stream capture begins, since the look-up is not a stream operation.
+//   * The slots this call will read are cleared on the stream first, so partial sums left by an earlier call are never seen.
+//   * One scratch per device: calls that may overlap on the GPU race on it.  Order them on one stream or with events.
+#include "lvb_api.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace lvb {
+namespace optim {
+
+constexpr long long kNoAllocMaxElems = 1LL << 31;
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) float g_noalloc_scratch[kMaxParts];
+
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+static std::mutex g_noalloc_mu;
+static thread_local char g_noalloc_err[192] = "";
+
+static int noalloc_fail(int code, const char* fmt, long long a = 0, long long b = 0) {
+  std::snprintf(g_noalloc_err, sizeof(g_noalloc_err), fmt, a, b);
+  return code;
+}
+
+// Address of this device's copy of the scratch array; resolved on first use.
+static int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return noalloc_fail(kErrCuda, "lvb_sumsq_noalloc: no current CUDA device");
+  if (dev >= kNoAllocMaxDevices)
+    return noalloc_fail(kErrBadArg, "lvb_sumsq_noalloc: device index %lld is beyond the supported %lld", dev, kNoAllocMaxDevices);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return noalloc_fail(kErrCuda, "lvb_sumsq_noalloc: cudaGetSymbolAddress failed with CUDA error %lld", static_cast<long long>(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return kErrOk;
+}
+
+}  // namespace optim
+}  // namespace lvb
+
+extern "C" long long lvb_sumsq_noalloc_max_elems(void) { return lvb::optim::kNoAllocMaxElems; }
+
+extern "C" const char* lvb_sumsq_noalloc_last_error(void) { return lvb::optim::g_noalloc_err; }
+
+extern "C" int lvb_sumsq_noalloc(const void* x, long long n, int is_bf16, float* out, int accumulate, void* stream) {
+  using namespace lvb;
+  using namespace lvb::optim;
+  g_noalloc_err[0] = '\0';
+  if (x == nullptr || out == nullptr) return noalloc_fail(kErrBadArg, "lvb_sumsq_noalloc: null pointer argument");
+  if (n <= 0) return noalloc_fail(kErrBadArg, "lvb_sumsq_noalloc: n = %lld must be positive", n);
+  if (n > kNoAllocMaxElems)
+    return noalloc_fail(kErrTooLarge, "lvb_sumsq_noalloc: n = %lld exceeds the maximum of %lld elements", n, kNoAllocMaxElems);
+  float* scratch = nullptr;
+  int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != kErrOk) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n);
+  if (cudaMemsetAsync(scratch, 0, sizeof(float) * grid, s) != cudaSuccess)
+    return noalloc_fail(kErrCuda, "lvb_sumsq_noalloc: clearing the scratch failed");
+  if (is_bf16)
+    sumsq_partial_kernel<__nv_bfloat16><<<grid, kBlock, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), n, scratch);
+  else
+    sumsq_partial_kernel<float><<<grid, kBlock, 0, s>>>(reinterpret_cast<const float*>(x), n, scratch);
+  sumsq_final_kernel<<<1, 32, 0, s>>>(scratch, grid, out, accumulate);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(kErrCuda, "lvb_sumsq_noalloc: launch failed with CUDA error %lld", static_cast<long long>(e));
+  return kErrOk;
+}
