@@ -165,8 +165,12 @@ def main():
 
         # ---- device-timed region: batch resident on the device, loss stays on the device
         dev_batch = next(it).to(dev)
-        for _ in range(args.warmup):
+        for w in range(args.warmup):
             trainer.device_step(state, dev_batch)
+            if w == 0:
+                # a kernel that recorded a timeout makes every later step slow: fail after one step, not after all of them
+                sync()
+                lib.check_status()
         sync()
         lib.check_status()
         sampler = ClockSampler(local_rank)

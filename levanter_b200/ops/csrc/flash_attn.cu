@@ -273,10 +273,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
       }
-      if (m_blk > m_used + kRescaleThreshold || (m_used == -INFINITY && m_blk > -INFINITY)) {
-        const float m_new = fmaxf(m_used, m_blk);
-        if (it > 0 && m_used > -INFINITY) {
-          const float alpha = exp2f(m_used - m_new);
+      // The rescale decision is per row, but the TMEM load/store are warp-collective: the whole warp takes the branch as
+      // soon as one row needs it, and rows that do not need it scale by exactly 1.
+      {
+        const bool want = (m_blk > m_used + kRescaleThreshold) || (m_used == -INFINITY && m_blk > -INFINITY);
+        const float m_new = want ? fmaxf(m_used, m_blk) : m_used;
+        const bool scale_row = want && it > 0 && m_used > -INFINITY;
+        if (__any_sync(0xffffffffu, scale_row)) {
+          const float alpha = scale_row ? exp2f(m_used - m_new) : 1.f;
           l_sum *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -288,8 +292,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tmem_st_32x32(tmem_O + lane_addr + c, v);
           }
           tmem_st_wait();
-        } else if (it > 0) {
-          // rows that were fully masked so far hold exact zeros in O (P was zero); nothing to rescale
         }
         m_used = m_new;
       }

@@ -266,11 +266,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float m_raw = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_blk = (m_raw == -INFINITY) ? -INFINITY : to_log2<kCap>(m_raw, scale_log2, p.scale, p.soft_cap);
 
-      // ---- lazy rescale of O (S_T ready implies the previous P_T V has retired)
-      if (m_blk > m_used + kRescaleThreshold || (m_used == -INFINITY && m_blk > -INFINITY)) {
-        const float m_new = fmaxf(m_used, m_blk);
-        if (it > 0 && m_used > -INFINITY) {
-          const float alpha = exp2f(m_used - m_new);
+      // ---- lazy rescale of O (S_T ready implies the previous P_T V has retired).  The decision is per row, but the
+      // TMEM load/store are warp-collective, so the whole warp takes the branch as soon as one row needs it and rows
+      // that do not need it scale by exactly 1.
+      {
+        const bool want = (m_blk > m_used + kRescaleThreshold) || (m_used == -INFINITY && m_blk > -INFINITY);
+        const float m_new = want ? fmaxf(m_used, m_blk) : m_used;
+        const bool scale_row = want && it > 0 && m_used > -INFINITY;
+        if (__any_sync(0xffffffffu, scale_row)) {
+          const float alpha = scale_row ? exp2f(m_used - m_new) : 1.f;
           l_sum *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {

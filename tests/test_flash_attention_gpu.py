@@ -18,10 +18,17 @@ def _close(a, b, tol):
     assert err / scale < tol, f"rel err {err / scale}"
 
 
-def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0):
+def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0, growing=False):
     torch.manual_seed(seed)
-    q = torch.randn(B, S, Hq, 128, device="cuda").bfloat16().requires_grad_()
-    k = torch.randn(B, S, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    q = torch.randn(B, S, Hq, 128, device="cuda")
+    k = torch.randn(B, S, Hkv, 128, device="cuda")
+    if growing:
+        # logits whose row maximum jumps by far more than the lazy-rescale threshold in later key blocks, and only for
+        # some rows of a warp: the running output must be rescaled mid-row, row by row
+        k[:, 128:] *= 3.0
+        k[:, 256:] *= 2.0
+        q[:, 1::3] *= 4.0
+    q, k = q.bfloat16().requires_grad_(), k.bfloat16().requires_grad_()
     v = torch.randn(B, S, Hkv, 128, device="cuda").bfloat16().requires_grad_()
     o = flash_attention_cuda(q, k, v, mask, logits_soft_cap=soft_cap)
     g = torch.randn_like(o)
@@ -40,6 +47,18 @@ def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0):
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 2, 2), (1, 512, 4, 1), (2, 384, 4, 2)])
 def test_causal(B, S, Hq, Hkv):
     _run(B, S, Hq, Hkv, AttentionMask.causal())
+
+
+@pytest.mark.parametrize("one_tile", [False, True])
+def test_running_max_rescale(one_tile):
+    from levanter_b200.ops import _flash_impl
+
+    _flash_impl._FORCE_ONE_TILE = one_tile
+    try:
+        _run(1, 512, 2, 2, AttentionMask.causal(), growing=True)
+        _run(2, 768, 2, 1, AttentionMask.causal(), growing=True, seed=1)
+    finally:
+        _flash_impl._FORCE_ONE_TILE = False
 
 
 def test_sliding_window():
