@@ -50,9 +50,19 @@ class Callback(abc.ABC, Generic[S]):
 class LambdaCallback(Callback[S]):
     def __init__(self, fn: Callable[[StepInfo[S]], Any]):
         self.fn = fn
+        # functions that declare a ``force`` parameter (checkpointing, the eval harness) are told about forced runs
+        try:
+            import inspect
+
+            self._takes_force = "force" in inspect.signature(fn).parameters
+        except (TypeError, ValueError):
+            self._takes_force = False
 
     def on_step(self, info: StepInfo[S], force: bool = False):
-        self.fn(info)
+        if self._takes_force:
+            self.fn(info, force=force)
+        else:
+            self.fn(info)
 
 
 class JitCallback(abc.ABC, Generic[S, M]):

@@ -346,7 +346,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
                         lo, fo, n = engine.segments[name]
                         slot = next(s for s in engine.slots if s.name == name)
                         a = fo - slot.offset
-                        leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype))
+                        leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype).reshape(leaf.shape))
                     return x
                 j = (lambda k: f"{p}.{k}" if p else str(k))
                 if isinstance(x, tuple) and hasattr(x, "_fields"):

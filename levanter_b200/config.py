@@ -12,6 +12,7 @@ import dataclasses
 import enum
 import functools
 import inspect
+import pathlib
 import os
 import sys
 import tempfile
@@ -166,11 +167,13 @@ _DECODERS: Dict[type, Callable[[Any], Any]] = {
     timedelta: lambda v: v if isinstance(v, timedelta) else parse_timedelta(str(v)),
     torch.dtype: parse_dtype,
     Policy: Policy.parse,
+    pathlib.Path: lambda v: pathlib.Path(str(v)),
 }
 _ENCODERS: Dict[type, Callable[[Any], Any]] = {
     timedelta: encode_timedelta,
     torch.dtype: dtype_name,
     Policy: str,
+    pathlib.Path: str,
 }
 
 
@@ -228,7 +231,21 @@ def _type_hints(cls) -> Dict[str, Any]:
     try:
         return typing.get_type_hints(cls)
     except Exception:
-        return {f.name: f.type for f in fields(cls)}
+        # one unresolvable forward reference must not turn every other field into a string: resolve field by field
+        import sys
+
+        out: Dict[str, Any] = {}
+        for klass in reversed(cls.__mro__):
+            ns = dict(vars(sys.modules.get(klass.__module__, typing)))
+            ns.update(vars(typing))
+            for name, ann in getattr(klass, "__annotations__", {}).items():
+                if isinstance(ann, str):
+                    try:
+                        ann = eval(ann, ns)  # noqa: S307 - annotations of our own config classes
+                    except Exception:
+                        ann = Any
+                out[name] = ann
+        return out
 
 
 def _coerce_scalar(tp, value, path):
@@ -401,6 +418,8 @@ def _decode_dataclass(tp, value, path):
 # --------------------------------------------------------------------------- encoding
 def encode(obj) -> Any:
     """Inverse of :func:`decode`: a YAML/JSON-able tree."""
+    if isinstance(obj, enum.Enum):  # before the scalar test: ``class E(str, Enum)`` members are also ``str``
+        return obj.name if not isinstance(obj.value, str) else str(obj.value)
     if obj is None or isinstance(obj, (bool, int, float, str)):
         return obj
     for tp, enc in _ENCODERS.items():

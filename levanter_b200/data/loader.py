@@ -225,3 +225,20 @@ def check_sharded_consistency(batch, mesh=None) -> None:
     dist.all_gather(parts, mine, group=mesh.model_group)
     if any(int(p) != int(mine) for p in parts):
         raise RuntimeError("data differs between tensor-parallel ranks that should hold identical batches")
+
+
+def stack_batches(example_iterator, Pos, Batch, shard: Optional[Tuple[int, int]] = None):
+    """Group an iterator of examples into stacked batches of ``Batch`` rows; a short last batch is padded with all-zero
+    examples (zero loss mask).  With ``shard=(index, count)`` each global batch is cut into ``count`` equal slices and only
+    slice ``index`` is stacked, so every data-parallel rank can run the same iterator."""
+    from .utils import batched
+
+    size = int(getattr(Batch, "size", Batch))
+    for rows in batched(example_iterator, size):
+        if len(rows) < size:
+            rows = rows + [_zeros_like_example(rows[0])] * (size - len(rows))
+        if shard is not None:
+            idx, cnt = shard
+            per = size // cnt
+            rows = rows[idx * per:(idx + 1) * per]
+        yield stack_tree(rows)

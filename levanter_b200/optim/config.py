@@ -19,6 +19,8 @@ import torch
 
 from ..config import ChoiceRegistry
 from . import transforms as T
+from .clip_update_norm import ClipUpdateNormConfig
+from .skipstep import SkipStepConfig
 from .transforms import GradientTransformation
 
 
@@ -346,8 +348,8 @@ class AdamConfig(OptimizerConfig):
     max_grad_norm: Optional[float] = 1.0
     nesterov: bool = False
     update_rms_clipping: Optional[float] = None
-    clip_update_norm: Optional["ClipUpdateNormConfig"] = None  # noqa: F821
-    skip_bad_steps: Union[bool, int, "SkipStepConfig"] = False  # noqa: F821
+    clip_update_norm: Optional[ClipUpdateNormConfig] = None
+    skip_bad_steps: Union[bool, int, SkipStepConfig] = False
     adamc_weight_decay: bool = False
 
     def build(self, num_train_steps: int, param_info: Optional[ParamInfo] = None) -> GradientTransformation:
