@@ -241,9 +241,10 @@ class DecodeState:
                         self.stop_tokens[s, :n, -L:] = st
         return self
 
-    def update_tokens(self, new_tokens, local_slot_ids, new_log_probs, num_new_tokens: int) -> "DecodeState":
+    def update_tokens(self, new_tokens, local_slot_ids, new_log_probs, num_new_tokens: int, enqueue: bool = True) -> "DecodeState":
         """Append sampled tokens to their sequences, detect stop sequences / length limits, and queue the tokens of
-        sequences that go on (finished ones are not fed back)."""
+        sequences that go on (finished ones are not fed back).  ``enqueue=False`` is for tokens the device has already fed
+        into its next round."""
         toks, slots = _np(new_tokens), _np(local_slot_ids)
         lps = None if new_log_probs is None else _np(new_log_probs)
         n = int(num_new_tokens)
@@ -270,9 +271,9 @@ class DecodeState:
             self.finished[sid] = done
             purge_mask[i] = done
             pos_ids[i] = pos
-        keep = ~purge_mask
-        k = int(keep.sum())
-        self.tqueue = self.tqueue.enqueue_tokens(toks[keep], slots[keep], pos_ids[keep], k)
+        if enqueue:
+            keep = ~purge_mask
+            self.tqueue = self.tqueue.enqueue_tokens(toks[keep], slots[keep], pos_ids[keep], int(keep.sum()))
         return self
 
     def is_finished(self, slot_id) -> np.ndarray:

@@ -322,7 +322,13 @@ class LlamaLMHeadModel(LmHeadModel):
         return self
 
     # -- paged-KV inference ------------------------------------------------------------------------------------
-    def initial_cache(self, max_pages: int, page_size: int, *, dtype=torch.bfloat16, device=None):
+    def initial_cache(self, max_pages, page_size: Optional[int] = None, *, dtype=torch.bfloat16, device=None):
+        """One ``KvPageCache`` per layer.  ``max_pages`` may be a page table (then its sizes are used), as in the reference
+        (src/levanter/models/llama.py:581-586)."""
+        if page_size is None and hasattr(max_pages, "num_pages"):
+            max_pages, page_size = max_pages.num_pages, max_pages.page_size
+        if device is None:
+            device = next(self.parameters()).device
         return self.transformer.initial_cache(max_pages, page_size, dtype=dtype, device=device)
 
     def decode(self, input_ids: torch.Tensor, kv_cache, batch_info, pos_ids: torch.Tensor):

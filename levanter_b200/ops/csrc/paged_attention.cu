@@ -1,0 +1,279 @@
+// Paged-KV kernels of the inference engine.
+//
+//  * kv_page_write: scatter the K/V rows of the packed tokens of one forward pass into their (page, slot) destinations.
+//  * paged_attention: causal attention of packed query tokens over the pages of their sequences (decode steps and chunked
+//    prefill), src/levanter/layers/attention.py:1710-1991 in the reference.
+//
+// Cache layout: kv_pages[page, slot, 2 * kv_heads, D] bf16 with K at even and V at odd head index, so one token's K and V
+// rows of a kv head are adjacent 2*D-element runs.
+//
+// paged_attention is bandwidth bound (every step re-reads the context once), so the work is cut for parallelism, not for
+// tensor cores: one CTA per (query token, kv head, partition of 256 keys).  A CTA scores its keys against the G query heads
+// that share the kv head (lanes split the head dimension, 8-byte loads), soft-maxes within the partition in shared memory,
+// accumulates P.V with one output dimension per thread, and writes an un-normalised partial (o, max, sum).  A second small
+// kernel merges the partitions of each (token, head).  Nothing here synchronises with the host: sequence boundaries,
+// lengths and the number of live sequences are read from device arrays, padding tokens produce zeros.
+#include "common.cuh"
+
+namespace lvb {
+namespace paged {
+
+constexpr int kPart = 256;     // keys per partition
+constexpr int kThreads = 128;  // 4 warps
+constexpr int kMaxG = 16;      // query heads per kv head
+
+__global__ void kv_page_write_kernel(__nv_bfloat16* __restrict__ kv_pages, const __nv_bfloat16* __restrict__ k,
+                                     const __nv_bfloat16* __restrict__ v, const int* __restrict__ dests, int kv_heads, int D,
+                                     long long total_slots) {
+  const int t = blockIdx.x;
+  const long long dest = dests[t];
+  if (dest < 0 || dest >= total_slots) return;  // padding token
+  const int row = kv_heads * D;                 // elements of K (or V) per token
+  const int vec = row / 8;                      // uint4 = 8 bf16
+  const uint4* ks = reinterpret_cast<const uint4*>(k + static_cast<long long>(t) * row);
+  const uint4* vs = reinterpret_cast<const uint4*>(v + static_cast<long long>(t) * row);
+  uint4* out = reinterpret_cast<uint4*>(kv_pages + dest * 2 * row);
+  const int per_head = D / 8;
+  for (int i = threadIdx.x; i < vec; i += blockDim.x) {
+    const int h = i / per_head, j = i % per_head;
+    out[(2 * h) * per_head + j] = ks[i];
+    out[(2 * h + 1) * per_head + j] = vs[i];
+  }
+}
+
+// kN consecutive bf16 (kN = 2, 4 or 8) with one load of 4, 8 or 16 bytes.
+template <int kN>
+__device__ __forceinline__ void load_row(const __nv_bfloat16* src, float* dst) {
+  if constexpr (kN == 2) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(src);
+    dst[0] = __low2float(a); dst[1] = __high2float(a);
+  } else if constexpr (kN == 4) {
+    const uint2 w = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w.x), b = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+    dst[0] = __low2float(a); dst[1] = __high2float(a); dst[2] = __low2float(b); dst[3] = __high2float(b);
+  } else {
+    const uint4 w = *reinterpret_cast<const uint4*>(src);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+      dst[2 * i] = __low2float(a); dst[2 * i + 1] = __high2float(a);
+    }
+  }
+}
+
+struct Params {
+  const __nv_bfloat16* q;         // [T, H, D]
+  const __nv_bfloat16* kv_pages;  // [P, ps, 2 * KV, D]
+  const int* kv_lens;             // [S]
+  const int* page_indices;        // [S, pages_per_seq]
+  const int* cu_q_lens;           // [S + 1]
+  const int* num_seqs;            // [1]
+  __nv_bfloat16* out;             // [T, H, D]
+  float* part_o;                  // [T, H, parts, D]
+  float* part_ml;                 // [T, H, parts, 2]
+  int T, H, KV, S, pages_per_seq, page_size, num_pages, parts;
+  float scale, soft_cap;
+};
+
+// Which sequence owns packed token t, and how many keys it may attend to.  Returns false for padding tokens.
+__device__ __forceinline__ bool locate(const Params& p, int t, int& seq, int& ctx) {
+  int n = p.num_seqs[0];
+  n = n < p.S ? n : p.S;
+  if (n <= 0 || t >= p.cu_q_lens[n]) return false;
+  int lo = 0, hi = n;  // first seq with cu[seq + 1] > t
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (p.cu_q_lens[mid + 1] > t) hi = mid; else lo = mid + 1;
+  }
+  seq = lo;
+  const int q0 = p.cu_q_lens[seq], q1 = p.cu_q_lens[seq + 1];
+  const int kl = p.kv_lens[seq];
+  if (kl <= 0 || kl > p.pages_per_seq * p.page_size) return false;
+  ctx = kl - (q1 - q0) + (t - q0) + 1;  // absolute position of the token + 1
+  return ctx > 0;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads) paged_attention_kernel(Params p) {
+  constexpr int kPerLane = D / 32;  // elements of a head row per lane
+  const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
+  const int G = p.H / p.KV;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float s_q[kMaxG * D];
+  __shared__ float s_p[kMaxG * kPart];
+  __shared__ float s_m[kMaxG], s_l[kMaxG];
+  __shared__ int s_rows[kPart];  // flat slot (page * page_size + offset) of each key of the partition
+
+  int seq = 0, ctx = 0;
+  const bool live = locate(p, t, seq, ctx);
+  const int k0 = part * kPart;
+  if (!live || k0 >= ctx) {
+    if (part == 0 && !live) {  // padding token: defined output
+      for (int i = threadIdx.x; i < G * D; i += kThreads)
+        p.out[(static_cast<long long>(t) * p.H + kvh * G) * D + i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  const int nk = min(kPart, ctx - k0);
+  for (int i = threadIdx.x; i < G * D; i += kThreads)
+    s_q[i] = __bfloat162float(p.q[(static_cast<long long>(t) * p.H + kvh * G) * D + i]) * p.scale;
+  for (int i = threadIdx.x; i < nk; i += kThreads) {
+    const int key = k0 + i;
+    const int page = p.page_indices[seq * p.pages_per_seq + key / p.page_size];
+    s_rows[i] = (page >= 0 && page < p.num_pages) ? page * p.page_size + key % p.page_size : -1;
+  }
+  __syncthreads();
+
+  const long long tok_stride = 2LL * p.KV * D;  // elements per cache slot
+  // ---- scores: warp w takes keys w, w + 4, ...; lanes split the head dimension
+  for (int i = warp; i < nk; i += kThreads / 32) {
+    const int r = s_rows[i];
+    float kf[kPerLane];
+    if (r >= 0) {
+      const __nv_bfloat16* krow = p.kv_pages + r * tok_stride + (2LL * kvh) * D + lane * kPerLane;
+      load_row<kPerLane>(krow, kf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < kPerLane; ++e) kf[e] = 0.f;
+    }
+    for (int g = 0; g < G; ++g) {
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < kPerLane; ++e) acc = fmaf(kf[e], s_q[g * D + lane * kPerLane + e], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) {
+        if (p.soft_cap > 0.f) acc = p.soft_cap * tanhf(acc / p.soft_cap);
+        s_p[g * kPart + i] = (r >= 0) ? acc : -INFINITY;
+      }
+    }
+  }
+  __syncthreads();
+  // ---- softmax within the partition: warp w handles heads w, w + 4, ...
+  for (int g = warp; g < G; g += kThreads / 32) {
+    float m = -INFINITY;
+    for (int i = lane; i < nk; i += 32) m = fmaxf(m, s_p[g * kPart + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+    for (int i = lane; i < nk; i += 32) {
+      const float e = (m == -INFINITY) ? 0.f : __expf(s_p[g * kPart + i] - m);
+      s_p[g * kPart + i] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) { s_m[g] = m; s_l[g] = l; }
+  }
+  __syncthreads();
+  // ---- P.V: thread d owns output dimension d (and d + 128 for D = 256) of every head
+  for (int d = threadIdx.x; d < D; d += kThreads) {
+    float o[kMaxG];
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g) o[g] = 0.f;
+    for (int i = 0; i < nk; ++i) {
+      const int r = s_rows[i];
+      if (r < 0) continue;
+      const float v = __bfloat162float(p.kv_pages[r * tok_stride + (2LL * kvh + 1) * D + d]);
+#pragma unroll
+      for (int g = 0; g < kMaxG; ++g)
+        if (g < G) o[g] = fmaf(s_p[g * kPart + i], v, o[g]);
+    }
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g) {
+      if (g >= G) continue;
+      const long long hrow = static_cast<long long>(t) * p.H + kvh * G + g;
+      if (p.parts == 1) {
+        const float l = s_l[g];
+        p.out[hrow * D + d] = __float2bfloat16(l > 0.f ? o[g] / l : 0.f);
+      } else {
+        p.part_o[(hrow * p.parts + part) * D + d] = o[g];
+      }
+    }
+  }
+  if (p.parts > 1 && threadIdx.x < G) {
+    const long long hrow = static_cast<long long>(t) * p.H + kvh * G + threadIdx.x;
+    p.part_ml[(hrow * p.parts + part) * 2 + 0] = s_m[threadIdx.x];
+    p.part_ml[(hrow * p.parts + part) * 2 + 1] = s_l[threadIdx.x];
+  }
+}
+
+// One CTA per (token, head): merge the partials of the partitions that were live for this token.
+template <int D>
+__global__ void __launch_bounds__(D <= 128 ? 128 : 256) paged_merge_kernel(Params p) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  int seq = 0, ctx = 0;
+  if (!locate(p, t, seq, ctx)) return;  // zeros were written by the attention kernel
+  const int np = (ctx + kPart - 1) / kPart;
+  const long long hrow = static_cast<long long>(t) * p.H + h;
+  float m = -INFINITY;
+  for (int i = 0; i < np; ++i) m = fmaxf(m, p.part_ml[(hrow * p.parts + i) * 2]);
+  float l = 0.f;
+  for (int i = 0; i < np; ++i) {
+    const float mi = p.part_ml[(hrow * p.parts + i) * 2];
+    l += (mi == -INFINITY) ? 0.f : p.part_ml[(hrow * p.parts + i) * 2 + 1] * __expf(mi - m);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.f;
+    for (int i = 0; i < np; ++i) {
+      const float mi = p.part_ml[(hrow * p.parts + i) * 2];
+      if (mi == -INFINITY) continue;
+      o = fmaf(p.part_o[(hrow * p.parts + i) * D + d], __expf(mi - m), o);
+    }
+    p.out[hrow * D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+  }
+}
+
+template <int D>
+int launch(const Params& p, cudaStream_t s) {
+  dim3 grid(p.T, p.KV, p.parts);
+  paged_attention_kernel<D><<<grid, kThreads, 0, s>>>(p);
+  if (p.parts > 1) paged_merge_kernel<D><<<dim3(p.T, p.H), D <= 128 ? 128 : 256, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+}  // namespace paged
+}  // namespace lvb
+
+// kv_pages[num_pages, page_size, 2 * kv_heads, D]; k, v [T, kv_heads, D] bf16; dests int32 [T] (page * page_size + slot;
+// out-of-range values are skipped).  D must be a multiple of 8.
+extern "C" int lvb_kv_page_write(void* kv_pages, const void* k, const void* v, const int* dests, int T, int kv_heads, int D,
+                                 long long total_slots, void* stream) {
+  using namespace lvb;
+  if (T <= 0) return kErrOk;
+  if (kv_heads <= 0 || D <= 0 || (D & 7)) return kErrBadArg;
+  paged::kv_page_write_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(kv_pages), reinterpret_cast<const __nv_bfloat16*>(k),
+      reinterpret_cast<const __nv_bfloat16*>(v), dests, kv_heads, D, total_slots);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+// Number of key partitions for a cache whose sequences hold at most max_context tokens: sizes the scratch buffers
+// part_o fp32 [T, H, parts, D] and part_ml fp32 [T, H, parts, 2] (unused when parts == 1).
+extern "C" int lvb_paged_attention_parts(int max_context) { return (max_context + lvb::paged::kPart - 1) / lvb::paged::kPart; }
+
+extern "C" int lvb_paged_attention(const void* q, const void* kv_pages, const int* kv_lens, const int* page_indices,
+                                   const int* cu_q_lens, const int* num_seqs, void* out, float* part_o, float* part_ml, int T,
+                                   int H, int KV, int D, int S, int pages_per_seq, int page_size, int num_pages, float scale,
+                                   float soft_cap, void* stream) {
+  using namespace lvb;
+  using namespace lvb::paged;
+  if (T <= 0) return kErrOk;
+  if (H <= 0 || KV <= 0 || H % KV != 0 || H / KV > kMaxG || S <= 0) return kErrBadArg;
+  Params p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.kv_pages = reinterpret_cast<const __nv_bfloat16*>(kv_pages);
+  p.kv_lens = kv_lens; p.page_indices = page_indices; p.cu_q_lens = cu_q_lens; p.num_seqs = num_seqs;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.part_o = part_o; p.part_ml = part_ml;
+  p.T = T; p.H = H; p.KV = KV; p.S = S; p.pages_per_seq = pages_per_seq; p.page_size = page_size; p.num_pages = num_pages;
+  p.parts = lvb_paged_attention_parts(pages_per_seq * page_size);
+  p.scale = scale; p.soft_cap = soft_cap;
+  if (p.parts > 1 && (part_o == nullptr || part_ml == nullptr)) return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (D) {
+    case 64: return launch<64>(p, s);
+    case 128: return launch<128>(p, s);
+    case 256: return launch<256>(p, s);
+    default: return kErrBadArg;
+  }
+}
