@@ -69,6 +69,11 @@ class RepoRef:
     def __str__(self):
         return self.model_name_or_path if self.revision is None else f"{self.model_name_or_path}@{self.revision}"
 
+    @classmethod
+    def from_config_value(cls, value) -> "RepoRef":
+        """Config files give a repo reference as a plain ``name[@revision]`` string."""
+        return cls.from_string(str(value))
+
 
 def _coerce_ref(ref) -> Optional[RepoRef]:
     if ref is None or isinstance(ref, RepoRef):
