@@ -1,0 +1,183 @@
+"""Micro-benchmarks of this library's kernels: ``python -m levanter_b200.ops.bench_kernels <kernel> [options]``.
+
+Each kernel is timed with CUDA events on the launching stream after warm-up iterations, with a buffer larger than the L2
+cache rewritten between timed iterations (``--no-flush`` turns that off), and reported as achieved TFLOP/s or GB/s and as a
+fraction of the measured peaks in ``MEASURED_PEAKS.json`` at the repository root (falling back to 1.59 PFLOP/s and
+6.65 TB/s when the file is absent).  ``--once`` runs warm-up plus a single launch, which is the shape of run a profiler
+capture wants."""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+
+import torch
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        p = json.load(open(path))
+        return p.get("bf16_tflops", 1590.0), p.get("hbm_gbs", 6650.0), "measured"
+    except Exception:  # noqa: BLE001
+        return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters: int, warmup: int, flush: bool):
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times), min(times)
+
+
+def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
+    tf_peak, bw_peak, how = _peaks()
+    out = {"kernel": name, "config": cfg, "ms_median": round(ms, 4), "ms_min": round(ms_min, 4)}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out[f"frac_of_{how}_bf16_peak"] = round(flops / ms / 1e9 / tf_peak, 3)
+    if nbytes:
+        out["gbs"] = round(nbytes / ms / 1e6, 1)
+        out[f"frac_of_{how}_hbm_peak"] = round(nbytes / ms / 1e6 / bw_peak, 3)
+    print(json.dumps(out))
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["gemm", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=None)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--context", type=int, default=4096, help="paged attention: tokens already in the cache per sequence")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--once", action="store_true", help="warm-up plus one launch (for profiler captures)")
+    a = ap.parse_args(argv)
+    from . import lib
+
+    assert lib.available(), "needs a B200 and the built kernel library"
+    if a.once:
+        a.iters = 1
+    torch.manual_seed(0)
+    dev = "cuda"
+    flush = not a.no_flush
+    bf = torch.bfloat16
+
+    if a.kernel == "gemm":
+        from .gemm import gemm
+
+        A = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        B = torch.randn(a.n, a.k, device=dev, dtype=bf)
+        C = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        ms, mn = _time(lambda: gemm(A, B, out=C), a.iters, a.warmup, flush)
+        return _report("gemm_bf16", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
+
+    if a.kernel in ("flash_fwd", "flash_bwd"):
+        from ..layers.attention import AttentionMask
+        from ._flash_impl import flash_attention_cuda
+
+        kvh = a.kv_heads or a.heads
+        q = torch.randn(a.batch, a.seq, a.heads, 128, device=dev, dtype=bf, requires_grad=True)
+        k = torch.randn(a.batch, a.seq, kvh, 128, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(a.batch, a.seq, kvh, 128, device=dev, dtype=bf, requires_grad=True)
+        mask = AttentionMask.causal()
+        causal_flops = 4.0 * a.batch * a.heads * a.seq * a.seq * 128 / 2
+        cfg = {"batch": a.batch, "seq": a.seq, "heads": a.heads, "kv_heads": kvh, "head_dim": 128, "causal": True}
+        if a.kernel == "flash_fwd":
+            with torch.no_grad():
+                ms, mn = _time(lambda: flash_attention_cuda(q, k, v, mask), a.iters, a.warmup, flush)
+            return _report("flash_attention_fwd", cfg, ms, mn, flops=causal_flops)
+        o = flash_attention_cuda(q, k, v, mask)
+        g = torch.randn_like(o)
+        ms, mn = _time(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), a.iters, a.warmup, flush)
+        return _report("flash_attention_bwd", cfg, ms, mn, flops=2.5 * causal_flops)
+
+    if a.kernel == "rmsnorm":
+        from .norm import rms_norm
+
+        rows = a.batch * a.seq
+        x = torch.randn(rows, a.hidden, device=dev, dtype=bf)
+        w = torch.ones(a.hidden, device=dev, dtype=torch.float32)
+        with torch.no_grad():
+            ms, mn = _time(lambda: rms_norm(x, w, None, 1e-5), a.iters, a.warmup, flush)
+        return _report("rmsnorm_fwd", {"rows": rows, "hidden": a.hidden}, ms, mn, nbytes=2.0 * rows * a.hidden * 2)
+
+    if a.kernel == "cross_entropy":
+        from .cross_entropy import fused_linear_cross_entropy
+
+        rows = a.batch * a.seq
+        x = torch.randn(rows, a.hidden, device=dev, dtype=bf, requires_grad=True)
+        w = (torch.randn(a.vocab, a.hidden, device=dev, dtype=bf) * 0.02).requires_grad_()
+        y = torch.randint(0, a.vocab, (rows,), device=dev)
+
+        def step():
+            loss, _ = fused_linear_cross_entropy(x, w, y)
+            loss.mean().backward()
+
+        ms, mn = _time(step, a.iters, a.warmup, flush)
+        return _report("fused_linear_cross_entropy_fwd_bwd", {"rows": rows, "hidden": a.hidden, "vocab": a.vocab}, ms, mn,
+                       flops=(2.0 + 2.0 + 4.0) * rows * a.hidden * a.vocab)
+
+    if a.kernel == "adamw":
+        from .optim_kernels import adamw
+
+        n = a.m * a.n
+        p = torch.randn(n, device=dev)
+        m = torch.zeros(n, device=dev)
+        v = torch.zeros(n, device=dev)
+        g = torch.randn(n, device=dev)
+        pb = torch.empty(n, device=dev, dtype=bf)
+        ms, mn = _time(lambda: adamw(p, m, v, g, pb, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1 - 0.9 ** 3, 1 - 0.95 ** 3, None), a.iters, a.warmup, flush)
+        return _report("fused_adamw", {"n": n}, ms, mn, nbytes=n * (4 * 4 + 3 * 4 + 2.0))
+
+    if a.kernel == "paged_attention":
+        from . import paged_attention as PA
+
+        kvh = a.kv_heads or a.heads
+        S, ps = a.batch, 16
+        pps = (a.context + ps) // ps + 1
+        P = S * pps
+        kv = torch.randn(P, ps, 2 * kvh, 128, device=dev, dtype=bf)
+        pages = torch.arange(P, device=dev, dtype=torch.int32).reshape(S, pps)
+        lens = torch.full((S,), a.context + 1, device=dev, dtype=torch.int32)
+        cu = torch.arange(S + 1, device=dev, dtype=torch.int32)
+        q = torch.randn(S, a.heads, 128, device=dev, dtype=bf)
+        n = torch.tensor(S, device=dev, dtype=torch.int32)
+        ms, mn = _time(lambda: PA.ragged_paged_attention(q, kv, lens, pages, cu, n, sm_scale=1 / math.sqrt(128)), a.iters, a.warmup, flush)
+        return _report("paged_attention_decode", {"seqs": S, "context": a.context, "heads": a.heads, "kv_heads": kvh}, ms, mn,
+                       nbytes=2.0 * S * (a.context + 1) * kvh * 128 * 2)
+
+    if a.kernel == "sampler":
+        from ..layers.sampler import Sampler
+
+        z = torch.randn(a.batch, a.vocab, device=dev, dtype=bf)
+        t = torch.full((a.batch,), 0.7, device=dev)
+        seeds = torch.arange(a.batch, device=dev, dtype=torch.int64)
+        s = Sampler()
+        ms, mn = _time(lambda: s._cuda(z, t, seeds), a.iters, a.warmup, flush)
+        return _report("sampler", {"rows": a.batch, "vocab": a.vocab}, ms, mn, nbytes=2.0 * a.batch * a.vocab)
+
+
+if __name__ == "__main__":
+    main()

@@ -9,8 +9,8 @@
 //
 // paged_attention is bandwidth bound (every step re-reads the context once), so the work is cut for parallelism, not for
 // tensor cores: one CTA per (query token, kv head, partition of 256 keys).  A CTA scores its keys against the G query heads
-// that share the kv head (lanes split the head dimension, 8-byte loads), soft-maxes within the partition in shared memory,
-// accumulates P.V with one output dimension per thread, and writes an un-normalised partial (o, max, sum).  A second small
+// that share the kv head (one key per thread, 16-byte loads), soft-maxes within the partition in shared memory,
+// accumulates P.V with eight output dimensions per thread, and writes an un-normalised partial (o, max, sum).  A second small
 // kernel merges the partitions of each (token, head).  Nothing here synchronises with the host: sequence boundaries,
 // lengths and the number of live sequences are read from device arrays, padding tokens produce zeros.
 #include "common.cuh"
@@ -94,13 +94,39 @@ __device__ __forceinline__ bool locate(const Params& p, int t, int& seq, int& ct
   return ctx > 0;
 }
 
+// Dot products of one key row (D bf16, read with 16-byte loads) with the G query rows in shared memory.
+template <int D>
+__device__ __forceinline__ void score_key(const __nv_bfloat16* __restrict__ krow, const float* __restrict__ s_q, int G, float* acc) {
+#pragma unroll
+  for (int g = 0; g < kMaxG; ++g) acc[g] = 0.f;
+#pragma unroll 4
+  for (int c = 0; c < D / 8; ++c) {
+    float kf[8];
+    load_row<8>(krow + c * 8, kf);
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g) {
+      if (g < G) {
+        const float4 qa = *reinterpret_cast<const float4*>(s_q + g * D + c * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(s_q + g * D + c * 8 + 4);
+        acc[g] = fmaf(kf[0], qa.x, acc[g]); acc[g] = fmaf(kf[1], qa.y, acc[g]);
+        acc[g] = fmaf(kf[2], qa.z, acc[g]); acc[g] = fmaf(kf[3], qa.w, acc[g]);
+        acc[g] = fmaf(kf[4], qb.x, acc[g]); acc[g] = fmaf(kf[5], qb.y, acc[g]);
+        acc[g] = fmaf(kf[6], qb.z, acc[g]); acc[g] = fmaf(kf[7], qb.w, acc[g]);
+      }
+    }
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads) paged_attention_kernel(Params p) {
-  constexpr int kPerLane = D / 32;  // elements of a head row per lane
+  constexpr int kDimGroups = D / 8;                   // 16-byte column groups of a row
+  constexpr int kKeyGroups = kThreads / kDimGroups;   // rows read side by side in the P.V phase
+  constexpr int kGChunk = 4;                          // heads accumulated per pass over V
   const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
   const int G = p.H / p.KV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ float s_q[kMaxG * D];
+  __shared__ __align__(16) float s_q[kMaxG * D];
+  __shared__ __align__(16) float s_red[(kKeyGroups / 2) * kGChunk * D];  // 2048 floats for every D
   __shared__ float s_p[kMaxG * kPart];
   __shared__ float s_m[kMaxG], s_l[kMaxG];
   __shared__ int s_rows[kPart];  // flat slot (page * page_size + offset) of each key of the partition
@@ -126,25 +152,20 @@ __global__ void __launch_bounds__(kThreads) paged_attention_kernel(Params p) {
   __syncthreads();
 
   const long long tok_stride = 2LL * p.KV * D;  // elements per cache slot
-  // ---- scores: warp w takes keys w, w + 4, ...; lanes split the head dimension
-  for (int i = warp; i < nk; i += kThreads / 32) {
+  // ---- scores: one key per thread, the whole row in 16-byte loads (rows of neighbouring threads are tok_stride apart, so
+  // every 32-byte sector is fetched once and its second half comes from L1)
+  for (int i = threadIdx.x; i < nk; i += kThreads) {
     const int r = s_rows[i];
-    float kf[kPerLane];
+    float acc[kMaxG];
     if (r >= 0) {
-      const __nv_bfloat16* krow = p.kv_pages + r * tok_stride + (2LL * kvh) * D + lane * kPerLane;
-      load_row<kPerLane>(krow, kf);
-    } else {
-#pragma unroll
-      for (int e = 0; e < kPerLane; ++e) kf[e] = 0.f;
+      score_key<D>(p.kv_pages + r * tok_stride + (2LL * kvh) * D, s_q, G, acc);
     }
-    for (int g = 0; g < G; ++g) {
-      float acc = 0.f;
 #pragma unroll
-      for (int e = 0; e < kPerLane; ++e) acc = fmaf(kf[e], s_q[g * D + lane * kPerLane + e], acc);
-      acc = warp_sum(acc);
-      if (lane == 0) {
-        if (p.soft_cap > 0.f) acc = p.soft_cap * tanhf(acc / p.soft_cap);
-        s_p[g * kPart + i] = (r >= 0) ? acc : -INFINITY;
+    for (int g = 0; g < kMaxG; ++g) {
+      if (g < G) {
+        float v = (r >= 0) ? acc[g] : -INFINITY;
+        if (p.soft_cap > 0.f && r >= 0) v = p.soft_cap * tanhf(v / p.soft_cap);
+        s_p[g * kPart + i] = v;
       }
     }
   }
@@ -165,28 +186,63 @@ __global__ void __launch_bounds__(kThreads) paged_attention_kernel(Params p) {
     if (lane == 0) { s_m[g] = m; s_l[g] = l; }
   }
   __syncthreads();
-  // ---- P.V: thread d owns output dimension d (and d + 128 for D = 256) of every head
-  for (int d = threadIdx.x; d < D; d += kThreads) {
-    float o[kMaxG];
+  // ---- P.V: thread (key group kg, dim group dg) walks keys kg, kg + kKeyGroups, ... and owns 8 output dimensions, so a
+  // warp reads whole 256-byte rows; heads are taken kGChunk at a time to bound registers (V re-reads hit L1/L2).
+  const int dg = threadIdx.x % kDimGroups, kg = threadIdx.x / kDimGroups;
+  for (int g0 = 0; g0 < G; g0 += kGChunk) {
+    float o[kGChunk][8];
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g) o[g] = 0.f;
-    for (int i = 0; i < nk; ++i) {
+    for (int g = 0; g < kGChunk; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
+    for (int i = kg; i < nk; i += kKeyGroups) {
       const int r = s_rows[i];
       if (r < 0) continue;
-      const float v = __bfloat162float(p.kv_pages[r * tok_stride + (2LL * kvh + 1) * D + d]);
+      float vf[8];
+      load_row<8>(p.kv_pages + r * tok_stride + (2LL * kvh + 1) * D + dg * 8, vf);
 #pragma unroll
-      for (int g = 0; g < kMaxG; ++g)
-        if (g < G) o[g] = fmaf(s_p[g * kPart + i], v, o[g]);
+      for (int g = 0; g < kGChunk; ++g) {
+        if (g0 + g < G) {
+          const float w = s_p[(g0 + g) * kPart + i];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[g][e] = fmaf(w, vf[e], o[g][e]);
+        }
+      }
     }
+    // tree-reduce the key groups through shared memory
+    for (int half = kKeyGroups / 2; half >= 1; half >>= 1) {
+      if (kg >= half && kg < 2 * half) {
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g) {
-      if (g >= G) continue;
-      const long long hrow = static_cast<long long>(t) * p.H + kvh * G + g;
-      if (p.parts == 1) {
-        const float l = s_l[g];
-        p.out[hrow * D + d] = __float2bfloat16(l > 0.f ? o[g] / l : 0.f);
-      } else {
-        p.part_o[(hrow * p.parts + part) * D + d] = o[g];
+        for (int g = 0; g < kGChunk; ++g)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s_red[((kg - half) * kGChunk + g) * D + dg * 8 + e] = o[g][e];
+      }
+      __syncthreads();
+      if (kg < half) {
+#pragma unroll
+        for (int g = 0; g < kGChunk; ++g)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[g][e] += s_red[(kg * kGChunk + g) * D + dg * 8 + e];
+      }
+      __syncthreads();
+    }
+    if (kg == 0) {
+#pragma unroll
+      for (int g = 0; g < kGChunk; ++g) {
+        if (g0 + g >= G) continue;
+        const long long hrow = static_cast<long long>(t) * p.H + kvh * G + g0 + g;
+        if (p.parts == 1) {
+          const float l = s_l[g0 + g];
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          uint4 w;
+          w.x = pack_bf16x2(o[g][0] * inv, o[g][1] * inv); w.y = pack_bf16x2(o[g][2] * inv, o[g][3] * inv);
+          w.z = pack_bf16x2(o[g][4] * inv, o[g][5] * inv); w.w = pack_bf16x2(o[g][6] * inv, o[g][7] * inv);
+          *reinterpret_cast<uint4*>(p.out + hrow * D + dg * 8) = w;
+        } else {
+          float4* dst = reinterpret_cast<float4*>(p.part_o + (hrow * p.parts + part) * D + dg * 8);
+          dst[0] = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
+          dst[1] = make_float4(o[g][4], o[g][5], o[g][6], o[g][7]);
+        }
       }
     }
   }

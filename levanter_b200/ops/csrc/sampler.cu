@@ -53,14 +53,36 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const T* __restrict__ 
   const float inv_t = greedy ? 1.f : 1.f / t;
   const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
   Acc a{-INFINITY, 0.f, -INFINITY, 0x7fffffff, 0.f};
-  for (int i = threadIdx.x; i < vocab; i += kThreads) {
-    float v;
-    if constexpr (sizeof(T) == 2) v = __bfloat162float(z[i]); else v = z[i];
+  auto visit = [&](float v, int i) {
     v *= inv_t;
     if (v > a.m) { a.s = a.s * __expf(a.m - v) + 1.f; a.m = v; }
     else if (v > -INFINITY) a.s += __expf(v - a.m);
     const float score = greedy ? v : v + gumbel(seed, i);
     if (score > a.best) { a.best = score; a.best_idx = i; a.zbest = v; }
+  };
+  int done = 0;
+  if constexpr (sizeof(T) == 2) {
+    // 16-byte loads (8 logits) when the row starts on a 16-byte boundary
+    if ((reinterpret_cast<uintptr_t>(z) & 15) == 0) {
+      const int nvec = vocab / 8;
+      const uint4* zv = reinterpret_cast<const uint4*>(z);
+      for (int c = threadIdx.x; c < nvec; c += kThreads) {
+        const uint4 w = zv[c];
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&u[j]);
+          visit(__low2float(h), c * 8 + 2 * j);
+          visit(__high2float(h), c * 8 + 2 * j + 1);
+        }
+      }
+      done = nvec * 8;
+    }
+  }
+  for (int i = done + threadIdx.x; i < vocab; i += kThreads) {
+    float v;
+    if constexpr (sizeof(T) == 2) v = __bfloat162float(z[i]); else v = z[i];
+    visit(v, i);
   }
   __shared__ Acc sm[kThreads / 32];
 #pragma unroll
