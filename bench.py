@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--attn", default=None, help="attention backend override")
     ap.add_argument("--remat", action="store_true")
+    ap.add_argument("--comm", default=None, choices=["nccl", "p2p", "multimem"], help="data-parallel collectives: library calls or the peer-memory kernels")
     return ap.parse_args()
 
 
@@ -121,6 +122,8 @@ def main():
     from levanter_b200.tracker import NoopConfig
     from levanter_b200.trainer import Trainer, TrainerConfig
 
+    if args.comm:
+        os.environ["LEVANTER_B200_COMM"] = args.comm
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -154,6 +157,7 @@ def main():
     with Trainer(tcfg, ocfg, add_default_hooks=False) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(vocab, seed=0, device=dev))
         n_params = sum(p.numel() for p in state.model.parameters())
+        comm_used = state.engine.comm if world > 1 else "none"
         ds = SyntheticLmDataset(vocab, S, seed=0)
         loader = trainer.data_loader(ds)
         it = iter(loader.iter_from_step(0))
@@ -227,7 +231,8 @@ def main():
                    "global_batch": B * world, "seq_len": S, "parallelism": f"fsdp{world}" if world > 1 else "single-gpu",
                    "microbatch_per_gpu": micro, "optimizer": "AdamW fp32 master + fp32 moments, global-norm clip 1.0",
                    "params": n_params, "l2_note": "inputs (activations + 13.5 GB of weights per pass) far exceed the 126 MB L2",
-                   "attention_backend": args.attn or "default"},
+                   "attention_backend": args.attn or "default",
+                   "collectives": comm_used},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4, "final_loss": last_loss},

@@ -1,0 +1,276 @@
+// Data-parallel collectives fused with the math around them, over peer-mapped memory (NVLink / NVSwitch).
+//
+// The sharded engine keeps, on every rank, a flat fp32 gradient buffer and a flat bf16 weight buffer with identical
+// layout, allocated as symmetric memory so that each rank holds device pointers to every peer's copy.  One optimizer step
+// then needs two kernels per owned range instead of reduce-scatter -> optimizer -> all-gather library calls:
+//
+//  * p2p_reduce_scatter: out[i] = scale * sum_r grad_r[off + i].  Each rank pulls its own range from every peer with
+//    16-byte loads (starting at a different peer per CTA so that the links are loaded evenly) and writes the reduced range
+//    locally; the per-block sum of squares of the result is produced in the same pass for the global gradient norm.
+//  * p2p_adamw_allgather: the AdamW update of the owned range (fp32 master weights and moments), whose bf16 result is
+//    stored straight into every peer's weight buffer (16-byte stores), i.e. the all-gather is the epilogue of the update.
+//
+// Ordering between ranks (all gradients complete before the pull, all weights stored before the next forward pass) is done
+// by the caller with barriers on the symmetric-memory signal pads; the kernels themselves never wait on another rank.
+// No load here carries a multicast qualifier; peers are addressed with plain global loads and stores.
+#include "common.cuh"
+
+namespace lvb {
+namespace p2p {
+
+constexpr int kBlock = 256;
+constexpr int kMaxWorld = 16;
+
+struct PeerPtrs {
+  void* p[kMaxWorld];
+};
+
+__global__ void __launch_bounds__(kBlock)
+reduce_scatter_kernel(PeerPtrs peers, int world, int rank, long long off, long long n4, float scale, float4* __restrict__ out,
+                      float* __restrict__ partial_sumsq) {
+  float acc_sq = 0.f;
+  const int first = (rank + 1 + blockIdx.x) % world;  // spread the first access over the peers
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int k = 0; k < world; ++k) {
+      int r = first + k;
+      if (r >= world) r -= world;
+      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peers.p[r]) + off)[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    out[i] = s;
+    acc_sq += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  acc_sq = warp_sum(acc_sq);
+  __shared__ float sm[kBlock / 32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc_sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kBlock / 32; ++w) t += sm[w];
+    partial_sumsq[blockIdx.x] = t;
+  }
+}
+
+__global__ void sumsq_accumulate_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out) {
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 32) acc += partial[i];
+  acc = warp_sum(acc);
+  if (threadIdx.x == 0) out[0] += acc;
+}
+
+// 8 elements per thread: fp32 state in two float4, bf16 result in one 16-byte store per peer.
+__global__ void __launch_bounds__(kBlock)
+adamw_allgather_kernel(float4* __restrict__ p, float4* __restrict__ m, float4* __restrict__ v, const float4* __restrict__ g,
+                       PeerPtrs peers, int world, int rank, long long off, long long n8, float lr, float b1, float b2, float eps,
+                       float wd, float bc1, float bc2, const float* __restrict__ grad_scale, int nesterov) {
+  const float gs = grad_scale != nullptr ? grad_scale[0] : 1.f;
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    float out[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long j = 2 * i + h;
+      const float4 gq = g[j];
+      float4 pq = p[j], mq = m[j], vq = v[j];
+      const float gv[4] = {gq.x * gs, gq.y * gs, gq.z * gs, gq.w * gs};
+      float* pv = reinterpret_cast<float*>(&pq);
+      float* mv = reinterpret_cast<float*>(&mq);
+      float* vv = reinterpret_cast<float*>(&vq);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mi = b1 * mv[e] + (1.f - b1) * gv[e];
+        const float vi = b2 * vv[e] + (1.f - b2) * gv[e] * gv[e];
+        mv[e] = mi;
+        vv[e] = vi;
+        float mhat = mi / bc1;
+        if (nesterov) mhat = b1 * (mi / (1.f - (1.f - bc1) * b1)) + (1.f - b1) * gv[e] / bc1;
+        const float u = mhat / (sqrtf(vi / bc2) + eps) + wd * pv[e];
+        pv[e] -= lr * u;
+        out[4 * h + e] = pv[e];
+      }
+      p[j] = pq; m[j] = mq; v[j] = vq;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(out[0], out[1]); w.y = pack_bf16x2(out[2], out[3]);
+    w.z = pack_bf16x2(out[4], out[5]); w.w = pack_bf16x2(out[6], out[7]);
+    const int first = (rank + blockIdx.x) % world;
+#pragma unroll 4
+    for (int k = 0; k < world; ++k) {
+      int r = first + k;
+      if (r >= world) r -= world;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peers.p[r]) + off)[i] = w;
+    }
+  }
+}
+
+
+// ---- the same two kernels through the NVSwitch multicast mapping of the buffers: one `multimem.ld_reduce` returns the sum
+// over all ranks (the reduction happens in the switch), one `multimem.st` stores to every rank's copy, so each element
+// crosses this GPU's links once instead of once per peer.
+__device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, uint4 w) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(w.x)),
+               "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kBlock)
+mm_reduce_scatter_kernel(const float* __restrict__ mc_grad, long long off, long long n4, float scale, float4* __restrict__ out,
+                         float* __restrict__ partial_sumsq) {
+  float acc_sq = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    float4 s = multimem_ld_reduce_add(mc_grad + off + 4 * i);
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    out[i] = s;
+    acc_sq += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  acc_sq = warp_sum(acc_sq);
+  __shared__ float sm[kBlock / 32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc_sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kBlock / 32; ++w) t += sm[w];
+    partial_sumsq[blockIdx.x] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+mm_adamw_allgather_kernel(float4* __restrict__ p, float4* __restrict__ m, float4* __restrict__ v, const float4* __restrict__ g,
+                          __nv_bfloat16* __restrict__ mc_param, long long off, long long n8, float lr, float b1, float b2, float eps,
+                          float wd, float bc1, float bc2, const float* __restrict__ grad_scale, int nesterov) {
+  const float gs = grad_scale != nullptr ? grad_scale[0] : 1.f;
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * kBlock) {
+    float out[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long j = 2 * i + h;
+      const float4 gq = g[j];
+      float4 pq = p[j], mq = m[j], vq = v[j];
+      const float gv[4] = {gq.x * gs, gq.y * gs, gq.z * gs, gq.w * gs};
+      float* pv = reinterpret_cast<float*>(&pq);
+      float* mv = reinterpret_cast<float*>(&mq);
+      float* vv = reinterpret_cast<float*>(&vq);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mi = b1 * mv[e] + (1.f - b1) * gv[e];
+        const float vi = b2 * vv[e] + (1.f - b2) * gv[e] * gv[e];
+        mv[e] = mi;
+        vv[e] = vi;
+        float mhat = mi / bc1;
+        if (nesterov) mhat = b1 * (mi / (1.f - (1.f - bc1) * b1)) + (1.f - b1) * gv[e] / bc1;
+        const float u = mhat / (sqrtf(vi / bc2) + eps) + wd * pv[e];
+        pv[e] -= lr * u;
+        out[4 * h + e] = pv[e];
+      }
+      p[j] = pq; m[j] = mq; v[j] = vq;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(out[0], out[1]); w.y = pack_bf16x2(out[2], out[3]);
+    w.z = pack_bf16x2(out[4], out[5]); w.w = pack_bf16x2(out[6], out[7]);
+    multimem_st_16(mc_param + off + 8 * i, w);
+  }
+}
+
+inline int grid_for(long long work) {
+  long long g = (work + kBlock - 1) / kBlock;
+  long long cap = static_cast<long long>(num_sms()) * 4;
+  if (cap > 1024) cap = 1024;
+  return static_cast<int>(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace p2p
+}  // namespace lvb
+
+// out[0 .. n) = scale * sum over ranks of grad_r[off .. off + n); sumsq[0] += sum(out^2).
+//   peer_grads : host array of `world` device pointers (fp32 bases of every rank's gradient buffer, own rank included)
+//   off, n     : elements; both multiples of 4, and the bases 16-byte aligned
+//   scratch    : fp32 [1024] device scratch for the block partials
+extern "C" int lvb_p2p_reduce_scatter(const void* const* peer_grads, int world, int rank, long long off, long long n, float scale,
+                                      float* out, float* sumsq, float* scratch, void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0) return kErrBadArg;
+  if ((off & 3) || (n & 3) || (reinterpret_cast<uintptr_t>(out) & 15)) return kErrBadArg;
+  PeerPtrs pp;
+  for (int r = 0; r < world; ++r) {
+    if (peer_grads[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_grads[r]) & 15)) return kErrBadArg;
+    pp.p[r] = const_cast<void*>(peer_grads[r]);
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 4);
+  reduce_scatter_kernel<<<grid, kBlock, 0, s>>>(pp, world, rank, off, n / 4, scale, reinterpret_cast<float4*>(out), scratch);
+  if (sumsq != nullptr) sumsq_accumulate_kernel<<<1, 32, 0, s>>>(scratch, grid, sumsq);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+// AdamW on the owned range [0, n) of p/m/v (fp32) with gradients g (fp32), then the bf16 weights are stored to
+// peer_params[r][off .. off + n) for every rank r (own rank included).  off and n multiples of 8; all bases 16-byte aligned.
+extern "C" int lvb_p2p_adamw_allgather(float* p, float* m, float* v, const float* g, const void* const* peer_params, int world,
+                                       int rank, long long off, long long n, float lr, float b1, float b2, float eps, float wd,
+                                       float bc1, float bc2, const float* grad_scale, int nesterov, void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0) return kErrBadArg;
+  if ((off & 7) || (n & 7)) return kErrBadArg;
+  for (const void* q : {static_cast<const void*>(p), static_cast<const void*>(m), static_cast<const void*>(v), static_cast<const void*>(g)})
+    if (reinterpret_cast<uintptr_t>(q) & 15) return kErrBadArg;
+  PeerPtrs pp;
+  for (int r = 0; r < world; ++r) {
+    if (peer_params[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_params[r]) & 15)) return kErrBadArg;
+    pp.p[r] = const_cast<void*>(peer_params[r]);
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  adamw_allgather_kernel<<<grid_for(n / 8), kBlock, 0, s>>>(reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(m),
+                                                          reinterpret_cast<float4*>(v), reinterpret_cast<const float4*>(g), pp,
+                                                          world, rank, off, n / 8, lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
+                                                          nesterov);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+// Multicast variants: mc_grad / mc_param are this rank's multicast addresses of the gradient / weight buffers (one address
+// that reaches every rank's copy through the switch).  Same contract as the peer-pointer entry points above.
+extern "C" int lvb_mm_reduce_scatter(const void* mc_grad, long long off, long long n, float scale, float* out, float* sumsq,
+                                     float* scratch, void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  if (mc_grad == nullptr || n <= 0 || (off & 3) || (n & 3) || (reinterpret_cast<uintptr_t>(mc_grad) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 4);
+  mm_reduce_scatter_kernel<<<grid, kBlock, 0, s>>>(reinterpret_cast<const float*>(mc_grad), off, n / 4, scale,
+                                                  reinterpret_cast<float4*>(out), scratch);
+  if (sumsq != nullptr) sumsq_accumulate_kernel<<<1, 32, 0, s>>>(scratch, grid, sumsq);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+extern "C" int lvb_mm_adamw_allgather(float* p, float* m, float* v, const float* g, void* mc_param, long long off, long long n,
+                                      float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                                      const float* grad_scale, int nesterov, void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  if (mc_param == nullptr || n <= 0 || (off & 7) || (n & 7) || (reinterpret_cast<uintptr_t>(mc_param) & 15)) return kErrBadArg;
+  for (const void* q : {static_cast<const void*>(p), static_cast<const void*>(m), static_cast<const void*>(v), static_cast<const void*>(g)})
+    if (reinterpret_cast<uintptr_t>(q) & 15) return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  mm_adamw_allgather_kernel<<<grid_for(n / 8), kBlock, 0, s>>>(reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(m),
+                                                             reinterpret_cast<float4*>(v), reinterpret_cast<const float4*>(g),
+                                                             reinterpret_cast<__nv_bfloat16*>(mc_param), off, n / 8, lr, b1, b2,
+                                                             eps, wd, bc1, bc2, grad_scale, nesterov);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}

@@ -83,7 +83,13 @@ def default_bucket_of(model: nn.Module) -> Callable[[str], str]:
 class ShardedEngine:
     def __init__(self, model: nn.Module, mp: Policy, mesh=None, *, device=None, shard_optimizer: bool = True,
                  grad_reduce_dtype: torch.dtype = torch.float32, is_trainable: Optional[Callable[[str], bool]] = None,
-                 bucket_of: Optional[Callable[[str], str]] = None):
+                 bucket_of: Optional[Callable[[str], str]] = None, comm: Optional[str] = None):
+        """``comm``: ``"nccl"`` (library reduce-scatter / all-gather per bucket) or ``"p2p"`` (gradient pull-reduce and AdamW with
+        an all-gather epilogue as two kernels over peer-mapped buffers); default from ``LEVANTER_B200_COMM``, else ``nccl``."""
+        import os as _os
+
+        self.comm = (comm or _os.environ.get("LEVANTER_B200_COMM", "nccl")).lower()  # nccl | p2p | multimem
+        self._sym_param = self._sym_grad = None
         self.model = model
         self.mp = mp
         self.mesh = mesh
@@ -142,8 +148,25 @@ class ShardedEngine:
             cur.end = cur.start + _round_up(off - cur.start, W * ALIGN)
             off = cur.end
         self.total = off
-        self.param_flat = torch.zeros(self.total, dtype=cd, device=self.device)
-        self.grad_flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        use_p2p = False
+        if self.comm in ("p2p", "multimem") and W > 1 and self.shard_optimizer and self.device.type == "cuda" and cd == torch.bfloat16:
+            from .symm import p2p_available
+
+            use_p2p = p2p_available(self.data_group)
+        if use_p2p:
+            from .symm import SymmetricBuffer
+
+            self._sym_param = SymmetricBuffer(self.total, cd, self.device, self.data_group)
+            self._sym_grad = SymmetricBuffer(self.total, torch.float32, self.device, self.data_group)
+            self.param_flat, self.grad_flat = self._sym_param.tensor, self._sym_grad.tensor
+            if self.comm == "multimem" and not (self._sym_param.multicast_ptr and self._sym_grad.multicast_ptr):
+                self.comm = "p2p"  # no multicast mapping on this fabric: plain peer loads and stores
+            self._p2p_scratch = torch.zeros(1024, dtype=torch.float32, device=self.device)
+            self._p2p_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        else:
+            self.comm = "nccl"
+            self.param_flat = torch.zeros(self.total, dtype=cd, device=self.device)
+            self.grad_flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         # owned slices, concatenated bucket by bucket
         self.shard_numel = self.total // W if self.shard_optimizer else self.total
         self.master_is_param = (pd == cd and W == 1) or (pd == cd and not self.shard_optimizer)
@@ -252,6 +275,11 @@ class ShardedEngine:
     def reduce_grads(self, scale: float = 1.0) -> None:
         """Average gradients over the data axis into the owned slices (and over replicas)."""
         W = self.world
+        if self._sym_grad is not None:
+            self._p2p_reduce_grads(scale)
+            if self.replica_group is not None:
+                dist.all_reduce(self.grad_shard, op=dist.ReduceOp.AVG, group=self.replica_group)
+            return
         if scale != 1.0:
             self.grad_flat.mul_(scale)
         if W > 1:
@@ -272,12 +300,46 @@ class ShardedEngine:
         if self.replica_group is not None:
             dist.all_reduce(self.grad_shard, op=dist.ReduceOp.AVG, group=self.replica_group)
 
+    def _p2p_reduce_grads(self, scale: float) -> None:
+        """Every rank pulls and sums its owned range of every bucket from all peers' gradient buffers (one kernel per bucket);
+        the sum of squares of the reduced range comes out of the same pass."""
+        from ..ops import lib
+
+        c = lib
+        f = getattr(self, "_f_rs", None)
+        if f is None:
+            f = self._f_rs = lib.fn("lvb_p2p_reduce_scatter", [c.c_void_p, c.c_int, c.c_int, c.c_longlong, c.c_longlong, c.c_float,
+                                                                c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p], launches=2)
+        W = self.world
+        self._sym_grad.barrier(0)  # every rank has finished writing its gradients
+        self._p2p_sumsq.zero_()
+        fm = None
+        if self.comm == "multimem":
+            fm = getattr(self, "_f_mrs", None)
+            if fm is None:
+                fm = self._f_mrs = lib.fn("lvb_mm_reduce_scatter", [c.c_void_p, c.c_longlong, c.c_longlong, c.c_float, c.c_void_p, c.c_void_p,
+                                                                    c.c_void_p, c.c_void_p], launches=2)
+        for b, lstart in zip(self.buckets, self._bucket_local_start):
+            lo, hi = b.shard_range(self.rank, W)
+            out = self.grad_shard[lstart:lstart + (hi - lo)]
+            if fm is not None:
+                rc = fm(self._sym_grad.multicast_ptr, lo, hi - lo, float(scale) / W, out.data_ptr(), self._p2p_sumsq.data_ptr(),
+                        self._p2p_scratch.data_ptr(), lib.stream_ptr())
+            else:
+                rc = f(self._sym_grad.c_ptrs, W, self.rank, lo, hi - lo, float(scale) / W, out.data_ptr(), self._p2p_sumsq.data_ptr(),
+                       self._p2p_scratch.data_ptr(), lib.stream_ptr())
+            lib.check_rc(rc, "lvb_p2p_reduce_scatter")
+        self._p2p_sumsq_valid = True
+
     def grad_sumsq(self) -> torch.Tensor:
         """Sum of squared gradients over *all* parameters (device scalar), reduced over the mesh."""
         from ..ops import lib
 
         g = self.grad_shard
-        if self.device.type == "cuda" and lib.available():
+        if self._sym_grad is not None and getattr(self, "_p2p_sumsq_valid", False) and self.replica_group is None:
+            sq = self._p2p_sumsq.clone()
+            self._p2p_sumsq_valid = False
+        elif self.device.type == "cuda" and lib.available():
             from ..ops.optim_kernels import sumsq
 
             sq = sumsq(g)
@@ -320,6 +382,9 @@ class ShardedEngine:
                 T.set_norm_reduce_group(None)
             T.apply_updates(params, updates)
         self.publish_params()
+        if self._sym_grad is not None:
+            # peers read this rank's gradients and write this rank's weights: nobody may run ahead into the next step
+            self._sym_param.barrier(1)
         self.zero_grad()
 
     def publish_params(self) -> None:
@@ -331,6 +396,8 @@ class ShardedEngine:
             if self.fused_adam is None or not self.fused_adam.writes_compute_copy:
                 self.param_flat.copy_(self.master)
             return
+        if self._sym_param is not None and self.fused_adam is not None and self.fused_adam.writes_compute_copy:
+            return  # the optimizer kernel stored the new weights into every peer's buffer
         for b, lstart in zip(self.buckets, self._bucket_local_start):
             lo, hi = b.shard_range(self.rank, W)
             n = hi - lo
@@ -518,6 +585,33 @@ class FusedAdamW:
         clip_coef(sq, float(c.max_grad_norm or 0.0), self.coef, self.norm)
         e.last_grad_norm = self.norm
         W = e.world
+        if e._sym_param is not None:
+            from ..ops import lib
+
+            cc = lib
+            f = getattr(self, "_f_ag", None)
+            if f is None:
+                f = self._f_ag = lib.fn("lvb_p2p_adamw_allgather", [cc.c_void_p] * 5 + [cc.c_int, cc.c_int, cc.c_longlong, cc.c_longlong]
+                                        + [cc.c_float] * 7 + [cc.c_void_p, cc.c_int, cc.c_void_p])
+            for lo, hi, wd in self.runs:
+                if hi <= lo:
+                    continue
+                hi8 = lo + ((hi - lo + 7) // 8) * 8  # the tail up to the next 8 is layout padding (zero weights, zero gradients)
+                if e.comm == "multimem":
+                    fm = getattr(self, "_f_mag", None)
+                    if fm is None:
+                        fm = self._f_mag = lib.fn("lvb_mm_adamw_allgather", [cc.c_void_p] * 5 + [cc.c_longlong, cc.c_longlong] + [cc.c_float] * 7
+                                                  + [cc.c_void_p, cc.c_int, cc.c_void_p])
+                    rc = fm(e.master[lo:hi8].data_ptr(), self.m[lo:hi8].data_ptr(), self.v[lo:hi8].data_ptr(), e.grad_shard[lo:hi8].data_ptr(),
+                            e._sym_param.multicast_ptr, self._local_to_flat(lo), hi8 - lo, lr, c.beta1, c.beta2, c.epsilon, wd, bc1, bc2,
+                            self.coef.data_ptr(), int(c.nesterov), lib.stream_ptr())
+                    lib.check_rc(rc, "lvb_mm_adamw_allgather")
+                    continue
+                rc = f(e.master[lo:hi8].data_ptr(), self.m[lo:hi8].data_ptr(), self.v[lo:hi8].data_ptr(), e.grad_shard[lo:hi8].data_ptr(),
+                       e._sym_param.c_ptrs, W, e.rank, self._local_to_flat(lo), hi8 - lo, lr, c.beta1, c.beta2, c.epsilon, wd, bc1, bc2,
+                       self.coef.data_ptr(), int(c.nesterov), lib.stream_ptr())
+                lib.check_rc(rc, "lvb_p2p_adamw_allgather")
+            return
         for lo, hi, wd in self.runs:
             if hi <= lo:
                 continue
