@@ -85,10 +85,12 @@ class ShardedEngine:
                  grad_reduce_dtype: torch.dtype = torch.float32, is_trainable: Optional[Callable[[str], bool]] = None,
                  bucket_of: Optional[Callable[[str], str]] = None, comm: Optional[str] = None):
         """``comm``: ``"nccl"`` (library reduce-scatter / all-gather per bucket) or ``"p2p"`` (gradient pull-reduce and AdamW with
-        an all-gather epilogue as two kernels over peer-mapped buffers); default from ``LEVANTER_B200_COMM``, else ``nccl``."""
+        an all-gather epilogue as two kernels over peer-mapped buffers); ``"multimem"`` is the same through the switch's multicast mapping (one reduced load, one broadcast store per
+        element).  Default: ``LEVANTER_B200_COMM`` if set, else ``multimem``, degrading to ``p2p`` and ``nccl`` when the fabric
+        or the runtime lacks what the mode needs."""
         import os as _os
 
-        self.comm = (comm or _os.environ.get("LEVANTER_B200_COMM", "nccl")).lower()  # nccl | p2p | multimem
+        self.comm = (comm or _os.environ.get("LEVANTER_B200_COMM", "multimem")).lower()  # nccl | p2p | multimem
         self._sym_param = self._sym_grad = None
         self.model = model
         self.mp = mp
@@ -156,8 +158,16 @@ class ShardedEngine:
         if use_p2p:
             from .symm import SymmetricBuffer
 
-            self._sym_param = SymmetricBuffer(self.total, cd, self.device, self.data_group)
-            self._sym_grad = SymmetricBuffer(self.total, torch.float32, self.device, self.data_group)
+            try:
+                self._sym_param = SymmetricBuffer(self.total, cd, self.device, self.data_group)
+                self._sym_grad = SymmetricBuffer(self.total, torch.float32, self.device, self.data_group)
+            except Exception as e:  # noqa: BLE001 - every rank takes the same path: the rendezvous is collective
+                import logging
+
+                logging.getLogger(__name__).warning(f"symmetric memory unavailable ({e}); using NCCL collectives")
+                self._sym_param = self._sym_grad = None
+                use_p2p = False
+        if use_p2p:
             self.param_flat, self.grad_flat = self._sym_param.tensor, self._sym_grad.tensor
             if self.comm == "multimem" and not (self._sym_param.multicast_ptr and self._sym_grad.multicast_ptr):
                 self.comm = "p2p"  # no multicast mapping on this fabric: plain peer loads and stores
