@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -92,6 +92,16 @@ def main(argv=None):
         C = torch.empty(a.m, a.n, device=dev, dtype=bf)
         ms, mn = _time(lambda: gemm(A, B, out=C), a.iters, a.warmup, flush)
         return _report("gemm_bf16", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
+
+    if a.kernel == "gemm_fp8":
+        from .fp8 import E4M3, fp8_gemm, quantize
+
+        A, sa = quantize(torch.randn(a.m, a.k, device=dev), E4M3)
+        B, sb = quantize(torch.randn(a.n, a.k, device=dev), E4M3)
+        C = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        sc = sa * sb
+        ms, mn = _time(lambda: fp8_gemm(A, B, sc, out=C), a.iters, a.warmup, flush)
+        return _report("gemm_fp8_e4m3", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
 
     if a.kernel in ("flash_fwd", "flash_bwd"):
         from ..layers.attention import AttentionMask

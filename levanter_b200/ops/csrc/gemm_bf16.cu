@@ -48,6 +48,8 @@ struct Params {
   float alpha;
   int tiles_m, tiles_n;
   int* status;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha (fp8: product of the two operand scales)
+  int a_fmt, b_fmt;        // fp8 only: 0 = e4m3, 1 = e5m2
 };
 
 template <int BN>
@@ -73,7 +75,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   nb = r / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// kF8: one-byte operands (both K-major); a stage row is still 128 bytes, i.e. 128 elements of K instead of 64.
+template <int BN, bool A_MN, bool B_MN, bool kF8 = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
   using L = SmemLayout<BN>;
@@ -90,7 +93,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  constexpr int BKE = kF8 ? 2 * BK : BK;  // elements of K per stage
+  const int k_blocks = (p.K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -131,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           } else {
@@ -153,7 +157,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = kF8 ? make_idesc_f8(BM, BN, p.a_fmt, p.b_fmt) : make_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -180,7 +184,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           constexpr uint32_t b_step = (B_MN ? 2048 : 32) >> 4;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16_ss(tmem_acc, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (kF8) umma_f8_ss(tmem_acc, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_bf16_ss(tmem_acc, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -198,6 +203,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     bool ok = true;
     const bool out_f32 = (p.flags & kOutF32) != 0;
     const bool accum = (p.flags & kAccumulate) != 0;
+    const float alpha = p.alpha_dev != nullptr ? p.alpha * p.alpha_dev[0] : p.alpha;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
@@ -217,7 +223,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (row < p.M && col0 < p.N) {
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
           const bool full = (col0 + 32 <= p.N);
           if (p.flags & kBias) {
             if (p.flags & kBiasF32) {
@@ -370,6 +376,8 @@ extern "C" int lvb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.flags = flags;
   p.alpha = alpha;
   p.status = status;
+  p.alpha_dev = nullptr;
+  p.a_fmt = p.b_fmt = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool wide = (N > 128);
   if (wide) {
@@ -383,4 +391,60 @@ extern "C" int lvb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     if (a_mn && b_mn) return launch<128, true, true>(A, B, p, lda, ldb, s, max_ctas);
     return launch<128, true, false>(A, B, p, lda, ldb, s, max_ctas);
   }
+}
+
+
+namespace lvb {
+namespace gemm {
+
+template <int BN>
+int launch_f8(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream, int max_ctas) {
+  using L = SmemLayout<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d_u8(&tmA, A, p.M, p.K, lda, BM);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_u8(&tmB, B, p.N, p.K, ldb, BN);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_kernel<BN, false, false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  int cap = num_sms();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  if (grid > cap) grid = cap;
+  kern<<<grid, kNumThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+}  // namespace gemm
+}  // namespace lvb
+
+// fp8 GEMM with per-tensor scales: C[M,N] = alpha * scale[0] * A[M,K] B[N,K]^T (+ C if accumulate).
+//   A, B   : one-byte floats, K contiguous (row strides lda / ldb bytes, multiples of 16); a_fmt / b_fmt: 0 = e4m3, 1 = e5m2
+//   scale  : optional device fp32 scalar (the product of the operands' de-quantisation scales), so no host sync is needed
+//   flags  : kOutF32 / kAccumulate / kBias / kBiasF32 / kResidual as for lvb_gemm_bf16; C is bf16 unless kOutF32
+extern "C" int lvb_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_fmt,
+                            int b_fmt, int flags, float alpha, const float* scale, const void* bias, const void* residual,
+                            int ldr, int max_ctas, int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 15) || (ldb & 15) || a_fmt < 0 || a_fmt > 1 || b_fmt < 0 || b_fmt > 1) return kErrBadArg;
+  Params p;
+  p.C = C;
+  p.bias = bias;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ldr = ldr;
+  p.flags = flags;
+  p.alpha = alpha;
+  p.status = status;
+  p.alpha_dev = scale;
+  p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return N > 128 ? launch_f8<256>(A, B, p, lda, ldb, s, max_ctas) : launch_f8<128>(A, B, p, lda, ldb, s, max_ctas);
 }

@@ -77,3 +77,24 @@ def test_gemm_deterministic():
     c1 = G.gemm(a, b).clone()
     c2 = G.gemm(a, b)
     assert torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 520, 384), (1024, 128, 2048)])
+@pytest.mark.parametrize("a_dt,b_dt", [("e4m3", "e4m3"), ("e5m2", "e4m3")])
+def test_fp8_gemm_matches_dequantised_reference(M, N, K, a_dt, b_dt):
+    from levanter_b200.ops.fp8 import E4M3, E5M2, fp8_gemm, quantize
+
+    dts = {"e4m3": E4M3, "e5m2": E5M2}
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda")
+    b = torch.randn(N, K, device="cuda")
+    aq, sa = quantize(a, dts[a_dt])
+    bq, sb = quantize(b, dts[b_dt])
+    got = fp8_gemm(aq, bq, sa * sb, out_dtype=torch.float32)
+    want = (aq.float() @ bq.float().t()) * (sa * sb)
+    torch.cuda.synchronize()
+    lib.check_status()
+    assert (got - want).abs().max() <= 1e-3 * want.abs().max()
+    acc = torch.ones(M, N, device="cuda")
+    fp8_gemm(aq, bq, sa * sb, out=acc, accumulate=True)
+    assert (acc - 1 - want).abs().max() <= 1e-3 * want.abs().max()
