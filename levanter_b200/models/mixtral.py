@@ -231,6 +231,13 @@ class MixtralLMHeadModel(LmHeadModel):
 
     @classmethod
     def init(cls, vocab_size: int, config, *, tp=None, ep=None):
+        if ep is None and getattr(config, "expert_parallel", False):
+            import torch.distributed as dist
+
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                from ..parallel.expert import ExpertParallel
+
+                ep = ExpertParallel(None)
         return cls(vocab_size, config, tp=tp, ep=ep)
 
     @property

@@ -120,6 +120,10 @@ class ShardedEngine:
                 continue
             seen[id(p)] = name
             trainable = p.requires_grad and (is_trainable is None or is_trainable(name))
+            if trainable and W > 1 and getattr(p, "ep_dim", None) is not None:
+                raise NotImplementedError(
+                    f"{name} is expert-parallel (a different slice on every rank); the sharded engine reduces every gradient over the "
+                    "data axis and does not keep rank-local parameters yet: train expert-parallel models with a local optimizer")
             if not trainable:
                 p.requires_grad_(False)
                 if p.is_floating_point():
