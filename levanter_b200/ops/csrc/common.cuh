@@ -318,17 +318,18 @@ inline EncodeTiledFn get_encode_tiled() {
 // cuTensorMapEncodeTiled is a driver call and needs a context bound to the
 // calling thread.  Threads that have only ever launched through the runtime
 // lazily (for example an autograd worker thread) may have none yet, so the
-// first encode on each thread binds the primary context of the device that
-// owns the operand.
-inline void ensure_context_for(const void* ptr) {
+// first encode on each thread binds the primary context of the thread's
+// CURRENT device.  The operand's own device must not be used here: an operand
+// may live in a peer GPU's memory (fused all-gather), and switching to that
+// device would send every later launch of this thread to the wrong GPU.
+inline void ensure_context_for(const void* /*ptr*/) {
   static thread_local bool bound = false;
   if (bound) return;
-  cudaPointerAttributes attr;
-  int dev = -1;
-  if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) dev = attr.device;
-  if (dev < 0) cudaGetDevice(&dev);
-  cudaSetDevice(dev);
-  cudaFree(nullptr);
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    cudaSetDevice(dev);
+    cudaFree(nullptr);
+  }
   bound = true;
 }
 

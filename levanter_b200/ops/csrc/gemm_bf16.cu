@@ -29,6 +29,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;     // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kNumThreads = 192;  // warp0 TMA, warp1 MMA, warps2-5 epilogue
+constexpr int kMaxPeers = 8;
 
 enum EpiFlags : int {
   kOutF32 = 1,       // C is float (else bf16)
@@ -50,6 +51,16 @@ struct Params {
   int* status;
   const float* alpha_dev;  // optional device scalar multiplied into alpha (fp8: product of the two operand scales)
   int a_fmt, b_fmt;        // fp8 only: 0 = e4m3, 1 = e5m2
+  // fused collectives (0 = off).  a_rows_per_map: rows [r * a_rows_per_map, (r + 1) * a_rows_per_map) of A live in rank r's
+  // memory and are fetched through tensor map r (all-gather fused into the operand loads).  c_rows_per_rank: rows of C in
+  // that range are stored to c_peer[r] (this rank's slot in rank r's staging buffer: the scatter half of a reduce-scatter).
+  int a_rows_per_map;
+  int c_rows_per_rank;
+  void* c_peer[kMaxPeers];
+};
+
+struct PeerMaps {
+  CUtensorMap maps[kMaxPeers];
 };
 
 template <int BN>
@@ -77,8 +88,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 
 // kF8: one-byte operands (both K-major); a stage row is still 128 bytes, i.e. 128 elements of K instead of 64.
 template <int BN, bool A_MN, bool B_MN, bool kF8 = false>
-__global__ void __launch_bounds__(kNumThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+__device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUtensorMap& tmB, const Params& p) {
+  const CUtensorMap& tmA = tmA_maps[0];
   using L = SmemLayout<BN>;
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -137,7 +148,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           const int k0 = kb * BKE;
           if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+            if (p.a_rows_per_map > 0) {
+              const int r = m0 / p.a_rows_per_map;  // the rank whose memory holds these rows
+              tma_load_2d(sa, tmA_maps + r, &full_bar[stage], k0, m0 - r * p.a_rows_per_map);
+            } else {
+              tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -213,6 +229,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
+      void* c_base = p.C;
+      size_t c_row = static_cast<size_t>(row);
+      if (p.c_rows_per_rank > 0 && row < p.M) {
+        const int d = row / p.c_rows_per_rank;
+        c_base = p.c_peer[d];
+        c_row = static_cast<size_t>(row - d * p.c_rows_per_rank);
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -259,7 +282,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
           if (out_f32) {
-            float* cp = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            float* cp = reinterpret_cast<float*>(c_base) + c_row * p.ldc + col0;
             if (full && (p.ldc & 3) == 0) {
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
@@ -276,7 +299,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (col0 + j < p.N) cp[j] = accum ? cp[j] + v[j] : v[j];
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(c_base) + c_row * p.ldc + col0;
             if (full && (p.ldc & 7) == 0) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -320,6 +343,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     tmem_dealloc<2 * BN>(tmem_base);
   }
+}
+
+template <int BN, bool A_MN, bool B_MN, bool kF8 = false>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, A_MN, B_MN, kF8>(&tmA, tmB, p);
+}
+
+// A's row blocks come from different ranks' memories: one tensor map per rank (plain TMA loads, no cluster qualifier).
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_gathered_a_kernel(const __grid_constant__ PeerMaps tmAs, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, false, false, false>(tmAs.maps, tmB, p);
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -378,6 +414,8 @@ extern "C" int lvb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.status = status;
   p.alpha_dev = nullptr;
   p.a_fmt = p.b_fmt = 0;
+  p.a_rows_per_map = 0;
+  p.c_rows_per_rank = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool wide = (N > 128);
   if (wide) {
@@ -445,6 +483,115 @@ extern "C" int lvb_gemm_fp8(const void* A, const void* B, void* C, int M, int N,
   p.status = status;
   p.alpha_dev = scale;
   p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.a_rows_per_map = 0;
+  p.c_rows_per_rank = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return N > 128 ? launch_f8<256>(A, B, p, lda, ldb, s, max_ctas) : launch_f8<128>(A, B, p, lda, ldb, s, max_ctas);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Tensor-parallel GEMMs with the collective fused in (sequence-parallel layout: activations are split by rows over ranks).
+namespace lvb {
+namespace gemm {
+
+template <int BN>
+int launch_gathered_a(const void* const* a_peers, const void* B, Params p, int world, int lda, int ldb, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  PeerMaps maps;
+  CUtensorMap tmB;
+  for (int r = 0; r < world; ++r) {
+    int rc = make_tmap_2d_bf16(&maps.maps[r], a_peers[r], p.a_rows_per_map, p.K, lda, BM, BK);
+    if (rc != kErrOk) return rc;
+  }
+  for (int r = world; r < kMaxPeers; ++r) maps.maps[r] = maps.maps[0];
+  int rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_gathered_a_kernel<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > num_sms()) grid = num_sms();
+  kern<<<grid, kNumThreads, L::kTotal, stream>>>(maps, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+}  // namespace gemm
+}  // namespace lvb
+
+// All-gather fused into a GEMM: C[M, N] = concat_r(A_r)[M, K] B[N, K]^T where A_r [M / world, K] (bf16, row stride lda)
+// is rank r's shard, read in place from rank r's memory by TMA (a_peers[r]: device pointer valid on this GPU; own rank
+// included).  M / world must be a multiple of 128.  The caller orders the ranks (every A_r complete before the launch).
+extern "C" int lvb_gemm_allgather_a(const void* const* a_peers, int world, const void* B, void* C, int M, int N, int K, int lda,
+                                    int ldb, int ldc, int flags, float alpha, const void* bias, int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (world <= 0 || world > kMaxPeers || M <= 0 || N <= 0 || K <= 0 || M % world != 0 || (M / world) % BM != 0) return kErrBadArg;
+  if ((lda & 7) || (ldb & 7)) return kErrBadArg;
+  Params p;
+  p.C = C; p.bias = bias; p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+  p.flags = flags; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.a_fmt = p.b_fmt = 0;
+  p.a_rows_per_map = M / world;
+  p.c_rows_per_rank = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return N > 128 ? launch_gathered_a<256>(a_peers, B, p, world, lda, ldb, s) : launch_gathered_a<128>(a_peers, B, p, world, lda, ldb, s);
+}
+
+// The scatter half of a reduce-scatter fused into a GEMM epilogue: this rank's partial product P[M, N] = A[M, K] B[N, K]^T
+// (K is the sharded dimension) is stored, rows [r * M / world, (r + 1) * M / world) to c_peers[r], which the caller points at
+// this rank's slot of rank r's staging buffer [world, M / world, ldc].  Every rank then sums its own staging buffer over the
+// slots (lvb_sum_slots).  Output dtype per flags (fp32 with kOutF32, else bf16).
+extern "C" int lvb_gemm_scatter_c(const void* A, const void* B, void* const* c_peers, int world, int M, int N, int K, int lda,
+                                  int ldb, int ldc, int flags, float alpha, int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (world <= 0 || world > kMaxPeers || M <= 0 || N <= 0 || K <= 0 || M % world != 0) return kErrBadArg;
+  if ((lda & 7) || (ldb & 7)) return kErrBadArg;
+  Params p;
+  p.C = c_peers[0]; p.bias = nullptr; p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+  p.flags = flags & kOutF32; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.a_fmt = p.b_fmt = 0;
+  p.a_rows_per_map = 0;
+  p.c_rows_per_rank = M / world;
+  for (int r = 0; r < kMaxPeers; ++r) p.c_peer[r] = c_peers[r < world ? r : 0];
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return N > 128 ? launch<256, false, false>(A, B, p, lda, ldb, s, 0) : launch<128, false, false>(A, B, p, lda, ldb, s, 0);
+}
+
+namespace lvb {
+namespace gemm {
+__global__ void sum_slots_kernel(const float4* __restrict__ staging, long long slot4, int world, float4* __restrict__ out_f32,
+                                 uint2* __restrict__ out_bf16, long long n4) {
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n4; i += gridDim.x * 256LL) {
+    float4 s = staging[i];
+    for (int r = 1; r < world; ++r) {
+      const float4 v = staging[r * slot4 + i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    if (out_f32 != nullptr) out_f32[i] = s;
+    if (out_bf16 != nullptr) out_bf16[i] = make_uint2(pack_bf16x2(s.x, s.y), pack_bf16x2(s.z, s.w));
+  }
+}
+}  // namespace gemm
+}  // namespace lvb
+
+// out[n] = sum over slots of staging[slot][n] (fp32 staging, n a multiple of 4); bf16 and/or fp32 output.
+extern "C" int lvb_sum_slots(const float* staging, long long slot_elems, int world, float* out_f32, void* out_bf16, long long n,
+                             void* stream) {
+  using namespace lvb;
+  if (world <= 0 || n <= 0 || (n & 3) || (slot_elems & 3)) return kErrBadArg;
+  long long blocks = (n / 4 + 255) / 256;
+  long long cap = static_cast<long long>(num_sms()) * 8;
+  gemm::sum_slots_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(staging), slot_elems / 4, world, reinterpret_cast<float4*>(out_f32),
+      reinterpret_cast<uint2*>(out_bf16), n / 4);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }

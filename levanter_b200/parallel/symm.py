@@ -18,6 +18,8 @@ class SymmetricBuffer:
     def __init__(self, numel: int, dtype: torch.dtype, device, group):
         import torch.distributed._symmetric_memory as symm_mem
 
+        if group is None:
+            group = dist.group.WORLD
         self.group = group
         self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
         self.tensor.zero_()
