@@ -51,13 +51,35 @@ struct Params {
   int* status;
   const float* alpha_dev;  // optional device scalar multiplied into alpha (fp8: product of the two operand scales)
   int a_fmt, b_fmt;        // fp8 only: 0 = e4m3, 1 = e5m2
-  // fused collectives (0 = off).  a_rows_per_map: rows [r * a_rows_per_map, (r + 1) * a_rows_per_map) of A live in rank r's
-  // memory and are fetched through tensor map r (all-gather fused into the operand loads).  c_rows_per_rank: rows of C in
-  // that range are stored to c_peer[r] (this rank's slot in rank r's staging buffer: the scatter half of a reduce-scatter).
-  int a_rows_per_map;
-  int c_rows_per_rank;
-  void* c_peer[kMaxPeers];
+  // ---- fused collectives (see the kernels at the end of this file); unused by the plain GEMM
+  int rank, world;
+  int m_rot;              // the tile raster starts at this m-block and wraps, so every rank begins with the rows nearest to hand
+  int a_rows_per_map;     // gathered A: rows [r * a_rows_per_map, ...) are fetched through tensor map r
+  const uint8_t* a_peer[kMaxPeers];  // gathered A: rank r's shard (a pointer into rank r's memory, valid on this GPU)
+  uint8_t* a_local;       // gathered A: local [M, K] copy that the remote shards are pulled into
+  int* a_cnt;             // gathered A: arrival counter per (rank, 128-row block) of a_local, zeroed before the launch
+  int a_units_per_block;  // gathered A: copy units (kCopyUnit bytes) per 128-row block
+  int c_rows_per_rank;    // scattered C: rows [r * c_rows_per_rank, ...) are stored to c_peer[r]
+  void* c_peer[kMaxPeers];   // scattered C: this rank's slot in rank r's staging buffer
+  int* c_cnt[kMaxPeers];     // scattered C: rank r's per-tile arrival counters (in rank r's memory); they only ever grow
+  int c_target;              // scattered C: value of a counter once all 4 * world parts of this call's tile have arrived
+  const float* rs_staging;   // scattered C: this rank's own staging buffer [world, slot]
+  long long rs_slot;         // elements per slot
+  void* rs_out;              // this rank's reduced rows [c_rows_per_rank, N] (bf16, or fp32 if rs_out_f32), row stride rs_ldo
+  int rs_ldo;
+  int rs_out_f32;
 };
+
+constexpr int kModePlain = 0;
+constexpr int kModeGatherA = 1;   // all-gather fused into the A operand
+constexpr int kModeScatterC = 2;  // reduce-scatter fused into the epilogue
+constexpr int kCopyUnit = 16384;  // bytes per bulk copy of the gather
+constexpr int kCopyExtra = 256 + 2 * kCopyUnit;  // extra dynamic shared memory of the gather kernel
+constexpr int kGatherThreads = kNumThreads + 32;  // + one copy warp
+constexpr int kReduceThreads = 128;  // scatter mode: four more warps that sum the staging slots
+constexpr int kScatterThreads = kNumThreads + kReduceThreads;
+constexpr int kEpiStride = 36;   // floats per staged row (144 B: 16-byte aligned, conflict-free for float4 rows)
+constexpr int kEpiExtra = 256 + 4 * 32 * kEpiStride * 4;  // extra dynamic shared memory of the scatter kernel
 
 struct PeerMaps {
   CUtensorMap maps[kMaxPeers];
@@ -75,6 +97,8 @@ struct SmemLayout {
   static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // +1024 for manual alignment
 };
 
+__device__ __forceinline__ void reduce_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kReduceThreads) : "memory"); }
+
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
   constexpr int GM = 8;
   int group_size = GM * tiles_n;
@@ -85,9 +109,22 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   mb = first_m + (r % gm);
   nb = r / gm;
 }
+__device__ __forceinline__ void tile_coords_rot(int t, int tiles_m, int tiles_n, int m_rot, int& mb, int& nb) {
+  tile_coords(t, tiles_m, tiles_n, mb, nb);
+  mb += m_rot;
+  if (mb >= tiles_m) mb -= tiles_m;
+}
+// Scatter raster: consecutive m-blocks of the raster go to consecutive ranks (next rank first, own rank last of each round),
+// so the peer stores are spread evenly over the kernel's duration and every rank's rows complete at a steady rate.
+__device__ __forceinline__ void tile_coords_interleaved(int t, int tiles_m, int tiles_n, int rank, int world, int& mb, int& nb) {
+  tile_coords(t, tiles_m, tiles_n, mb, nb);
+  int dest = rank + 1 + mb % world;
+  if (dest >= world) dest -= world;
+  mb = dest * (tiles_m / world) + mb / world;
+}
 
 // kF8: one-byte operands (both K-major); a stage row is still 128 bytes, i.e. 128 elements of K instead of 64.
-template <int BN, bool A_MN, bool B_MN, bool kF8 = false>
+template <int BN, bool A_MN, bool B_MN, bool kF8 = false, int MODE = kModePlain>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUtensorMap& tmB, const Params& p) {
   const CUtensorMap& tmA = tmA_maps[0];
   using L = SmemLayout<BN>;
@@ -100,6 +137,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // gather mode only: two copy barriers and two staging buffers behind the GEMM's own shared memory
+  uint64_t* copy_bar = reinterpret_cast<uint64_t*>(smem + ((L::kTileBytes + L::kBarBytes + 127) & ~127));
+  uint8_t* copy_buf = reinterpret_cast<uint8_t*>(copy_bar) + 128;
+  // scatter mode only: a 32 x 32 fp32 transposition buffer per epilogue warp in the same place
+  float* epi_buf = reinterpret_cast<float*>(copy_bar);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -116,6 +158,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 4);  // one arrival per epilogue warp
+    }
+    if constexpr (MODE == kModeGatherA) {
+      mbar_init(&copy_bar[0], 1);
+      mbar_init(&copy_bar[1], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -136,10 +182,26 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int ready_block = -1;  // gather mode: last m-block whose rows are known to have arrived
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb;
-        tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        if constexpr (MODE == kModePlain) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
+        else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
+        int a_map = 0, a_row = m0;
+        if constexpr (MODE == kModeGatherA) {
+          a_map = m0 / p.a_rows_per_map;  // the rank these rows belong to
+          a_row = m0 - a_map * p.a_rows_per_map;
+          if (a_map != p.rank && mb != ready_block) {
+            // rows of another rank: wait until the copy warps (of all CTAs) have pulled this 128-row block into a_local
+            const int blocks_per_rank = p.a_rows_per_map / BM;
+            ok = flag_wait_ge(p.a_cnt + a_map * blocks_per_rank + a_row / BM, p.a_units_per_block, false, abort_flag, p.status, 110, mb);
+            if (!ok) break;
+            fence_proxy_async_all();  // the block was written by bulk stores of other CTAs; the loads below are TMA
+            ready_block = mb;
+          }
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100, stage);
           if (!ok) break;
@@ -148,12 +210,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           const int k0 = kb * BKE;
           if constexpr (!A_MN) {
-            if (p.a_rows_per_map > 0) {
-              const int r = m0 / p.a_rows_per_map;  // the rank whose memory holds these rows
-              tma_load_2d(sa, tmA_maps + r, &full_bar[stage], k0, m0 - r * p.a_rows_per_map);
-            } else {
-              tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
-            }
+            tma_load_2d(sa, tmA_maps + a_map, &full_bar[stage], k0, a_row);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -211,7 +268,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
         if (++buf == 2) { buf = 0; tphase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     int buf = 0;
@@ -222,7 +279,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
     const float alpha = p.alpha_dev != nullptr ? p.alpha * p.alpha_dev[0] : p.alpha;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      if constexpr (MODE == kModePlain) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
+      else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300, buf);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -231,10 +290,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       const int n0 = nb * BN;
       void* c_base = p.C;
       size_t c_row = static_cast<size_t>(row);
-      if (p.c_rows_per_rank > 0 && row < p.M) {
-        const int d = row / p.c_rows_per_rank;
-        c_base = p.c_peer[d];
-        c_row = static_cast<size_t>(row - d * p.c_rows_per_rank);
+      int c_dest = 0;
+      if constexpr (MODE == kModeScatterC) {
+        // the whole tile belongs to one rank (c_rows_per_rank is a multiple of BM): store it into that rank's staging slot
+        c_dest = (mb * BM) / p.c_rows_per_rank;
+        c_base = p.c_peer[c_dest];
+        c_row = static_cast<size_t>(row - c_dest * p.c_rows_per_rank);
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
@@ -243,6 +304,61 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col0 = n0 + c;
+        if constexpr (MODE == kModeScatterC) {
+          // Peer stores: turn the row-per-lane fragment into row-contiguous 128-byte segments through shared memory, so a
+          // store instruction covers 4 rows x 128 B instead of 32 rows x 16 B (NVLink moves short writes poorly).
+          if (col0 < p.N) {  // warp-uniform; every row of the tile is valid (M / world is a multiple of BM)
+            float* eb = epi_buf + (warp - 2) * (32 * kEpiStride);
+            if (out_f32) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(eb + lane * kEpiStride + 4 * q) =
+                    make_float4(__uint_as_float(r[4 * q]) * alpha, __uint_as_float(r[4 * q + 1]) * alpha,
+                                __uint_as_float(r[4 * q + 2]) * alpha, __uint_as_float(r[4 * q + 3]) * alpha);
+              __syncwarp();
+              const int col = col0 + 4 * (lane & 7);
+              float* dst = reinterpret_cast<float*>(c_base) + (c_row - lane) * p.ldc + col;  // row 0 of this warp's 32 rows
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rl = (lane >> 3) + 4 * i;
+                const float4 val = *reinterpret_cast<const float4*>(eb + rl * kEpiStride + 4 * (lane & 7));
+                if (col < p.N) *reinterpret_cast<float4*>(dst + static_cast<size_t>(rl) * p.ldc) = val;
+              }
+              __syncwarp();
+            } else {
+              // bf16 staging: two 32-column fragments make one 128-byte row segment (the loop below advances c by 64)
+              uint32_t r2[32];
+              tmem_ld_32x32(taddr + c + 32, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * q + 0]) * alpha, __uint_as_float(r[8 * q + 1]) * alpha);
+                o.y = pack_bf16x2(__uint_as_float(r[8 * q + 2]) * alpha, __uint_as_float(r[8 * q + 3]) * alpha);
+                o.z = pack_bf16x2(__uint_as_float(r[8 * q + 4]) * alpha, __uint_as_float(r[8 * q + 5]) * alpha);
+                o.w = pack_bf16x2(__uint_as_float(r[8 * q + 6]) * alpha, __uint_as_float(r[8 * q + 7]) * alpha);
+                *reinterpret_cast<uint4*>(eb + lane * kEpiStride + 4 * q) = o;
+                o.x = pack_bf16x2(__uint_as_float(r2[8 * q + 0]) * alpha, __uint_as_float(r2[8 * q + 1]) * alpha);
+                o.y = pack_bf16x2(__uint_as_float(r2[8 * q + 2]) * alpha, __uint_as_float(r2[8 * q + 3]) * alpha);
+                o.z = pack_bf16x2(__uint_as_float(r2[8 * q + 4]) * alpha, __uint_as_float(r2[8 * q + 5]) * alpha);
+                o.w = pack_bf16x2(__uint_as_float(r2[8 * q + 6]) * alpha, __uint_as_float(r2[8 * q + 7]) * alpha);
+                *reinterpret_cast<uint4*>(eb + lane * kEpiStride + 16 + 4 * q) = o;
+              }
+              __syncwarp();
+              const int col = col0 + 8 * (lane & 7);
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_base) + (c_row - lane) * p.ldc + col;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rl = (lane >> 3) + 4 * i;
+                const uint4 val = *reinterpret_cast<const uint4*>(eb + rl * kEpiStride + 4 * (lane & 7));
+                if (col < p.N) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rl) * p.ldc) = val;
+              }
+              __syncwarp();
+              c += 32;
+            }
+          }
+          continue;
+        }
         if (row < p.M && col0 < p.N) {
           float v[32];
 #pragma unroll
@@ -331,9 +447,183 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       }
       // all TMEM reads of this warp are complete (tmem_ld_wait above)
       tc_fence_before();
+      if constexpr (MODE == kModeScatterC) __threadfence_system();  // this lane's stores before the arrival below
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[buf]);
+        if constexpr (MODE == kModeScatterC) {
+          const int mb_local = mb - c_dest * (p.c_rows_per_rank / BM);
+          red_release_sys_add(p.c_cnt[c_dest] + mb_local * p.tiles_n + nb, 1);
+        }
+      }
       if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+  } else if constexpr (MODE == kModeGatherA) {
+    // ------------------------------------------------------------ gather copy warp (warp 6)
+    // The remote shards are cut into kCopyUnit-byte units, numbered in the order the tile raster needs them (nearest rank
+    // first); CTA b moves units b, b + grid, ...: peer memory -> shared memory -> a_local, both legs as bulk copies, one
+    // load in flight while the previous unit is stored.  Each finished unit bumps its 128-row block's arrival counter.
+    if (lane == 0 && p.world > 1) {
+      const long long blocks_per_rank = p.a_rows_per_map / BM;
+      const long long per_rank = blocks_per_rank * p.a_units_per_block;
+      const long long total = per_rank * (p.world - 1);
+      const long long shard_bytes = static_cast<long long>(p.a_rows_per_map) * p.K * 2;
+      auto src_rank = [&](long long g) { int r = p.rank + 1 + static_cast<int>(g / per_rank); return r >= p.world ? r - p.world : r; };
+      auto issue = [&](long long g, int b) {
+        const int r = src_rank(g);
+        const long long off = (g % per_rank) * kCopyUnit;
+        mbar_expect_tx(&copy_bar[b], kCopyUnit);
+        bulk_load(copy_buf + b * kCopyUnit, p.a_peer[r] + off, kCopyUnit, &copy_bar[b]);
+      };
+      auto signal = [&](long long g) {
+        const int r = src_rank(g);
+        const long long blk = (g % per_rank) / p.a_units_per_block;
+        fence_proxy_async_all();  // bulk-store writes (async proxy) before the generic-proxy release below
+        __threadfence();
+        red_release_gpu_add(p.a_cnt + r * blocks_per_rank + blk, 1);
+      };
+      long long g = blockIdx.x, prev = -1;
+      uint32_t ph0 = 0, ph1 = 0;
+      int j = 0;
+      bool ok = true, pending_load = false;
+      if (g < total) issue(g, 0);
+      while (g < total) {
+        const long long gn = g + gridDim.x;
+        const int b = j & 1;
+        pending_load = false;
+        if (gn < total) {
+          bulk_wait_read<0>();  // the store that last read the other buffer has drained it
+          issue(gn, b ^ 1);
+          pending_load = true;
+        }
+        ok = mbar_wait(&copy_bar[b], b ? ph1 : ph0, abort_flag, p.status, 400, b);
+        if (!ok) break;
+        if (b) ph1 ^= 1; else ph0 ^= 1;
+        const int r = src_rank(g);
+        bulk_store(p.a_local + r * shard_bytes + (g % per_rank) * kCopyUnit, copy_buf + b * kCopyUnit, kCopyUnit);
+        bulk_commit();
+        if (prev >= 0) {
+          bulk_wait<1>();  // the previous unit's store is complete
+          signal(prev);
+        }
+        prev = g;
+        g = gn;
+        ++j;
+      }
+      bulk_wait<0>();
+      if (ok && prev >= 0) signal(prev);
+      if (!ok && pending_load) mbar_wait_quiet(&copy_bar[(j & 1) ^ 1], (j & 1) ? ph0 : ph1);  // let the load in flight land
+    }
+  } else if constexpr (MODE == kModeScatterC) {
+    // ------------------------------------------------------------ reduce warps (warps 6-9)
+    // This rank's rows, concurrently with the main loop: tile by tile, in the order the raster produces them, wait until all
+    // 4 * world epilogue warps (own and remote) have delivered their part of the tile into the staging slots, then sum the
+    // slots.  Every rank produces the tiles of a given rank at the same steady rate, so these warps trail the tensor cores
+    // closely and little is left to reduce when the last tile has been multiplied.
+    const int rtid = threadIdx.x - kNumThreads;
+    const int own_tiles = (p.c_rows_per_rank / BM) * p.tiles_n;
+    const bool out_f32 = p.rs_out_f32 != 0;
+    for (int t = blockIdx.x; t < own_tiles; t += gridDim.x) {
+      if (rtid == 0 && !*abort_flag)
+        flag_wait_ge(p.c_cnt[p.rank] + t, p.c_target, true, abort_flag, p.status, 500, t);
+      reduce_bar_sync();
+      if (*abort_flag) break;
+      const int mb_local = t / p.tiles_n, nb = t - mb_local * p.tiles_n;
+      if (!(p.flags & kOutF32)) {
+        // bf16 staging slots: 8 elements per 16-byte load, fp32 accumulation
+        constexpr int kVec8PerRow = BN / 8;
+        constexpr int kU = 4;
+        const __nv_bfloat16* stg = reinterpret_cast<const __nv_bfloat16*>(p.rs_staging);
+        for (int i0 = rtid; i0 < BM * kVec8PerRow; i0 += kU * kReduceThreads) {
+          float acc[kU][8];
+          size_t off[kU];
+          bool live[kU];
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const int i = i0 + u * kReduceThreads;
+            const int r = i / kVec8PerRow;
+            const int col = nb * BN + (i - r * kVec8PerRow) * 8;
+            live[u] = (i < BM * kVec8PerRow) && (col < p.N);
+            off[u] = (static_cast<size_t>(mb_local) * BM + r) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+          }
+          for (int w = 0; w < p.world; ++w) {
+            uint4 v[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u)
+              v[u] = live[u] ? __ldcg(reinterpret_cast<const uint4*>(stg + w * p.rs_slot + off[u])) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[u][2 * j] += f.x;
+                acc[u][2 * j + 1] += f.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            if (!live[u]) continue;
+            const int i = i0 + u * kReduceThreads;
+            const int r = i / kVec8PerRow;
+            const int col = nb * BN + (i - r * kVec8PerRow) * 8;
+            const size_t row = static_cast<size_t>(mb_local) * BM + r;
+            if (out_f32) {
+              float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col);
+              o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+              o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+            } else {
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo + col) =
+                  make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                             pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+            }
+          }
+        }
+        reduce_bar_sync();
+        continue;
+      }
+      constexpr int kVecPerRow = BN / 4;
+      constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread and slot
+      for (int i0 = rtid; i0 < BM * kVecPerRow; i0 += kUnroll * kReduceThreads) {
+        float4 acc[kUnroll];
+        size_t off[kUnroll];
+        bool live[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int i = i0 + u * kReduceThreads;
+          const int r = i / kVecPerRow;
+          const int col = nb * BN + (i - r * kVecPerRow) * 4;
+          live[u] = (i < BM * kVecPerRow) && (col < p.N);
+          off[u] = (static_cast<size_t>(mb_local) * BM + r) * p.ldc + col;
+          acc[u] = live[u] ? __ldcg(reinterpret_cast<const float4*>(p.rs_staging + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int w = 1; w < p.world; ++w) {
+          float4 v[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u)
+            v[u] = live[u] ? __ldcg(reinterpret_cast<const float4*>(p.rs_staging + w * p.rs_slot + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (!live[u]) continue;
+          const int i = i0 + u * kReduceThreads;
+          const int r = i / kVecPerRow;
+          const int col = nb * BN + (i - r * kVecPerRow) * 4;
+          const size_t row = static_cast<size_t>(mb_local) * BM + r;
+          if (out_f32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col) = acc[u];
+          } else {
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo + col) =
+                make_uint2(pack_bf16x2(acc[u].x, acc[u].y), pack_bf16x2(acc[u].z, acc[u].w));
+          }
+        }
+      }
+      reduce_bar_sync();  // nobody is still reading the abort flag when thread 0 starts the next wait
     }
   }
 
@@ -351,11 +641,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   gemm_body<BN, A_MN, B_MN, kF8>(&tmA, tmB, p);
 }
 
-// A's row blocks come from different ranks' memories: one tensor map per rank (plain TMA loads, no cluster qualifier).
+// All-gather fused into the A operand: A's row blocks belong to different ranks; the copy warp pulls the remote ones into
+// local memory while the tensor cores work on the rows already here (plain bulk loads, no cluster qualifier).
 template <int BN>
-__global__ void __launch_bounds__(kNumThreads, 1)
-gemm_gathered_a_kernel(const __grid_constant__ PeerMaps tmAs, const __grid_constant__ CUtensorMap tmB, Params p) {
-  gemm_body<BN, false, false, false>(tmAs.maps, tmB, p);
+__global__ void __launch_bounds__(kGatherThreads, 1)
+gemm_gather_a_kernel(const __grid_constant__ PeerMaps tmAs, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, false, false, false, kModeGatherA>(tmAs.maps, tmB, p);
+}
+
+// Reduce-scatter fused into the epilogue: tiles go to the staging slot of the rank that owns their rows, while four more
+// warps of every CTA sum this rank's own rows over the slots as the contributions arrive.
+template <int BN>
+__global__ void __launch_bounds__(kScatterThreads, 1)
+gemm_scatter_c_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, false, false, false, kModeScatterC>(&tmA, tmB, p);
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -414,6 +713,7 @@ extern "C" int lvb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.status = status;
   p.alpha_dev = nullptr;
   p.a_fmt = p.b_fmt = 0;
+  p.rank = 0; p.world = 1; p.m_rot = 0;
   p.a_rows_per_map = 0;
   p.c_rows_per_rank = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -483,6 +783,7 @@ extern "C" int lvb_gemm_fp8(const void* A, const void* B, void* C, int M, int N,
   p.status = status;
   p.alpha_dev = scale;
   p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.rank = 0; p.world = 1; p.m_rot = 0;
   p.a_rows_per_map = 0;
   p.c_rows_per_rank = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -496,102 +797,135 @@ namespace lvb {
 namespace gemm {
 
 template <int BN>
-int launch_gathered_a(const void* const* a_peers, const void* B, Params p, int world, int lda, int ldb, cudaStream_t stream) {
+int launch_gather_a(const void* B, Params p, int ldb, cudaStream_t stream) {
   using L = SmemLayout<BN>;
+  constexpr int kSmem = L::kTotal + kCopyExtra;
+  static_assert(kSmem <= 232448, "gather kernel exceeds the shared memory of an SM");
   PeerMaps maps;
   CUtensorMap tmB;
-  for (int r = 0; r < world; ++r) {
-    int rc = make_tmap_2d_bf16(&maps.maps[r], a_peers[r], p.a_rows_per_map, p.K, lda, BM, BK);
+  const size_t shard_bytes = static_cast<size_t>(p.a_rows_per_map) * p.K * 2;
+  for (int r = 0; r < p.world; ++r) {
+    // own rows are read in place; the other ranks' rows from the local copy that the copy warps fill
+    const void* base = (r == p.rank) ? static_cast<const void*>(p.a_peer[r]) : static_cast<const void*>(p.a_local + r * shard_bytes);
+    int rc = make_tmap_2d_bf16(&maps.maps[r], base, p.a_rows_per_map, p.K, p.K, BM, BK);
     if (rc != kErrOk) return rc;
   }
-  for (int r = world; r < kMaxPeers; ++r) maps.maps[r] = maps.maps[0];
+  for (int r = p.world; r < kMaxPeers; ++r) maps.maps[r] = maps.maps[0];
   int rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
   if (rc != kErrOk) return rc;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  auto kern = gemm_gathered_a_kernel<BN>;
+  auto kern = gemm_gather_a_kernel<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  const int blocks = p.world * (p.a_rows_per_map / BM);
+  if (cudaMemsetAsync(p.a_cnt, 0, sizeof(int) * blocks, stream) != cudaSuccess) return kErrCuda;
+  // one CTA per SM even when there are fewer tiles: every CTA's copy warp moves a share of the remote rows
+  kern<<<num_sms(), kGatherThreads, kSmem, stream>>>(maps, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+template <int BN>
+int launch_scatter_c(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  constexpr int kSmem = L::kTotal + kEpiExtra;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d_bf16(&tmA, A, p.M, p.K, lda, BM, BK);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_scatter_c_kernel<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
     attr_set = true;
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > num_sms()) grid = num_sms();
-  kern<<<grid, kNumThreads, L::kTotal, stream>>>(maps, tmB, p);
+  kern<<<grid, kScatterThreads, kSmem, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
 
 }  // namespace gemm
 }  // namespace lvb
 
-// All-gather fused into a GEMM: C[M, N] = concat_r(A_r)[M, K] B[N, K]^T where A_r [M / world, K] (bf16, row stride lda)
-// is rank r's shard, read in place from rank r's memory by TMA (a_peers[r]: device pointer valid on this GPU; own rank
-// included).  M / world must be a multiple of 128.  The caller orders the ranks (every A_r complete before the launch).
-extern "C" int lvb_gemm_allgather_a(const void* const* a_peers, int world, const void* B, void* C, int M, int N, int K, int lda,
-                                    int ldb, int ldc, int flags, float alpha, const void* bias, int* status, void* stream) {
+// Number of int32 arrival counters lvb_gemm_allgather_a needs for an M-row gathered operand.
+extern "C" int lvb_gemm_allgather_a_counters(int M) { return (M + lvb::gemm::BM - 1) / lvb::gemm::BM; }
+
+// All-gather fused into a GEMM: C[M, N] = concat_r(A_r)[M, K] B[N, K]^T (+ bias).  A_r [M / world, K] (bf16, contiguous)
+// is rank r's shard at a_peers[r], a pointer into rank r's memory that is valid on this GPU (own rank included).  The
+// kernel starts with this rank's own rows while its copy warps pull the other shards, nearest rank first, into
+// a_local [M, K] (local scratch; the own rows of it are not written), and each later row block is multiplied as soon as
+// its arrival counter (a_cnt, lvb_gemm_allgather_a_counters(M) ints of local memory) says it is complete.
+// M / world must be a multiple of 128 and K of 64.  The caller orders the ranks: every A_r complete before the launch,
+// and no A_r overwritten until every rank's kernel has finished.
+extern "C" int lvb_gemm_allgather_a(const void* const* a_peers, int rank, int world, void* a_local, int* a_cnt, const void* B,
+                                    void* C, int M, int N, int K, int ldb, int ldc, int flags, float alpha, const void* bias,
+                                    int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::gemm;
-  if (world <= 0 || world > kMaxPeers || M <= 0 || N <= 0 || K <= 0 || M % world != 0 || (M / world) % BM != 0) return kErrBadArg;
-  if ((lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (world <= 0 || world > kMaxPeers || rank < 0 || rank >= world || M <= 0 || N <= 0 || K <= 0) return kErrBadArg;
+  if (M % world != 0 || (M / world) % BM != 0 || K % 64 != 0 || (ldb & 7)) return kErrBadArg;
+  if (a_local == nullptr || a_cnt == nullptr) return kErrBadArg;
   Params p;
   p.C = C; p.bias = bias; p.residual = nullptr;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
-  p.flags = flags; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.flags = flags & (kOutF32 | kBias | kBiasF32); p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
   p.a_fmt = p.b_fmt = 0;
+  p.rank = rank; p.world = world;
   p.a_rows_per_map = M / world;
+  p.m_rot = rank * (p.a_rows_per_map / BM);
+  for (int r = 0; r < kMaxPeers; ++r) p.a_peer[r] = reinterpret_cast<const uint8_t*>(a_peers[r < world ? r : 0]);
+  p.a_local = reinterpret_cast<uint8_t*>(a_local);
+  p.a_cnt = a_cnt;
+  p.a_units_per_block = (BM * K * 2) / kCopyUnit;
   p.c_rows_per_rank = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return N > 128 ? launch_gathered_a<256>(a_peers, B, p, world, lda, ldb, s) : launch_gathered_a<128>(a_peers, B, p, world, lda, ldb, s);
+  return N > 128 ? launch_gather_a<256>(B, p, ldb, s) : launch_gather_a<128>(B, p, ldb, s);
 }
 
-// The scatter half of a reduce-scatter fused into a GEMM epilogue: this rank's partial product P[M, N] = A[M, K] B[N, K]^T
-// (K is the sharded dimension) is stored, rows [r * M / world, (r + 1) * M / world) to c_peers[r], which the caller points at
-// this rank's slot of rank r's staging buffer [world, M / world, ldc].  Every rank then sums its own staging buffer over the
-// slots (lvb_sum_slots).  Output dtype per flags (fp32 with kOutF32, else bf16).
-extern "C" int lvb_gemm_scatter_c(const void* A, const void* B, void* const* c_peers, int world, int M, int N, int K, int lda,
-                                  int ldb, int ldc, int flags, float alpha, int* status, void* stream) {
+// Reduce-scatter fused into a GEMM: out[M / world, N] = rows [rank * M / world, ...) of sum_s A_s[M, K_s] B_s[N, K_s]^T, where
+// every rank s calls this with its own partial operands.  Tile by tile the epilogue stores the partial product (fp32, or
+// bf16 when staging_f32 is 0: half the NVLink traffic, partial sums rounded as in a bf16 NCCL reduce-scatter) into slot
+// `rank` of the staging buffer of the rank that owns the tile's rows (c_slots[r]: a pointer to that slot in rank r's memory;
+// staging layout [world, M / world, ldc] elements) and adds 1 to that rank's arrival counter of the tile (cnt_peers[r]:
+// (M / world / 128) * lvb_gemm_tiles_n(N) ints in rank r's memory).  The raster deals the m-blocks round-robin over the
+// ranks.  Four more warps per CTA sum this rank's own tiles over the slots (`staging`: this rank's own buffer) as soon as a
+// tile's counter reaches `target`.  The counters are never reset: the caller passes target = 4 * world * (number of
+// products, this one included, that have used these counters), and alternates between two staging areas with their own
+// counters from call to call, which makes any cross-rank barrier between calls unnecessary: a rank can only be one call
+// ahead of its slowest peer, because its own call completes only when every peer's parts of that call have arrived.
+// M / world must be a multiple of 128, N of 8.
+extern "C" int lvb_gemm_reduce_scatter(const void* A, const void* B, void* const* c_slots, int* const* cnt_peers, int rank,
+                                       int world, const void* staging, long long slot_elems, int staging_f32, int target,
+                                       void* out, int ldo, int out_f32, int M, int N, int K, int lda, int ldb, int ldc,
+                                       float alpha, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::gemm;
-  if (world <= 0 || world > kMaxPeers || M <= 0 || N <= 0 || K <= 0 || M % world != 0) return kErrBadArg;
-  if ((lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (world <= 0 || world > kMaxPeers || rank < 0 || rank >= world || M <= 0 || N <= 0 || K <= 0) return kErrBadArg;
+  if (M % world != 0 || (M / world) % BM != 0 || (N & 7) || (ldc & 7) || (ldo & 7) || (lda & 7) || (ldb & 7)) return kErrBadArg;
   Params p;
-  p.C = c_peers[0]; p.bias = nullptr; p.residual = nullptr;
+  p.C = c_slots[rank]; p.bias = nullptr; p.residual = nullptr;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
-  p.flags = flags & kOutF32; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.flags = staging_f32 ? kOutF32 : 0; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
   p.a_fmt = p.b_fmt = 0;
+  p.rank = rank; p.world = world;
   p.a_rows_per_map = 0;
   p.c_rows_per_rank = M / world;
-  for (int r = 0; r < kMaxPeers; ++r) p.c_peer[r] = c_peers[r < world ? r : 0];
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return N > 128 ? launch<256, false, false>(A, B, p, lda, ldb, s, 0) : launch<128, false, false>(A, B, p, lda, ldb, s, 0);
-}
-
-namespace lvb {
-namespace gemm {
-__global__ void sum_slots_kernel(const float4* __restrict__ staging, long long slot4, int world, float4* __restrict__ out_f32,
-                                 uint2* __restrict__ out_bf16, long long n4) {
-  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n4; i += gridDim.x * 256LL) {
-    float4 s = staging[i];
-    for (int r = 1; r < world; ++r) {
-      const float4 v = staging[r * slot4 + i];
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    }
-    if (out_f32 != nullptr) out_f32[i] = s;
-    if (out_bf16 != nullptr) out_bf16[i] = make_uint2(pack_bf16x2(s.x, s.y), pack_bf16x2(s.z, s.w));
+  p.m_rot = 0;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    p.c_peer[r] = c_slots[r < world ? r : 0];
+    p.c_cnt[r] = cnt_peers[r < world ? r : 0];
   }
+  p.rs_staging = reinterpret_cast<const float*>(staging); p.rs_slot = slot_elems; p.rs_out = out; p.rs_ldo = ldo; p.rs_out_f32 = out_f32; p.c_target = target;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return N > 128 ? launch_scatter_c<256>(A, B, p, lda, ldb, s) : launch_scatter_c<128>(A, B, p, lda, ldb, s);
 }
-}  // namespace gemm
-}  // namespace lvb
 
-// out[n] = sum over slots of staging[slot][n] (fp32 staging, n a multiple of 4); bf16 and/or fp32 output.
-extern "C" int lvb_sum_slots(const float* staging, long long slot_elems, int world, float* out_f32, void* out_bf16, long long n,
-                             void* stream) {
-  using namespace lvb;
-  if (world <= 0 || n <= 0 || (n & 3) || (slot_elems & 3)) return kErrBadArg;
-  long long blocks = (n / 4 + 255) / 256;
-  long long cap = static_cast<long long>(num_sms()) * 8;
-  gemm::sum_slots_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const float4*>(staging), slot_elems / 4, world, reinterpret_cast<float4*>(out_f32),
-      reinterpret_cast<uint2*>(out_bf16), n / 4);
-  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
-}
+// Tiles along N of the kernels above for an N-column output (sizes the per-tile counters).
+extern "C" int lvb_gemm_tiles_n(int N) { return N > 128 ? (N + 255) / 256 : 1; }
