@@ -68,13 +68,18 @@ class PassthroughTokenizer:
         return [int(t) for t in toks] if not isinstance(toks, str) else int(toks)
 
     def __call__(self, text: Union[str, Sequence[str]], return_attention_mask: bool = False, truncation=False, max_length=None,
-                 add_special_tokens: bool = False, **kw):
+                 add_special_tokens: bool = False, padding=False, **kw):
         single = isinstance(text, str)
         texts = [text] if single else list(text)
         ids = [self._tokenize(t) for t in texts]
         if truncation and max_length:
             ids = [x[:max_length] for x in ids]
+        masks = [[1] * len(x) for x in ids]
+        if padding:  # "max_length" pads to max_length, True / "longest" to the longest row of the batch
+            width = max_length if (padding == "max_length" and max_length) else max((len(x) for x in ids), default=0)
+            masks = [m + [0] * (width - len(m)) for m in masks]
+            ids = [x + [self.pad_token_id] * (width - len(x)) for x in ids]
         out = {"input_ids": ids[0] if single else ids}
         if return_attention_mask:
-            out["attention_mask"] = [1] * len(ids[0]) if single else [[1] * len(x) for x in ids]
+            out["attention_mask"] = masks[0] if single else masks
         return out

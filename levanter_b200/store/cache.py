@@ -520,6 +520,8 @@ def build_or_load_cache(cache_dir: str, source, processor: BatchProcessor, await
                         force_flush: bool = False) -> TreeCache:
     """Open the cache at ``cache_dir``, building (or resuming the build of) it from ``source`` through ``processor`` when it is
     not finished.  With ``await_finished=False`` the returned cache can be read while rows are still being added."""
+    if options is None:
+        options = CacheOptions.default()
     metadata = CacheMetadata(preprocessor_metadata=processor.metadata)
     try:
         return TreeCache.load(cache_dir, processor.output_exemplar, metadata)

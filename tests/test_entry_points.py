@@ -145,14 +145,18 @@ def _class_for(name):
         return LoraLmConfig
     if name.startswith("convert"):
         return None  # needs command-line arguments
+    if name.startswith("whisper"):
+        from levanter_b200.main.train_asr import TrainASRConfig
+
+        return TrainASRConfig
     return TrainLmConfig
 
 
 @pytest.mark.skipif(not os.path.isdir(REF_CONFIGS), reason="reference configs not present")
 def test_reference_yaml_configs_parse():
     """Every training/SFT/LoRA config of the reference decodes into the matching config class here.  Exempt: a config whose
-    model type the reference itself no longer ships, and the ASR config (audio data pipeline)."""
-    exempt = {"backpack_nano.yaml", "whisper_tiny_librispeech.yaml"}
+    model type the reference itself no longer ships."""
+    exempt = {"backpack_nano.yaml"}
     failures = []
     n = 0
     for p in sorted(glob.glob(f"{REF_CONFIGS}/*.yaml")):
