@@ -266,8 +266,11 @@ def _coerce_scalar(tp, value, path):
             try:
                 return int(value)
             except ValueError:
-                f = float(value)
-                if f.is_integer():
+                try:
+                    f = float(value)  # "1e3" style integers
+                except ValueError:
+                    f = None
+                if f is not None and f.is_integer():
                     return int(f)
         raise ConfigError(f"{path}: expected int, got {value!r}")
     if tp is float:
@@ -276,7 +279,10 @@ def _coerce_scalar(tp, value, path):
         if isinstance(value, (int, float)):
             return float(value)
         if isinstance(value, str):
-            return float(value)
+            try:
+                return float(value)
+            except ValueError:
+                pass
         raise ConfigError(f"{path}: expected float, got {value!r}")
     if tp is str:
         if isinstance(value, (dict, list)):
