@@ -33,11 +33,11 @@ class WatchCallback(JitCallback):
         sharded = group is not None
         kw = dict(split_scan_layers=self.split_scan_layers, include_histogram=self.include_histogram,
                   include_norms=self.include_norms, include_per_parameter_norms=self.include_per_parameter_norms,
-                  group=group, sharded=sharded)
+                  group=group, sharded=sharded, all_names=[s.name for s in engine.slots] if sharded else None)
         if "grads" in self.watch_targets:
             # gradients in the accumulator are not yet reduced over data ranks at this point; use local full grads
             g = {s.name: s.param.main_grad for s in engine.slots}
-            out.update(summary_statistics_for_tree("grad", g, **{**kw, "group": None, "sharded": False}))
+            out.update(summary_statistics_for_tree("grad", g, **{**kw, "group": None, "sharded": False, "all_names": None}))
         if "params" in self.watch_targets:
             out.update(summary_statistics_for_tree("params", engine.master_tree(), **kw))
         if "opt_state" in self.watch_targets and engine.opt_state is not None:

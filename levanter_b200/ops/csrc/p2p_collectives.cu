@@ -274,3 +274,42 @@ extern "C" int lvb_mm_adamw_allgather(float* p, float* m, float* v, const float*
                                                              eps, wd, bc1, bc2, grad_scale, nesterov);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Bounded wait on a flag, as a kernel of its own: one thread waits until *flag >= target or until limit_ns of the global
+// timer have passed, then records the outcome and returns (the context stays usable either way).
+//   result[0] = 1 reached / 2 gave up, result[1] = last value seen, result[2..3] = waited nanoseconds (lo, hi).
+// A give-up also records kTimeoutFlag in `status` like every other wait in this library.  Used by hosts that want to
+// learn whether a peer ever signalled without committing a full collective to it, and by the tests of the time-out path
+// (a flag that nothing sets).
+namespace lvb {
+__global__ void flag_wait_probe_kernel(const int* flag, int target, unsigned long long limit_ns, int sys_scope, int* result,
+                                       int* status) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  const unsigned long long t0 = globaltimer_ns();
+  int v = 0;
+  int outcome = 2;
+  unsigned long long waited = 0;
+  while (true) {
+    v = sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    waited = globaltimer_ns() - t0;
+    if (v >= target) { outcome = 1; break; }
+    if (waited > limit_ns) break;
+    __nanosleep(200);
+  }
+  result[0] = outcome;
+  result[1] = v;
+  result[2] = static_cast<int>(waited & 0xffffffffull);
+  result[3] = static_cast<int>(waited >> 32);
+  if (outcome == 2) record_status(status, kTimeoutFlag, 900, target);
+}
+}  // namespace lvb
+
+extern "C" int lvb_flag_wait_probe(const int* flag, int target, unsigned long long limit_ns, int sys_scope, int* result, int* status,
+                                   void* stream) {
+  using namespace lvb;
+  if (flag == nullptr || result == nullptr) return kErrBadArg;
+  if (limit_ns > 5000000000ull) limit_ns = 5000000000ull;  // never more than 5 s
+  flag_wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, target, limit_ns, sys_scope, result, status);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}

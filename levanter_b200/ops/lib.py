@@ -109,6 +109,12 @@ def check_status(reset: bool = True) -> None:
             )
 
 
+def clear_status() -> None:
+    """Zero the status word without raising (after a time-out the caller expected)."""
+    for buf in _status.values():
+        buf.zero_()
+
+
 def check_rc(rc: int, what: str) -> None:
     if rc != 0:
         names = {-1: "bad argument", -2: "CUDA launch error", -3: "tensor-map encode failed", -4: "size beyond limit"}

@@ -496,7 +496,7 @@ class ShardedEngine:
         shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=self.device)
         for name, (lo, fo, n) in self.segments.items():
             if tree.get(name) is not None:
-                shard[lo:lo + n].copy_(tree[name])
+                shard[lo:lo + n].copy_(tree[name].reshape(-1))
         return self.deferred_named(shard)
 
     def _gather_leaf_tree(self, tree: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -509,7 +509,7 @@ class ShardedEngine:
         shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=self.device)
         for name, (lo, fo, n) in self.segments.items():
             if tree.get(name) is not None:
-                shard[lo:lo + n].copy_(tree[name])
+                shard[lo:lo + n].copy_(tree[name].reshape(-1))
         full = self._gather_named(shard)
         keys = set()
         # a leaf may be absent on this rank but present on another; every masked-in parameter is exported

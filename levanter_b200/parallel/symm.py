@@ -54,3 +54,23 @@ def p2p_available(group) -> bool:
     except Exception:  # noqa: BLE001
         return False
     return dist.get_world_size(group) > 1
+
+
+def wait_for_flag(flag: "torch.Tensor", target: int, limit_seconds: float = 1.0, *, system_scope: bool = True):
+    """Wait on the device (one thread, bounded) until ``flag[0] >= target``.  Returns ``(reached, last_value, waited_seconds)``
+    after a synchronisation of the current stream; a wait that ran out also leaves ``flag wait timed out`` in the library's
+    status word, which the caller clears with ``ops.lib.check_status`` (it raises) or ``ops.lib.clear_status``.  The CUDA
+    context stays usable whatever the outcome."""
+    import torch
+
+    from ..ops import lib
+
+    assert flag.is_cuda and flag.dtype == torch.int32
+    result = torch.zeros(4, dtype=torch.int32, device=flag.device)
+    f = lib.fn("lvb_flag_wait_probe", [lib.c_void_p, lib.c_int, lib.ctypes.c_ulonglong, lib.c_int, lib.c_void_p, lib.c_void_p, lib.c_void_p])
+    rc = f(flag.data_ptr(), int(target), int(limit_seconds * 1e9), 1 if system_scope else 0, result.data_ptr(),
+           lib.status_buffer().data_ptr(), lib.stream_ptr())
+    lib.check_rc(rc, "lvb_flag_wait_probe")
+    r = result.tolist()
+    waited = ((r[3] & 0xFFFFFFFF) << 32 | (r[2] & 0xFFFFFFFF)) * 1e-9
+    return r[0] == 1, r[1], waited

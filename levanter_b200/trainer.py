@@ -41,6 +41,8 @@ from .tracker.wandb import WandbConfig
 from .trainer_state import TrainerState, make_training_key
 from .utils.logging import LoadingTimeTrackerIterator, init_logging
 
+from .utils.watchdog import PeerFailure, WatchdogConfig  # noqa: E402
+
 logger = logging.getLogger(__name__)
 DEFAULT_JAX_CONFIG: Dict[str, Any] = {"jax_threefry_partitionable": True, "jax_softmax_custom_jvp": True}
 
@@ -180,6 +182,8 @@ class TrainerConfig:
     shutdown_at_exit: Union[bool, float] = False
 
     # knobs of this framework's engine
+    watchdog: WatchdogConfig = field(default_factory=WatchdogConfig)
+    """host-side failure detection: heartbeat files and a check between steps (off by default)"""
     shard_optimizer: bool = True
     grad_reduce_dtype: str = "float32"
     use_fused_optimizer: Optional[bool] = None
@@ -553,16 +557,37 @@ class Trainer:
     def training_steps(self, state: TrainerState, train_loader: Iterable) -> Iterator[StepInfo]:
         """Generator over steps until ``num_train_steps`` (src/levanter/trainer.py:415-433)."""
         iter_data = LoadingTimeTrackerIterator(iter(train_loader))
-        while int(state.step) < self.num_train_steps:
-            with trk.helpers.capture_time() as loading_time:
-                try:
-                    example = next(iter_data)
-                except StopIteration:
-                    logger.info("Reached end of training data loader")
-                    break
-            info = self.train_step(state, example)
-            trk.log({"throughput/loading_time": loading_time()}, step=info.step)
-            yield info
+        watchdog = self._start_watchdog()
+        try:
+            while int(state.step) < self.num_train_steps:
+                with trk.helpers.capture_time() as loading_time:
+                    try:
+                        example = next(iter_data)
+                    except StopIteration:
+                        logger.info("Reached end of training data loader")
+                        break
+                if watchdog is not None:
+                    watchdog.raise_if_failed()  # before anything is launched that would wait for a missing peer
+                info = self.train_step(state, example)
+                if watchdog is not None:
+                    watchdog.beat(info.step)
+                trk.log({"throughput/loading_time": loading_time()}, step=info.step)
+                yield info
+        except BaseException as e:
+            if watchdog is not None and not isinstance(e, (GeneratorExit, PeerFailure)):
+                watchdog.mark_failed(f"{type(e).__name__}: {e}")
+            raise
+        finally:
+            if watchdog is not None:
+                watchdog.stop()
+
+    def _start_watchdog(self):
+        import torch.distributed as dist
+
+        rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
+        world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        wd = self.config.watchdog.build(rank, world, str(self.config.log_dir / self.run_id / "heartbeats"))
+        return wd.start() if wd is not None else None
 
     def train(self, state: TrainerState, train_loader: Iterable) -> StepInfo:
         if self._add_default_hooks:

@@ -1,0 +1,195 @@
+"""Multi-process behaviour on CPU (gloo, two ranks): sharded training equals single-process training, the loader gives each
+rank its slice, and failures surface as errors on the survivors rather than hangs: a peer that dies is noticed through its
+heartbeat before the next step, and a collective with a short time-out ends with an error."""
+import datetime
+import json
+import os
+import sys
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+VOCAB = 64
+
+
+def _init(rank, world, port, timeout_s=60):
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      CUDA_VISIBLE_DEVICES="")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=timeout_s))
+    return dist
+
+
+def _train(tmp, steps=3, batch=8):
+    from levanter_b200 import config as C
+    from levanter_b200.data.dataset import ListAsyncDataset
+    from levanter_b200.models.llama import LlamaConfig
+    from levanter_b200.models.lm_model import LmExample, compute_next_token_loss
+    from levanter_b200.optim import AdamConfig
+    from levanter_b200.trainer import Trainer, TrainerConfig
+
+    cfg = C.decode(TrainerConfig, {"num_train_steps": steps, "train_batch_size": batch, "require_accelerator": False, "tracker": {"type": "noop"},
+                                   "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"}})
+    g = torch.Generator().manual_seed(0)
+    starts = torch.randint(0, VOCAB, (64,), generator=g)
+    data = ListAsyncDataset([LmExample.causal(((s + torch.arange(16)) % VOCAB).to(torch.int32)) for s in starts], is_complete=True)
+    mcfg = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
+    opt = AdamConfig(learning_rate=3e-3, warmup=0.0, weight_decay=0.0, lr_schedule="constant", min_lr_ratio=1.0)
+    losses = {}
+    with Trainer(cfg, opt, compute_next_token_loss) as trainer:
+        state = trainer.initial_state(0, model_init=lambda: mcfg.build(VOCAB, seed=3))
+        trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
+        info = trainer.train(state, trainer.data_loader(data).iter_from_step(int(state.step)))
+    return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
+
+
+def _sharded_worker(rank, world, port, tmp):
+    dist = _init(rank, world, port)
+    try:
+        params, losses = _train(tmp)
+        if rank == 0:
+            torch.save({"params": params, "losses": losses}, f"{tmp}/dist.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_training_matches_single_process(tmp_path):
+    single, losses = _train(str(tmp_path / "single"))
+    mp.spawn(_sharded_worker, args=(2, 29711, str(tmp_path)), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+def _first_half_worker(rank, world, port, tmp):
+    dist = _init(rank, world, port)
+    try:
+        _train(tmp, steps=3)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
+    """Resume on a different process count: the sharded optimizer state is gathered on save and re-sliced on load."""
+    full, losses = _train(str(tmp_path / "full"), steps=6)
+    mp.spawn(_first_half_worker, args=(2, 29715, str(tmp_path / "res")), nprocs=2, join=True)
+    resumed, tail = _train(str(tmp_path / "res"), steps=6)
+    assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=3e-5)
+    for k, v in full.items():
+        assert torch.allclose(v, resumed[k], atol=3e-5), k
+
+
+def _loader_worker(rank, world, port, tmp):
+    dist = _init(rank, world, port)
+    try:
+        from levanter_b200.data.dataset import ListAsyncDataset
+        from levanter_b200.data.loader import DataLoader
+        from levanter_b200.parallel.mesh import DeviceMesh
+
+        mesh = DeviceMesh.create(replica=1, data=world, model=1) if hasattr(DeviceMesh, "create") else DeviceMesh(1, world, 1)
+        ds = ListAsyncDataset([torch.tensor([i]) for i in range(40)], is_complete=True)
+        dl = DataLoader(ds, 8, mesh=mesh, max_buffered_batches=0, pin_memory=False)
+        it = dl.iter_from_step(2)
+        rows = [next(it).reshape(-1).tolist() for _ in range(2)]
+        json.dump(rows, open(f"{tmp}/rows{rank}.json", "w"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_loader_gives_each_rank_its_slice_and_resumes_by_step(tmp_path):
+    mp.spawn(_loader_worker, args=(2, 29712, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (json.load(open(tmp_path / f"rows{r}.json")) for r in range(2))
+    # global batch 2 is rows 16..23, batch 3 is 24..31; rank 0 takes the first half of each
+    assert r0 == [[16, 17, 18, 19], [24, 25, 26, 27]] and r1 == [[20, 21, 22, 23], [28, 29, 30, 31]]
+
+
+def _dying_peer_worker(rank, world, port, tmp):
+    dist = _init(rank, world, port, timeout_s=5)
+    from levanter_b200.utils.watchdog import PeerFailure, Watchdog
+
+    out = {}
+    try:
+        wd = Watchdog(f"{tmp}/hb", rank, world, interval=0.1, peer_timeout=1.0).start()
+        t = torch.ones(1)
+        dist.all_reduce(t)  # step 0: both ranks are here
+        wd.beat(0)
+        if rank == 1:
+            wd.stop()       # rank 1 leaves between steps, with nothing in flight
+            os._exit(0)
+        t0 = time.time()
+        try:
+            while True:     # rank 0 checks the heartbeats before each further "launch"
+                wd.raise_if_failed()
+                time.sleep(0.05)
+                if time.time() - t0 > 20:
+                    out["outcome"] = "never noticed"
+                    break
+        except PeerFailure as e:
+            out["outcome"], out["after"], out["message"] = "peer failure", time.time() - t0, str(e)
+        # and a collective that is issued anyway ends with an error after the group's short time-out instead of hanging
+        t1 = time.time()
+        try:
+            dist.all_reduce(torch.ones(1))
+            out["collective"] = "returned"
+        except Exception as e:  # noqa: BLE001
+            out["collective"], out["collective_after"] = type(e).__name__, time.time() - t1
+        wd.stop()
+    finally:
+        if rank == 0:
+            json.dump(out, open(f"{tmp}/out.json", "w"))
+            os._exit(0)  # the group cannot be destroyed cleanly with a dead peer
+
+
+def test_dead_peer_is_noticed_before_the_next_step_and_collectives_time_out(tmp_path):
+    ctx = mp.spawn(_dying_peer_worker, args=(2, 29713, str(tmp_path)), nprocs=2, join=False)
+    deadline = time.time() + 90
+    while not os.path.exists(tmp_path / "out.json") and time.time() < deadline:
+        time.sleep(0.2)
+    time.sleep(0.3)
+    for p in ctx.processes:
+        p.join(timeout=5)
+        if p.is_alive():
+            p.terminate()
+    out = json.load(open(tmp_path / "out.json"))
+    assert out["outcome"] == "peer failure" and out["after"] < 10 and "rank 1" in out["message"]
+    assert out["collective"] != "returned" and out["collective_after"] < 30
+
+
+def _raising_rank_worker(rank, world, port, tmp):
+    dist = _init(rank, world, port, timeout_s=5)
+    from levanter_b200.utils.watchdog import PeerFailure, Watchdog
+
+    try:
+        with Watchdog(f"{tmp}/hb", rank, world, interval=0.1, peer_timeout=30.0) as wd:
+            dist.barrier()
+            if rank == 1:
+                raise ValueError("loss is NaN")  # the context manager writes the failure marker on the way out
+            t0 = time.time()
+            while time.time() - t0 < 20:
+                wd.raise_if_failed()
+                time.sleep(0.05)
+    except PeerFailure as e:
+        json.dump({"message": str(e), "after": time.time() - t0}, open(f"{tmp}/out.json", "w"))
+    except ValueError:
+        pass
+    finally:
+        os._exit(0)
+
+
+def test_failure_marker_carries_the_reason_to_the_peers(tmp_path):
+    ctx = mp.spawn(_raising_rank_worker, args=(2, 29714, str(tmp_path)), nprocs=2, join=False)
+    deadline = time.time() + 60
+    while not os.path.exists(tmp_path / "out.json") and time.time() < deadline:
+        time.sleep(0.2)
+    time.sleep(0.3)
+    for p in ctx.processes:
+        p.join(timeout=5)
+    out = json.load(open(tmp_path / "out.json"))
+    assert "rank 1 failed" in out["message"] and "loss is NaN" in out["message"] and out["after"] < 5
