@@ -89,6 +89,58 @@ class GenerationResult:
     total_generated: int
 
 
+class _DecodeGraph:
+    """Static input/output buffers and the captured graph of one decode round."""
+
+    def __init__(self, engine: "InferenceEngine", example: PageBatchInfo):
+        from ..ops import lib
+
+        dev = engine.device
+        T = engine.config.max_seqs
+        self.tok = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.pos = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.seeds = torch.zeros(T, dtype=torch.int64, device=dev)
+        self.temps = torch.zeros(T, dtype=torch.float32, device=dev)
+        z = lambda t: torch.zeros(t.shape, dtype=t.dtype, device=dev)  # noqa: E731
+        # warm-up and capture run on tables that address nothing: no sequences, every token destination invalid
+        self.binfo = PageBatchInfo(z(example.slot_ids), z(example.page_indices), z(example.seq_lens), z(example.cu_q_lens),
+                                   z(example.num_seqs), torch.full(example.new_token_dests.shape, INVALID, dtype=example.new_token_dests.dtype, device=dev),
+                                   example.page_size)
+        self._shapes = self._shape_key(example)
+        if lib.available():
+            lib.status_buffer()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(2):  # lazy initialisation (kernel attributes, scratch buffers, cuBLAS handles) happens here
+                self._round(engine)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.out_tok, self.out_lp = self._round(engine)
+            self.tok.copy_(self.out_tok)
+
+    def _round(self, engine):
+        logits = engine._forward(self.tok, self.binfo, self.pos)
+        return engine.sampler(logits, self.temps, key=self.seeds)
+
+    @staticmethod
+    def _shape_key(b: PageBatchInfo):
+        return tuple(tuple(t.shape) for t in (b.slot_ids, b.page_indices, b.seq_lens, b.cu_q_lens, b.num_seqs, b.new_token_dests))
+
+    def matches(self, b: PageBatchInfo) -> bool:
+        return self._shape_key(b) == self._shapes
+
+    def load_round(self, b: PageBatchInfo, pos: torch.Tensor, seeds: torch.Tensor) -> None:
+        s = self.binfo
+        for dst, src in ((s.slot_ids, b.slot_ids), (s.page_indices, b.page_indices), (s.seq_lens, b.seq_lens), (s.cu_q_lens, b.cu_q_lens),
+                         (s.num_seqs, b.num_seqs), (s.new_token_dests, b.new_token_dests)):
+            dst.copy_(src, non_blocking=True)
+        self.pos.copy_(pos)
+        self.seeds.copy_(seeds)
+
+
 def _caches(cache) -> List[KvPageCache]:
     if isinstance(cache, KvPageCache):
         return [cache]
@@ -116,7 +168,8 @@ class InferenceEngine:
         self.local_map: Dict[int, Tuple[int, int]] = {}  # slot -> (request id, choice)
         self.request_queue: Deque[Request] = deque()
         self.results: Dict[int, Dict[int, DecodeResult]] = {}
-        self._graphs: Dict[Tuple[int, int], object] = {}
+        self._graph: Optional[_DecodeGraph] = None
+        self.stats: Dict[str, float] = {"prefill_tokens": 0, "prefill_seconds": 0.0, "decode_tokens": 0, "decode_seconds": 0.0}
 
     # -- construction -------------------------------------------------------------------------------------------
     @classmethod
@@ -197,10 +250,21 @@ class InferenceEngine:
         total = 0
         stalled = 0
         while self.request_queue or self.local_map:
-            admitted = self._admit_from_queue()
+            t_a = self._now()
+            before = sum(len(r.prompt_tokens) for r in self.request_queue)
+            admitted = False
+            while self._admit_from_queue():  # fill the batch before decoding: rounds over a half-empty batch cost the same
+                admitted = True
+            if admitted:
+                self.stats["prefill_seconds"] += self._now() - t_a
+                self.stats["prefill_tokens"] += before - sum(len(r.prompt_tokens) for r in self.request_queue)
             running = bool(self.local_map)
             if running:
-                total += self._decode_call()
+                t_d = self._now()
+                kept = self._decode_call()
+                self.stats["decode_seconds"] += self._now() - t_d
+                self.stats["decode_tokens"] += kept
+                total += kept
             self._release_finished()
             if not admitted and not running:
                 stalled += 1
@@ -322,6 +386,7 @@ class InferenceEngine:
     # -- decode -----------------------------------------------------------------------------------------------------
     def _decode_call(self) -> int:
         """One device call of up to ``max_rounds`` rounds over every live sequence.  Returns the number of tokens kept."""
+        t_plan = time.perf_counter()
         ds = self.gen_state.decode_state
         ds, packed = ds.pack_next_sequence(self.config.max_seqs)
         n = packed.num_tokens
@@ -362,13 +427,34 @@ class InferenceEngine:
         out_tok = torch.empty((R, T), dtype=torch.int32, device=dev)
         out_lp = torch.empty((R, T), dtype=torch.float32, device=dev)
         # the batch rows of a PageBatchInfo are in order of first appearance, and tokens are sorted by slot: row i = token i
-        for r in range(R):
-            b = binfos[r].to(dev)
-            logits = self._forward(d_tok, b, d_pos[r])
-            d_tok, lp = self.sampler(logits, d_temps, key=d_seeds[r])
-            out_tok[r], out_lp[r] = d_tok, lp
+        t_dev = time.perf_counter()
+        self.stats["decode_rounds"] = self.stats.get("decode_rounds", 0) + R
+        self.stats["decode_plan_seconds"] = self.stats.get("decode_plan_seconds", 0.0) + (t_dev - t_plan)
+        graph = self._decode_graph(binfos[0]) if (self.config.use_cuda_graph and dev.type == "cuda") else None
+        if graph is not None:
+            # one captured round, replayed R times: only the small per-round tables are copied into its static inputs; the
+            # sampled tokens are fed back to the token input inside the graph
+            graph.tok.copy_(d_tok)
+            graph.temps.copy_(d_temps)
+            # the tables of all R rounds cross to the device in one copy per field; each round then refreshes the graph's static
+            # inputs with device-to-device copies, so the host never waits for a round to finish before queueing the next
+            fields = ("slot_ids", "page_indices", "seq_lens", "cu_q_lens", "num_seqs", "new_token_dests")
+            staged = {f: torch.stack([getattr(b, f) for b in binfos]).to(dev, non_blocking=True) for f in fields}
+            for r in range(R):
+                graph.load_round(PageBatchInfo(*(staged[f][r] for f in fields), binfos[r].page_size), d_pos[r], d_seeds[r])
+                graph.graph.replay()
+                out_tok[r].copy_(graph.out_tok)
+                out_lp[r].copy_(graph.out_lp)
+        else:
+            for r in range(R):
+                b = binfos[r].to(dev)
+                logits = self._forward(d_tok, b, d_pos[r])
+                d_tok, lp = self.sampler(logits, d_temps, key=d_seeds[r])
+                out_tok[r], out_lp[r] = d_tok, lp
         toks = out_tok.cpu().numpy()
         lps = out_lp.cpu().numpy()
+        t_post = time.perf_counter()
+        self.stats["decode_device_seconds"] = self.stats.get("decode_device_seconds", 0.0) + (t_post - t_dev)
         # apply stop conditions round by round; a finished sequence's later tokens are dropped
         kept = 0
         alive = np.ones(n, dtype=bool)
@@ -380,7 +466,22 @@ class InferenceEngine:
             self._ingest(toks[r, idx], slots[idx], lps[r, idx])
             kept += len(idx)
             alive[idx] = ~ds.finished[slots[idx]]
+        self.stats["decode_post_seconds"] = self.stats.get("decode_post_seconds", 0.0) + (time.perf_counter() - t_post)
         return kept
+
+    def _now(self) -> float:
+        """Host time after the device has drained (phase timings for ``stats``)."""
+        if self.device is not None and torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize(self.device)
+        return time.perf_counter()
+
+    def _decode_graph(self, example: PageBatchInfo) -> Optional["_DecodeGraph"]:
+        """The CUDA graph of one decode round (forward over ``max_seqs`` packed tokens, sampling, token feedback), captured
+        on first use.  Returns None when the round's table shapes differ from the captured ones (the caller runs eagerly)."""
+        g = self._graph
+        if g is None:
+            g = self._graph = _DecodeGraph(self, example)
+        return g if g.matches(example) else None
 
     # -- outputs ----------------------------------------------------------------------------------------------------
     def _ingest(self, tokens: np.ndarray, slots: np.ndarray, lps: Optional[np.ndarray]) -> None:

@@ -250,27 +250,55 @@ class DecodeState:
         n = int(num_new_tokens)
         pos_ids = np.full(len(toks), INVALID, dtype=np.int32)
         purge_mask = np.ones(len(toks), dtype=bool)
-        for i in range(n):
-            sid = int(slots[i])
-            if not (0 <= sid < self.max_seqs):
-                continue
-            pos = int(self.seq_lens[sid])
-            if pos >= self.max_tokens:
-                self.finished[sid] = True
-                continue
-            self.tokens[sid, pos] = toks[i]
+        sl = np.asarray(slots[:n]).astype(np.int64)
+        in_range = (sl >= 0) & (sl < self.max_seqs)
+        if n > 0 and len(np.unique(sl[in_range])) == int(in_range.sum()):
+            # one token per sequence (every decode round): all sequences at once
+            idx = np.nonzero(in_range)[0]
+            sid = sl[idx]
+            pos = self.seq_lens[sid].astype(np.int64)
+            over = pos >= self.max_tokens
+            self.finished[sid[over]] = True
+            idx, sid, pos = idx[~over], sid[~over], pos[~over]
+            self.tokens[sid, pos] = toks[idx]
             if self.logprobs is not None and lps is not None:
-                self.logprobs[sid, pos] = lps[i]
+                self.logprobs[sid, pos] = lps[idx]
             self.seq_lens[sid] = pos + 1
-            done = (pos + 1) >= int(self.max_num_tokens[sid])
-            if not done and self.stop_tokens is not None and self.stop_tokens.shape[1] > 0:
-                L = self.stop_tokens.shape[2]
-                row = self.tokens[sid, max(0, pos + 1 - L):pos + 1]
-                tail = np.concatenate([np.full(L - len(row), INVALID, dtype=np.int32), row])
-                done = is_stop_signal(tail, self.stop_tokens[sid])
+            done = (pos + 1) >= self.max_num_tokens[sid]
+            if self.stop_tokens is not None and self.stop_tokens.shape[1] > 0 and len(sid):
+                stops = self.stop_tokens[sid]                      # [m, stop_seq, L], left padded with INVALID
+                valid = is_valid(stops)
+                if valid.any():
+                    L = stops.shape[2]
+                    at = pos[:, None] + 1 - L + np.arange(L)[None, :]
+                    tail = np.where(at >= 0, self.tokens[sid[:, None], np.clip(at, 0, None)], INVALID)[:, None, :]
+                    match = ((tail == stops) & (tail != INVALID)).sum(axis=-1) == valid.sum(axis=-1)
+                    done = done | (valid.any(axis=-1) & match).any(axis=-1)
             self.finished[sid] = done
-            purge_mask[i] = done
-            pos_ids[i] = pos
+            purge_mask[idx] = done
+            pos_ids[idx] = pos
+        else:
+            for i in range(n):
+                sid = int(slots[i])
+                if not (0 <= sid < self.max_seqs):
+                    continue
+                pos = int(self.seq_lens[sid])
+                if pos >= self.max_tokens:
+                    self.finished[sid] = True
+                    continue
+                self.tokens[sid, pos] = toks[i]
+                if self.logprobs is not None and lps is not None:
+                    self.logprobs[sid, pos] = lps[i]
+                self.seq_lens[sid] = pos + 1
+                done = (pos + 1) >= int(self.max_num_tokens[sid])
+                if not done and self.stop_tokens is not None and self.stop_tokens.shape[1] > 0:
+                    L = self.stop_tokens.shape[2]
+                    row = self.tokens[sid, max(0, pos + 1 - L):pos + 1]
+                    tail = np.concatenate([np.full(L - len(row), INVALID, dtype=np.int32), row])
+                    done = is_stop_signal(tail, self.stop_tokens[sid])
+                self.finished[sid] = done
+                purge_mask[i] = done
+                pos_ids[i] = pos
         if enqueue:
             keep = ~purge_mask
             self.tqueue = self.tqueue.enqueue_tokens(toks[keep], slots[keep], pos_ids[keep], int(keep.sum()))

@@ -120,6 +120,15 @@ def gemm(
             residual = residual.to(torch.bfloat16).contiguous()
         residual = residual.view(M, N) if residual.dim() != 2 else residual
         ldr = residual.stride(0)
+    if M <= SKINNY_MAX_ROWS and not a_mn and not b_mn and not accumulate and max_ctas == 0:
+        # one row block (decode steps, small batches): the weight-streaming kernel
+        rc = _skinny_fn()(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), flags, float(alpha),
+            lib.ptr(bias), lib.ptr(residual), ldr, 0, 0, _skinny_workspace(a.device, M, N),
+            lib.status_buffer().data_ptr(), lib.stream_ptr(),
+        )
+        lib.check_rc(rc, "lvb_gemm_skinny")
+        return out
     rc = _fn()(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr, int(max_ctas),
@@ -127,6 +136,38 @@ def gemm(
     )
     lib.check_rc(rc, "lvb_gemm_bf16")
     return out
+
+
+SKINNY_MAX_ROWS = 128
+_skinny = None
+
+
+def _skinny_fn():
+    global _skinny
+    if _skinny is None:
+        c = lib
+        _skinny = lib.fn("lvb_gemm_skinny", [c.c_void_p, c.c_void_p, c.c_void_p] + [c.c_int] * 7 + [c.c_float, c.c_void_p, c.c_void_p,
+                                                                                                  c.c_int, c.c_int, c.c_int, c.c_void_p, c.c_void_p,
+                                                                                                  c.c_void_p], launches=2)
+    return _skinny
+
+
+_skinny_ws = {}
+
+
+def _skinny_workspace(device, M: int, N: int) -> int:
+    """Address of the per-device scratch for the split-K partials of the streaming kernel, or 0 when the launcher will not
+    split (wide outputs already give every SM a tile).  Successive GEMMs on a stream reuse the scratch safely: each one's
+    second kernel has consumed it before the next one's first kernel writes it."""
+    if N > _SKINNY_SPLIT_MAX_N:
+        return 0
+    ws = _skinny_ws.get(device)
+    if ws is None:
+        ws = _skinny_ws[device] = torch.empty(8 * SKINNY_MAX_ROWS * _SKINNY_SPLIT_MAX_N * 4, dtype=torch.uint8, device=device)
+    return ws.data_ptr()
+
+
+_SKINNY_SPLIT_MAX_N = 128 * 74  # more 128-column tiles than half the SMs: the launcher does not split K
 
 
 class _LinearFn(torch.autograd.Function):

@@ -98,3 +98,24 @@ def test_fp8_gemm_matches_dequantised_reference(M, N, K, a_dt, b_dt):
     acc = torch.ones(M, N, device="cuda")
     fp8_gemm(aq, bq, sa * sb, out=acc, accumulate=True)
     assert (acc - 1 - want).abs().max() <= 1e-3 * want.abs().max()
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (1, 6144, 1024), (128, 14336, 512), (17, 136, 200), (100, 32768, 256), (8, 40, 64)])
+def test_single_row_block_shapes_use_the_streaming_kernel(M, N, K):
+    """M <= 128 (decode, small batches) goes to the weight-streaming kernel: partial A boxes, deep B ring, tiles of 32 to 128 columns."""
+    torch.manual_seed(2)
+    a, b = _rand(M, K), _rand(N, K)
+    bias = _rand(N)
+    c = G.gemm(a, b, bias=bias)
+    torch.cuda.synchronize()
+    lib.check_status()
+    ref = a.float() @ b.float().t() + bias.float()
+    _check(c, ref, K)
+    # residual and fp32 output through the same kernel; rows beyond M of the 128-row MMA must not leak anywhere
+    res = _rand(M, N)
+    guard = torch.full((M + 8, N), 7.0, device="cuda")
+    G.gemm(a, b, residual=res, out=guard[:M])
+    torch.cuda.synchronize()
+    lib.check_status()
+    _check(guard[:M], a.float() @ b.float().t() + res.float(), K)
+    assert bool((guard[M:] == 7.0).all())
