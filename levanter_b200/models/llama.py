@@ -26,7 +26,7 @@ from ..ops.gemm import linear_residual
 from ..ops.glu import gated_activation
 from ..utils.activation import ActivationFunctionEnum
 from ..utils.flop_utils import lm_flops_per_token
-from ..utils.remat import ScanCheckpointPolicy, should_recompute
+from ..utils.remat import ScanCheckpointPolicy, checkpoint_layer, keeps_attention, should_recompute
 from .lm_model import LmConfig, LmHeadModel
 
 
@@ -247,9 +247,10 @@ class LlamaTransformer(nn.Module):
 
     def forward(self, x, mask=None, pos_ids=None):
         remat = should_recompute(self.config.gradient_checkpointing) and torch.is_grad_enabled() and self.training
+        keep = keeps_attention(self.config.gradient_checkpointing)
         for layer in self.layers:
             if remat:
-                x = checkpoint(layer, x, mask, pos_ids, use_reentrant=False)
+                x = checkpoint_layer(layer, x, mask, pos_ids, keep_attention=keep)
             else:
                 x = layer(x, mask, pos_ids)
         return self.norm(x)

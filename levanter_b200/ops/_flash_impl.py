@@ -1,6 +1,7 @@
 """Autograd binding of the tcgen05 flash-attention kernels (``csrc/flash_attn.cu``)."""
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional
 
@@ -34,20 +35,54 @@ def _bwd():
     return _f["b"]
 
 
+# Activation checkpointing that keeps attention outputs (utils/remat.py:checkpoint_layer): during the first pass of a
+# checkpointed layer the forward below appends (o, lse) to ``_keep``; during the recomputation it takes them back from
+# ``_replay`` in the same order and launches nothing.
+_keep: Optional[list] = None
+_replay: Optional[list] = None
+
+
+@contextlib.contextmanager
+def keeping_outputs(store: list):
+    global _keep
+    prev, _keep = _keep, store
+    try:
+        yield store
+    finally:
+        _keep = prev
+
+
+@contextlib.contextmanager
+def replaying_outputs(store: list):
+    global _replay
+    prev, _replay = _replay, list(store)
+    try:
+        yield
+    finally:
+        _replay = prev
+
+
 class _FlashFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window):
         B, S, Hq, D = q.shape
         Hkv = k.shape[2]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o = torch.empty_like(q)
-        lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-        # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
-        fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
-        rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
-                    B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(),
-                    lib.stream_ptr())
-        lib.check_rc(rc, "lvb_flash_attn_fwd")
+        if _replay:
+            o, lse2 = _replay.pop(0)
+            if o.shape != q.shape:
+                raise RuntimeError("the recomputation of a checkpointed layer called attention in a different order than its first pass")
+        else:
+            o = torch.empty_like(q)
+            lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+            # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
+            fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
+            rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+                     B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(),
+                     lib.stream_ptr())
+            lib.check_rc(rc, "lvb_flash_attn_fwd")
+            if _keep is not None:
+                _keep.append((o, lse2))
         ctx.save_for_backward(q, k, v, o, lse2, q_seg, k_seg)
         ctx.args = (scale, soft_cap, window)
         return o
