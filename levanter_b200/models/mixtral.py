@@ -144,6 +144,12 @@ class MixtralSparseMoeBlock(nn.Module):
             from ..parallel.expert import dispatch_combine
 
             out_repeat = dispatch_combine(self.ep, x_flat, sort_idx, group_sizes, k, self.experts)
+        elif x_flat.is_cuda:
+            # one grouped launch per projection over a padded expert-sorted layout; nothing is read back by the host
+            from ..ops.moe import grouped_mlp_padded
+
+            e = self.experts
+            out_repeat = grouped_mlp_padded(x_flat, topk_idx, e.w1, e.w3, e.w2, e.act)
         else:
             x_sorted = x_flat.index_select(0, sort_idx // k)
             out_sorted = self.experts(x_sorted, group_sizes)

@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -177,6 +177,35 @@ def main(argv=None):
         ms, mn = _time(lambda: PA.ragged_paged_attention(q, kv, lens, pages, cu, n, sm_scale=1 / math.sqrt(128)), a.iters, a.warmup, flush)
         return _report("paged_attention_decode", {"seqs": S, "context": a.context, "heads": a.heads, "kv_heads": kvh}, ms, mn,
                        nbytes=2.0 * S * (a.context + 1) * kvh * 128 * 2)
+
+    if a.kernel == "moe_mlp":
+        # Mixtral-style expert MLP, forward + backward: one grouped launch per projection against a launch per expert
+        from ..utils.activation import ActivationFunctionEnum
+        from .moe import grouped_mlp, grouped_mlp_padded
+
+        T, E, k, H, M = a.batch * a.seq, 8, 2, a.hidden, a.n if a.n != 8192 else 14336
+        x = (torch.randn(T, H, device=dev) * 0.5).to(bf).requires_grad_()
+        w1, w3 = ((torch.randn(E, M, H, device=dev) * 0.02).to(bf).requires_grad_() for _ in range(2))
+        w2 = (torch.randn(E, H, M, device=dev) * 0.02).to(bf).requires_grad_()
+        idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)])
+        act = ActivationFunctionEnum.silu
+
+        def grouped():
+            grouped_mlp_padded(x, idx, w1, w3, w2, act).sum().backward()
+
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+
+        def looped():
+            sizes = torch.bincount(flat, minlength=E)  # read back by the loop: one host synchronisation per call
+            grouped_mlp(x.index_select(0, order // k), sizes, w1, w3, w2, act).sum().backward()
+
+        flops = 3 * 3 * 2.0 * T * k * H * M  # three projections, forward + two backward GEMMs each
+        ms_g, mn_g = _time(grouped, a.iters, a.warmup, flush)
+        ms_l, mn_l = _time(looped, a.iters, a.warmup, flush)
+        cfg = {"tokens": T, "experts": E, "top_k": k, "hidden": H, "mlp": M}
+        _report("moe_mlp_grouped_fwd_bwd", cfg, ms_g, mn_g, flops=flops)
+        return _report("moe_mlp_per_expert_loop_fwd_bwd", cfg, ms_l, mn_l, flops=flops)
 
     if a.kernel == "sampler":
         from ..layers.sampler import Sampler

@@ -68,11 +68,17 @@ struct Params {
   void* rs_out;              // this rank's reduced rows [c_rows_per_rank, N] (bf16, or fp32 if rs_out_f32), row stride rs_ldo
   int rs_ldo;
   int rs_out_f32;
+  // ---- grouped GEMM (see lvb_gemm_grouped)
+  const int* g_tile_group;  // K-major A: group of every 128-row block of A, or -1 for a block past the last group (skipped)
+  int g_b_rows;             // K-major A: rows (K-major B) or reduction rows (MN-major B) of one group's B inside the stacked B
+  const int* g_offsets;     // MN-major A (weight gradient): reduction rows [g_offsets[g], g_offsets[g + 1]) belong to group g
+  int g_tiles_m;            // MN-major A: 128-row blocks of C per group
 };
 
 constexpr int kModePlain = 0;
 constexpr int kModeGatherA = 1;   // all-gather fused into the A operand
 constexpr int kModeScatterC = 2;  // reduce-scatter fused into the epilogue
+constexpr int kModeGrouped = 3;   // one B matrix (or one K range) per group of rows: the expert GEMMs of a mixture-of-experts layer
 constexpr int kCopyUnit = 16384;  // bytes per bulk copy of the gather
 constexpr int kCopyExtra = 256 + 2 * kCopyUnit;  // extra dynamic shared memory of the gather kernel
 constexpr int kGatherThreads = kNumThreads + 32;  // + one copy warp
@@ -121,6 +127,24 @@ __device__ __forceinline__ void tile_coords_interleaved(int t, int tiles_m, int 
   int dest = rank + 1 + mb % world;
   if (dest >= world) dest -= world;
   mb = dest * (tiles_m / world) + mb / world;
+}
+
+// Grouped mode: what a tile has to do.  K-major A (forward, input gradient): the tile's row block belongs to group g (skip when
+// g < 0) and the whole K is reduced.  MN-major A (weight gradient): row block mb of C belongs to group mb / g_tiles_m and only
+// that group's rows of the two operands are reduced (k-blocks [kb0, kb1); nothing to do when the group is empty).
+template <bool A_MN>
+__device__ __forceinline__ bool grouped_tile(const Params& p, int mb, int k_blocks, int& group, int& kb0, int& kb1) {
+  if constexpr (!A_MN) {
+    group = p.g_tile_group[mb];
+    kb0 = 0;
+    kb1 = k_blocks;
+    return group >= 0;
+  } else {
+    group = mb / p.g_tiles_m;
+    kb0 = p.g_offsets[group] / BK;
+    kb1 = p.g_offsets[group + 1] / BK;
+    return kb1 > kb0;
+  }
 }
 
 // kF8: one-byte operands (both K-major); a stage row is still 128 bytes, i.e. 128 elements of K instead of 64.
@@ -185,11 +209,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       int ready_block = -1;  // gather mode: last m-block whose rows are known to have arrived
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb;
-        if constexpr (MODE == kModePlain) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        if constexpr (MODE == kModePlain || MODE == kModeGrouped) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
         else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
         else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
         int a_map = 0, a_row = m0;
+        int group = 0, kb_begin = 0, kb_end = k_blocks;
+        if constexpr (MODE == kModeGrouped) {
+          if (!grouped_tile<A_MN>(p, mb, k_blocks, group, kb_begin, kb_end)) continue;
+        }
         if constexpr (MODE == kModeGatherA) {
           a_map = m0 / p.a_rows_per_map;  // the rank these rows belong to
           a_row = m0 - a_map * p.a_rows_per_map;
@@ -202,7 +230,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
             ready_block = mb;
           }
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        // grouped mode: where this tile's operands sit inside the stacked tensors
+        int a_col = m0, b_row = n0, b_k = 0;
+        if constexpr (MODE == kModeGrouped) {
+          if constexpr (A_MN) a_col = (mb - group * p.g_tiles_m) * BM;      // C rows are stacked per group, A's columns are not
+          else if constexpr (!B_MN) b_row = group * p.g_b_rows + n0;        // K-major B: [groups * N, K]
+          else b_k = group * p.g_b_rows;                                    // MN-major B: [groups * K, N]
+        }
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100, stage);
           if (!ok) break;
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -214,14 +249,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_load_2d(sa + c * (64 * BK * 2), &tmA, &full_bar[stage], m0 + 64 * c, k0);
+              tma_load_2d(sa + c * (64 * BK * 2), &tmA, &full_bar[stage], a_col + 64 * c, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, b_row);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (64 * BK * 2), &tmB, &full_bar[stage], n0 + 64 * c, k0);
+              tma_load_2d(sb + c * (64 * BK * 2), &tmB, &full_bar[stage], n0 + 64 * c, k0 + b_k);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -237,11 +272,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       uint32_t tphase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int n_kb = k_blocks;
+        if constexpr (MODE == kModeGrouped) {
+          int mb, nb, group, kb0, kb1;
+          tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+          if (!grouped_tile<A_MN>(p, mb, k_blocks, group, kb0, kb1)) continue;
+          n_kb = kb1 - kb0;
+        }
         ok = mbar_wait(&tempty_bar[buf], tphase ^ 1, abort_flag, p.status, 200, buf);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < n_kb; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201, stage);
           if (!ok) break;
           tc_fence_after();
@@ -279,9 +321,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
     const float alpha = p.alpha_dev != nullptr ? p.alpha * p.alpha_dev[0] : p.alpha;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      if constexpr (MODE == kModePlain) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      if constexpr (MODE == kModePlain || MODE == kModeGrouped) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
       else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
       else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
+      if constexpr (MODE == kModeGrouped) {
+        int group, kb0, kb1;
+        if (!grouped_tile<A_MN>(p, mb, k_blocks, group, kb0, kb1)) continue;
+      }
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300, buf);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -657,6 +703,13 @@ gemm_scatter_c_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   gemm_body<BN, false, false, false, kModeScatterC>(&tmA, tmB, p);
 }
 
+// Grouped GEMM: the same pipeline with a per-tile group look-up (see grouped_tile and lvb_gemm_grouped).
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, A_MN, B_MN, false, kModeGrouped>(&tmA, tmB, p);
+}
+
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream, int max_ctas) {
   using L = SmemLayout<BN>;
@@ -929,3 +982,83 @@ extern "C" int lvb_gemm_reduce_scatter(const void* A, const void* B, void* const
 
 // Tiles along N of the kernels above for an N-column output (sizes the per-tile counters).
 extern "C" int lvb_gemm_tiles_n(int N) { return N > 128 ? (N + 255) / 256 : 1; }
+
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Grouped GEMMs for mixture-of-experts layers.  Rows (tokens) are sorted by group (expert) and every group's segment is padded
+// with zero rows to a multiple of 128, so no 128-row block straddles two groups; the group boundaries live in device memory,
+// and nothing about them is read back by the host.
+namespace lvb {
+namespace gemm {
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_grouped(const void* A, const void* B, Params p, int a_rows, int a_cols, int lda, int b_rows, int b_cols, int ldb,
+                   cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, a_rows, a_cols, lda, BM, BK);
+  else       rc = make_tmap_2d_bf16(&tmA, A, a_rows, a_cols, lda, BK, 64);
+  if (rc != kErrOk) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, B, b_rows, b_cols, ldb, BN, BK);
+  else       rc = make_tmap_2d_bf16(&tmB, B, b_rows, b_cols, ldb, BK, 64);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_grouped_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > num_sms()) grid = num_sms();
+  kern<<<grid, kNumThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+}  // namespace gemm
+}  // namespace lvb
+
+// kind 0, forward:          C[Tp, N] = A[Tp, K] B[g][N, K]^T      A: padded sorted rows; B: [groups, N, K] (row stride ldb)
+// kind 1, input gradient:   C[Tp, N] = A[Tp, K] B[g][K, N]        B: [groups, K, N], i.e. the forward weight [groups, out, in] as it is
+// kind 2, weight gradient:  C[g][M, N] (+)= A[rows of g, M]^T B[rows of g, N]     A, B: padded sorted rows; C: [groups, M, N]
+// tile_group: int32[ceil(Tp / 128)], the group of every 128-row block of A, -1 beyond the last group (kinds 0 and 1).
+// offsets:    int32[groups + 1], padded row offsets (multiples of 128) of the groups (kind 2).
+// For kinds 0 and 1, Tp is the static capacity of the padded buffer; blocks marked -1 are neither read nor written.
+// flags as lvb_gemm_bf16 (kOutF32, kAccumulate); M, N multiples of 8; for kind 2 M must be a multiple of 128.
+extern "C" int lvb_gemm_grouped(int kind, const void* A, const void* B, void* C, int groups, int Tp, int M, int N, int K, int lda,
+                                int ldb, int ldc, int flags, float alpha, const int* tile_group, const int* offsets, int* status,
+                                void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (groups <= 0 || Tp <= 0 || (Tp % BM) != 0 || N <= 0 || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  Params p;
+  p.C = C; p.bias = nullptr; p.residual = nullptr;
+  p.ldc = ldc; p.ldr = 0;
+  p.flags = flags & (kOutF32 | kAccumulate); p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.a_fmt = p.b_fmt = 0;
+  p.rank = 0; p.world = 1; p.m_rot = 0;
+  p.a_rows_per_map = 0; p.c_rows_per_rank = 0;
+  p.g_tile_group = tile_group; p.g_offsets = offsets; p.g_b_rows = 0; p.g_tiles_m = 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 0) {
+    if (tile_group == nullptr || K <= 0) return kErrBadArg;
+    p.M = Tp; p.N = N; p.K = K; p.g_b_rows = N;
+    return N > 128 ? launch_grouped<256, false, false>(A, B, p, Tp, K, lda, groups * N, K, ldb, s)
+                   : launch_grouped<128, false, false>(A, B, p, Tp, K, lda, groups * N, K, ldb, s);
+  }
+  if (kind == 1) {
+    if (tile_group == nullptr || K <= 0) return kErrBadArg;
+    p.M = Tp; p.N = N; p.K = K; p.g_b_rows = K;
+    return N > 128 ? launch_grouped<256, false, true>(A, B, p, Tp, K, lda, groups * K, N, ldb, s)
+                   : launch_grouped<128, false, true>(A, B, p, Tp, K, lda, groups * K, N, ldb, s);
+  }
+  if (kind == 2) {
+    if (offsets == nullptr || M <= 0 || (M % BM) != 0) return kErrBadArg;
+    p.M = groups * M; p.N = N; p.K = Tp; p.g_tiles_m = M / BM;
+    return N > 128 ? launch_grouped<256, true, true>(A, B, p, Tp, M, lda, Tp, N, ldb, s)
+                   : launch_grouped<128, true, true>(A, B, p, Tp, M, lda, Tp, N, ldb, s);
+  }
+  return kErrBadArg;
+}
