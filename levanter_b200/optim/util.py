@@ -54,8 +54,11 @@ scale_by_update_rms_clipping = scan_aware_clip_by_block_rms
 def hvp(f: Callable[[Dict[str, torch.Tensor]], torch.Tensor], params: Dict[str, torch.Tensor], v: Tree) -> Tree:
     """Hessian-vector product of scalar ``f(params)`` along ``v`` by double backward."""
     names = [k for k, p in params.items() if p is not None and v.get(k) is not None]
+    # leaves that do not require gradients (plain tensors handed in by a caller) are differentiated through a detached alias
+    params = {k: (p if (p is None or p.requires_grad) else p.detach().requires_grad_()) for k, p in params.items()}
     ps = [params[k] for k in names]
-    loss = f(params)
+    with torch.enable_grad():
+        loss = f(params)
     grads = torch.autograd.grad(loss, ps, create_graph=True, allow_unused=True)
     dot = sum((g * v[k].to(g.dtype)).sum() for g, k in zip(grads, names) if g is not None)
     hv = torch.autograd.grad(dot, ps, allow_unused=True)
