@@ -1,0 +1,89 @@
+"""Checkpoint leaves on disk: tree round trips with scalars / None / named tuples, missing leaves, the zarr layout, corruption
+(modelled on the reference's test_tensorstore_serialization.py and the fault tests: a removed or damaged leaf is an error, or is
+skipped when partial checkpoints are allowed)."""
+import json
+import os
+import shutil
+from typing import NamedTuple
+
+import numpy as np
+import pytest
+import torch
+
+from levanter_b200 import tensorstore_serialization as tss
+from levanter_b200.store.zarr_array import ZarrArray
+
+
+class _Pair(NamedTuple):
+    mu: dict
+    count: int
+
+
+def _tree():
+    g = torch.Generator().manual_seed(0)
+    return {"model": {"a.weight": torch.randn(5, 3, generator=g), "a.bias": torch.randn(3, generator=g).bfloat16()},
+            "opt": _Pair({"a.weight": torch.randn(5, 3, generator=g)}, 7), "step": 12, "lr": 0.25, "flag": True, "nothing": None,
+            "arr": np.arange(6, dtype=np.int64).reshape(2, 3)}
+
+
+def test_tree_round_trip_with_scalars_none_and_named_tuples(tmp_path):
+    tree = _tree()
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), tree)
+    like = {"model": {"a.weight": torch.zeros(5, 3), "a.bias": torch.zeros(3, dtype=torch.bfloat16)}, "opt": _Pair({"a.weight": torch.zeros(5, 3)}, 0),
+            "step": 0, "lr": 0.0, "flag": False, "nothing": None, "arr": np.zeros((2, 3), dtype=np.int64)}
+    back = tss.tree_deserialize_leaves_tensorstore(str(tmp_path), like)
+    assert torch.equal(back["model"]["a.weight"], tree["model"]["a.weight"]) and back["model"]["a.bias"].dtype == torch.bfloat16
+    assert torch.equal(back["model"]["a.bias"], tree["model"]["a.bias"])
+    assert isinstance(back["opt"], _Pair) and back["opt"].count == 7 and torch.equal(back["opt"].mu["a.weight"], tree["opt"].mu["a.weight"])
+    assert back["step"] == 12 and back["lr"] == 0.25 and back["flag"] is True and back["nothing"] is None
+    assert np.array_equal(back["arr"], tree["arr"])
+
+
+def test_leaf_is_a_zarr_v2_array_with_dot_separated_chunks(tmp_path):
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), {"w": torch.arange(12, dtype=torch.float32).reshape(3, 4)})
+    leaf = [os.path.join(r, d) for r, ds, _ in os.walk(tmp_path) for d in ds if os.path.exists(os.path.join(r, d, ".zarray"))]
+    assert len(leaf) == 1
+    meta = json.load(open(os.path.join(leaf[0], ".zarray")))
+    assert meta["zarr_format"] == 2 and meta["shape"] == [3, 4] and meta["dtype"] in ("<f4", "float32") and meta.get("dimension_separator", ".") == "."
+    assert any(f.replace(".", "").isdigit() for f in os.listdir(leaf[0]))  # chunk files named like 0.0
+    assert torch.equal(ZarrArray.open(leaf[0]).read_tensor(), torch.arange(12, dtype=torch.float32).reshape(3, 4))
+    part = ZarrArray.open(leaf[0]).read_tensor([1, 1], [3, 3])
+    assert torch.equal(part, torch.tensor([[5.0, 6.0], [9.0, 10.0]]))
+
+
+def test_missing_leaf_is_an_error_unless_allowed(tmp_path):
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), {"a": torch.ones(2), "b": torch.zeros(2)})
+    victim = next(os.path.join(r, d) for r, ds, _ in os.walk(tmp_path) for d in ds if d == "b")
+    shutil.rmtree(victim)
+    like = {"a": torch.zeros(2), "b": torch.full((2,), 5.0)}
+    with pytest.raises(FileNotFoundError, match="b"):
+        tss.tree_deserialize_leaves_tensorstore(str(tmp_path), like)
+    back = tss.tree_deserialize_leaves_tensorstore(str(tmp_path), like, allow_missing=True)
+    assert torch.equal(back["a"], torch.ones(2)) and torch.equal(back["b"], torch.full((2,), 5.0))
+
+
+def test_damaged_chunk_is_detected(tmp_path):
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), {"w": torch.randn(64, 64)})
+    leaf = next(os.path.join(r, d) for r, ds, _ in os.walk(tmp_path) for d in ds if os.path.exists(os.path.join(r, d, ".zarray")))
+    chunk = next(os.path.join(leaf, f) for f in os.listdir(leaf) if not f.startswith("."))
+    data = bytearray(open(chunk, "rb").read())
+    open(chunk, "wb").write(bytes(data[: len(data) // 2]))  # truncated file
+    with pytest.raises(Exception):
+        ZarrArray.open(leaf).read_tensor()
+
+
+def test_stacked_reference_layout_for_layer_parameters(tmp_path):
+    """Per-layer torch parameters are stored as one array stacked over layers, under the reference's key names."""
+    from levanter_b200.models.llama import LlamaConfig
+
+    m = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=3, num_heads=2, num_kv_heads=2).build(50, seed=0)
+    layouts = tss.layouts_of(m)
+    params = {n: p.detach() for n, p in m.named_parameters()}
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), {"model": params}, layouts=layouts)
+    name = "transformer.layers.1.mlp.gate_proj.weight"
+    key, layer = tss.reference_key_for(name)
+    assert layer == 1 and "layers" in key
+    got = tss.read_param(str(tmp_path), "model", name, layouts.get(name), tuple(params[name].shape))
+    assert torch.equal(got, params[name])
+    stacked = ZarrArray.open(tss._fs_path(str(tmp_path), f"model.{key}"))
+    assert stacked.shape[0] == 3
