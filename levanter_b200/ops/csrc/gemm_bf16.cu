@@ -446,14 +446,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
           if (out_f32) {
             float* cp = reinterpret_cast<float*>(c_base) + c_row * p.ldc + col0;
             if (full && (p.ldc & 3) == 0) {
+              if (accum) {
+                // C += tile as vector reductions resolved in L2: the epilogue does not wait for the old values to come back,
+                // and every element has exactly one adder per launch, so the sum stays deterministic
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                if (accum) {
-                  float4 old = reinterpret_cast<float4*>(cp)[q];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                reinterpret_cast<float4*>(cp)[q] = o;
+                for (int q = 0; q < 8; ++q)
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + 4 * q), "f"(v[4 * q]), "f"(v[4 * q + 1]),
+                               "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
+                               : "memory");
+              } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  reinterpret_cast<float4*>(cp)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
               }
             } else {
 #pragma unroll
