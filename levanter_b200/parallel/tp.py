@@ -66,3 +66,20 @@ class TensorParallel:
         parts = [torch.empty_like(x) for _ in range(self.size)]
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)
+
+
+def shard_full_state_(model: torch.nn.Module, full_state: dict, tp: Optional["TensorParallel"]) -> None:
+    """Fill a tensor-parallel ``model`` from the tensors of the unsharded model: every parameter marked ``tp_dim`` takes
+    this rank's slice along that dimension (heads and MLP columns are contiguous per rank), the others are copied whole.
+    Used to serve (or continue training) a checkpoint on a model axis of any size."""
+    rank = tp.rank if tp is not None else 0
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            src = full_state[name]
+            dim = getattr(p, "tp_dim", None)
+            if dim is not None and src.shape != p.shape:
+                n = p.shape[dim]
+                src = src.narrow(dim, rank * n, n)
+            if src.shape != p.shape:
+                raise ValueError(f"{name}: cannot place {tuple(full_state[name].shape)} into {tuple(p.shape)} (tp_dim={dim})")
+            p.copy_(src.to(p.dtype))
