@@ -133,16 +133,16 @@ class MixtralSparseMoeBlock(nn.Module):
         shape = x.shape
         x_flat = x.reshape(-1, shape[-1])
         T = x_flat.shape[0]
+        from ..ops.moe import moe_route
+
         router_logits = self.gate(x_flat).float()
-        router_probs = torch.softmax(router_logits, dim=-1)
-        topk_w, topk_idx = torch.topk(router_probs, k, dim=-1)
-        topk_w = topk_w / topk_w.sum(-1, keepdim=True)
+        # softmax, top-k, renormalised weights, tokens per expert, probability sums and log-sum-exp in one kernel per direction
+        topk_w, topk_idx, group_sizes, p_sum, lse = moe_route(router_logits, k)
         flat_idx = topk_idx.reshape(-1)
-        sort_idx = torch.argsort(flat_idx, stable=True)
-        group_sizes = torch.bincount(flat_idx, minlength=E)
         if self.ep is not None and self.ep.size > 1:
             from ..parallel.expert import dispatch_combine
 
+            sort_idx = torch.argsort(flat_idx, stable=True)
             out_repeat = dispatch_combine(self.ep, x_flat, sort_idx, group_sizes, k, self.experts)
         elif x_flat.is_cuda:
             # one grouped launch per projection over a padded expert-sorted layout; nothing is read back by the host
@@ -151,6 +151,7 @@ class MixtralSparseMoeBlock(nn.Module):
             e = self.experts
             out_repeat = grouped_mlp_padded(x_flat, topk_idx, e.w1, e.w3, e.w2, e.act)
         else:
+            sort_idx = torch.argsort(flat_idx, stable=True)
             x_sorted = x_flat.index_select(0, sort_idx // k)
             out_sorted = self.experts(x_sorted, group_sizes)
             inv = torch.empty_like(sort_idx)
@@ -161,10 +162,10 @@ class MixtralSparseMoeBlock(nn.Module):
         extras: Dict[str, torch.Tensor] = {"expert_loads": loads}
         if c.lbl_coef is not None:
             f = loads * E / k
-            p = router_probs.mean(0)
+            p = p_sum / T
             extras["load_balancing_loss"] = c.lbl_coef * (f * p).sum()
         if c.rzl_coef is not None:
-            extras["router_z_loss"] = c.rzl_coef * (torch.logsumexp(router_logits, dim=-1) ** 2).mean()
+            extras["router_z_loss"] = c.rzl_coef * (lse ** 2).mean()
         return out.view(shape), extras
 
 

@@ -161,3 +161,69 @@ def grouped_mlp_padded(x_flat: torch.Tensor, topk_idx: torch.Tensor, w1: torch.T
     h = gated_activation(grouped_linear(x_pad, w1, tile_group, offsets), grouped_linear(x_pad, w3, tile_group, offsets), act)
     y = grouped_linear(h, w2, tile_group, offsets)
     return y.index_select(0, dest)
+
+
+# ------------------------------------------------------------------------------------------------ routing
+def moe_route_reference(router_logits: torch.Tensor, k: int):
+    """``(topk_w[T, k], topk_idx[T, k], counts[E], p_sum[E], lse[T])`` with PyTorch ops (CPU path and oracle)."""
+    z = router_logits.float()
+    probs = torch.softmax(z, dim=-1)
+    w, idx = torch.topk(probs, k, dim=-1)
+    w = w / w.sum(-1, keepdim=True)
+    counts = torch.bincount(idx.reshape(-1), minlength=z.shape[-1])
+    return w, idx, counts, probs.sum(0), torch.logsumexp(z, dim=-1)
+
+
+class _MoeRoute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k):
+        from . import lib
+
+        c = lib
+        T, E = logits.shape
+        z = logits.float().contiguous()
+        dev = z.device
+        idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, k, dtype=torch.float32, device=dev)
+        probs = torch.empty(T, E, dtype=torch.float32, device=dev)
+        lse = torch.empty(T, dtype=torch.float32, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        psum = torch.empty(E, dtype=torch.float32, device=dev)
+        scratch = torch.empty(((T + 127) // 128) * E, dtype=torch.float32, device=dev)
+        f = lib.fn("lvb_moe_route_fwd", [c.c_void_p, c.c_int, c.c_int, c.c_int] + [c.c_void_p] * 8, launches=2)
+        rc = f(z.data_ptr(), T, E, k, idx.data_ptr(), w.data_ptr(), probs.data_ptr(), lse.data_ptr(), counts.data_ptr(), psum.data_ptr(),
+               scratch.data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_moe_route_fwd")
+        ctx.save_for_backward(probs, idx)
+        ctx.k = k
+        ctx.in_dtype = logits.dtype
+        idx64 = idx.long()
+        ctx.mark_non_differentiable(idx64, counts)
+        return w, idx64, counts, psum, lse
+
+    @staticmethod
+    def backward(ctx, d_w, _d_idx, _d_counts, d_psum, d_lse):
+        from . import lib
+
+        c = lib
+        probs, idx = ctx.saved_tensors
+        T, E = probs.shape
+        dz = torch.empty_like(probs)
+        prep = lambda t: None if t is None else t.float().contiguous()  # noqa: E731
+        d_w, d_psum, d_lse = prep(d_w), prep(d_psum), prep(d_lse)
+        f = lib.fn("lvb_moe_route_bwd", [c.c_void_p] * 5 + [c.c_int] * 3 + [c.c_void_p, c.c_void_p])
+        rc = f(probs.data_ptr(), idx.data_ptr(), lib.ptr(d_w), lib.ptr(d_psum), lib.ptr(d_lse), T, E, ctx.k, dz.data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_moe_route_bwd")
+        return dz.to(ctx.in_dtype), None
+
+
+def moe_route(router_logits: torch.Tensor, k: int):
+    """Routing of ``router_logits[T, E]``: renormalised top-``k`` weights and indices, tokens per expert, per-expert sums of
+    the router probabilities (for the load-balancing loss) and the per-token log-sum-exp (for the router z-loss).
+    Differentiable in the weights, the probability sums and the log-sum-exp."""
+    from . import lib
+
+    E = router_logits.shape[-1]
+    if router_logits.is_cuda and lib.available() and E <= 64 and k <= 8:
+        return _MoeRoute.apply(router_logits, k)
+    return moe_route_reference(router_logits, k)
