@@ -430,7 +430,8 @@ class Attention(nn.Module):
         """``residual + attention(x)`` with the add done in the output-projection GEMM epilogue."""
         return self.forward(x, mask, pos_ids, residual=residual)
 
-    def paged_decode(self, x: torch.Tensor, kv_cache: "KvPageCache", batch_info, pos_ids: torch.Tensor):
+    def paged_decode(self, x: torch.Tensor, kv_cache: "KvPageCache", batch_info, pos_ids: torch.Tensor,
+                     residual: Optional[torch.Tensor] = None):
         """Decode/prefill step over packed tokens ``x[T, E]``; writes K/V into the page cache and attends over
         the pages of each sequence (src/levanter/layers/attention.py:1559-1604)."""
         from ..ops import paged_attention as PA
@@ -443,6 +444,12 @@ class Attention(nn.Module):
                                         batch_info.cu_q_lens, batch_info.num_seqs, sm_scale=scale,
                                         soft_cap=c.logits_soft_cap)
         out = out.reshape(x.shape[0], self.local_heads * c.head_size).to(x.dtype)
+        if residual is not None:
+            if type(self.o_proj) is Linear:
+                from ..ops.gemm import linear_residual
+
+                return linear_residual(out, self.o_proj.weight, self.o_proj.bias, residual), kv_cache
+            return self.o_proj(out) + residual, kv_cache
         return self.o_proj(out), kv_cache
 
     def empty_page_cache(self, max_pages: int, page_size: int, *, dtype=torch.bfloat16, device=None) -> "KvPageCache":

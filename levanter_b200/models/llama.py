@@ -225,17 +225,21 @@ class LlamaDecoderLayer(nn.Module):
 
     def decode(self, x, kv_cache: KvPageCache, batch_info, pos_ids):
         h = self.input_layernorm(x)
-        attn_out, kv_cache = self.self_attn.paged_decode(h, kv_cache, batch_info, pos_ids)
-        if self.tp is not None and self.tp.size > 1:
-            attn_out = self.tp.all_reduce(attn_out)
-        if self.post_attn_layernorm is not None:
-            attn_out = self.post_attn_layernorm(attn_out)
-        x = x + attn_out
+        tp_on = self.tp is not None and self.tp.size > 1
+        if not tp_on and self.post_attn_layernorm is None:
+            # both residual adds ride in the epilogues of the output and down projections
+            x, kv_cache = self.self_attn.paged_decode(h, kv_cache, batch_info, pos_ids, residual=x)
+        else:
+            attn_out, kv_cache = self.self_attn.paged_decode(h, kv_cache, batch_info, pos_ids)
+            if tp_on:
+                attn_out = self.tp.all_reduce(attn_out)
+            if self.post_attn_layernorm is not None:
+                attn_out = self.post_attn_layernorm(attn_out)
+            x = x + attn_out
         h = self.post_attention_layernorm(x)
-        m = self.mlp(h)
-        if self.post_mlp_layernorm is not None:
-            m = self.post_mlp_layernorm(m)
-        return x + m, kv_cache
+        if self.post_mlp_layernorm is None:
+            return self.mlp(h, residual=x), kv_cache
+        return x + self.post_mlp_layernorm(self.mlp(h)), kv_cache
 
 
 class LlamaTransformer(nn.Module):

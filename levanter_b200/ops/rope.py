@@ -51,6 +51,30 @@ class _RopeFn(torch.autograd.Function):
         return dq, dk, None, None, None, None
 
 
+_last_cos_sin = None  # (key, position tensor kept alive, cos, sin)
+
+
+def _cos_sin_once(rot: RotaryEmbeddings, pos_ids: torch.Tensor):
+    """cos/sin rows for explicit positions, computed once per forward pass instead of once per layer: every layer of a model
+    passes the same position tensor.  The entry holds a reference to that tensor (so its address cannot be reused while the
+    entry lives) and is keyed on its version counter (in-place updates invalidate it) and on whether a CUDA graph is being
+    captured (tables made before a capture must not be baked into the graph as constants)."""
+    global _last_cos_sin
+    capturing = torch.cuda.is_current_stream_capturing() if pos_ids.is_cuda else False
+    sig = getattr(rot, "_value_signature", None)
+    if sig is None:  # layers build their own embedding objects from the same config: compare them by value
+        f = rot.inv_freq
+        sig = rot._value_signature = (rot.head_dim, rot.position_scale, rot.temperature, f.numel(), float(f[0]), float(f[-1]), float(f.sum()))
+    key = (pos_ids.data_ptr(), pos_ids._version, pos_ids.numel(), capturing, sig)
+    hit = _last_cos_sin
+    if hit is not None and hit[0] == key:
+        return hit[2], hit[3]
+    cos, sin = rot.cos_sin(pos_ids.reshape(-1))
+    cos, sin = cos.contiguous(), sin.contiguous()
+    _last_cos_sin = (key, pos_ids, cos, sin)
+    return cos, sin
+
+
 def apply_rope(q: torch.Tensor, k: torch.Tensor, rot: RotaryEmbeddings, pos_ids=None):
     """Rotate ``q[..., S, H, D]`` and ``k[..., S, KV, D]``.
 
@@ -64,10 +88,10 @@ def apply_rope(q: torch.Tensor, k: torch.Tensor, rot: RotaryEmbeddings, pos_ids=
             cos, sin = rot.table(S, q.device)
             period = S
         elif pos_ids.numel() == S and tokens % S == 0:
-            cos, sin = rot.cos_sin(pos_ids.reshape(-1))
+            cos, sin = _cos_sin_once(rot, pos_ids)
             period = S
         elif pos_ids.numel() == tokens:
-            cos, sin = rot.cos_sin(pos_ids.reshape(-1))
+            cos, sin = _cos_sin_once(rot, pos_ids)
             period = tokens
         else:
             raise ValueError(f"pos_ids of shape {tuple(pos_ids.shape)} does not match q {tuple(q.shape)}")
