@@ -15,13 +15,14 @@ constexpr int kBlock = 128;
 __global__ void __launch_bounds__(kBlock)
 route_fwd_kernel(const float* __restrict__ logits, int T, int E, int k, int* __restrict__ topk_idx, float* __restrict__ topk_w,
                  float* __restrict__ probs, float* __restrict__ lse, int* __restrict__ counts, float* __restrict__ psum_partial) {
-  __shared__ float s_psum[kMaxExperts];
+  __shared__ float s_psum[kBlock / 32][kMaxExperts];  // one row per warp, summed in warp order below
   __shared__ int s_cnt[kMaxExperts];
-  for (int e = threadIdx.x; e < E; e += kBlock) { s_psum[e] = 0.f; s_cnt[e] = 0; }
+  for (int e = threadIdx.x; e < E; e += kBlock) s_cnt[e] = 0;
   __syncthreads();
   const int t = blockIdx.x * kBlock + threadIdx.x;
+  float p[kMaxExperts];
+  for (int e = 0; e < E; ++e) p[e] = 0.f;
   if (t < T) {
-    float p[kMaxExperts];
     const float* z = logits + static_cast<size_t>(t) * E;
     float mx = -INFINITY;
     for (int e = 0; e < E; ++e) { p[e] = z[e]; mx = fmaxf(mx, p[e]); }
@@ -32,7 +33,6 @@ route_fwd_kernel(const float* __restrict__ logits, int T, int E, int k, int* __r
     for (int e = 0; e < E; ++e) {
       p[e] *= inv;
       probs[static_cast<size_t>(t) * E + e] = p[e];
-      atomicAdd(&s_psum[e], p[e]);  // shared-memory partial; the cross-block sum below is ordered
     }
     // top-k by repeated selection (k <= 8, E <= 64); ties go to the lower expert index
     unsigned long long taken = 0ull;
@@ -55,9 +55,18 @@ route_fwd_kernel(const float* __restrict__ logits, int T, int E, int k, int* __r
       atomicAdd(&s_cnt[idx[j]], 1);
     }
   }
+  // probability sums: butterfly within the warp, then the warps in order, then (second kernel) the blocks in order
+  for (int e = 0; e < E; ++e) {
+    float v = p[e];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) s_psum[threadIdx.x >> 5][e] = v;
+  }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += kBlock) {
-    psum_partial[static_cast<size_t>(blockIdx.x) * E + e] = s_psum[e];
+    float v = 0.f;
+    for (int w = 0; w < kBlock / 32; ++w) v += s_psum[w][e];
+    psum_partial[static_cast<size_t>(blockIdx.x) * E + e] = v;
     if (s_cnt[e]) atomicAdd(&counts[e], s_cnt[e]);
   }
 }
