@@ -89,6 +89,9 @@ class GenerationResult:
     total_generated: int
 
 
+PREFILL_PAD = 256  # packed prefill tokens are padded to this multiple (two query tiles of the flash-attention kernel)
+
+
 class _DecodeGraph:
     """Static input/output buffers and the captured graph of one decode round."""
 
@@ -169,6 +172,12 @@ class InferenceEngine:
         self.request_queue: Deque[Request] = deque()
         self.results: Dict[int, Dict[int, DecodeResult]] = {}
         self._graph: Optional[_DecodeGraph] = None
+        try:
+            import inspect
+
+            self._decode_takes_rows = "logit_rows" in inspect.signature(model.decode).parameters
+        except (TypeError, ValueError):
+            self._decode_takes_rows = False
         self.stats: Dict[str, float] = {"prefill_tokens": 0, "prefill_seconds": 0.0, "decode_tokens": 0, "decode_seconds": 0.0}
 
     # -- construction -------------------------------------------------------------------------------------------
@@ -226,8 +235,13 @@ class InferenceEngine:
 
     # -- model calls ----------------------------------------------------------------------------------------------
     @torch.no_grad()
-    def _forward(self, tokens: torch.Tensor, binfo: PageBatchInfo, pos: torch.Tensor) -> torch.Tensor:
-        logits, cache = self.model.decode(tokens, self.gen_state.cache, binfo, pos)
+    def _forward(self, tokens: torch.Tensor, binfo: PageBatchInfo, pos: torch.Tensor, logit_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if logit_rows is not None and self._decode_takes_rows:
+            logits, cache = self.model.decode(tokens, self.gen_state.cache, binfo, pos, logit_rows=logit_rows)
+        else:
+            logits, cache = self.model.decode(tokens, self.gen_state.cache, binfo, pos)
+            if logit_rows is not None:
+                logits = logits.index_select(0, logit_rows)
         self.gen_state.cache = cache
         return logits
 
@@ -333,26 +347,35 @@ class InferenceEngine:
             slots += [s] * len(prompt)
             pos += list(range(len(prompt)))
             primary.append((r, s))
-        ds.page_table, binfo = ds.page_table.allocate_for_seq(np.asarray(slots, np.int32), np.asarray(pos, np.int32))
+        # every sequence of a prefill starts at position 0: attention runs densely over the packed tokens, one segment per
+        # prompt; pad the packed length to the attention kernel's tile (padding: no slot, no page, segment -1)
+        seg = [i for i, r in enumerate(batch) for _ in range(max(len(r.prompt_tokens), 1))]
+        pad = (-len(toks)) % PREFILL_PAD
+        slots_np = np.asarray(slots + [INVALID] * pad, np.int32)
+        pos_alloc = np.asarray(pos + [INVALID] * pad, np.int32)
+        ds.page_table, binfo = ds.page_table.allocate_for_seq(slots_np, pos_alloc)
+        binfo = dataclasses.replace(binfo, prefill_segment_ids=torch.tensor(seg + [-1] * pad, dtype=torch.int32))
         dev = self.device
-        logits = self._forward(torch.tensor(toks, dtype=torch.int32, device=dev), binfo.to(dev), torch.tensor(pos, dtype=torch.int32, device=dev))
         # the last prompt token of each sequence predicts its first new token; clones sample the same row with their own key
         last_index, cursor = {}, 0
         for r, s in primary:
             cursor += max(len(r.prompt_tokens), 1)
             last_index[s] = cursor - 1
-        rows, row_slots = [], []
+        # one logits row per generation: the primary and each of its clones read the row of the prompt's last token
+        rows = [last_index[s] for r, s in primary for _ in range(r.n_generations)]
+        logits = self._forward(torch.tensor(toks + [0] * pad, dtype=torch.int32, device=dev), binfo.to(dev),
+                               torch.tensor(pos + [0] * pad, dtype=torch.int32, device=dev), torch.tensor(rows, dtype=torch.long, device=dev))
+        # clones are made after the forward pass: they copy pages that the pass has just filled
+        row_slots = []
         for r, s in primary:
-            rows.append(last_index[s])
             row_slots.append(s)
             for k in range(1, r.n_generations):
                 c = self._take_slot()
                 self._clone(s, c, r, k)
-                rows.append(last_index[s])
                 row_slots.append(c)
         row_slots_np = np.asarray(row_slots, np.int32)
         sample_pos = ds.seq_lens[row_slots_np]
-        tokens, lps = self._sample(logits[torch.tensor(rows, device=logits.device)], row_slots_np, sample_pos)
+        tokens, lps = self._sample(logits, row_slots_np, sample_pos)
         ds.update_tokens(tokens, row_slots_np, lps, len(row_slots_np))
         self._ingest(tokens, row_slots_np, lps)
 

@@ -67,6 +67,10 @@ class PageBatchInfo:
     num_seqs: torch.Tensor  # i32[]
     new_token_dests: torch.Tensor  # i32[position]: page * page_size + slot of every packed token, or INVALID
     page_size: int
+    prefill_segment_ids: Optional[torch.Tensor] = None
+    """i32[position], set only when every packed sequence starts at position 0 (a pure prefill): the index of the sequence each
+    token belongs to, -1 for padding.  Attention then needs no cached context and can run as dense causal attention over the
+    packed tokens with these segment ids."""
 
     def pages_and_slots(self) -> Tuple[torch.Tensor, torch.Tensor]:
         d = self.new_token_dests
@@ -77,7 +81,8 @@ class PageBatchInfo:
     def to(self, device, non_blocking: bool = True) -> "PageBatchInfo":
         mv = lambda t: t.to(device, non_blocking=non_blocking)  # noqa: E731
         return PageBatchInfo(mv(self.slot_ids), mv(self.page_indices), mv(self.seq_lens), mv(self.cu_q_lens), mv(self.num_seqs),
-                             mv(self.new_token_dests), self.page_size)
+                             mv(self.new_token_dests), self.page_size,
+                             None if self.prefill_segment_ids is None else mv(self.prefill_segment_ids))
 
 
 @dataclass

@@ -440,9 +440,17 @@ class Attention(nn.Module):
         q, k, v = self._compute_qkv(x, pos_ids)
         kv_cache = kv_cache.update(batch_info, k, v)
         scale = c.scaling_factor if c.scaling_factor is not None else 1.0 / math.sqrt(c.head_size)
-        out = PA.ragged_paged_attention(q, kv_cache.kv_pages, batch_info.seq_lens, batch_info.page_indices,
-                                        batch_info.cu_q_lens, batch_info.num_seqs, sm_scale=scale,
-                                        soft_cap=c.logits_soft_cap)
+        seg = getattr(batch_info, "prefill_segment_ids", None)
+        if seg is not None and x.is_cuda:
+            # pure prefill: nothing to read from the cache, so this is causal attention over the packed tokens with one segment
+            # per sequence (the flash kernel), instead of the decode kernel walking pages
+            m = AttentionMask.causal(sliding_window=c.sliding_window).with_segment_ids(seg.unsqueeze(0))
+            out = dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), m, attn_backend=c.attn_backend,
+                                        logits_soft_cap=c.logits_soft_cap, scaling_factor=c.scaling_factor, inference=True).squeeze(0)
+        else:
+            out = PA.ragged_paged_attention(q, kv_cache.kv_pages, batch_info.seq_lens, batch_info.page_indices,
+                                            batch_info.cu_q_lens, batch_info.num_seqs, sm_scale=scale,
+                                            soft_cap=c.logits_soft_cap)
         out = out.reshape(x.shape[0], self.local_heads * c.head_size).to(x.dtype)
         if residual is not None:
             if type(self.o_proj) is Linear:

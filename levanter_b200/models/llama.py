@@ -336,10 +336,13 @@ class LlamaLMHeadModel(LmHeadModel):
             device = next(self.parameters()).device
         return self.transformer.initial_cache(max_pages, page_size, dtype=dtype, device=device)
 
-    def decode(self, input_ids: torch.Tensor, kv_cache, batch_info, pos_ids: torch.Tensor):
-        """Logits for packed tokens ``[T]`` given the paged KV cache (src/levanter/models/llama.py:589-634)."""
+    def decode(self, input_ids: torch.Tensor, kv_cache, batch_info, pos_ids: torch.Tensor, logit_rows: Optional[torch.Tensor] = None):
+        """Logits for packed tokens ``[T]`` given the paged KV cache (src/levanter/models/llama.py:589-634); with
+        ``logit_rows`` only for those token rows (a prefill needs the last token of every prompt, not ``T x vocab`` logits)."""
         x = self.embeddings.embed(input_ids)
         x, kv_cache = self.transformer.decode(x, kv_cache, batch_info, pos_ids)
+        if logit_rows is not None:
+            x = x.index_select(0, logit_rows)
         head = self.get_lm_head()
         logits = torch.nn.functional.linear(x, head.to(x.dtype))
         return logits, kv_cache
