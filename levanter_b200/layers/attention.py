@@ -267,7 +267,15 @@ def dot_product_attention(q, k, v, mask: Union[None, torch.Tensor, AttentionMask
             return KFA.flash_attention(q, k, v, mask, logits_soft_cap=logits_soft_cap, scaling_factor=scaling_factor)
         if backend == AttentionBackend.B200:
             raise ValueError("the B200 flash-attention kernel does not support this call (bias, dropout, explicit mask, dtype or head size)")
-        backend = AttentionBackend.TORCH_FLASH if q.shape[1] > 1 else AttentionBackend.VANILLA
+        plain = mask is None or (isinstance(mask, AttentionMask) and mask.explicit_mask is None and mask.segment_ids is None
+                                 and mask.sliding_window is None and _structured_only(mask))
+        if q.is_cuda and plain and bias is None and no_drop and logits_soft_cap is None and q.dtype in (torch.bfloat16, torch.float16) \
+                and q.shape[1] == k.shape[1]:
+            # shapes the tcgen05 kernel does not cover yet (head sizes other than 128): the library's fused attention rather
+            # than the blockwise PyTorch loop
+            backend = AttentionBackend.SDPA
+        else:
+            backend = AttentionBackend.TORCH_FLASH if q.shape[1] > 1 else AttentionBackend.VANILLA
 
     if backend == AttentionBackend.SDPA and bias is None and no_drop and logits_soft_cap is None:
         B, Sq, H, D = q.shape

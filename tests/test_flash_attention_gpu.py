@@ -102,3 +102,20 @@ def test_deterministic_forward():
     a = flash_attention_cuda(q, k, v, AttentionMask.causal()).clone()
     b = flash_attention_cuda(q, k, v, AttentionMask.causal())
     assert torch.equal(a, b)
+
+
+def test_head_sizes_the_kernel_does_not_cover_take_the_fused_library_path():
+    """Head size 64 (GPT-2) on CUDA: same numbers as the plain implementation, with and without grouped-query heads."""
+    import math
+
+    from levanter_b200.layers.attention import AttentionMask, dot_product_attention, simple_attention_with_dropout
+
+    torch.manual_seed(0)
+    for Hq, Hkv in ((4, 4), (4, 2)):
+        q = torch.randn(2, 256, Hq, 64, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(2, 256, Hkv, 64, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(2, 256, Hkv, 64, device="cuda", dtype=torch.bfloat16)
+        for mask in (AttentionMask.causal(), None):
+            out = dot_product_attention(q, k, v, mask)
+            ref = simple_attention_with_dropout(q.float(), k.float(), v.float(), mask)
+            assert (out.float() - ref).abs().max().item() < 2e-2
