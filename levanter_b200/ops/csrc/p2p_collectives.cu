@@ -313,3 +313,99 @@ extern "C" int lvb_flag_wait_probe(const int* flag, int target, unsigned long lo
   flag_wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, target, limit_ns, sys_scope, result, status);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// All-reduce of a symmetric buffer in place (tensor-parallel activations): rank r reduces elements [r * n / world, ...) and
+// publishes them to every rank.  The caller orders the ranks around the launch (inputs complete before, results read after).
+//   multicast: one multimem.ld_reduce (the switch adds the copies) and one multimem.st (the switch writes every copy).
+//   peer pointers: loads from every rank's copy, stores to every rank's copy.
+namespace lvb {
+namespace p2p {
+
+__global__ void __launch_bounds__(kBlock)
+mm_all_reduce_bf16_kernel(__nv_bfloat16* mc, long long off8, long long n8) {
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * kBlock) {
+    __nv_bfloat16* a = mc + (off8 + i) * 8;
+    uint32_t r0, r1, r2, r3;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "l"(a)
+                 : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+                 : "memory");
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+mm_all_reduce_f32_kernel(float* mc, long long off4, long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n4; i += static_cast<long long>(gridDim.x) * kBlock) {
+    float* a = mc + (off4 + i) * 4;
+    const float4 s = multimem_ld_reduce_add(a);
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(s.x), "f"(s.y), "f"(s.z), "f"(s.w) : "memory");
+  }
+}
+
+struct PeerBufs {
+  void* p[8];
+};
+
+__global__ void __launch_bounds__(kBlock)
+p2p_all_reduce_bf16_kernel(PeerBufs bufs, int world, long long off8, long long n8) {
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * kBlock) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const uint4 w = reinterpret_cast<const uint4*>(bufs.p[r])[off8 + i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint4*>(bufs.p[r])[off8 + i] = o;
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+p2p_all_reduce_f32_kernel(PeerBufs bufs, int world, long long off4, long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n4; i += static_cast<long long>(gridDim.x) * kBlock) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = reinterpret_cast<const float4*>(bufs.p[r])[off4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    for (int r = 0; r < world; ++r) reinterpret_cast<float4*>(bufs.p[r])[off4 + i] = acc;
+  }
+}
+
+}  // namespace p2p
+}  // namespace lvb
+
+// n elements (bf16: is_f32 = 0, a multiple of 8 * world; fp32: a multiple of 4 * world) at the start of the symmetric buffer.
+// mc: this rank's multicast address of the buffer, or null to use the peer pointers.
+extern "C" int lvb_all_reduce_symmetric(void* mc, void* const* peers, int rank, int world, long long n, int is_f32, void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  const int vec = is_f32 ? 4 : 8;
+  if (world <= 0 || world > 8 || rank < 0 || rank >= world || n <= 0 || (n % (static_cast<long long>(vec) * world)) != 0) return kErrBadArg;
+  if (mc == nullptr && peers == nullptr) return kErrBadArg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long per = n / world / vec;  // vectors in this rank's slice
+  const long long off = per * rank;
+  const int grid = grid_for(per);
+  if (mc != nullptr) {
+    if (reinterpret_cast<uintptr_t>(mc) & 15) return kErrBadArg;
+    if (is_f32) mm_all_reduce_f32_kernel<<<grid, kBlock, 0, s>>>(reinterpret_cast<float*>(mc), off, per);
+    else mm_all_reduce_bf16_kernel<<<grid, kBlock, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(mc), off, per);
+  } else {
+    PeerBufs b;
+    for (int r = 0; r < 8; ++r) b.p[r] = peers[r < world ? r : 0];
+    if (is_f32) p2p_all_reduce_f32_kernel<<<grid, kBlock, 0, s>>>(b, world, off, per);
+    else p2p_all_reduce_bf16_kernel<<<grid, kBlock, 0, s>>>(b, world, off, per);
+  }
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}

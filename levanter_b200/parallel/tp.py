@@ -3,10 +3,15 @@
 The reference gets TP from axis names (``tensor_parallel_axes: [mlp, heads]`` mapped to the ``model`` mesh axis,
 src/levanter/trainer.py:677,851-855) and lets XLA insert the collectives.  Here the column-parallel side (q/k/v,
 gate/up) needs no forward communication and an all-reduce of the input gradient; the row-parallel side (o_proj,
-down_proj) all-reduces its forward output.  This NCCL path is the baseline and oracle; ``parallel.fused`` supplies the
-kernels that overlap these collectives with the GEMMs."""
+down_proj) all-reduces its forward output.
+
+The all-reduce itself runs on this library's kernels when the model axis lives on one NVSwitch node: the tensor is staged
+in a symmetric buffer and reduced in place, by ``multimem.ld_reduce`` / ``multimem.st`` through the switch or by peer loads
+and stores (``ops/csrc/p2p_collectives.cu``); ``LEVANTER_B200_TP_COMM=nccl`` (or a CPU group) keeps NCCL / gloo, which is
+also the oracle in the tests.  ``ops.fused_tp`` has the GEMMs with the collective fused in."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -15,23 +20,19 @@ import torch.distributed as dist
 
 class _CopyToRegion(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, group):
-        ctx.group = group
+    def forward(ctx, x, tp):
+        ctx.tp = tp
         return x
 
     @staticmethod
     def backward(ctx, g):
-        g = g.contiguous()
-        dist.all_reduce(g, group=ctx.group)
-        return g, None
+        return ctx.tp.all_reduce(g.contiguous()), None
 
 
 class _ReduceFromRegion(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, group):
-        x = x.contiguous()
-        dist.all_reduce(x, group=group)
-        return x
+    def forward(ctx, x, tp):
+        return tp.all_reduce(x.contiguous())
 
     @staticmethod
     def backward(ctx, g):
@@ -39,10 +40,14 @@ class _ReduceFromRegion(torch.autograd.Function):
 
 
 class TensorParallel:
-    def __init__(self, group: Optional[dist.ProcessGroup], size: int, rank: int):
+    def __init__(self, group: Optional[dist.ProcessGroup], size: int, rank: int, comm: Optional[str] = None):
         self.group = group
         self.size = size
         self.rank = rank
+        self.comm = (comm or os.environ.get("LEVANTER_B200_TP_COMM", "auto")).lower()  # auto | multimem | p2p | nccl
+        self._sym = None          # symmetric staging buffer (bytes), grown on demand by every rank at the same call
+        self._sym_failed = False
+        self.kernel_all_reduces = 0
 
     @staticmethod
     def from_mesh(mesh) -> Optional["TensorParallel"]:
@@ -52,14 +57,62 @@ class TensorParallel:
         return TensorParallel(ax.group, ax.size, ax.rank)
 
     def copy_to_region(self, x: torch.Tensor) -> torch.Tensor:
-        return _CopyToRegion.apply(x, self.group)
+        return _CopyToRegion.apply(x, self)
 
     def reduce_from_region(self, x: torch.Tensor) -> torch.Tensor:
-        return _ReduceFromRegion.apply(x, self.group)
+        return _ReduceFromRegion.apply(x, self)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of ``x`` over the model axis, in place when possible."""
         x = x.contiguous()
+        if self._kernel_path_ok(x):
+            try:
+                return self._kernel_all_reduce(x)
+            except Exception:  # noqa: BLE001  (no symmetric memory on this fabric, allocation failure): NCCL from now on
+                if self.comm in ("multimem", "p2p"):
+                    raise
+                self._sym_failed = True
         dist.all_reduce(x, group=self.group)
+        return x
+
+    # -- own kernels over symmetric memory -----------------------------------------------------------------------
+    def _kernel_path_ok(self, x: torch.Tensor) -> bool:
+        if self.comm == "nccl" or self._sym_failed or not x.is_cuda or self.size <= 1 or self.size > 8:
+            return False
+        if x.dtype not in (torch.bfloat16, torch.float32):
+            return False
+        from ..ops import lib
+
+        return lib.available()
+
+    def _kernel_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        from ..ops import lib
+        from .symm import SymmetricBuffer
+
+        es = x.element_size()
+        vec = (16 // es) * self.size
+        n = x.numel()
+        n_pad = -(-n // vec) * vec
+        need = n_pad * es
+        if self._sym is None or self._sym.tensor.numel() < need:
+            # every rank reaches this line at the same call with the same size, so the rendezvous inside is collective
+            self._sym = SymmetricBuffer(max(need, 64 << 20), torch.uint8, x.device, self.group)
+        sym = self._sym
+        stage = sym.tensor[:need].view(x.dtype)
+        stage[:n].copy_(x.reshape(-1))
+        if n_pad > n:
+            stage[n:].zero_()
+        use_mc = sym.multicast_ptr != 0 and self.comm != "p2p"
+        if self.comm == "multimem" and not use_mc:
+            raise RuntimeError("no multicast mapping on this fabric")
+        c = lib
+        f = lib.fn("lvb_all_reduce_symmetric", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_longlong, c.c_int, c.c_void_p])
+        sym.barrier(0)  # every rank's input is staged
+        rc = f(sym.multicast_ptr if use_mc else 0, sym.c_ptrs, sym.rank, self.size, n_pad, 1 if x.dtype == torch.float32 else 0, lib.stream_ptr())
+        lib.check_rc(rc, "lvb_all_reduce_symmetric")
+        sym.barrier(1)  # every rank's slice has been published
+        x.reshape(-1).copy_(stage[:n])
+        self.kernel_all_reduces += 1
         return x
 
     def all_gather_last_dim(self, x: torch.Tensor) -> torch.Tensor:

