@@ -95,8 +95,18 @@ class TensorParallel:
         n_pad = -(-n // vec) * vec
         need = n_pad * es
         if self._sym is None or self._sym.tensor.numel() < need:
-            # every rank reaches this line at the same call with the same size, so the rendezvous inside is collective
-            self._sym = SymmetricBuffer(max(need, 64 << 20), torch.uint8, x.device, self.group)
+            # every rank reaches this line at the same call with the same size, so the rendezvous inside is collective; the
+            # ranks then agree (over NCCL) that all of them got their buffer, so that no rank is left alone on either path
+            try:
+                sym_new = SymmetricBuffer(max(need, 64 << 20), torch.uint8, x.device, self.group)
+                ok = 1
+            except Exception:  # noqa: BLE001
+                sym_new, ok = None, 0
+            flag = torch.tensor([ok], device=x.device, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            if int(flag.item()) == 0:
+                raise RuntimeError("symmetric memory is not available on every rank of the model axis")
+            self._sym = sym_new
         sym = self._sym
         stage = sym.tensor[:need].view(x.dtype)
         stage[:n].copy_(x.reshape(-1))
