@@ -409,3 +409,88 @@ extern "C" int lvb_all_reduce_symmetric(void* mc, void* const* peers, int rank, 
   }
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One-shot all-reduce for small tensors (decode-size activations) in ONE launch: every rank pushes its input into slot
+// `rank` of every rank's staging area, bumps an arrival counter there, waits (bounded) until all `world` slots of its own
+// area have arrived and sums them.  Two areas used alternately and counters that only grow make a barrier between calls
+// unnecessary: a rank can be at most one call ahead of its slowest peer, because its own call completes only when every
+// peer's push of that call has arrived.  Latency is one NVLink round trip instead of several launches.
+namespace lvb {
+namespace p2p {
+
+struct OneShotArgs {
+  unsigned char* stage[8];  // rank r's staging area for this call's parity: [world][cap_bytes]
+  int* flags[8];            // rank r's arrival counters for this call's parity: [world]
+};
+
+
+__global__ void __launch_bounds__(kBlock)
+one_shot_all_reduce_kernel(OneShotArgs a, const uint4* __restrict__ in, uint4* __restrict__ out, long long n16, long long cap16,
+                           int rank, int world, int target, int is_f32, int* status) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  // push: this block's share of the input into slot `rank` of every rank's area
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n16; i += static_cast<long long>(gridDim.x) * kBlock) {
+    const uint4 v = in[i];
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint4*>(a.stage[r])[rank * cap16 + i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < world; ++r) red_release_sys_add(a.flags[r] + rank, 1);
+    // wait until every rank's blocks have all pushed into this rank's area
+    for (int r = 0; r < world && !s_abort; ++r)
+      flag_wait_ge(a.flags[rank] + r, target, true, &s_abort, status, 700, r);
+  }
+  __syncthreads();
+  if (s_abort) return;
+  const uint4* mine = reinterpret_cast<const uint4*>(a.stage[rank]);
+  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n16; i += static_cast<long long>(gridDim.x) * kBlock) {
+    if (is_f32) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const uint4 w = __ldcg(mine + r * cap16 + i);
+        acc.x += __uint_as_float(w.x); acc.y += __uint_as_float(w.y); acc.z += __uint_as_float(w.z); acc.w += __uint_as_float(w.w);
+      }
+      out[i] = make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z), __float_as_uint(acc.w));
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < world; ++r) {
+        const uint4 w = __ldcg(mine + r * cap16 + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      out[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
+}  // namespace p2p
+}  // namespace lvb
+
+// in/out: local tensors of `bytes` bytes (a multiple of 16, at most cap_bytes); may be the same tensor.
+// stage[r] / flags[r]: rank r's staging area ([world][cap_bytes]) and arrival counters ([world] ints) of this call's parity.
+// target: blocks * (number of calls, this one included, that have used this parity); blocks: the grid size, equal on every rank.
+extern "C" int lvb_all_reduce_one_shot(const void* in, void* out, void* const* stage, int* const* flags, int rank, int world,
+                                       long long bytes, long long cap_bytes, int blocks, int target, int is_f32, int* status,
+                                       void* stream) {
+  using namespace lvb;
+  using namespace lvb::p2p;
+  if (world <= 0 || world > 8 || rank < 0 || rank >= world || bytes <= 0 || (bytes & 15) || bytes > cap_bytes || (cap_bytes & 15) ||
+      blocks <= 0 || blocks > num_sms())
+    return kErrBadArg;
+  OneShotArgs a;
+  for (int r = 0; r < 8; ++r) {
+    a.stage[r] = reinterpret_cast<unsigned char*>(stage[r < world ? r : 0]);
+    a.flags[r] = flags[r < world ? r : 0];
+  }
+  one_shot_all_reduce_kernel<<<blocks, kBlock, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      a, reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), bytes / 16, cap_bytes / 16, rank, world, target, is_f32, status);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}

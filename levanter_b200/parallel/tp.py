@@ -11,11 +11,19 @@ and stores (``ops/csrc/p2p_collectives.cu``); ``LEVANTER_B200_TP_COMM=nccl`` (or
 also the oracle in the tests.  ``ops.fused_tp`` has the GEMMs with the collective fused in."""
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
 import torch
 import torch.distributed as dist
+
+
+ONE_SHOT_MAX_BYTES = 2 << 20  # tensors up to this size take the single-launch all-reduce
+
+
+class _UseNccl(Exception):
+    pass
 
 
 class _CopyToRegion(torch.autograd.Function):
@@ -45,6 +53,8 @@ class TensorParallel:
         self.size = size
         self.rank = rank
         self.comm = (comm or os.environ.get("LEVANTER_B200_TP_COMM", "auto")).lower()  # auto | multimem | p2p | nccl
+        self._os = None           # symmetric areas + counters of the one-shot kernel
+        self._os_calls = 0
         self._sym = None          # symmetric staging buffer (bytes), grown on demand by every rank at the same call
         self._sym_failed = False
         self.kernel_all_reduces = 0
@@ -67,7 +77,14 @@ class TensorParallel:
         x = x.contiguous()
         if self._kernel_path_ok(x):
             try:
+                nbytes = x.numel() * x.element_size()
+                if nbytes <= ONE_SHOT_MAX_BYTES and nbytes % 16 == 0 and self.comm in ("auto", "p2p", "multimem"):
+                    return self._one_shot_all_reduce(x)
+                if self.comm == "auto":
+                    raise _UseNccl()  # large tensors: NCCL measured faster than the staged two-shot kernels (2 GPUs)
                 return self._kernel_all_reduce(x)
+            except _UseNccl:
+                pass
             except Exception:  # noqa: BLE001  (no symmetric memory on this fabric, allocation failure): NCCL from now on
                 if self.comm in ("multimem", "p2p"):
                     raise
@@ -76,6 +93,46 @@ class TensorParallel:
         return x
 
     # -- own kernels over symmetric memory -----------------------------------------------------------------------
+    def _agree(self, ok: bool, device) -> None:
+        """All ranks got their buffer, or none uses the kernel path (decided over NCCL so that no rank is left alone)."""
+        flag = torch.tensor([1 if ok else 0], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            raise RuntimeError("symmetric memory is not available on every rank of the model axis")
+
+    def _one_shot_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Small tensors (decode-size activations): one launch, push to every peer + arrival counters (see the kernel)."""
+        from ..ops import lib
+        from .symm import SymmetricBuffer
+
+        W, cap = self.size, ONE_SHOT_MAX_BYTES
+        area = W * cap
+        if self._os is None:
+            try:
+                buf = SymmetricBuffer(2 * area + 2 * 64 * 4, torch.uint8, x.device, self.group)  # zeroed: counters start at 0
+                ok = True
+            except Exception:  # noqa: BLE001
+                buf, ok = None, False
+            self._agree(ok, x.device)
+            buf.barrier(0)  # nobody pushes into an area whose counters are not cleared yet
+            self._os, self._os_calls = buf, 0
+        sym = self._os
+        n = self._os_calls
+        self._os_calls = n + 1
+        parity, uses = n & 1, n // 2 + 1
+        nbytes = x.numel() * x.element_size()
+        blocks = max(1, min(torch.cuda.get_device_properties(x.device).multi_processor_count, -(-(nbytes // 16) // 256)))
+        stage = (ctypes.c_void_p * W)(*[p + parity * area for p in sym.peer_ptrs])
+        flags = (ctypes.c_void_p * W)(*[p + 2 * area + parity * 64 * 4 for p in sym.peer_ptrs])
+        c = lib
+        f = lib.fn("lvb_all_reduce_one_shot", [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_longlong, c.c_longlong,
+                                               c.c_int, c.c_int, c.c_int, c.c_void_p, c.c_void_p])
+        rc = f(x.data_ptr(), x.data_ptr(), stage, flags, sym.rank, W, nbytes, cap, blocks, blocks * uses,
+               1 if x.dtype == torch.float32 else 0, lib.status_buffer().data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_all_reduce_one_shot")
+        self.kernel_all_reduces += 1
+        return x
+
     def _kernel_path_ok(self, x: torch.Tensor) -> bool:
         if self.comm == "nccl" or self._sym_failed or not x.is_cuda or self.size <= 1 or self.size > 8:
             return False

@@ -60,6 +60,19 @@ def _worker(rank, world, port, out_dir):
                 res["times"][f"{comm}/{label}"] = timeit(lambda: tp.all_reduce(x))
                 if comm == "p2p":
                     res["times"][f"nccl/{label}"] = timeit(lambda: dist.all_reduce(x))
+        # the default: one launch for small tensors, NCCL for large ones; many calls in a row exercise the alternating areas
+        tp = TensorParallel(dist.group.WORLD, world, rank)
+        for i in range(9):
+            x = torch.randn(64 * 4096 + 8 * i, device=dev, generator=torch.Generator(device=dev).manual_seed(100 * rank + i)).bfloat16()
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            got = tp.all_reduce(x.clone())
+            torch.cuda.synchronize()
+            res["errs"][f"auto/{i}"] = float((got.float() - ref).abs().max() / ref.abs().max())
+        assert tp.kernel_all_reduces == 9
+        big = torch.randn(8192 * 4096, device=dev).bfloat16()
+        tp.all_reduce(big)
+        assert tp.kernel_all_reduces == 9  # large tensors stay on NCCL by default
         lib.check_status()
         torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
