@@ -476,7 +476,8 @@ one_shot_all_reduce_kernel(OneShotArgs a, const uint4* __restrict__ in, uint4* _
 
 // in/out: local tensors of `bytes` bytes (a multiple of 16, at most cap_bytes); may be the same tensor.
 // stage[r] / flags[r]: rank r's staging area ([world][cap_bytes]) and arrival counters ([world] ints) of this call's parity.
-// target: blocks * (number of calls, this one included, that have used this parity); blocks: the grid size, equal on every rank.
+// blocks: the grid size, equal on every rank for a given call.  target: the sum of `blocks` over all calls, this one included,
+// that have used this parity (every block of a pusher adds one arrival to each counter).
 extern "C" int lvb_all_reduce_one_shot(const void* in, void* out, void* const* stage, int* const* flags, int rank, int world,
                                        long long bytes, long long cap_bytes, int blocks, int target, int is_f32, int* status,
                                        void* stream) {

@@ -115,11 +115,11 @@ class TensorParallel:
                 buf, ok = None, False
             self._agree(ok, x.device)
             buf.barrier(0)  # nobody pushes into an area whose counters are not cleared yet
-            self._os, self._os_calls = buf, 0
+            self._os, self._os_calls, self._os_arrivals = buf, 0, [0, 0]
         sym = self._os
         n = self._os_calls
         self._os_calls = n + 1
-        parity, uses = n & 1, n // 2 + 1
+        parity = n & 1
         nbytes = x.numel() * x.element_size()
         blocks = max(1, min(torch.cuda.get_device_properties(x.device).multi_processor_count, -(-(nbytes // 16) // 256)))
         stage = (ctypes.c_void_p * W)(*[p + parity * area for p in sym.peer_ptrs])
@@ -127,7 +127,9 @@ class TensorParallel:
         c = lib
         f = lib.fn("lvb_all_reduce_one_shot", [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_longlong, c.c_longlong,
                                                c.c_int, c.c_int, c.c_int, c.c_void_p, c.c_void_p])
-        rc = f(x.data_ptr(), x.data_ptr(), stage, flags, sym.rank, W, nbytes, cap, blocks, blocks * uses,
+        # the counters only grow: after this call each of them has received `blocks` more arrivals (one per block of the pusher)
+        self._os_arrivals[parity] += blocks
+        rc = f(x.data_ptr(), x.data_ptr(), stage, flags, sym.rank, W, nbytes, cap, blocks, self._os_arrivals[parity],
                1 if x.dtype == torch.float32 else 0, lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_all_reduce_one_shot")
         self.kernel_all_reduces += 1
