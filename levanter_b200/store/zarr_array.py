@@ -12,8 +12,10 @@ from __future__ import annotations
 import ctypes
 import itertools
 import json
-import math
 import os
+import threading
+import time
+import math
 import zlib
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
@@ -118,6 +120,23 @@ def _numpy_to_torch(a: np.ndarray, dtype_str: str) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a))
 
 
+def _write_json_atomically(fs, path: str, obj) -> None:
+    """Readers (a trainer reading a cache that is still being built) must never see a half-written metadata file: write a
+    sibling and rename it over the target; file systems without rename fall back to a plain write."""
+    tmp = f"{path}.tmp{os.getpid()}"
+    with fs.open(tmp, "w") as f:
+        json.dump(obj, f, indent=1)
+    try:
+        fs.mv(tmp, path)
+    except Exception:  # noqa: BLE001
+        with fs.open(path, "w") as f:
+            json.dump(obj, f, indent=1)
+        try:
+            fs.rm(tmp)
+        except Exception:  # noqa: BLE001
+            pass
+
+
 class ZarrArray:
     """One zarr-v2 array stored under ``path`` (any fsspec URL)."""
 
@@ -162,15 +181,22 @@ class ZarrArray:
         if overwrite and fs.exists(root):
             fs.rm(root, recursive=True)
         fs.makedirs(root, exist_ok=True)
-        with fs.open(f"{root}/.zarray", "w") as f:
-            json.dump(meta, f, indent=1)
+        _write_json_atomically(fs, f"{root}/.zarray", meta)
         return ZarrArray(path, meta)
 
     @staticmethod
     def open(path: str) -> "ZarrArray":
         fs, root = url_to_fs(path.rstrip("/"))
-        with fs.open(f"{root}/.zarray", "r") as f:
-            meta = json.load(f)
+        meta = None
+        for attempt in range(50):  # a writer on a file system without atomic rename may be in the middle of rewriting the file
+            try:
+                with fs.open(f"{root}/.zarray", "r") as f:
+                    meta = json.load(f)
+                break
+            except json.JSONDecodeError:
+                if attempt == 49:
+                    raise
+                time.sleep(0.01)
         if meta.get("zarr_format") != 2:
             raise NotImplementedError(f"zarr_format {meta.get('zarr_format')} is not supported")
         return ZarrArray(path, meta)
@@ -180,10 +206,24 @@ class ZarrArray:
         fs, root = url_to_fs(path.rstrip("/"))
         return fs.exists(f"{root}/.zarray")
 
+    def _write_chunk(self, key: str, blob: bytes) -> None:
+        """Chunk files are replaced, never rewritten in place: a concurrent reader sees the old chunk or the new one."""
+        tmp = f"{key}.tmp{os.getpid()}_{threading.get_ident()}"
+        with self.fs.open(tmp, "wb") as f:
+            f.write(blob)
+        try:
+            self.fs.mv(tmp, key)
+        except Exception:  # noqa: BLE001  (no rename on this file system)
+            with self.fs.open(key, "wb") as f:
+                f.write(blob)
+            try:
+                self.fs.rm(tmp)
+            except Exception:  # noqa: BLE001
+                pass
+
     def _write_meta(self):
         self.meta["shape"] = list(self.shape)
-        with self.fs.open(f"{self.root}/.zarray", "w") as f:
-            json.dump(self.meta, f, indent=1)
+        _write_json_atomically(self.fs, f"{self.root}/.zarray", self.meta)
 
     # -- chunk helpers -----------------------------------------------------------------------------------------
     def _chunk_key(self, idx: Tuple[int, ...]) -> str:
@@ -268,8 +308,7 @@ class ZarrArray:
             data = data.astype(self.np_dtype)
         if nd == 0:
             blob = self._encode([data.reshape(1)])[0]
-            with self.fs.open(self._chunk_key(()), "wb") as f:
-                f.write(blob)
+            self._write_chunk(self._chunk_key(()), blob)
             return
         lo = [0] * nd if lo is None else list(lo)
         hi = [l + s for l, s in zip(lo, data.shape)]
@@ -294,8 +333,7 @@ class ZarrArray:
             chunks_out.append(chunk)
         blobs = self._encode(chunks_out)
         for idx, blob in zip(idxs, blobs):
-            with self.fs.open(self._chunk_key(idx), "wb") as f:
-                f.write(blob)
+            self._write_chunk(self._chunk_key(idx), blob)
 
     def resize(self, new_shape: Sequence[int]) -> None:
         self.shape = tuple(int(s) for s in new_shape)
