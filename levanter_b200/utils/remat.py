@@ -86,7 +86,9 @@ def checkpoint_layer(fn, *args, keep_attention: bool = True):
 
     if not torch.is_grad_enabled():
         return fn(*args)
-    if not keep_attention:
+    if not keep_attention or not any(isinstance(a, torch.Tensor) and a.requires_grad for a in args):
+        # (a custom autograd function only produces a differentiable output when one of its tensor inputs requires gradients;
+        # with frozen embeddings, as under LoRA, the first layer's input does not, although parameters inside the layer do)
         from torch.utils.checkpoint import checkpoint
 
         return checkpoint(fn, *args, use_reentrant=False)

@@ -66,3 +66,13 @@ def test_no_grad_pass_runs_directly():
     with torch.no_grad():
         y = checkpoint_layer(blk, torch.randn(2, 8))
     assert not y.requires_grad
+
+
+def test_input_without_gradient_but_trainable_parameters_inside():
+    """Frozen embeddings (LoRA): the layer input does not require gradients, the parameters inside the layer do."""
+    blk = _Block()
+    x = torch.randn(4, 8)  # requires_grad False
+    y = checkpoint_layer(blk, x)
+    assert y.requires_grad
+    y.sum().backward()
+    assert blk.a.weight.grad is not None
