@@ -25,6 +25,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..layers.normalization import LayerNormConfigBase, RmsNormConfig
 from ..nn import Embedding, Linear
+from ..ops.delta_rule import chunk_state_scan
 from ..utils.activation import ActivationFunctionEnum
 from ..utils.flop_utils import lm_flops_per_token
 from ..utils.remat import should_recompute
@@ -76,16 +77,13 @@ def delta_rule_chunked_scan(q, k, v, g, beta, chunk_size: int = 64, initial_stat
     T = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
     u = T @ vb  # values to write if the state entering the chunk were zero
     w = T @ (kb * g.exp()[..., None])  # what has to be corrected for the state entering the chunk
-    S = torch.zeros(B, H, dk, dv, device=q.device) if initial_state is None else initial_state.float().clone()
-    out = torch.empty(B, H, N, C, dv, device=q.device)
+    # the loop over chunks only carries the state; everything it consumes is formed here for all chunks at once
     strict_upper = torch.triu(torch.ones(C, C, dtype=torch.bool, device=q.device), diagonal=1)
-    for n in range(N):
-        qn, kn, gn = q[:, :, n], k[:, :, n], g[:, :, n]
-        v_new = u[:, :, n] - w[:, :, n] @ S
-        intra = ((qn @ kn.transpose(-1, -2)) * decay[:, :, n]).masked_fill(strict_upper, 0.0)
-        out[:, :, n] = (qn * gn.exp()[..., None]) @ S + intra @ v_new
-        g_last = gn[..., -1]
-        S = S * g_last.exp()[..., None, None] + (kn * (g_last[..., None] - gn).exp()[..., None]).transpose(-1, -2) @ v_new
+    scores = ((q @ k.transpose(-1, -2)) * decay).masked_fill(strict_upper, 0.0)
+    qg = q * g.exp()[..., None]
+    g_last = g[..., -1]
+    kd = k * (g_last[..., None] - g).exp()[..., None]
+    out, S = chunk_state_scan(w, qg, kd, scores, u, g_last.exp(), initial_state)
     out = out.reshape(B, H, N * C, dv)[:, :, :L]
     return out.to(dtype), S
 

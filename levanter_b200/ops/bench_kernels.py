@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -206,6 +206,46 @@ def main(argv=None):
         cfg = {"tokens": T, "experts": E, "top_k": k, "hidden": H, "mlp": M}
         _report("moe_mlp_grouped_fwd_bwd", cfg, ms_g, mn_g, flops=flops)
         return _report("moe_mlp_per_expert_loop_fwd_bwd", cfg, ms_l, mn_l, flops=flops)
+
+    if a.kernel == "delta_rule":
+        # the carried-state loop of the gated delta rule: one launch per direction against the same loop on framework ops
+        from .delta_rule import chunk_state_scan, chunk_state_scan_reference
+
+        B, H, N, C, dk, dv = a.batch, a.heads, a.seq // 64, 64, 128, 128
+        w, qg, kd = ((torch.randn(B, H, N, C, dk, device=dev) * 0.02).requires_grad_() for _ in range(3))
+        P = (torch.randn(B, H, N, C, C, device=dev) * 0.1).tril().requires_grad_()
+        u = torch.randn(B, H, N, C, dv, device=dev).requires_grad_()
+        dec = torch.rand(B, H, N, device=dev).mul(0.4).add(0.4).requires_grad_()  # contraction: the state stays bounded
+        cfg = {"batch": B, "heads": H, "seq": N * C, "d_k": dk, "d_v": dv}
+        per_chunk = 2.0 * C * dk * dv * 3 + 2.0 * C * C * dv  # w S, qg S, kd^T v_new, P v_new
+        flops = B * H * N * per_chunk
+        tile_bytes = 4.0 * B * H * N * (3 * C * dk + C * C + 2 * C * dv)
+
+        def fwd():
+            with torch.no_grad():
+                chunk_state_scan(w, qg, kd, P, u, dec)
+
+        def fwd_ops():
+            with torch.no_grad():
+                chunk_state_scan_reference(w, qg, kd, P, u, dec)
+
+        def fwd_bwd():
+            chunk_state_scan(w, qg, kd, P, u, dec)[0].sum().backward()
+
+        def fwd_bwd_ops():
+            chunk_state_scan_reference(w, qg, kd, P, u, dec)[0].sum().backward()
+
+        if a.once:
+            fwd(); fwd_bwd(); torch.cuda.synchronize()
+            return None
+        ms, mn = _time(fwd, a.iters, a.warmup, flush)
+        _report("delta_rule_scan_fwd", cfg, ms, mn, flops=flops, nbytes=tile_bytes)
+        ms, mn = _time(fwd_ops, max(a.iters // 4, 2), 2, flush)
+        _report("delta_rule_scan_fwd_framework_ops", cfg, ms, mn, flops=flops)
+        ms, mn = _time(fwd_bwd, a.iters, a.warmup, flush)
+        _report("delta_rule_scan_fwd_bwd", cfg, ms, mn, flops=3 * flops)
+        ms, mn = _time(fwd_bwd_ops, max(a.iters // 4, 2), 2, flush)
+        return _report("delta_rule_scan_fwd_bwd_framework_ops", cfg, ms, mn, flops=3 * flops)
 
     if a.kernel == "sampler":
         from ..layers.sampler import Sampler
