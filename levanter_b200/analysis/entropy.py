@@ -15,7 +15,11 @@ logger = logging.getLogger(__name__)
 
 
 def entropy_from_logits(logits: torch.Tensor, axis: int = -1) -> torch.Tensor:
-    """``H = logsumexp(z) - sum(softmax(z) * z)`` in fp32."""
+    """``H = logsumexp(z) - sum(softmax(z) * z)`` in fp32 (one streaming pass over the logits on a B200)."""
+    if logits.is_cuda and axis in (-1, logits.dim() - 1):
+        from ..ops.analysis_kernels import entropy_top2
+
+        return entropy_top2(logits)[0]
     z = logits.float()
     lse = torch.logsumexp(z, dim=axis, keepdim=True)
     p = torch.exp(z - lse)
@@ -24,6 +28,10 @@ def entropy_from_logits(logits: torch.Tensor, axis: int = -1) -> torch.Tensor:
 
 def top2_gap_from_logits(logits: torch.Tensor, axis: int = -1) -> torch.Tensor:
     """Difference between the largest and the second largest logit."""
+    if logits.is_cuda and axis in (-1, logits.dim() - 1):
+        from ..ops.analysis_kernels import entropy_top2
+
+        return entropy_top2(logits)[1]
     top = torch.topk(logits.float(), 2, dim=axis).values
     a, b = top.unbind(dim=axis)
     return a - b

@@ -26,6 +26,7 @@ from torch.utils.checkpoint import checkpoint
 from ..layers.normalization import LayerNormConfigBase, RmsNormConfig
 from ..nn import Embedding, Linear
 from ..ops.delta_rule import chunk_state_scan
+from ..ops.dwconv import causal_dwconv
 from ..utils.activation import ActivationFunctionEnum
 from ..utils.flop_utils import lm_flops_per_token
 from ..utils.remat import should_recompute
@@ -164,9 +165,8 @@ class GatedDeltaNetLayer(nn.Module):
             p._no_weight_decay = True
 
     def _conv(self, conv: nn.Conv1d, x: torch.Tensor) -> torch.Tensor:
-        L = x.shape[1]
-        y = conv(x.transpose(1, 2).to(conv.weight.dtype))[..., :L].transpose(1, 2)
-        return F.silu(y).to(x.dtype)
+        # depthwise causal filter + SiLU over [B, L, C]; one kernel per direction on CUDA, conv1d between transposes elsewhere
+        return causal_dwconv(x, conv.weight, conv.bias, silu=True)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         c = self.config

@@ -180,7 +180,9 @@ class HyenaOperator(nn.Module):
         B, L, _ = u.shape
         l_filter = min(L, c.seq_len)
         u = self.in_proj(u)
-        uc = self.short_filter(u.transpose(1, 2).to(self.short_filter.weight.dtype))[..., :l_filter].transpose(1, 2).to(u.dtype)
+        from ..ops.dwconv import causal_dwconv
+
+        uc = causal_dwconv(u, self.short_filter.weight, self.short_filter.bias)[:, :l_filter]  # causal: truncation commutes
         nb = c.num_blocks if l_filter == c.seq_len else 1
         per = l_filter // nb
         # [B, blocks, pos, heads, (order + 1), head_size]

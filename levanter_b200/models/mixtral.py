@@ -44,6 +44,7 @@ class MixtralConfig(MistralConfig):
     flash_attention_block_size: Optional[int] = 2048
     reference_checkpoint: str = "mistralai/Mixtral-8x7B-v0.1"
     expert_parallel: bool = False  # shard experts over the data axis and route tokens by all-to-all
+    expert_capacity_factor: float = 2.0  # rows an expert-parallel rank can receive, relative to a balanced load of T * k
 
     hf_model_type = "mixtral"
     hf_architecture = "MixtralForCausalLM"
@@ -140,10 +141,16 @@ class MixtralSparseMoeBlock(nn.Module):
         topk_w, topk_idx, group_sizes, p_sum, lse = moe_route(router_logits, k)
         flat_idx = topk_idx.reshape(-1)
         if self.ep is not None and self.ep.size > 1:
-            from ..parallel.expert import dispatch_combine
+            from ..parallel.expert import dispatch_combine, dispatch_combine_peer
 
             sort_idx = torch.argsort(flat_idx, stable=True)
-            out_repeat = dispatch_combine(self.ep, x_flat, sort_idx, group_sizes, k, self.experts)
+            # own kernels over peer memory where the ranks share a node (permutation and exchange in one launch per direction,
+            # no host read-back); otherwise all-to-all through the collective library
+            ex = self.ep.peer_exchange(E, shape[-1], T * k, x_flat.dtype, c.expert_capacity_factor) if x_flat.is_cuda else None
+            if ex is not None:
+                out_repeat = dispatch_combine_peer(ex, x_flat, sort_idx, group_sizes, k, self.experts)
+            else:
+                out_repeat = dispatch_combine(self.ep, x_flat, sort_idx, group_sizes, k, self.experts)
         elif x_flat.is_cuda:
             # one grouped launch per projection over a padded expert-sorted layout; nothing is read back by the host
             from ..ops.moe import grouped_mlp_padded

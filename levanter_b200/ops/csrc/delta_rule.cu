@@ -88,6 +88,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_newest() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // rows x COLS fp32 from global (row stride src_ld floats, 16-byte aligned rows) into shared memory (row stride ld floats)
 template <int COLS>
@@ -118,7 +119,7 @@ struct FwdSmem {
   static constexpr int oK = oQ + kC * ldQ;
   static constexpr int oP = oK + kC * ldK;
   static constexpr int oV = oP + kC * ldP;
-  static constexpr int oS = oV + kC * ldV;
+  static constexpr int oS = oV + 2 * kC * ldV;  // u / v_new is double-buffered
   static constexpr int floats = oS + DK * ldS;
 };
 
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
   float* sQ = smem + L::oQ;
   float* sK = smem + L::oK;
   float* sP = smem + L::oP;
-  float* sV = smem + L::oV;
+  float* sVbuf = smem + L::oV;
   float* sS = smem + L::oS;
 
   const int bh = blockIdx.y;
@@ -148,12 +149,15 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
   const float* gu = p.u + static_cast<size_t>(bh) * p.N * kC * DV + dv0;
   float* gout = p.out + static_cast<size_t>(bh) * p.N * kC * DV + dv0;
 
-  // chunk 0 tiles
+  // chunk 0 tiles.  Copy groups complete in order and every wait below is "all but the newest group": the keys of a chunk
+  // are only needed by its last step, so their copy (always the newest group at the top of an iteration) stays in flight
+  // through the first two steps.
   tile_load_async<DK>(sW, L::ldW, gw, DK, kC);
   tile_load_async<DK>(sQ, L::ldQ, gq, DK, kC);
-  tile_load_async<DK>(sK, L::ldK, gk, DK, kC);
   tile_load_async<kC>(sP, L::ldP, gP, kC, kC);
-  tile_load_async<DVT>(sV, L::ldV, gu, DV, kC);
+  tile_load_async<DVT>(sVbuf, L::ldV, gu, DV, kC);
+  cp_async_commit();
+  tile_load_async<DK>(sK, L::ldK, gk, DK, kC);
   cp_async_commit();
   for (int i = threadIdx.x; i < DK * DVT; i += kThreads) {
     const int r = i / DVT, c = i - r * DVT;
@@ -169,9 +173,10 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
   const int ms = (warp % MW) * 16, ns = (warp / MW) * (DVT / NW);
 
   for (int n = 0; n < p.N; ++n) {
-    cp_async_wait_all();
+    cp_async_wait_but_newest();  // everything but this chunk's keys
     __syncthreads();
     const bool more = n + 1 < p.N;
+    float* sV = sVbuf + (n & 1) * kC * L::ldV;
     {  // v_new = u - w S (in place over u)
       float acc[NT_O][4];
       zero_acc(acc);
@@ -186,10 +191,11 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
         }
     }
     __syncthreads();
-    if (more) {
+    if (more) {  // the other u buffer was last read by the previous chunk's state update
       tile_load_async<DK>(sW, L::ldW, gw + (n + 1) * tile_k, DK, kC);
-      cp_async_commit();
+      tile_load_async<DVT>(sVbuf + ((n + 1) & 1) * kC * L::ldV, L::ldV, gu + static_cast<size_t>(n + 1) * kC * DV, DV, kC);
     }
+    cp_async_commit();  // committed even when empty, so that "all but the newest" always means the same groups
     {  // o = qg S + P v_new; P is lower triangular, so rows mo..mo+15 need k < mo + 16 only
       float acc[NT_O][4];
       zero_acc(acc);
@@ -206,12 +212,13 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
           *reinterpret_cast<float2*>(o + static_cast<size_t>(r) * DV + c) = make_float2(acc[j][2 * h], acc[j][2 * h + 1]);
         }
     }
+    cp_async_wait_but_newest();  // this chunk's keys have landed (the newest group is the next w / u)
     __syncthreads();
     if (more) {
       tile_load_async<DK>(sQ, L::ldQ, gq + (n + 1) * tile_k, DK, kC);
       tile_load_async<kC>(sP, L::ldP, gP + static_cast<size_t>(n + 1) * kC * kC, kC, kC);
-      cp_async_commit();
     }
+    cp_async_commit();
     {  // S = a S + kd^T v_new; the entering state is saved for the backward pass
       const float a = p.a[static_cast<size_t>(bh) * p.N + n];
       float acc[NT_S][4];
@@ -237,11 +244,8 @@ __global__ void __launch_bounds__(kThreads) delta_fwd_kernel(const FwdParams p) 
         }
     }
     __syncthreads();
-    if (more) {
-      tile_load_async<DK>(sK, L::ldK, gk + (n + 1) * tile_k, DK, kC);
-      tile_load_async<DVT>(sV, L::ldV, gu + static_cast<size_t>(n + 1) * kC * DV, DV, kC);
-      cp_async_commit();
-    }
+    if (more) tile_load_async<DK>(sK, L::ldK, gk + (n + 1) * tile_k, DK, kC);
+    cp_async_commit();
   }
   if (p.S_final)
     for (int i = threadIdx.x; i < DK * DVT; i += kThreads) {

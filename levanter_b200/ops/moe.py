@@ -163,6 +163,17 @@ def grouped_mlp_padded(x_flat: torch.Tensor, topk_idx: torch.Tensor, w1: torch.T
     return y.index_select(0, dest)
 
 
+def grouped_mlp_on_padded(x_pad: torch.Tensor, tile_group: torch.Tensor, offsets: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor,
+                          w2: torch.Tensor, act: ActivationFunctionEnum) -> torch.Tensor:
+    """The expert MLP over rows that are already in the padded expert-sorted layout (``offsets[E + 1]`` padded starts,
+    ``tile_group`` the expert of every 128-row block, both on the device): what the expert-parallel exchange delivers."""
+    dt = x_pad.dtype
+    if w1.dtype != dt:
+        w1, w3, w2 = w1.to(dt), w3.to(dt), w2.to(dt)
+    h = gated_activation(grouped_linear(x_pad, w1, tile_group, offsets), grouped_linear(x_pad, w3, tile_group, offsets), act)
+    return grouped_linear(h, w2, tile_group, offsets)
+
+
 # ------------------------------------------------------------------------------------------------ routing
 def moe_route_reference(router_logits: torch.Tensor, k: int):
     """``(topk_w[T, k], topk_idx[T, k], counts[E], p_sum[E], lse[T])`` with PyTorch ops (CPU path and oracle)."""

@@ -28,6 +28,18 @@ class Histogram:
     @staticmethod
     def from_array(array: torch.Tensor, num_bins: int = NUM_BINS, group: Optional[dist.ProcessGroup] = None,
                    sharded: bool = False) -> "Histogram":
+        if array.is_cuda and array.numel() > 0 and num_bins <= 256 and not (sharded and dist.is_initialized()):
+            from ..ops import analysis_kernels as ak
+            from ..ops import lib
+
+            if lib.available():
+                # two reads of the tensor (summary, then bins over the range the summary left on the device), one read-back
+                a = array.detach().reshape(-1)
+                a = a if a.dtype in (torch.float32, torch.bfloat16) else a.float()
+                summary, counts = ak.summary_and_histogram(a, num_bins)
+                mn, mx, total, total_sq = summary.tolist()
+                edges = np.linspace(mn, mx if mx > mn else mn + 1.0, num_bins + 1, dtype=np.float32)
+                return Histogram(mn, mx, a.numel(), total, total_sq, edges, counts.cpu().numpy().astype(np.float32))
         a = array.detach().float().reshape(-1)
         stats = torch.stack([a.min() if a.numel() else torch.tensor(float("inf"), device=a.device),
                              -(a.max() if a.numel() else torch.tensor(-float("inf"), device=a.device))])
@@ -53,6 +65,15 @@ def sharded_histogram(a: torch.Tensor, bins: int = NUM_BINS, range=None, group=N
     if not (hi > lo):
         hi = lo + 1.0
     edges = torch.linspace(lo, hi, bins + 1, device=a.device)
+    if a.is_cuda and a.numel() > 0 and bins <= 256:
+        from ..ops import analysis_kernels as ak
+        from ..ops import lib
+
+        if lib.available():
+            counts = ak.histogram_counts(a, lo, hi, bins).to(torch.float32)
+            if reduce and dist.is_available() and dist.is_initialized():
+                dist.all_reduce(counts, group=group)
+            return counts, edges
     idx = torch.clamp(((a - lo) / (hi - lo) * bins).floor().long(), 0, bins - 1)
     inside = (a >= lo) & (a <= hi)
     counts = torch.bincount(idx[inside], minlength=bins).to(torch.float32)
