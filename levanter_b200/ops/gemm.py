@@ -213,9 +213,16 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, dres
 
 
+def _tma_shapes_ok(weight: torch.Tensor) -> bool:
+    """Forward, input-gradient and weight-gradient GEMMs each read ``weight`` or the activations with one of the two feature
+    sizes as the row stride, and a TMA row stride must be a multiple of 16 bytes: both sizes must be multiples of 8 (a
+    router with 4 experts, for one, goes to the library GEMM)."""
+    return weight.dim() == 2 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Linear layer on the tcgen05 GEMM when running bf16 on a B200; ``F.linear`` otherwise."""
-    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _tma_shapes_ok(weight):
         return _LinearFn.apply(x, weight, bias, None)
     return torch.nn.functional.linear(x, weight, bias)
 
@@ -227,6 +234,6 @@ def linear_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
     if weight.dtype != x.dtype:
         weight = weight.to(x.dtype)
         bias = bias.to(x.dtype) if bias is not None else None
-    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16:
+    if x.is_cuda and lib.available() and x.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16 and _tma_shapes_ok(weight):
         return _LinearFn.apply(x, weight, bias, residual)
     return torch.nn.functional.linear(x, weight, bias) + residual
