@@ -110,7 +110,7 @@ class MixtralMoEMlp(nn.Module):
             if w.device.type != "meta":
                 trunc_normal_(w, init_std)
             w.lev_permute = (0, 2, 1)
-            w.lev_shape = (w.shape[0], w.shape[2], w.shape[1])
+            w.lev_shape = (num_experts, w.shape[2], w.shape[1])  # checkpoints hold every expert, whatever the slicing
             w.ep_dim = 0 if n != num_experts else None
 
     def forward(self, x_sorted: torch.Tensor, group_sizes: torch.Tensor) -> torch.Tensor:

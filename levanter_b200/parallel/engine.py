@@ -49,6 +49,7 @@ class ParamSlot:
     numel: int
     offset: int  # in the flat buffers
     bucket: int
+    ep_dim: Optional[int] = None  # expert-parallel parameters: the axis the experts are sliced over (each rank holds its slice)
 
 
 @dataclass
@@ -58,8 +59,11 @@ class Bucket:
     start: int
     end: int  # padded: (end - start) % (W * ALIGN) == 0
     slots: List[ParamSlot] = field(default_factory=list)
+    local: bool = False  # rank-local parameters (expert parallelism): owned whole by this rank, never reduced or gathered
 
     def shard_range(self, rank: int, world: int) -> Tuple[int, int]:
+        if self.local:
+            return self.start, self.end
         n = (self.end - self.start) // world
         return self.start + rank * n, self.start + (rank + 1) * n
 
@@ -120,16 +124,23 @@ class ShardedEngine:
                 continue
             seen[id(p)] = name
             trainable = p.requires_grad and (is_trainable is None or is_trainable(name))
-            if trainable and W > 1 and getattr(p, "ep_dim", None) is not None:
-                raise NotImplementedError(
-                    f"{name} is expert-parallel (a different slice on every rank); the sharded engine reduces every gradient over the "
-                    "data axis and does not keep rank-local parameters yet: train expert-parallel models with a local optimizer")
+            if trainable and W > 1 and getattr(p, "ep_dim", None) is not None and not self.shard_optimizer:
+                raise NotImplementedError(f"{name} is expert-parallel: rank-local parameters need the sharded optimizer")
             if not trainable:
                 p.requires_grad_(False)
                 if p.is_floating_point():
                     p.data = p.data.to(device=self.device, dtype=cd)
                 continue
             named.append((name, p))
+        # expert-parallel parameters (a different slice of the experts on every rank) get buckets of their own, which this
+        # rank owns whole: their gradients already hold every rank's tokens (the token exchange brought them here), so they
+        # are scaled, not reduced, and their new weights are not gathered
+        is_local = {name: (W > 1 and getattr(p, "ep_dim", None) is not None) for name, p in named}
+        plain_bucket_of = bucket_of
+
+        def bucket_of(name: str) -> str:  # noqa: F811
+            return plain_bucket_of(name) + ("#experts" if is_local[name] else "")
+
         order: Dict[str, int] = {}
         for name, _ in named:
             order.setdefault(bucket_of(name), len(order))
@@ -144,9 +155,9 @@ class ShardedEngine:
                 if cur is not None:
                     cur.end = cur.start + _round_up(off - cur.start, W * ALIGN)
                     off = cur.end
-                cur = Bucket(len(self.buckets), b, off, off)
+                cur = Bucket(len(self.buckets), b, off, off, local=is_local[name])
                 self.buckets.append(cur)
-            slot = ParamSlot(name, p, tuple(p.shape), p.numel(), off, cur.index)
+            slot = ParamSlot(name, p, tuple(p.shape), p.numel(), off, cur.index, getattr(p, "ep_dim", None) if is_local[name] else None)
             cur.slots.append(slot)
             self.slots.append(slot)
             off = _round_up(off + p.numel(), ALIGN)
@@ -182,7 +193,8 @@ class ShardedEngine:
             self.param_flat = torch.zeros(self.total, dtype=cd, device=self.device)
             self.grad_flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         # owned slices, concatenated bucket by bucket
-        self.shard_numel = self.total // W if self.shard_optimizer else self.total
+        self.shard_numel = sum(b.end - b.start if b.local else (b.end - b.start) // W for b in self.buckets) if self.shard_optimizer else self.total
+        self.has_local = any(b.local for b in self.buckets)
         self.master_is_param = (pd == cd and W == 1) or (pd == cd and not self.shard_optimizer)
         if self.master_is_param:
             self.master = self.param_flat
@@ -299,9 +311,12 @@ class ShardedEngine:
         if W > 1:
             if self.shard_optimizer:
                 for b, lstart in zip(self.buckets, self._bucket_local_start):
+                    inp = self.grad_flat[b.start:b.end]
+                    if b.local:  # the average over ranks of a gradient that already sums every rank's tokens
+                        self.grad_shard[lstart:lstart + (b.end - b.start)].copy_(inp).div_(W)
+                        continue
                     n = (b.end - b.start) // W
                     out = self.grad_shard[lstart:lstart + n]
-                    inp = self.grad_flat[b.start:b.end]
                     if self.grad_reduce_dtype != torch.float32:
                         tmp = inp.to(self.grad_reduce_dtype)
                         o2 = torch.empty(n, dtype=self.grad_reduce_dtype, device=self.device)
@@ -336,7 +351,10 @@ class ShardedEngine:
         for b, lstart in zip(self.buckets, self._bucket_local_start):
             lo, hi = b.shard_range(self.rank, W)
             out = self.grad_shard[lstart:lstart + (hi - lo)]
-            if fm is not None:
+            if b.local:  # a "reduction" over this rank alone: scale, copy and sum of squares in the same kernel
+                rc = f(self._self_ptrs(self._sym_grad), 1, 0, lo, hi - lo, float(scale) / W, out.data_ptr(), self._p2p_sumsq.data_ptr(),
+                       self._p2p_scratch.data_ptr(), lib.stream_ptr())
+            elif fm is not None:
                 rc = fm(self._sym_grad.multicast_ptr, lo, hi - lo, float(scale) / W, out.data_ptr(), self._p2p_sumsq.data_ptr(),
                         self._p2p_scratch.data_ptr(), lib.stream_ptr())
             else:
@@ -344,6 +362,16 @@ class ShardedEngine:
                        self._p2p_scratch.data_ptr(), lib.stream_ptr())
             lib.check_rc(rc, "lvb_p2p_reduce_scatter")
         self._p2p_sumsq_valid = True
+
+    def _self_ptrs(self, buf):
+        """A one-entry peer table holding this rank's own copy of a symmetric buffer (for rank-local buckets)."""
+        import ctypes
+
+        cache = self.__dict__.setdefault("_self_ptr_cache", {})
+        key = id(buf)
+        if key not in cache:
+            cache[key] = (ctypes.c_void_p * 1)(buf.peer_ptrs[buf.rank])
+        return cache[key]
 
     def grad_sumsq(self) -> torch.Tensor:
         """Sum of squared gradients over *all* parameters (device scalar), reduced over the mesh."""
@@ -418,7 +446,8 @@ class ShardedEngine:
             own = self.param_flat[lo:hi]
             if self.fused_adam is None or not self.fused_adam.writes_compute_copy:
                 own.copy_(self.master[lstart:lstart + n])
-            dist.all_gather_into_tensor(self.param_flat[b.start:b.end], own, group=self.data_group)
+            if not b.local:
+                dist.all_gather_into_tensor(self.param_flat[b.start:b.end], own, group=self.data_group)
 
     # ------------------------------------------------------------------------------------------ state export
     def full_master(self) -> Dict[str, torch.Tensor]:
@@ -431,10 +460,37 @@ class ShardedEngine:
             flat = shard
         else:
             flat = torch.empty(self.total, dtype=shard.dtype, device=self.device)
+            local_full: Dict[str, torch.Tensor] = {}
             for b, lstart in zip(self.buckets, self._bucket_local_start):
+                if b.local:
+                    local_full.update(self._gather_local_bucket(b, shard[lstart:lstart + (b.end - b.start)]))
+                    continue
                 n = (b.end - b.start) // W
                 dist.all_gather_into_tensor(flat[b.start:b.end], shard[lstart:lstart + n].contiguous(), group=self.data_group)
+            return {s.name: local_full[s.name] if s.ep_dim is not None else flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots}
         return {s.name: flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots}
+
+    def _gather_local_bucket(self, b: Bucket, mine: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """Full tensors of a rank-local bucket: every rank's slice of the experts, concatenated along the expert axis."""
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine.contiguous(), group=self.data_group)
+        out = {}
+        for s in b.slots:
+            o = s.offset - b.start
+            out[s.name] = torch.cat([p[o:o + s.numel].view(s.shape) for p in parts], dim=s.ep_dim)
+        return out
+
+    def _full_shape(self, s: ParamSlot) -> Tuple[int, ...]:
+        if s.ep_dim is None:
+            return s.shape
+        return tuple(d * self.world if i == s.ep_dim else d for i, d in enumerate(s.shape))
+
+    def _own_part(self, s: ParamSlot, full: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a full tensor: all of it, or its slice of the experts."""
+        if s.ep_dim is None or full.shape[s.ep_dim] == s.shape[s.ep_dim]:
+            return full
+        n = s.shape[s.ep_dim]
+        return full.narrow(s.ep_dim, self.rank * n, n)
 
     def deferred_named(self, shard: torch.Tensor) -> Dict[str, Any]:
         """name -> leaf for checkpoint writing.  Unsharded state yields plain views; sharded state yields
@@ -448,6 +504,12 @@ class ShardedEngine:
         cache: Dict[str, Any] = {"bucket": -1, "flat": None}
 
         def fetch(slot: ParamSlot) -> torch.Tensor:
+            if slot.ep_dim is not None:
+                if cache["bucket"] != slot.bucket:
+                    b = self.buckets[slot.bucket]
+                    lstart = self._bucket_local_start[slot.bucket]
+                    cache["bucket"], cache["flat"] = slot.bucket, self._gather_local_bucket(b, shard[lstart:lstart + (b.end - b.start)])
+                return cache["flat"][slot.name]
             if cache["bucket"] != slot.bucket:
                 b = self.buckets[slot.bucket]
                 lstart = self._bucket_local_start[slot.bucket]
@@ -459,7 +521,7 @@ class ShardedEngine:
             o = slot.offset - b.start
             return cache["flat"][o:o + slot.numel].view(slot.shape)
 
-        return {s.name: DeferredLeaf(lambda s=s: fetch(s), s.shape, shard.dtype) for s in self.slots}
+        return {s.name: DeferredLeaf(lambda s=s: fetch(s), self._full_shape(s), shard.dtype) for s in self.slots}
 
     def scatter_named(self, full: Dict[str, torch.Tensor], shard: torch.Tensor) -> None:
         """Inverse of :meth:`_gather_named`: copy the owned part of each full tensor into ``shard``."""
@@ -470,14 +532,14 @@ class ShardedEngine:
                     continue
                 lo, fo, n = seg
                 a = fo - s.offset
-                shard[lo:lo + n].copy_(full[s.name].reshape(-1)[a:a + n].to(shard.dtype))
+                shard[lo:lo + n].copy_(self._own_part(s, full[s.name]).reshape(-1)[a:a + n].to(shard.dtype))
 
     def load_full_params(self, full: Dict[str, torch.Tensor]) -> None:
         """Set parameters (master and compute copies) from full tensors."""
         with torch.no_grad():
             for s in self.slots:
                 if s.name in full:
-                    s.param.data.copy_(full[s.name].to(device=self.device, dtype=self.param_flat.dtype).view(s.shape))
+                    s.param.data.copy_(self._own_part(s, full[s.name]).to(device=self.device, dtype=self.param_flat.dtype).reshape(s.shape))
         if not self.master_is_param:
             self.scatter_named({k: v.to(self.device) for k, v in full.items()}, self.master)
 
@@ -526,7 +588,7 @@ class ShardedEngine:
                 if tree.get(name) is not None:
                     s = next(sl for sl in self.slots if sl.name == name)
                     a = fo - s.offset
-                    out[name] = tree[name].reshape(-1)[a:a + n].to(device=self.device, dtype=torch.float32).clone()
+                    out[name] = self._own_part(s, tree[name]).reshape(-1)[a:a + n].to(device=self.device, dtype=torch.float32).clone()
             return out
 
         self.opt_state = _map_state(state, scatter)
@@ -611,6 +673,12 @@ class FusedAdamW:
                 if hi <= lo:
                     continue
                 hi8 = lo + ((hi - lo + 7) // 8) * 8  # the tail up to the next 8 is layout padding (zero weights, zero gradients)
+                if e.has_local and self._run_is_local(lo):  # rank-local experts: the new weights go to this rank's buffer only
+                    rc = f(e.master[lo:hi8].data_ptr(), self.m[lo:hi8].data_ptr(), self.v[lo:hi8].data_ptr(), e.grad_shard[lo:hi8].data_ptr(),
+                           e._self_ptrs(e._sym_param), 1, 0, self._local_to_flat(lo), hi8 - lo, lr, c.beta1, c.beta2, c.epsilon, wd, bc1, bc2,
+                           self.coef.data_ptr(), int(c.nesterov), lib.stream_ptr())
+                    lib.check_rc(rc, "lvb_p2p_adamw_allgather")
+                    continue
                 if e.comm == "multimem":
                     fm = getattr(self, "_f_mag", None)
                     if fm is None:
@@ -633,6 +701,13 @@ class FusedAdamW:
             dst = self._compute_view(lo, hi)
             adamw(e.master[lo:hi], self.m[lo:hi], self.v[lo:hi], e.grad_shard[lo:hi], dst, lr, c.beta1, c.beta2, c.epsilon,
                   wd, bc1, bc2, self.coef, 1.0, c.nesterov)
+
+    def _run_is_local(self, lo: int) -> bool:
+        e = self.e
+        for b, ls in zip(reversed(e.buckets), reversed(e._bucket_local_start)):
+            if lo >= ls:
+                return b.local
+        return False
 
     def _local_to_flat(self, lo: int) -> int:
         e = self.e

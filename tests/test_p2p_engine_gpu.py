@@ -9,7 +9,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, out_dir: str, moe: bool = False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
@@ -26,11 +26,17 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     try:
         mesh = DeviceMesh(replica=1, data=world, model=1)
         cfg = LlamaConfig(seq_len=256, hidden_dim=256, intermediate_dim=512, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
+        if moe:  # experts sliced over the two ranks: rank-local buckets next to the sharded ones
+            from levanter_b200.models.mixtral import MixtralConfig
+
+            cfg = MixtralConfig(seq_len=256, hidden_dim=256, intermediate_dim=512, num_layers=2, num_heads=2, num_kv_heads=2, n_routed_experts=8,
+                                num_experts_per_tok=2, gradient_checkpointing=False, expert_parallel=True)
         results = {}
         for comm in ("nccl", "p2p", "multimem"):
             model = cfg.build(512, seed=0, device=torch.device("cuda", rank))
             eng = ShardedEngine(model, Policy.parse("p=f32,c=bfloat16"), mesh, device=torch.device("cuda", rank), comm=comm)
             assert eng.comm == comm or (comm == "multimem" and eng.comm == "p2p"), eng.comm
+            assert eng.has_local == moe
             ocfg = AdamConfig(learning_rate=1e-2, warmup=0.0, weight_decay=0.1, max_grad_norm=1.0)
             eng.set_optimizer(ocfg.build(10, ParamInfo(model)), optimizer_config=ocfg, num_train_steps=10)
             g = torch.Generator().manual_seed(100 + rank)
@@ -68,3 +74,24 @@ def test_p2p_step_matches_nccl_step(tmp_path):
     # every rank holds the same weights after the fused all-gather
     for mode in ("p2p", "multimem"):
         assert torch.equal(res[0][mode][0], res[1][mode][0]), mode
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_step_on_peer_memory_matches_nccl_step(tmp_path):
+    """Mixtral with its experts sliced over two ranks through the engine: the peer-memory step (which scales the rank-local
+    expert gradients and updates them in place, and reduces / gathers everything else) against the NCCL step."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_worker, args=(world, 29633, str(tmp_path), True), nprocs=world, join=True)
+    res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for r in range(world):
+        p_nccl, m_nccl, n_nccl, l_nccl = res[r]["nccl"]
+        assert all(l == l for l in l_nccl) and l_nccl[-1] < l_nccl[0] + 0.5
+        for mode in ("p2p", "multimem"):
+            p_p2p, m_p2p, n_p2p, l_p2p = res[r][mode]
+            assert abs(n_nccl - n_p2p) <= 2e-3 * abs(n_nccl)
+            assert torch.allclose(m_nccl, m_p2p, atol=1e-4, rtol=1e-3), mode
+            assert all(abs(a - b) < 3e-2 for a, b in zip(l_nccl, l_p2p)), mode
+    # the ranks hold different experts, so their buffers differ, but only inside the expert buckets
+    assert not torch.equal(res[0]["p2p"][0], res[1]["p2p"][0])
