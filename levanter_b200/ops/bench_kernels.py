@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule", "rmsnorm_bwd", "rope", "dwconv", "entropy", "histogram"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -246,6 +246,85 @@ def main(argv=None):
         _report("delta_rule_scan_fwd_bwd", cfg, ms, mn, flops=3 * flops)
         ms, mn = _time(fwd_bwd_ops, max(a.iters // 4, 2), 2, flush)
         return _report("delta_rule_scan_fwd_bwd_framework_ops", cfg, ms, mn, flops=3 * flops)
+
+    if a.kernel == "rmsnorm_bwd":
+        from .norm import rms_norm
+
+        rows = a.batch * a.seq
+        x = torch.randn(rows, a.hidden, device=dev, dtype=bf, requires_grad=True)
+        w = torch.ones(a.hidden, device=dev, dtype=torch.float32, requires_grad=True)
+        gy = torch.randn(rows, a.hidden, device=dev, dtype=bf)
+
+        def step():
+            x.grad = None
+            rms_norm(x, w, None, 1e-5).backward(gy)
+
+        ms, mn = _time(step, a.iters, a.warmup, flush)
+        # forward reads x, writes y; backward reads x, dy, writes dx
+        return _report("rmsnorm_fwd_bwd", {"rows": rows, "hidden": a.hidden}, ms, mn, nbytes=5.0 * rows * a.hidden * 2)
+
+    if a.kernel == "rope":
+        from ..layers.rotary import DefaultRotaryEmbeddingsConfig
+        from .rope import apply_rope
+
+        kv = a.kv_heads or a.heads
+        q = torch.randn(a.batch, a.seq, a.heads, 128, device=dev, dtype=bf)
+        k = torch.randn(a.batch, a.seq, kv, 128, device=dev, dtype=bf)
+        rot = DefaultRotaryEmbeddingsConfig().build(128)
+        with torch.no_grad():
+            ms, mn = _time(lambda: apply_rope(q, k, rot), a.iters, a.warmup, flush)
+        return _report("rope_q_and_k", {"batch": a.batch, "seq": a.seq, "heads": a.heads, "kv_heads": kv}, ms, mn,
+                       nbytes=2.0 * 2 * a.batch * a.seq * (a.heads + kv) * 128)
+
+    if a.kernel == "dwconv":
+        from .dwconv import causal_dwconv, causal_dwconv_reference
+
+        x = torch.randn(a.batch, a.seq, a.hidden, device=dev, dtype=bf, requires_grad=True)
+        w = (torch.randn(a.hidden, 1, 4, device=dev) * 0.5).requires_grad_()
+        gy = torch.randn(a.batch, a.seq, a.hidden, device=dev, dtype=bf)
+        cfg = {"batch": a.batch, "seq": a.seq, "channels": a.hidden, "k": 4, "act": "silu"}
+        nb = 2.0 * a.batch * a.seq * a.hidden
+        with torch.no_grad():
+            ms, mn = _time(lambda: causal_dwconv(x, w, None, True), a.iters, a.warmup, flush)
+        _report("dwconv_silu_fwd", cfg, ms, mn, nbytes=2 * nb)
+        if a.once:
+            causal_dwconv(x, w, None, True).backward(gy)
+            return None
+        wb = w.detach().to(bf).requires_grad_()
+        with torch.no_grad():
+            ms, mn = _time(lambda: causal_dwconv_reference(x, wb, None, True), a.iters, a.warmup, flush)
+        _report("dwconv_silu_fwd_library_conv1d", cfg, ms, mn, nbytes=2 * nb)
+
+        def step(fn, weight):
+            x.grad = None
+            fn(x, weight, None, True).backward(gy)
+
+        ms, mn = _time(lambda: step(causal_dwconv, w), a.iters, a.warmup, flush)
+        # forward: x, y; gradient prologue: x, dy, dpre; input gradient: dpre, dx
+        _report("dwconv_silu_fwd_bwd", cfg, ms, mn, nbytes=7 * nb)
+        ms, mn = _time(lambda: step(causal_dwconv_reference, wb), a.iters, a.warmup, flush)
+        return _report("dwconv_silu_fwd_bwd_library_conv1d", cfg, ms, mn, nbytes=7 * nb)
+
+    if a.kernel == "entropy":
+        from .analysis_kernels import entropy_top2, entropy_top2_reference
+
+        rows = a.batch * a.seq
+        z = torch.randn(rows, a.vocab, device=dev, dtype=bf)
+        cfg = {"rows": rows, "vocab": a.vocab}
+        ms, mn = _time(lambda: entropy_top2(z), a.iters, a.warmup, flush)
+        _report("entropy_top2_lse", cfg, ms, mn, nbytes=2.0 * rows * a.vocab)
+        if a.once:
+            return None
+        ms, mn = _time(lambda: entropy_top2_reference(z), max(a.iters // 4, 2), 2, flush)
+        return _report("entropy_top2_lse_framework_ops", cfg, ms, mn, nbytes=2.0 * rows * a.vocab)
+
+    if a.kernel == "histogram":
+        from ..tracker.histogram import Histogram
+
+        n = a.m * a.n
+        x = torch.randn(n, device=dev)
+        ms, mn = _time(lambda: Histogram.from_array(x), a.iters, a.warmup, flush)  # includes the read-back of the result
+        return _report("summary_and_histogram_31_bins", {"elements": n}, ms, mn, nbytes=2 * 4.0 * n)
 
     if a.kernel == "sampler":
         from ..layers.sampler import Sampler
