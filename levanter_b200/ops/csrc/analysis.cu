@@ -154,10 +154,34 @@ entropy_top2_kernel(const void* __restrict__ logits, int V, long long ld, float*
     for (int i = threadIdx.x; i < V / 8; i += kBlock) {
       const uint4 q = __ldg(p + i);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      float v[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        stat_add(r, __uint_as_float(w[j] << 16));
-        stat_add(r, __uint_as_float(w[j] & 0xffff0000u));
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+      // eight values at once: one rescale of the running sums to the new maximum, then branch-free accumulation
+      float m8 = v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) m8 = fmaxf(m8, v[j]);
+      if (m8 > r.m) {
+        const float c = __expf(r.m - m8);  // 0 while the running maximum is still -inf
+        r.z *= c;
+        r.s *= c;
+        r.m = m8;
+      }
+      if (r.m != -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float e = __expf(v[j] - r.m);  // exp(-inf) = 0 for masked logits
+          r.z += e;
+          r.s = fmaf(e, v[j] == -INFINITY ? 0.f : v[j], r.s);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // top two without branches
+        r.b = fmaxf(r.b, fminf(r.a, v[j]));
+        r.a = fmaxf(r.a, v[j]);
       }
     }
   } else {

@@ -14,7 +14,8 @@ namespace lvb {
 namespace dwconv {
 
 constexpr int kBlock = 128;
-constexpr int kRun = 64;  // positions per thread
+constexpr int kRun = 64;     // positions per thread, gradient prologue (its partial sums are written once per run)
+constexpr int kRunFwd = 32;  // positions per thread, convolution: shorter runs put more loads in flight
 
 template <bool BF16>
 struct Vec {
@@ -60,7 +61,7 @@ conv_kernel(const void* __restrict__ x, const float* __restrict__ w, const float
   const int cv = blockIdx.x * kBlock + threadIdx.x;
   if (cv * N >= C) return;
   const int c0 = cv * N;
-  const int l0 = blockIdx.y * kRun;
+  const int l0 = blockIdx.y * kRunFwd;
   const size_t row0 = static_cast<size_t>(blockIdx.z) * L;
   float wr[N][K], br[N], win[K - 1][N];
 #pragma unroll
@@ -78,7 +79,8 @@ conv_kernel(const void* __restrict__ x, const float* __restrict__ w, const float
 #pragma unroll
       for (int i = 0; i < N; ++i) win[j][i] = 0.f;
   }
-  const int l_end = min(l0 + kRun, L);
+  const int l_end = min(l0 + kRunFwd, L);
+#pragma unroll 4
   for (int l = l0; l < l_end; ++l) {
     float cur[N], out[N];
     Vec<BF16>::load(x, pos(l), cur);
@@ -129,6 +131,7 @@ bwd_prep_kernel(const void* __restrict__ x, const void* __restrict__ dy, const f
       for (int i = 0; i < N; ++i) win[j][i] = 0.f;
   }
   const int l_end = min(l0 + kRun, L);
+#pragma unroll 2
   for (int l = l0; l < l_end; ++l) {
     float cur[N], g[N];
     const size_t at = (row0 + l) * C + c0;
@@ -176,7 +179,7 @@ __global__ void bwd_reduce_kernel(const float* __restrict__ partial, int parts, 
 template <bool BF16, int K>
 int launch_conv(const void* x, const float* w, const float* bias, void* y, int B, int L, int C, int act, int flip, cudaStream_t s) {
   constexpr int N = Vec<BF16>::N;
-  dim3 grid((C / N + kBlock - 1) / kBlock, (L + kRun - 1) / kRun, B);
+  dim3 grid((C / N + kBlock - 1) / kBlock, (L + kRunFwd - 1) / kRunFwd, B);
   conv_kernel<BF16, K><<<grid, kBlock, 0, s>>>(x, w, bias, y, L, C, act, flip);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
