@@ -200,6 +200,49 @@ class RayConfig:
     def initialize(self):
         if self.address is not None:
             logger.info("a Ray address was configured; this framework tokenises with local worker processes instead")
+        if self.auto_start_cluster and self.address is not None:
+            auto_ray_cluster(address=self.address, start_workers=self.start_workers)
+
+
+_ray_initialized = False
+
+
+def auto_ray_cluster(address: Optional[str] = None, namespace: Optional[str] = "levanter", start_workers: bool = True,
+                     fail_if_cluster_already_initialized: bool = False, **kwargs) -> bool:
+    """Join (or, on the first SLURM node, start) a Ray cluster for users whose own preprocessing uses Ray
+    (src/levanter/distributed.py:200-312).  The address comes from the argument, ``RAY_ADDRESS``, or the first node of the
+    SLURM allocation with a port derived from the job id.  Nothing in this framework needs Ray (caches are built by local
+    worker processes), so without the ``ray`` package this logs and returns False instead of failing; a second call is ignored
+    as in the reference.  Returns True when ``ray.init`` ran."""
+    global _ray_initialized
+    if _ray_initialized:
+        logger.warning("auto_ray_cluster has already been called. Ignoring subsequent calls.")
+        return False
+    try:
+        import ray  # type: ignore
+    except ImportError:
+        logger.info("ray is not installed: no Ray cluster is started (none is needed by this framework)")
+        return False
+    if address is None:
+        address = os.environ.get("RAY_ADDRESS")
+    if address is None and LevanterSlurmCluster.is_env_present():
+        cluster = LevanterSlurmCluster()
+        host = cluster.get_coordinator_address().split(":")[0]
+        port = 6379 + int(os.environ.get("SLURM_JOB_ID", "0")) % 1000
+        address = f"{host}:{port}"
+        if cluster.get_process_id() == 0 and is_local_leader():
+            import subprocess
+
+            subprocess.run(["ray", "start", "--head", "--port", str(port)], check=False)
+        elif start_workers and is_local_leader():
+            import subprocess
+
+            subprocess.run(["ray", "start", "--address", address], check=False)
+    if ray.is_initialized() and fail_if_cluster_already_initialized:
+        raise RuntimeError("a Ray cluster is already initialised in this process")
+    ray.init(address=address, namespace=namespace, ignore_reinit_error=not fail_if_cluster_already_initialized, **kwargs)
+    _ray_initialized = True
+    return True
 
 
 def is_local_leader() -> bool:
@@ -231,6 +274,13 @@ def barrier_sync(timeout: float = 200.0) -> None:
 
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.barrier()
+
+
+def sync_global_devices(name: str = "sync", timeout: float = 200.0) -> None:
+    """Every process reaches this point before any goes on (the reference's barrier before uploads,
+    src/levanter/utils/cloud_utils.py:169; src/levanter/compat/hf_checkpoints.py:1099).  ``name`` only labels the log line."""
+    logger.debug(f"barrier: {name}")
+    barrier_sync(timeout)
 
 
 def broadcast_one_to_all(obj, src: int = 0):

@@ -7,7 +7,7 @@ import shutil
 import tempfile
 from typing import Optional
 
-from ..distributed import process_index
+from ..distributed import process_index, sync_global_devices  # noqa: F401  (the barrier taken before uploads is re-exported)
 
 
 @contextlib.contextmanager
