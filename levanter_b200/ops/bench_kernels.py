@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule", "rmsnorm_bwd", "rope", "dwconv", "entropy", "histogram"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule", "rmsnorm_bwd", "rope", "dwconv", "entropy", "histogram", "gdn_layer"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -325,6 +325,34 @@ def main(argv=None):
         x = torch.randn(n, device=dev)
         ms, mn = _time(lambda: Histogram.from_array(x), a.iters, a.warmup, flush)  # includes the read-back of the result
         return _report("summary_and_histogram_31_bins", {"elements": n}, ms, mn, nbytes=2 * 4.0 * n)
+
+    if a.kernel == "gdn_layer":
+        # one gated delta-rule token mixer (projections, short convolutions, scan, gated norm), forward + backward, with the
+        # scan and convolution kernels against the same layer on framework ops
+        from ..models import gated_deltanet as G
+        from .delta_rule import chunk_state_scan_reference
+        from .dwconv import causal_dwconv_reference
+
+        cfg = G.GatedDeltaNetConfig(seq_len=a.seq, hidden_dim=a.hidden, num_heads=a.heads, head_k_dim=128, head_v_dim=128, num_layers=1)
+        with torch.device(dev):
+            layer = G.GatedDeltaNetLayer(cfg).bfloat16()
+        x = torch.randn(a.batch, a.seq, a.hidden, device=dev, dtype=bf, requires_grad=True)
+        gy = torch.randn(a.batch, a.seq, a.hidden, device=dev, dtype=bf)
+
+        def step():
+            x.grad = None
+            layer(x).backward(gy)
+
+        shape = {"batch": a.batch, "seq": a.seq, "hidden": a.hidden, "heads": a.heads}
+        ms, mn = _time(step, a.iters, a.warmup, flush)
+        _report("gated_deltanet_layer_fwd_bwd", shape, ms, mn)
+        kernels = (G.chunk_state_scan, G.causal_dwconv)
+        G.chunk_state_scan, G.causal_dwconv = chunk_state_scan_reference, causal_dwconv_reference
+        try:
+            ms, mn = _time(step, max(a.iters // 4, 2), 2, flush)
+        finally:
+            G.chunk_state_scan, G.causal_dwconv = kernels
+        return _report("gated_deltanet_layer_fwd_bwd_framework_ops", shape, ms, mn)
 
     if a.kernel == "sampler":
         from ..layers.sampler import Sampler
