@@ -295,6 +295,14 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
     engine = state.engine
     layouts = tss.layouts_of(state.model)
     shapes = {s.name: s.shape for s in engine.slots}
+    slot_of = {s.name: s for s in engine.slots}
+
+    def read_own(prefix: str, name: str):
+        """This rank's part of a saved parameter-shaped leaf: all of it, or (expert-parallel parameters, which checkpoints hold
+        with every expert) its slice of the experts."""
+        slot = slot_of[name]
+        full = tss.read_param(checkpoint_path, prefix, name, layouts.get(name), engine._full_shape(slot))
+        return None if full is None else engine._own_part(slot, full)
     missing: List[str] = []
 
     def fill_shard(prefix: str, shard: torch.Tensor, names: Optional[Sequence[str]] = None):
@@ -302,7 +310,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
             seg = engine.segments.get(name)
             if seg is None:
                 continue
-            full = tss.read_param(checkpoint_path, prefix, name, layouts.get(name), shapes[name])
+            full = read_own(prefix, name)
             if full is None:
                 missing.append(f"{prefix}.{name}")
                 continue
@@ -314,7 +322,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
     with torch.no_grad():
         # parameters: master slices, then the compute-dtype copies everywhere
         for s in engine.slots:
-            full = tss.read_param(checkpoint_path, "model", s.name, layouts.get(s.name), s.shape)
+            full = read_own("model", s.name)
             if full is None:
                 missing.append(f"model.{s.name}")
                 continue
@@ -339,7 +347,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
                     for name, leaf in x.items():
                         if leaf is None:
                             continue
-                        full = tss.read_param(checkpoint_path, p, name, layouts.get(name), shapes[name])
+                        full = read_own(p, name)
                         if full is None:
                             missing.append(f"{p}.{name}")
                             continue
@@ -374,7 +382,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
             engine.opt_state = rec(engine.opt_state, "opt_state")
         if state.model_averaging is not None:
             for name, leaf in state.model_averaging.model_params.items():
-                full = tss.read_param(checkpoint_path, "model_averaging.model", name, layouts.get(name), shapes[name])
+                full = read_own("model_averaging.model", name)
                 if full is None:
                     missing.append(f"model_averaging.model.{name}")
                     continue

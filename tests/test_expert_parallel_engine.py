@@ -88,3 +88,15 @@ def test_expert_parallel_training_matches_single_process_and_resumes_on_one(tmp_
     assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=5e-5)
     for k, v in single.items():
         assert torch.allclose(v, resumed[k], atol=5e-5), k
+
+
+def test_expert_parallel_checkpoint_resumes_on_two_ranks(tmp_path):
+    """The checkpoint holds every expert; on resume with sliced experts every rank reads back its own slice (parameters and
+    optimizer moments)."""
+    _, losses = _train(str(tmp_path / "single"), steps=6)
+    (tmp_path / "ep").mkdir()
+    mp.spawn(_worker, args=(2, 29735, str(tmp_path / "ep"), 3), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29737, str(tmp_path / "ep"), 6), nprocs=2, join=True)
+    for rank in range(2):
+        got = torch.load(tmp_path / "ep" / f"rank{rank}.pt")
+        assert len(got["losses"]) == 3 and got["losses"] == pytest.approx(losses[3:], abs=5e-5)
