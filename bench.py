@@ -36,6 +36,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # shape overrides for quick functional checks; a run that uses them is labelled in "config" and is not the headline
+    ap.add_argument("--model", default="llama", choices=["llama", "mixtral_ep"],
+                    help="llama: the headline model; mixtral_ep: Mixtral 8x7B layer shapes with the experts sliced over the GPUs (a side "
+                         "measurement, never the headline: give --layers so that it fits)")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--per-gpu-batch", type=int, default=8)
@@ -151,8 +154,14 @@ def main():
                        num_layers=args.layers, num_heads=args.hidden // 128, num_kv_heads=args.hidden // 128,
                        gradient_checkpointing=bool(args.remat), initializer_range=0.02,
                        attn_backend=AttentionBackend(args.attn) if args.attn else None)
+    if args.model == "mixtral_ep":
+        from levanter_b200.models.mixtral import MixtralConfig
+
+        mcfg = MixtralConfig(seq_len=S, hidden_dim=args.hidden, intermediate_dim=14336, num_layers=args.layers, num_heads=args.hidden // 128,
+                             num_kv_heads=8, n_routed_experts=8, num_experts_per_tok=2, expert_parallel=world > 1,
+                             gradient_checkpointing=bool(args.remat), initializer_range=0.02)
     ocfg = AdamConfig(learning_rate=3e-4, weight_decay=0.1, warmup=100, max_grad_norm=1.0)
-    headline = (args.layers == 32 and S == 4096 and B == 8 and args.hidden == 4096 and not args.remat)
+    headline = (args.model == "llama" and args.layers == 32 and S == 4096 and B == 8 and args.hidden == 4096 and not args.remat)
 
     with Trainer(tcfg, ocfg, add_default_hooks=False) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(vocab, seed=0, device=dev))
@@ -227,12 +236,12 @@ def main():
         "dtype": "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights std 0.02",
         "impl": "ours",
         "config": {"model": "Llama-2 7B (32L, hidden 4096, 32 heads MHA, SwiGLU 11008, vocab 32000, RoPE 1e4)" if headline
-                   else f"NOT THE HEADLINE CONFIG: layers={args.layers} hidden={args.hidden} seq={S} per_gpu_batch={B} remat={args.remat}",
-                   "global_batch": B * world, "seq_len": S, "parallelism": f"fsdp{world}" if world > 1 else "single-gpu",
+                   else f"NOT THE HEADLINE CONFIG: model={args.model} layers={args.layers} hidden={args.hidden} seq={S} per_gpu_batch={B} remat={args.remat}",
+                   "global_batch": B * world, "seq_len": S, "parallelism": (f"fsdp{world}" + (f"+ep{world}" if args.model == "mixtral_ep" else "")) if world > 1 else "single-gpu",
                    "microbatch_per_gpu": micro, "optimizer": "AdamW fp32 master + fp32 moments, global-norm clip 1.0",
                    "params": n_params, "l2_note": "inputs (activations + 13.5 GB of weights per pass) far exceed the 126 MB L2",
                    "attention_backend": args.attn or "default",
-                   "collectives": comm_used},
+                   "collectives": comm_used, "expert_exchange": os.environ.get("LEVANTER_B200_EP_COMM", "peer") if args.model == "mixtral_ep" else None},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4, "final_loss": last_loss},
