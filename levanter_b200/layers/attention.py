@@ -597,3 +597,12 @@ class KvPageCache:
     def copy_page(self, src_page: int, dst_page: int) -> "KvPageCache":
         self.kv_pages[dst_page].copy_(self.kv_pages[src_page])
         return self
+
+
+def default_ragged_paged_attention(q, kv_pages, kv_lens, page_indices, cu_q_lens, num_seqs, sm_scale: float = 1.0, soft_cap=None):
+    """The plain statement of ragged paged attention (src/levanter/layers/attention.py:1856-1991): per sequence, causal by
+    absolute position over the pages it owns.  The engine calls ``ops.paged_attention.ragged_paged_attention`` (the CUDA kernel
+    on a B200); this is its oracle under the reference's name."""
+    from ..ops.paged_attention import ragged_paged_attention_reference
+
+    return ragged_paged_attention_reference(q, kv_pages, kv_lens, page_indices, cu_q_lens, num_seqs, sm_scale, soft_cap)

@@ -92,3 +92,30 @@ def _shadow_with(model: nn.Module, params: Dict[str, torch.Tensor], mp: Policy) 
 
 def make_training_key(seed: int) -> torch.Tensor:
     return torch.tensor([seed & 0xFFFFFFFF, 0], dtype=torch.int64)
+
+
+def saveable_training_mask(state: TrainerState, is_trainable: Optional[Callable[[str], bool]] = None) -> Dict[str, Any]:
+    """Which parts of a trainer state a checkpoint holds (src/levanter/trainer_state.py:229-240): the step, the RNG key, the
+    optimizer state and the model average whole, and of the model only the trainable floating-point parameters (frozen
+    weights come from wherever the run initialised them, e.g. the base model of a LoRA run).  Returned as a dict with a
+    ``model`` entry mapping parameter names to booleans."""
+    keep = is_trainable if is_trainable is not None else (state.is_trainable or (lambda name: True))
+    model_mask = {name: bool(p.requires_grad and p.is_floating_point() and keep(name)) for name, p in state.model.named_parameters()}
+    return {"step": True, "training_key": True, "opt_state": True, "model_averaging": state.model_averaging is not None, "model": model_mask}
+
+
+def take_train_step(optimizer, params: Dict[str, torch.Tensor], opt_state, grads: Dict[str, torch.Tensor], *,
+                    obj_fun: Optional[Callable] = None, loss: Optional[torch.Tensor] = None,
+                    is_trainable: Optional[Callable[[str], bool]] = None):
+    """One optimizer step on a name -> tensor tree, outside the sharded engine (src/levanter/trainer_state.py:243-275):
+    gradients and parameters are restricted to the trainable names, the transformation sees ``obj_fn`` (Sophia's Hessian
+    estimate) and ``loss`` (skip-step), and the updates are added in place.  Returns ``(params, new optimizer state, updates)``.
+    The engine's own step (``ShardedEngine.step``) is the sharded form of the same call."""
+    from .optim import transforms as T
+
+    keep = is_trainable or (lambda name: True)
+    train_grads = {k: g for k, g in grads.items() if g is not None and keep(k)}
+    train_params = {k: params[k] for k in train_grads}
+    updates, opt_state = optimizer.update(train_grads, opt_state, train_params, obj_fn=obj_fun, loss=loss)
+    T.apply_updates(train_params, updates)
+    return params, opt_state, updates

@@ -1,0 +1,68 @@
+"""Functional helpers kept for parity with the reference's public surface: a train step on a plain parameter tree, the
+saveable-state mask, matrix views of linear layers, and the paged-attention oracle under its reference name."""
+import torch
+
+
+def test_take_train_step_matches_manual_adam_and_respects_the_trainable_filter():
+    from levanter_b200.optim import AdamConfig
+    from levanter_b200.trainer_state import take_train_step
+
+    torch.manual_seed(0)
+    params = {"a.weight": torch.randn(4, 3), "b.weight": torch.randn(2, 2)}
+    before = {k: v.clone() for k, v in params.items()}
+    grads = {k: torch.randn_like(v) for k, v in params.items()}
+    opt = AdamConfig(learning_rate=1e-2, weight_decay=0.0, warmup=0.0, lr_schedule="constant", min_lr_ratio=1.0, max_grad_norm=None).build(10)
+    state = opt.init({"a.weight": params["a.weight"]})
+    out, state, updates = take_train_step(opt, params, state, grads, is_trainable=lambda n: n.startswith("a."))
+    assert out is params and set(updates) == {"a.weight"}
+    assert torch.equal(params["b.weight"], before["b.weight"])  # frozen
+    # first Adam step with bias correction: -lr * sign-like g / (|g| + eps)
+    g = grads["a.weight"]
+    expect = before["a.weight"] - 1e-2 * g / (g.abs() + 1e-8)
+    torch.testing.assert_close(params["a.weight"], expect, atol=1e-5, rtol=1e-4)
+
+
+def test_saveable_training_mask_keeps_trainable_float_parameters_only():
+    from levanter_b200.config import Policy
+    from levanter_b200.models.llama import LlamaConfig
+    from levanter_b200.parallel.engine import ShardedEngine
+    from levanter_b200.trainer_state import TrainerState, make_training_key, saveable_training_mask
+
+    model = LlamaConfig(seq_len=8, hidden_dim=16, intermediate_dim=32, num_layers=1, num_heads=2, num_kv_heads=2).build(32, seed=0)
+    trainable = lambda n: "mlp" in n  # noqa: E731
+    eng = ShardedEngine(model, Policy.parse("f32"), None, device="cpu", is_trainable=trainable)
+    st = TrainerState(0, model, eng, make_training_key(0), Policy.parse("f32"), None, trainable)
+    mask = saveable_training_mask(st)
+    assert mask["step"] and mask["training_key"] and mask["opt_state"] and not mask["model_averaging"]
+    assert any(mask["model"].values()) and all(("mlp" in k) == v for k, v in mask["model"].items())
+
+
+def test_linear_layers_as_matrices():
+    from levanter_b200.optim.util import flatten_linear_layers, map_flattened_linear_layers, unflatten_linear_layers
+
+    tree = {"w": torch.randn(4, 3), "experts": torch.randn(2, 5, 4, 3), "bias": torch.randn(4), "none": None}
+    flat = flatten_linear_layers(tree)
+    assert flat["w"].shape == (1, 4, 3) and flat["experts"].shape == (10, 4, 3) and flat["bias"].shape == (4,)
+    back = unflatten_linear_layers(tree, flat)
+    assert all(back[k] is None if tree[k] is None else torch.equal(back[k], tree[k]) for k in tree)
+    # per-matrix map: Frobenius normalisation of each matrix, biases doubled
+    out = map_flattened_linear_layers(lambda m: m / m.norm(), tree, or_else=lambda v: 2 * v)
+    assert out["experts"].shape == tree["experts"].shape
+    torch.testing.assert_close(out["experts"].reshape(10, -1).norm(dim=1), torch.ones(10))
+    torch.testing.assert_close(out["w"].norm(), torch.tensor(1.0))
+    assert torch.equal(out["bias"], 2 * tree["bias"]) and out["none"] is None
+
+
+def test_default_ragged_paged_attention_is_the_oracle():
+    from levanter_b200.layers.attention import default_ragged_paged_attention
+    from levanter_b200.ops.paged_attention import ragged_paged_attention_reference
+
+    torch.manual_seed(0)
+    q = torch.randn(3, 4, 8)
+    pages = torch.randn(6, 4, 4, 8)  # [page, slot, 2 * kv_head, head]
+    kv_lens = torch.tensor([5, 6], dtype=torch.int32)
+    page_idx = torch.tensor([[0, 1, -1], [2, 3, -1]], dtype=torch.int32)
+    cu = torch.tensor([0, 1, 3], dtype=torch.int32)
+    a = default_ragged_paged_attention(q, pages, kv_lens, page_idx, cu, 2, 0.35)
+    b = ragged_paged_attention_reference(q, pages, kv_lens, page_idx, cu, 2, 0.35)
+    assert torch.equal(a, b)
