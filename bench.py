@@ -101,8 +101,8 @@ class ClockSampler:
 
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
-                      "offline install of /root/reference fails: build backend uv_build and its dependencies "
-                      "(jax, haliax, equinox, optax, jmp, draccus, tensorstore) are not in /opt/wheelhouse"}))
+                      "offline install of the reference fails: its build backend (uv_build) and its dependencies "
+                      "(jax, haliax, equinox, optax, jmp, draccus, tensorstore) are not in the offline wheelhouse"}))
     return 0
 
 
