@@ -14,6 +14,8 @@
 // kernel merges the partitions of each (token, head).  Nothing here synchronises with the host: sequence boundaries,
 // lengths and the number of live sequences are read from device arrays, padding tokens produce zeros.
 #include "common.cuh"
+#include <cstdlib>
+#include <string>
 
 namespace lvb {
 namespace paged {
@@ -253,6 +255,188 @@ __global__ void __launch_bounds__(kThreads) paged_attention_kernel(Params p) {
   }
 }
 
+// Staged variant for D = 128 and at most 8 query heads per KV head.  K and V of a key are adjacent in the cache (512 bytes
+// per (slot, kv head)), so a stage of 32 keys is 16 KB that the CTA copies into shared memory with fully coalesced 16-byte
+// cp.async requests (one pass over the cache instead of separate K and V passes with strided rows), double-buffered
+// against the arithmetic.  Scores, an online softmax (running maximum and sum per head) and P.V all run from shared
+// memory; rows are padded to 576 bytes, which makes the 16-byte reads of a quarter-warp conflict-free in both phases.
+constexpr int kStageKeys = 32;
+constexpr int kStageRow = 2 * 128 + 32;  // bf16 elements per staged row: K (128), V (128), padding (32)
+constexpr int kStagedMaxG = 8;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads) paged_attention_staged_kernel(Params p) {
+  constexpr int D = 128;
+  const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
+  const int G = p.H / p.KV;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ __align__(16) __nv_bfloat16 s_kv[2][kStageKeys * kStageRow];  // 36 KB
+  __shared__ __align__(16) float s_q[kStagedMaxG * D];                      // 4 KB; reused for the final reduction
+  __shared__ float s_p[kStagedMaxG * kStageKeys];
+  __shared__ float s_m[kStagedMaxG], s_l[kStagedMaxG], s_alpha[kStagedMaxG];
+  __shared__ int s_rows[kPart];
+
+  int seq = 0, ctx = 0;
+  const bool live = locate(p, t, seq, ctx);
+  const int k0 = part * kPart;
+  if (!live || k0 >= ctx) {
+    if (part == 0 && !live) {
+      for (int i = threadIdx.x; i < G * D; i += kThreads)
+        p.out[(static_cast<long long>(t) * p.H + kvh * G) * D + i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  const int nk = min(kPart, ctx - k0);
+  for (int i = threadIdx.x; i < G * D; i += kThreads)
+    s_q[i] = __bfloat162float(p.q[(static_cast<long long>(t) * p.H + kvh * G) * D + i]) * p.scale;
+  for (int i = threadIdx.x; i < nk; i += kThreads) {
+    const int key = k0 + i;
+    const int page = p.page_indices[seq * p.pages_per_seq + key / p.page_size];
+    s_rows[i] = (page >= 0 && page < p.num_pages) ? page * p.page_size + key % p.page_size : -1;
+  }
+  if (threadIdx.x < kStagedMaxG) { s_m[threadIdx.x] = -INFINITY; s_l[threadIdx.x] = 0.f; }
+  __syncthreads();
+
+  const long long tok_stride = 2LL * p.KV * D;
+  const int stages = (nk + kStageKeys - 1) / kStageKeys;
+  // copy of one stage: 32 rows x 32 chunks of 16 bytes, 8 per thread; rows without a key (or a bad page) are zero-filled
+  auto issue = [&](int st) {
+    __nv_bfloat16* dst = s_kv[st & 1];
+    for (int c = threadIdx.x; c < kStageKeys * 32; c += kThreads) {
+      const int r = c >> 5, ch = c & 31;
+      const int i = st * kStageKeys + r;
+      const int slot = i < nk ? s_rows[i] : -1;
+      __nv_bfloat16* d = dst + r * kStageRow + ch * 8;
+      if (slot >= 0) cp_async_16(d, p.kv_pages + slot * tok_stride + (2LL * kvh) * D + ch * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(0);
+
+  const int key_l = threadIdx.x >> 2, quarter = threadIdx.x & 3;   // scoring: 4 threads per key
+  const int dg = threadIdx.x & 15, kg = threadIdx.x >> 4;          // P.V: 16 dimension groups x 8 key groups
+  float o[kStagedMaxG][8];
+#pragma unroll
+  for (int g = 0; g < kStagedMaxG; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
+
+  for (int st = 0; st < stages; ++st) {
+    if (st + 1 < stages) issue(st + 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");  // keep "all but the newest group" meaning the current stage
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const __nv_bfloat16* buf = s_kv[st & 1];
+    {  // scores of key key_l: this thread takes chunks quarter, quarter + 4, ... of the K row
+      float acc[kStagedMaxG];
+#pragma unroll
+      for (int g = 0; g < kStagedMaxG; ++g) acc[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int ch = j * 4 + quarter;
+        float kf[8];
+        load_row<8>(buf + key_l * kStageRow + ch * 8, kf);
+#pragma unroll
+        for (int g = 0; g < kStagedMaxG; ++g) {
+          if (g < G) {
+            const float4 qa = *reinterpret_cast<const float4*>(s_q + g * D + ch * 8);
+            const float4 qb = *reinterpret_cast<const float4*>(s_q + g * D + ch * 8 + 4);
+            acc[g] = fmaf(kf[0], qa.x, acc[g]); acc[g] = fmaf(kf[1], qa.y, acc[g]);
+            acc[g] = fmaf(kf[2], qa.z, acc[g]); acc[g] = fmaf(kf[3], qa.w, acc[g]);
+            acc[g] = fmaf(kf[4], qb.x, acc[g]); acc[g] = fmaf(kf[5], qb.y, acc[g]);
+            acc[g] = fmaf(kf[6], qb.z, acc[g]); acc[g] = fmaf(kf[7], qb.w, acc[g]);
+          }
+        }
+      }
+      const int i = st * kStageKeys + key_l;
+      const bool valid = i < nk && s_rows[i] >= 0;
+#pragma unroll
+      for (int g = 0; g < kStagedMaxG; ++g) {
+        if (g < G) {
+          float v = acc[g];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          if (p.soft_cap > 0.f) v = p.soft_cap * tanhf(v / p.soft_cap);
+          if (quarter == 0) s_p[g * kStageKeys + key_l] = valid ? v : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+    // online softmax: warp w updates heads w, w + 4; one key per lane
+    for (int g = warp; g < G; g += kThreads / 32) {
+      const float sc = s_p[g * kStageKeys + lane];
+      float m_st = sc;
+#pragma unroll
+      for (int of = 16; of > 0; of >>= 1) m_st = fmaxf(m_st, __shfl_xor_sync(0xffffffffu, m_st, of));
+      const float m_old = s_m[g];
+      const float m_new = fmaxf(m_old, m_st);
+      const float e = (sc == -INFINITY || m_new == -INFINITY) ? 0.f : __expf(sc - m_new);
+      const float alpha = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
+      const float sum = warp_sum(e);
+      s_p[g * kStageKeys + lane] = e;
+      if (lane == 0) { s_m[g] = m_new; s_l[g] = s_l[g] * alpha + sum; s_alpha[g] = alpha; }
+    }
+    __syncthreads();
+    {  // P.V: keys kg, kg + 8, kg + 16, kg + 24 of the stage; 8 output dimensions per thread
+#pragma unroll
+      for (int g = 0; g < kStagedMaxG; ++g) {
+        if (g < G) {
+          const float a = s_alpha[g];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[g][e] *= a;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kStageKeys / 8; ++j) {
+        const int r = kg + 8 * j;
+        float vf[8];
+        load_row<8>(buf + r * kStageRow + D + dg * 8, vf);
+#pragma unroll
+        for (int g = 0; g < kStagedMaxG; ++g) {
+          if (g < G) {
+            const float w = s_p[g * kStageKeys + r];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[g][e] = fmaf(w, vf[e], o[g][e]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // the next iteration's copy overwrites the other buffer, its scores overwrite s_p
+  }
+  // sum the 8 key groups (through the first stage buffer, which nothing reads any more) and write the result
+  float* s_red = reinterpret_cast<float*>(&s_kv[0][0]);  // 8 groups x G x 128 floats <= 32 KB
+#pragma unroll
+  for (int g = 0; g < kStagedMaxG; ++g) {
+    if (g < G) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_red[(kg * kStagedMaxG + g) * D + dg * 8 + e] = o[g][e];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kThreads) {
+    const int g = idx / D, d = idx - g * D;
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += s_red[(k * kStagedMaxG + g) * D + d];
+    const long long hrow = static_cast<long long>(t) * p.H + kvh * G + g;
+    if (p.parts == 1) {
+      const float l = s_l[g];
+      p.out[hrow * D + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+    } else {
+      p.part_o[(hrow * p.parts + part) * D + d] = acc;
+    }
+  }
+  if (p.parts > 1 && threadIdx.x < G) {
+    const long long hrow = static_cast<long long>(t) * p.H + kvh * G + threadIdx.x;
+    p.part_ml[(hrow * p.parts + part) * 2 + 0] = s_m[threadIdx.x];
+    p.part_ml[(hrow * p.parts + part) * 2 + 1] = s_l[threadIdx.x];
+  }
+}
+
 // One CTA per (token, head): merge the partials of the partitions that were live for this token.
 template <int D>
 __global__ void __launch_bounds__(D <= 128 ? 128 : 256) paged_merge_kernel(Params p) {
@@ -279,10 +463,22 @@ __global__ void __launch_bounds__(D <= 128 ? 128 : 256) paged_merge_kernel(Param
   }
 }
 
+// LVB_PAGED_ATTENTION=direct selects the kernel that reads the cache rows straight from global memory for every shape.
+inline bool staged_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LVB_PAGED_ATTENTION");
+    return !(v != nullptr && std::string(v) == "direct");
+  }();
+  return on;
+}
+
 template <int D>
 int launch(const Params& p, cudaStream_t s) {
   dim3 grid(p.T, p.KV, p.parts);
-  paged_attention_kernel<D><<<grid, kThreads, 0, s>>>(p);
+  if (D == 128 && p.H / p.KV <= kStagedMaxG && staged_enabled())
+    paged_attention_staged_kernel<<<grid, kThreads, 0, s>>>(p);
+  else
+    paged_attention_kernel<D><<<grid, kThreads, 0, s>>>(p);
   if (p.parts > 1) paged_merge_kernel<D><<<dim3(p.T, p.H), D <= 128 ? 128 : 256, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
