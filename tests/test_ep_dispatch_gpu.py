@@ -30,7 +30,7 @@ def _expected_layout(assign, W, E):
     return layouts, offsets
 
 
-@pytest.mark.parametrize("W,E,T,k,H", [(2, 4, 300, 2, 256), (4, 8, 517, 2, 128), (2, 8, 64, 1, 64)])
+@pytest.mark.parametrize("W,E,T,k,H", [(2, 4, 300, 2, 256), (4, 8, 517, 2, 128), (2, 8, 64, 1, 64), (8, 8, 200, 2, 128)])
 def test_exchange_kernels_with_ranks_emulated_on_one_device(W, E, T, k, H):
     from levanter_b200.ops import ep_dispatch as K
     from levanter_b200.ops import lib
