@@ -85,6 +85,7 @@ class Checkpointer:
 
     def on_step(self, info, force: bool = False):
         step = info.step
+        self._manager.drain()  # surface an error from a commit that finished in the background
         if step == 0:
             self._last_save_time = self._dt_now_injection()
             if not force:

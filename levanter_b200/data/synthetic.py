@@ -35,7 +35,10 @@ class SyntheticLmDataset(AsyncDataset[LmExample]):
         return self.length
 
     def tokens_at(self, index: int) -> torch.Tensor:
-        rng = np.random.Generator(np.random.Philox(key=self.seed, counter=index))
+        # The example index is part of the Philox KEY, not the counter: the counter advances by one per block of draws, so
+        # streams that differ only in their starting counter are shifted copies of one another.
+        key = np.array([np.uint64(self.seed & 0xFFFFFFFFFFFFFFFF), np.uint64(index & 0xFFFFFFFFFFFFFFFF)], dtype=np.uint64)
+        rng = np.random.Generator(np.random.Philox(key=key))
         return torch.from_numpy(rng.integers(0, self.vocab_size, size=self.seq_len, dtype=np.int32))
 
     async def get_batch(self, indices: Sequence[int]):

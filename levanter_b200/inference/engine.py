@@ -476,6 +476,10 @@ class InferenceEngine:
                 out_tok[r], out_lp[r] = d_tok, lp
         toks = out_tok.cpu().numpy()
         lps = out_lp.cpu().numpy()
+        if dev.type == "cuda":
+            from ..ops import lib as _lib
+
+            _lib.check_status()  # e.g. a tensor-parallel all-reduce whose wait for a peer ran out: the tokens are not to be trusted
         t_post = time.perf_counter()
         self.stats["decode_device_seconds"] = self.stats.get("decode_device_seconds", 0.0) + (t_post - t_dev)
         # apply stop conditions round by round; a finished sequence's later tokens are dropped

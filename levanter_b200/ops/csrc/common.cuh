@@ -17,11 +17,11 @@
 
 namespace lvb {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: the default, see wait_limit_ns
 
 // status word layout (int32[8], owned by the caller, zeroed by the caller)
 //   [0] first error code (0 = ok)   [1] blockIdx.x   [2] role / site id
-//   [3] extra (stage, tile, ...)
+//   [3] extra (stage, tile, ...)    [4] wait limit in milliseconds set by the host (0 = the 2 s default)
 enum StatusCode : int {
   kOk = 0,
   kTimeoutMbarrier = 1,
@@ -38,6 +38,16 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// The limit of every bounded wait: the host may raise it (entry [4] of the status word, milliseconds) above the skew it
+// expects between ranks; read only on the slow path of a wait.
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int* status) {
+  if (status != nullptr) {
+    const int ms = reinterpret_cast<const volatile int*>(status)[4];
+    if (ms > 0) return static_cast<unsigned long long>(ms) * 1000000ull;
+  }
+  return kWaitLimitNs;
 }
 
 __device__ __forceinline__ void record_status(int* status, int code, int site, int extra) {
@@ -88,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > wait_limit_ns(status)) {
         *abort_flag = 1;
         record_status(status, kTimeoutMbarrier, site, extra);
         return false;
@@ -126,16 +136,18 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded wait until *flag >= target (sys: the writers may be other GPUs).  Same failure protocol as mbar_wait.
+// Counters that only ever grow are compared modulo 2^32 (difference, not magnitude), so a long-lived process may let them
+// wrap; the host passes its running target reduced to 32 bits.
 __device__ __forceinline__ bool flag_wait_ge(const int* flag, int target, bool sys, volatile int* abort_flag, int* status,
                                              int site, int extra) {
   unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     const int v = sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
-    if (v >= target) return true;
+    if (static_cast<int>(static_cast<unsigned>(v) - static_cast<unsigned>(target)) >= 0) return true;
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > wait_limit_ns(status)) {
         *abort_flag = 1;
         record_status(status, kTimeoutFlag, site, extra);
         return false;

@@ -29,8 +29,28 @@ def cuda_ok() -> bool:
     return torch.cuda.is_available()
 
 
+_tls = threading.local()
+
+
+class reference_ops:
+    """Context manager: inside it :func:`available` is False on this thread, so every op takes its differentiable PyTorch
+    statement.  Used for passes that need second derivatives (Sophia's Hessian-vector product): the hand-written kernels
+    define first derivatives only."""
+
+    def __enter__(self):
+        self._prev = getattr(_tls, "reference", 0)
+        _tls.reference = self._prev + 1
+        return self
+
+    def __exit__(self, *exc):
+        _tls.reference = self._prev
+        return False
+
+
 def available() -> bool:
     """True when the native kernels can run here (a CUDA device of compute capability 10.x)."""
+    if getattr(_tls, "reference", 0):
+        return False
     if not cuda_ok():
         return False
     major, _ = torch.cuda.get_device_capability()
@@ -85,12 +105,27 @@ def status_buffer() -> torch.Tensor:
     buf = _status.get(dev)
     if buf is None:
         buf = torch.zeros(8, dtype=torch.int32, device=f"cuda:{dev}")
+        if _wait_limit_ms:
+            buf[4] = _wait_limit_ms
         _status[dev] = buf
     return buf
 
 
 class KernelStatusError(RuntimeError):
     pass
+
+
+_wait_limit_ms = 0
+
+
+def set_wait_limit(seconds: float) -> None:
+    """Limit of the kernels' bounded waits (default 2 s).  Set it above the largest skew expected between ranks: a rank that
+    reaches a peer-synchronised kernel later than that (a rank-0-only hook, an uneven checkpoint copy) makes its peers' waits
+    run out, which the step loop then reports as :class:`KernelStatusError`."""
+    global _wait_limit_ms
+    _wait_limit_ms = max(0, int(seconds * 1000))
+    for buf in _status.values():
+        buf[4] = _wait_limit_ms
 
 
 def check_status(reset: bool = True) -> None:
@@ -101,18 +136,24 @@ def check_status(reset: bool = True) -> None:
         vals = buf.tolist()
         if vals[0] != 0:
             if reset:
-                buf.zero_()
+                buf[:4].zero_()
             names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument", 4: "bounds check"}
+            hint = ""
+            if vals[0] == 4 and vals[2] in (30, 31, 32):
+                hint = (": the expert-parallel exchange received more rows than its capacity and dropped some; raise "
+                        "expert_capacity_factor or select ep_comm: nccl")
+            elif vals[0] in (1, 2):
+                hint = ": a peer did not arrive within the wait limit (see TrainerConfig.kernel_wait_limit)"
             raise KernelStatusError(
                 f"kernel status on cuda:{dev}: {names.get(vals[0], vals[0])} "
-                f"(cta={vals[1]}, site={vals[2]}, extra={vals[3]})"
+                f"(cta={vals[1]}, site={vals[2]}, extra={vals[3]}){hint}"
             )
 
 
 def clear_status() -> None:
     """Zero the status word without raising (after a time-out the caller expected)."""
     for buf in _status.values():
-        buf.zero_()
+        buf[:4].zero_()
 
 
 def check_rc(rc: int, what: str) -> None:

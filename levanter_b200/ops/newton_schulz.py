@@ -3,9 +3,14 @@
 Five (or ten) iterations of ``A = X X^T; B = b A + c A^2; X = a X + B X`` with ``(a, b, c) = (3.4445, -4.7750, 2.0315)``
 on the Frobenius-normalised matrix (transposed first when it is tall).  On a B200 the three products per iteration run on
 the tcgen05 GEMM in bf16 with fp32 accumulation; none of them needs a transposed copy because the kernel reads either
-operand K-major or MN-major.  The reference reshards each matrix over the whole mesh before iterating (:189-192); here
-whole matrices are distributed round-robin over the data ranks by the optimizer, so every product is local."""
+operand K-major or MN-major.  The reference reshards each matrix over the whole mesh before iterating (:189-192); here a
+call of :func:`zeropower_via_newtonschulz5` works on one whole local matrix, and :func:`orthogonalize_tree` deals the
+matrices of a step out over the ranks that hold identical copies of them (largest first, to the least loaded rank), each
+rank iterates its own share and broadcasts the results: the step costs ``1/W`` of the matrix products per rank plus one
+pass of the orthogonalised matrices over the interconnect, and no matrix is ever cut up."""
 from __future__ import annotations
+
+from typing import Dict, Optional
 
 import torch
 
@@ -41,3 +46,43 @@ def zeropower_via_newtonschulz5(X: torch.Tensor, steps: int = 5, eps: float = 1e
     if transpose:
         X = X.t()
     return X.to(out_dtype)
+
+
+_layer_group = None
+
+
+def set_layer_parallel_group(group) -> None:
+    """Ranks of ``group`` hold identical optimizer inputs (unsharded optimizer on data-parallel ranks): let them share the
+    orthogonalisations.  ``None`` switches the sharing off."""
+    global _layer_group
+    _layer_group = group
+
+
+def assign_owners(costs: Dict[str, float], world: int) -> Dict[str, int]:
+    """Deterministic longest-processing-time assignment of matrices to ranks (the same on every rank)."""
+    load = [0.0] * world
+    owner: Dict[str, int] = {}
+    for k in sorted(costs, key=lambda k: (-costs[k], k)):
+        r = min(range(world), key=lambda i: (load[i], i))
+        owner[k] = r
+        load[r] += costs[k]
+    return owner
+
+
+def orthogonalize_tree(mats: Dict[str, torch.Tensor], steps: int = 5, eps: float = 1e-7) -> Dict[str, torch.Tensor]:
+    """Newton-Schulz on every matrix of ``mats``, shared over the layer-parallel group when one is set."""
+    import torch.distributed as dist
+
+    group = _layer_group
+    world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
+    if world <= 1:
+        return {k: zeropower_via_newtonschulz5(m, steps=steps, eps=eps) for k, m in mats.items()}
+    rank = dist.get_rank(group)
+    owner = assign_owners({k: float(min(m.shape) ** 2 * max(m.shape)) for k, m in mats.items()}, world)
+    out: Dict[str, torch.Tensor] = {}
+    for k, m in mats.items():
+        out[k] = zeropower_via_newtonschulz5(m, steps=steps, eps=eps).contiguous() if owner[k] == rank else torch.empty_like(m)
+    pending = [dist.broadcast(out[k], src=dist.get_global_rank(group, owner[k]), group=group, async_op=True) for k in sorted(out)]
+    for w in pending:
+        w.wait()
+    return out

@@ -4,7 +4,9 @@
 Linear weights (2-D ``[out, in]``; never embeddings or the LM head) get ``momentum(0.95, nesterov)`` -> five Newton-Schulz
 iterations -> scale ``sqrt(max(1, out/in))`` (or Kimi's ``0.2 sqrt(max(out, in))``) -> weight decay -> ``-lr``.  Biases, norms,
 embeddings and the LM head use AdamW with its own ``adam_lr`` (:91-111).  Muon needs whole matrices, so the engine runs it
-unsharded (gradients all-reduced, every rank updates full tensors)."""
+unsharded (gradients all-reduced, momentum on every rank); the Newton-Schulz iterations, which are nearly all of the
+optimizer's arithmetic, are dealt out matrix by matrix over the data ranks (``ops/newton_schulz.py:orthogonalize_tree``)
+where the reference reshards every matrix over the mesh (:186-194)."""
 from __future__ import annotations
 
 import math
@@ -13,7 +15,7 @@ from typing import Dict, NamedTuple, Optional
 
 import torch
 
-from ..ops.newton_schulz import zeropower_via_newtonschulz5
+from ..ops.newton_schulz import orthogonalize_tree
 from . import transforms as T
 from .config import OptimizerConfig, ParamInfo, _decay
 from .transforms import GradientTransformation, Tree
@@ -36,15 +38,15 @@ def scale_with_muon(momentum: float = 0.95, nesterov: bool = True, steps: int = 
             g = updates[k]
             buf = state.momentum_buffer[k]
             buf.mul_(momentum).add_(g)
-            u = momentum * buf + g if nesterov else buf
-            if u.dim() == 2:
-                o = zeropower_via_newtonschulz5(u, steps=steps, eps=muon_eps)
-                if not use_kimi_scaling:
-                    o = o * math.sqrt(max(1.0, o.shape[0] / o.shape[1]))
-                else:
-                    o = o * (0.2 * math.sqrt(max(o.shape[0], o.shape[1])))
-                u = o
-            out[k] = u
+            out[k] = momentum * buf + g if nesterov else buf
+        # the matrices of the step are orthogonalised together: on several ranks each one is iterated by one rank only
+        ortho = orthogonalize_tree({k: u for k, u in out.items() if u is not None and u.dim() == 2}, steps=steps, eps=muon_eps)
+        for k, o in ortho.items():
+            if not use_kimi_scaling:
+                o = o * math.sqrt(max(1.0, o.shape[0] / o.shape[1]))
+            else:
+                o = o * (0.2 * math.sqrt(max(o.shape[0], o.shape[1])))
+            out[k] = o
         return out, state
 
     return GradientTransformation(init, update)

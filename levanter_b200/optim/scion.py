@@ -9,7 +9,7 @@ from typing import Dict, NamedTuple, Optional
 
 import torch
 
-from ..ops.newton_schulz import zeropower_via_newtonschulz5
+from ..ops.newton_schulz import orthogonalize_tree
 from . import transforms as T
 from .config import OptimizerConfig, ParamInfo, _decay
 from .muon import linear_weight_labels
@@ -44,13 +44,10 @@ def scale_with_scion(momentum: float = 0.95, steps: int = 5, scion_eps: float = 
         for k in T.tree_keys(updates):
             buf = state.momentum_buffer[k]
             buf.mul_(momentum).add_(updates[k], alpha=1 - momentum)
-            u = buf
-            if u.dim() == 2:
-                o = zeropower_via_newtonschulz5(u, steps=steps, eps=scion_eps)
-                u = o * math.sqrt(max(1.0, o.shape[0] / o.shape[1]))
-            else:
-                u = u.clone()
-            out[k] = u
+            out[k] = buf if buf.dim() == 2 else buf.clone()
+        ortho = orthogonalize_tree({k: u for k, u in out.items() if u is not None and u.dim() == 2}, steps=steps, eps=scion_eps)
+        for k, o in ortho.items():
+            out[k] = o * math.sqrt(max(1.0, o.shape[0] / o.shape[1]))
         return out, state
 
     return GradientTransformation(init, update)

@@ -417,11 +417,17 @@ class ShardedEngine:
         else:
             grads = self.grad_tree()
             params = self.master_tree()
+            from ..ops.newton_schulz import set_layer_parallel_group
+
             T.set_norm_reduce_group(self.data_group if (self.world > 1 and self.shard_optimizer) else None)
+            # unsharded optimizer on several data ranks: every rank holds the same gradients, so matrix-valued work
+            # (Newton-Schulz) is dealt out over them instead of being repeated on each
+            set_layer_parallel_group(self.data_group if (self.world > 1 and not self.shard_optimizer) else None)
             try:
                 updates, self.opt_state = self.opt.update(grads, self.opt_state, params, loss=loss, **extra)
             finally:
                 T.set_norm_reduce_group(None)
+                set_layer_parallel_group(None)
             T.apply_updates(params, updates)
         self.publish_params()
         if self._sym_grad is not None:

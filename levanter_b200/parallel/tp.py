@@ -128,8 +128,10 @@ class TensorParallel:
         f = lib.fn("lvb_all_reduce_one_shot", [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_longlong, c.c_longlong,
                                                c.c_int, c.c_int, c.c_int, c.c_void_p, c.c_void_p])
         # the counters only grow: after this call each of them has received `blocks` more arrivals (one per block of the pusher)
-        self._os_arrivals[parity] += blocks
-        rc = f(x.data_ptr(), x.data_ptr(), stage, flags, sym.rank, W, nbytes, cap, blocks, self._os_arrivals[parity],
+        # (kept modulo 2^32 and handed over as a signed 32-bit value; the kernel compares differences, so wrapping is harmless)
+        self._os_arrivals[parity] = (self._os_arrivals[parity] + blocks) & 0xFFFFFFFF
+        target = self._os_arrivals[parity] - (1 << 32) if self._os_arrivals[parity] >= (1 << 31) else self._os_arrivals[parity]
+        rc = f(x.data_ptr(), x.data_ptr(), stage, flags, sym.rank, W, nbytes, cap, blocks, target,
                1 if x.dtype == torch.float32 else 0, lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_all_reduce_one_shot")
         self.kernel_all_reduces += 1

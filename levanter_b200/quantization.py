@@ -2,8 +2,9 @@
 ``trainer.quantization``, src/levanter/trainer.py:648, config/gpt2_small_fast_fp8.yaml:17-18).
 
 ``fp8: true`` selects fp8 GEMMs for the Linear layers named by ``targets`` (all by default): e4m3 for forward operands,
-e5m2 for output gradients, with one scale per 128 values along the reduction dimension (block scaling) instead of the
-reference's per-tensor delayed scaling.  ``quantize_linear_layers`` swaps matching ``Linear`` modules for ``Fp8Linear``;
+e5m2 for output gradients, with one scale per tensor taken from a rolling history of absolute maxima (delayed scaling, as
+in the reference).  ``block_size`` is accepted for configs that name it and is not used: scaling is per tensor.
+``quantize_linear_layers`` swaps matching ``Linear`` modules for ``Fp8Linear``;
 master weights, optimizer state and checkpoints are unchanged."""
 from __future__ import annotations
 

@@ -187,14 +187,28 @@ def reference_key_for(name: str) -> Tuple[str, Optional[int]]:
 # ------------------------------------------------------------------------------------------------ save
 class AsyncSerializer:
     """Background writer: ``serialize`` returns once every leaf has been copied to host memory; chunk compression and
-    file writes proceed on a thread pool; ``wait_until_finished`` joins them and runs commit callbacks."""
+    file writes proceed on a thread pool.  A committer thread joins each save's writes as soon as they finish, agrees with
+    the other ranks that all of them are done, and then runs the save's commit callback, so a save made in the middle of a
+    run becomes discoverable shortly after its writes complete, not when the run ends (the reference commits from its async
+    manager's background thread, src/levanter/tensorstore_serialization.py:36-96).
+
+    The ranks agree through marker files under ``<sync_dir>/.commit/`` (collectives must not be issued off the main
+    thread): every rank drops ``rank-<r>-<save id>`` when its own writes are durable; rank 0 waits for all of them, runs its callback
+    (which writes ``metadata.json``) and drops ``done-<save id>``; the other ranks run theirs once that file exists."""
+
+    COMMIT_TIMEOUT_S = 1800.0
 
     def __init__(self, max_workers: int = 8):
         self._pool = ThreadPoolExecutor(max_workers=max_workers)
-        self._pending: List[Tuple[List[Future], Optional[Callable[[], None]]]] = []
         self._lock = threading.Lock()
+        self._idle = threading.Condition(self._lock)
+        self._queue: List[Tuple[List[Future], Optional[Callable[[], None]], Optional[str], int, int, str]] = []
+        self._in_flight = 0
+        self._errors: List[BaseException] = []
+        self._committer: Optional[threading.Thread] = None
 
-    def serialize(self, leaves: Sequence[Tuple[str, Any]], on_commit: Optional[Callable[[], None]] = None) -> None:
+    def serialize(self, leaves: Sequence[Tuple[str, Any]], on_commit: Optional[Callable[[], None]] = None,
+                  sync_dir: Optional[str] = None) -> None:
         rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
         world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
         futures: List[Future] = []
@@ -208,19 +222,92 @@ class AsyncSerializer:
                 t = torch.from_numpy(np.ascontiguousarray(t))
             host = t.detach().to("cpu", copy=True) if t.device.type != "cpu" else t.detach().clone()
             futures.append(self._pool.submit(_write_leaf, path, host))
+        nonce = ""
+        if world > 1 and sync_dir is not None:
+            # a name for this save that every rank knows (a directory can be written more than once, e.g. after a resume)
+            import uuid
+
+            box = [uuid.uuid4().hex[:12] if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            nonce = box[0]
         with self._lock:
-            self._pending.append((futures, on_commit))
+            self._queue.append((futures, on_commit, sync_dir, rank, world, nonce))
+            self._in_flight += 1
+            if self._committer is None or not self._committer.is_alive():
+                self._committer = threading.Thread(target=self._commit_loop, name="checkpoint-committer", daemon=True)
+                self._committer.start()
+            self._idle.notify_all()
+
+    def _commit_loop(self) -> None:
+        while True:
+            with self._lock:
+                while not self._queue:
+                    if not self._idle.wait(timeout=5.0) and not self._queue:
+                        self._committer = None
+                        return
+                item = self._queue.pop(0)
+            try:
+                self._commit_one(*item)
+            except BaseException as e:  # noqa: BLE001 - reported to the thread that calls wait_until_finished
+                logger.exception("checkpoint commit failed")
+                with self._lock:
+                    self._errors.append(e)
+            finally:
+                with self._lock:
+                    self._in_flight -= 1
+                    self._idle.notify_all()
+
+    def _commit_one(self, futures, cb, sync_dir, rank, world, nonce) -> None:
+        import time
+
+        for f in futures:
+            f.result()
+        if world > 1 and sync_dir is not None:
+            from fsspec.core import url_to_fs
+
+            fs, plain = url_to_fs(str(sync_dir))
+            cdir = plain.rstrip("/") + "/.commit"
+            fs.makedirs(cdir, exist_ok=True)
+            with fs.open(f"{cdir}/rank-{rank}-{nonce}", "w") as fh:
+                fh.write("ok")
+            deadline = time.monotonic() + self.COMMIT_TIMEOUT_S
+            want = [f"{cdir}/rank-{r}-{nonce}" for r in range(world)] if rank == 0 else [f"{cdir}/done-{nonce}"]
+            while not all(fs.exists(w) for w in want):
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"ranks did not all finish writing {sync_dir} within {self.COMMIT_TIMEOUT_S:.0f} s")
+                time.sleep(0.05)
+                try:
+                    fs.invalidate_cache(cdir)
+                except Exception:  # noqa: BLE001
+                    pass
+            if rank == 0:
+                if cb is not None:
+                    cb()
+                with fs.open(f"{cdir}/done-{nonce}", "w") as fh:
+                    fh.write("ok")
+                for r in range(world):
+                    try:
+                        fs.rm(f"{cdir}/rank-{r}-{nonce}")
+                    except Exception:  # noqa: BLE001
+                        pass
+                return
+        if cb is not None:
+            cb()
+
+    def drain(self) -> None:
+        """Non-blocking: raise an error a finished commit left behind (called from the step loop)."""
+        with self._lock:
+            errs, self._errors = self._errors, []
+        if errs:
+            raise errs[0]
 
     def wait_until_finished(self) -> None:
         with self._lock:
-            pending, self._pending = self._pending, []
-        for futures, cb in pending:
-            for f in futures:
-                f.result()
-            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-                dist.barrier()
-            if cb is not None:
-                cb()
+            while self._in_flight > 0:
+                self._idle.wait(timeout=1.0)
+            errs, self._errors = self._errors, []
+        if errs:
+            raise errs[0]
 
 
 def _write_leaf(path: str, t: torch.Tensor) -> None:
@@ -236,7 +323,7 @@ def tree_serialize_leaves_tensorstore(checkpoint_dir: str, tree: Any, manager: O
     manager = manager or AsyncSerializer()
     tree = convert_state_for_save(tree, layouts)
     leaves = [(_fs_path(checkpoint_dir, kp), leaf) for kp, leaf in leaf_key_paths(tree)]
-    manager.serialize(leaves, on_commit=commit_callback)
+    manager.serialize(leaves, on_commit=commit_callback, sync_dir=checkpoint_dir)
     if own:
         manager.wait_until_finished()
 

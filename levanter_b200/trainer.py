@@ -187,6 +187,21 @@ class TrainerConfig:
     shard_optimizer: bool = True
     grad_reduce_dtype: str = "float32"
     use_fused_optimizer: Optional[bool] = None
+    zero_stage: int = 3
+    """3: layer weights exist only as 1/W slices per rank and are gathered layer by layer, weight gradients are
+    reduce-scattered as they are produced (needs >1 data rank, a sharded optimizer and bf16 compute; otherwise the engine
+    falls back to 1).  1: weights and the fp32 gradient accumulator are whole on every rank, only fp32 master weights and
+    optimizer moments are sliced."""
+    comm: Optional[str] = None
+    """data-parallel collectives: ``multimem`` (NVSwitch multicast loads/stores from the library's own kernels), ``p2p``
+    (plain peer loads/stores) or ``nccl``; unset: ``LEVANTER_B200_COMM`` or ``multimem``"""
+    tp_comm: Optional[str] = None
+    """tensor-parallel all-reduce: ``peer`` (own kernels over symmetric memory) or ``nccl``"""
+    ep_comm: Optional[str] = None
+    """expert-parallel token exchange: ``peer`` or ``nccl`` (all-to-all)"""
+    kernel_wait_limit: float = 2.0
+    """seconds after which a device-side wait for a peer gives up (the step loop then raises ``KernelStatusError``); set it
+    above the largest host-side skew between ranks"""
 
     def __post_init__(self):
         if self.wandb is not None:
@@ -300,8 +315,28 @@ class TrainerConfig:
                 self.id = broadcast_one_to_all(gen)
             logger.info(f"Setting run id to {self.id}")
 
+    def _apply_comm_choices(self):
+        """Hand the collective choices to the engine, tensor-parallel and expert-parallel layers (they read environment
+        variables, so entry points that build those objects without a trainer config still work).  A run with failure
+        detection switched on must not use the multicast (``multimem``) paths: a rank that dies while its memory is bound to
+        a multicast object takes its peers' GPUs with it, whereas plain peer accesses and NCCL fail on their own rank only."""
+        for key, val in (("LEVANTER_B200_COMM", self.comm), ("LEVANTER_B200_TP_COMM", self.tp_comm), ("LEVANTER_B200_EP_COMM", self.ep_comm)):
+            if val is not None:
+                os.environ[key] = str(val).lower()
+        if self.watchdog.enabled:
+            chosen = os.environ.get("LEVANTER_B200_COMM")
+            if chosen is None:
+                os.environ["LEVANTER_B200_COMM"] = "p2p"
+            elif chosen.lower() == "multimem":
+                raise ValueError("watchdog.enabled needs comm: p2p or nccl (multicast mappings do not survive the loss of a rank)")
+        if torch.cuda.is_available():
+            from .ops import lib
+
+            lib.set_wait_limit(self.kernel_wait_limit)
+
     def _validate_and_set_defaults(self):
         n = self.num_devices
+        self._apply_comm_choices()
         if n % self.model_axis_size != 0:
             raise ValueError(f"num_devices ({n}) is not divisible by model_axis_size ({self.model_axis_size})")
         if self.train_batch_size == -1 and self.per_device_parallelism == -1:
@@ -520,7 +555,10 @@ class Trainer:
             if self.hooks.stateful_hooks:
                 engine.collect_grads()
                 cb_infos = self.hooks.run_jit_hooks(state, engine, state.step)
-            engine.step(loss=loss_acc)
+            extra = {}
+            if getattr(self.optimizer_config, "needs_objective", False):
+                extra["obj_fn"] = self._batch_objective(model, micro, batch_kwargs)
+            engine.step(loss=loss_acc, **extra)
             if state.model_averaging is not None:
                 state.model_averaging.update(engine.master_tree(), state.step)
             if engine.fused_adam is not None:
@@ -534,12 +572,40 @@ class Trainer:
             dist.all_reduce(loss_acc, op=dist.ReduceOp.AVG)
         return loss_acc, jit_metrics, cb_infos
 
+    def _batch_objective(self, model: nn.Module, micro: List[Any], batch_kwargs) -> Callable[[Dict[str, torch.Tensor]], torch.Tensor]:
+        """``params -> loss of this step's batch`` for optimizers that differentiate the objective themselves (Sophia's
+        Hutchinson estimate; the reference builds the same closure, src/levanter/trainer.py:561-568).  The parameters of the
+        tree (master dtype, full tensors) are cast to the compute dtype and substituted into the model; the pass runs on the
+        differentiable PyTorch statements of the ops, because it is differentiated twice."""
+        from torch.nn.utils.stateless import _reparametrize_module
+
+        from .ops import lib
+
+        cd = self.config.mp.compute_dtype
+        loss_fn = self.loss_fn
+
+        def obj_fn(params: Dict[str, torch.Tensor]) -> torch.Tensor:
+            cast = {k: (v.to(cd) if v.is_floating_point() else v) for k, v in params.items() if v is not None}
+            total = None
+            with lib.reference_ops(), _reparametrize_module(model, cast, tie_weights=True):
+                for mb in micro:
+                    loss = loss_fn(model, mb, **batch_kwargs)
+                    loss = loss.mean() if loss.dim() > 0 else loss
+                    total = loss if total is None else total + loss
+            return total / len(micro)
+
+        return obj_fn
+
     def train_step(self, state: TrainerState, batch, **batch_kwargs) -> StepInfo:
         """One optimizer step on ``batch`` (this rank's shard of the global batch, in pinned host memory or on the
         device), followed by the host part: loss read-back, NaN/Inf checks, hooks and metric logging."""
         t0 = time.perf_counter()
         loss_acc, jit_metrics, cb_infos = self.device_step(state, batch, **batch_kwargs)
         loss_val = loss_acc.item()  # device -> host: the one synchronisation per step
+        if self.device.type == "cuda":
+            from .ops import lib
+
+            lib.check_status()  # a bounded wait that ran out left wrong values behind: stop here, not many steps later
         if self.config.crash_on_nan and loss_val != loss_val:
             raise RuntimeError("Loss is NaN")
         if self.config.crash_on_inf and loss_val in (float("inf"), float("-inf")):

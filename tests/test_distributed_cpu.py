@@ -26,7 +26,7 @@ def _init(rank, world, port, timeout_s=60):
     return dist
 
 
-def _train(tmp, steps=3, batch=8):
+def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None):
     from levanter_b200 import config as C
     from levanter_b200.data.dataset import ListAsyncDataset
     from levanter_b200.models.llama import LlamaConfig
@@ -35,12 +35,17 @@ def _train(tmp, steps=3, batch=8):
     from levanter_b200.trainer import Trainer, TrainerConfig
 
     cfg = C.decode(TrainerConfig, {"num_train_steps": steps, "train_batch_size": batch, "require_accelerator": False, "tracker": {"type": "noop"},
-                                   "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"}})
+                                   "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"},
+                                   **(trainer_extra or {})})
     g = torch.Generator().manual_seed(0)
     starts = torch.randint(0, VOCAB, (64,), generator=g)
     data = ListAsyncDataset([LmExample.causal(((s + torch.arange(16)) % VOCAB).to(torch.int32)) for s in starts], is_complete=True)
     mcfg = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
     opt = AdamConfig(learning_rate=3e-3, warmup=0.0, weight_decay=0.0, lr_schedule="constant", min_lr_ratio=1.0)
+    if opt_dict is not None:
+        from levanter_b200.optim import OptimizerConfig
+
+        opt = C.decode(OptimizerConfig, opt_dict)
     losses = {}
     with Trainer(cfg, opt, compute_next_token_loss) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(VOCAB, seed=3))
@@ -49,10 +54,10 @@ def _train(tmp, steps=3, batch=8):
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
 
 
-def _sharded_worker(rank, world, port, tmp):
+def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None):
     dist = _init(rank, world, port)
     try:
-        params, losses = _train(tmp)
+        params, losses = _train(tmp, opt_dict=opt_dict, trainer_extra=trainer_extra)
         if rank == 0:
             torch.save({"params": params, "losses": losses}, f"{tmp}/dist.pt")
     finally:
@@ -62,6 +67,29 @@ def _sharded_worker(rank, world, port, tmp):
 def test_two_rank_sharded_training_matches_single_process(tmp_path):
     single, losses = _train(str(tmp_path / "single"))
     mp.spawn(_sharded_worker, args=(2, 29711, str(tmp_path)), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+MUON = {"type": "muon", "learning_rate": 2e-2, "adam_lr": 3e-3, "warmup": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0}
+
+
+def test_two_rank_muon_shares_newton_schulz_and_matches_single_process(tmp_path):
+    """Muon on two data ranks: every matrix is orthogonalised by one rank and broadcast; the trajectory equals one process."""
+    single, losses = _train(str(tmp_path / "single"), opt_dict=MUON)
+    mp.spawn(_sharded_worker, args=(2, 29721, str(tmp_path), MUON), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=5e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=5e-5), k
+
+
+def test_two_replicas_take_the_same_step_as_one_process(tmp_path):
+    """replica axis 2 x data axis 1 (pure data parallelism): gradients are averaged over the replicas."""
+    single, losses = _train(str(tmp_path / "single"))
+    mp.spawn(_sharded_worker, args=(2, 29722, str(tmp_path), None, {"replica_ici_axis_size": 2}), nprocs=2, join=True)
     got = torch.load(tmp_path / "dist.pt")
     assert got["losses"] == pytest.approx(losses, abs=2e-5)
     for k, v in single.items():

@@ -11,7 +11,8 @@ import torch
 
 from levanter_b200 import config as C
 
-REF_CONFIGS = "/root/reference/config"
+# directory holding the reference project's YAML configs (its ``config/``); the parse-them-all test is skipped without it
+REF_CONFIGS = os.environ.get("LEVANTER_REFERENCE_CONFIGS", "")
 
 
 def _write_data(d, n=200, vocab=250):
@@ -152,7 +153,7 @@ def _class_for(name):
     return TrainLmConfig
 
 
-@pytest.mark.skipif(not os.path.isdir(REF_CONFIGS), reason="reference configs not present")
+@pytest.mark.skipif(not (REF_CONFIGS and os.path.isdir(REF_CONFIGS)), reason="set LEVANTER_REFERENCE_CONFIGS to the reference's config directory")
 def test_reference_yaml_configs_parse():
     """Every training/SFT/LoRA config of the reference decodes into the matching config class here.  Exempt: a config whose
     model type the reference itself no longer ships."""

@@ -140,3 +140,65 @@ def test_save_and_load_tree_round_trip(tmp_path):
     assert discover_latest_checkpoint(str(tmp_path)).endswith("step-12")
     with pytest.raises(FileNotFoundError):
         load_checkpoint(m2, str(tmp_path / "nothing_here"))
+
+
+def test_sophia_h_through_trainer(tmp_path):
+    """Sophia-H gets the batch objective from the trainer: the run passes the Hessian refresh and the estimate changes."""
+    from levanter_b200.optim import OptimizerConfig
+
+    ocfg = C.decode(OptimizerConfig, {"type": "sophia-h", "learning_rate": 1e-3, "warmup": 0.0, "update_interval": 2,
+                                      "lr_schedule": "constant", "min_lr_ratio": 1.0})
+    cfg = _cfg(str(tmp_path), steps=5, pdp=4)
+    with Trainer(cfg, ocfg, compute_next_token_loss) as trainer:
+        state = trainer.initial_state(0, model_init=lambda: _model_cfg().build(VOCAB, seed=3))
+        info = trainer.train(state, trainer.data_loader(_data()).iter_from_step(0))
+    assert info.step == 4
+
+    def find(st):
+        if hasattr(st, "hessian_count"):
+            return st
+        if isinstance(st, (tuple, list)):
+            for x in st:
+                r = find(x)
+                if r is not None:
+                    return r
+        for name in ("inner_state",):
+            if hasattr(st, name):
+                return find(getattr(st, name))
+        return None
+
+    soph = find(state.engine.opt_state)
+    assert soph is not None and soph.hessian_count == 2  # steps 2 and 4 of 5
+    assert any(float(h.abs().sum()) > 0 for h in soph.h.values())
+
+
+def test_mid_run_checkpoint_commits_without_waiting(tmp_path):
+    """A save made by ``on_step`` becomes discoverable on its own (no ``wait_until_finished``), and the temporary checkpoint
+    it replaces is deleted while the run is still going."""
+    import time
+    from types import SimpleNamespace
+
+    cfg = _cfg(str(tmp_path), steps=1)
+    with Trainer(cfg, _opt(), compute_next_token_loss) as trainer:
+        state = trainer.initial_state(0, model_init=lambda: _model_cfg().build(VOCAB, seed=3))
+        base = str(tmp_path / "ck")
+        now = [datetime.datetime(2024, 1, 1)]
+        ck = Checkpointer(base, datetime.timedelta(minutes=10), [], dt_now_injection=lambda: now[0])
+        ck.on_step(SimpleNamespace(step=0, state=state))
+        found = []
+        for step in (1, 2):
+            now[0] += datetime.timedelta(minutes=11)
+            ck.on_step(SimpleNamespace(step=step, state=state))
+            deadline = time.monotonic() + 30
+            while time.monotonic() < deadline:
+                latest = discover_latest_checkpoint(base)
+                if latest is not None and latest.endswith(f"step-{step}"):
+                    break
+                time.sleep(0.05)
+            found.append(discover_latest_checkpoint(base))
+        assert found[0].endswith("step-1") and found[1].endswith("step-2")
+        deadline = time.monotonic() + 30
+        while os.path.exists(os.path.join(base, "step-1")) and time.monotonic() < deadline:
+            time.sleep(0.05)
+        assert not os.path.exists(os.path.join(base, "step-1")), "the replaced temporary checkpoint is still there"
+        ck.wait_until_finished()
