@@ -12,7 +12,17 @@ Two timed regions, each after W untimed warm-up steps and bracketed by a barrier
     events on the launching stream, max over ranks;
   * ``e2e``: K steps through the public ``Trainer.train_step``: each step copies its batch from pinned host memory to the
     device and reads the loss back to the host.
-``--impl reference`` would run the unmodified reference; it cannot be installed offline here, so it reports that.
+
+Arms (``--impl``):
+  * ``ours``: this framework.  After its own two regions it frees its state and times the stock-PyTorch arm for a few steps
+    in the same process, on the same GPUs and clocks, and reports ``vs_baseline`` = ours / that (``--no-baseline`` skips it).
+  * ``torch_baseline``: the same model, batch, dtype policy and optimizer on stock PyTorch only (cuBLAS, the library's fused
+    attention, ``torch.distributed.fsdp`` over NCCL, fused AdamW): ``baseline/torch_baseline.py``.
+  * ``reference``: would run the unmodified reference; it cannot be installed offline here, so it reports that.
+
+Parallelism of ``ours`` on N > 1 GPUs: ``--zero-stage 3`` (default) keeps every decoder layer's weights only as 1/N slices
+and gathers / reduce-scatters them layer by layer from inside the GEMM kernels; ``--zero-stage 1`` keeps bf16 weights and
+the fp32 gradient accumulator whole on every GPU and slices only master weights and optimizer moments.
 """
 from __future__ import annotations
 
@@ -34,7 +44,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_baseline"])
+    ap.add_argument("--zero-stage", type=int, default=3, choices=[1, 3], help="see the module docstring")
+    ap.add_argument("--no-baseline", action="store_true", help="ours: do not time the stock-PyTorch arm in the same call")
+    ap.add_argument("--baseline-steps", type=int, default=5, help="timed steps of the in-call stock-PyTorch arm (after 3 warm-up steps)")
     # shape overrides for quick functional checks; a run that uses them is labelled in "config" and is not the headline
     ap.add_argument("--model", default="llama", choices=["llama", "mixtral_ep"],
                     help="llama: the headline model; mixtral_ep: Mixtral 8x7B layer shapes with the experts sliced over the GPUs (a side "
@@ -106,10 +119,115 @@ def run_reference(args):
     return 0
 
 
+def _env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local_rank
+
+
+def _ensure_process_group(world: int, rank: int):
+    """NCCL process group, also for a single rank (``fully_shard`` of the stock-PyTorch arm wants one)."""
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        return
+    if world > 1:
+        dist.init_process_group("nccl")
+        return
+    import socket
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+
+
+def _micro(args, world: int) -> int:
+    micro = args.microbatch or (2 if world == 1 else 4)
+    micro = min(micro, args.per_gpu_batch)
+    while args.per_gpu_batch % micro:
+        micro -= 1
+    return micro
+
+
+def _peak_tflops() -> float:
+    try:
+        return json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained", 1434.2)
+    except Exception:
+        return 1434.2
+
+
+MODEL_NAME = "Llama-2 7B (32L, hidden 4096, 32 heads MHA, SwiGLU 11008, vocab 32000, RoPE 1e4)"
+DATA_NAME = "synthetic uniform-random token ids (fixed seed), random-init weights std 0.02"
+
+
+def _is_headline(args) -> bool:
+    return (args.model == "llama" and args.layers == 32 and args.seq_len == 4096 and args.per_gpu_batch == 8 and args.hidden == 4096
+            and not args.remat)
+
+
+def run_torch_baseline(args, steps: int, warmup: int, sample_clocks: bool = True) -> dict:
+    """The stock-PyTorch arm (see ``baseline/torch_baseline.py``); returns its measurements (every rank gets the same dict)."""
+    import torch
+
+    from baseline.torch_baseline import LlamaShape, run
+
+    world, rank, local_rank = _env()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    _ensure_process_group(world, rank)
+    shape = LlamaShape(vocab=32000, hidden=args.hidden, intermediate=11008 if args.hidden == 4096 else args.hidden * 8 // 3 // 128 * 128,
+                       layers=args.layers, heads=args.hidden // 128, kv_heads=args.hidden // 128, seq_len=args.seq_len)
+    return run(shape, world=world, rank=rank, device=dev, per_gpu_batch=args.per_gpu_batch, micro=_micro(args, world), steps=steps,
+               warmup=warmup, clock_sampler=ClockSampler(local_rank) if sample_clocks else None)
+
+
+def main_torch_baseline(args):
+    import torch
+    import torch.distributed as dist
+
+    world, rank, _ = _env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    r = run_torch_baseline(args, args.steps, args.warmup)
+    from levanter_b200.models.llama import LlamaConfig  # only for the FLOP count, so that both arms' MFU use one formula
+
+    fpt = 3 * LlamaConfig(seq_len=args.seq_len, hidden_dim=args.hidden, intermediate_dim=11008 if args.hidden == 4096 else args.hidden * 8 // 3 // 128 * 128,
+                          num_layers=args.layers, num_heads=args.hidden // 128, num_kv_heads=args.hidden // 128).flops_per_token(32000)
+    out = {
+        "metric": "train tokens/sec (device-timed, max over ranks) Llama-7B FSDP",
+        "value": r["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": 1.0, "dtype": "bf16",
+        "data": DATA_NAME, "impl": "torch_baseline",
+        "config": {"model": MODEL_NAME if _is_headline(args) else f"NOT THE HEADLINE CONFIG: layers={args.layers} hidden={args.hidden} seq={args.seq_len}",
+                   "global_batch": args.per_gpu_batch * world, "seq_len": args.seq_len,
+                   "parallelism": f"fsdp{world} (torch.distributed.fsdp.fully_shard, NCCL)" if world > 1 else "single-gpu (fully_shard over one rank)",
+                   "microbatch_per_gpu": r["microbatch_per_gpu"], "optimizer": "torch.optim.AdamW(fused=True), fp32 parameters, bf16 compute, clip 1.0",
+                   "params": r["params"], "l2_note": "inputs (activations + 13.5 GB of weights per pass) far exceed the 126 MB L2",
+                   "kernels": "cuBLAS, F.scaled_dot_product_attention, eager PyTorch"},
+        "clocks": r["clocks"],
+        "e2e": {"value": r["e2e_value"], "unit": "tokens/s", "ms_per_step": r["e2e_ms_per_step"], "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": 4, "final_loss": r["final_loss"]},
+        "gpu_launches": 0, "gpu_launches_note": "this arm launches none of this repository's kernels by construction",
+        "mfu_vs_measured_sustained_cublas": fpt * r["value"] / world / (_peak_tflops() * 1e12),
+        "peak_mem_gib": r["peak_mem_gib"],
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "torch_baseline":
+        return main_torch_baseline(args)
+
+    import gc
 
     import torch
     import torch.distributed as dist
@@ -127,9 +245,7 @@ def main():
 
     if args.comm:
         os.environ["LEVANTER_B200_COMM"] = args.comm
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world, rank, local_rank = _env()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     if not torch.cuda.is_available():
@@ -139,16 +255,13 @@ def main():
 
     vocab = 32000
     S, B = args.seq_len, args.per_gpu_batch
-    micro = args.microbatch or (2 if world == 1 else 4)
-    micro = min(micro, B)
-    while B % micro:
-        micro -= 1
+    micro = _micro(args, world)
     tmp = tempfile.mkdtemp(prefix="lvb_bench_")
     tcfg = TrainerConfig(
         seed=0, mp=Policy.parse("p=f32,c=bfloat16"), num_train_steps=1_000_000, train_batch_size=B * world,
         per_device_parallelism=micro, tracker=NoopConfig(), log_dir=os.path.join(tmp, "logs"), id="bench",
         checkpointer=CheckpointerConfig(base_path=os.path.join(tmp, "ckpt"), save_interval=None, keep=[dict(every=10**9)]),
-        load_checkpoint=False)
+        load_checkpoint=False, zero_stage=args.zero_stage)
     tcfg.initialize()
     mcfg = LlamaConfig(seq_len=S, hidden_dim=args.hidden, intermediate_dim=11008 if args.hidden == 4096 else args.hidden * 8 // 3 // 128 * 128,
                        num_layers=args.layers, num_heads=args.hidden // 128, num_kv_heads=args.hidden // 128,
@@ -161,12 +274,13 @@ def main():
                              num_kv_heads=8, n_routed_experts=8, num_experts_per_tok=2, expert_parallel=world > 1,
                              gradient_checkpointing=bool(args.remat), initializer_range=0.02)
     ocfg = AdamConfig(learning_rate=3e-4, weight_decay=0.1, warmup=100, max_grad_norm=1.0)
-    headline = (args.model == "llama" and args.layers == 32 and S == 4096 and B == 8 and args.hidden == 4096 and not args.remat)
+    headline = _is_headline(args)
 
     with Trainer(tcfg, ocfg, add_default_hooks=False) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(vocab, seed=0, device=dev))
         n_params = sum(p.numel() for p in state.model.parameters())
         comm_used = state.engine.comm if world > 1 else "none"
+        stage_used = getattr(state.engine, "zero_stage", 1) if world > 1 else None
         ds = SyntheticLmDataset(vocab, S, seed=0)
         loader = trainer.data_loader(ds)
         it = iter(loader.iter_from_step(0))
@@ -200,7 +314,7 @@ def main():
         launches = lib.launch_count - launches0
         clocks = sampler.stop()
 
-        # ---- end-to-end region: pinned host batch -> device copy and loss read-back every step
+        # ---- end-to-end region: pinned host batch -> device copy and loss read-back every step (fresh data every step)
         host_batches = [next(it) for _ in range(args.steps + 1)]
         h2d = sum(t.numel() * t.element_size() for t in (host_batches[0].tokens, host_batches[0].loss_mask))
         info = trainer.train_step(state, host_batches[0])  # one warm step through the public path
@@ -218,41 +332,63 @@ def main():
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = float(times[0]), float(times[1])
         mem_gb = torch.cuda.max_memory_allocated() / 2**30
+        del state, loader, it, dev_batch, host_batches, info
 
     tokens_per_step = B * world * S
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
     flops_per_token = 3 * mcfg.flops_per_token(vocab)
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak_tf = peaks.get("bf16_tflops_sustained", 1434.2)
+    peak_tf = _peak_tflops()
+
+    # ---- the stock-PyTorch arm in the same call (same GPUs, same clocks), after this arm's memory is released
+    base, vs_baseline, vs_e2e = None, None, None
+    if not args.no_baseline and args.model == "llama":
+        del trainer
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        try:
+            base = run_torch_baseline(args, max(1, args.baseline_steps), 3)
+            vs_baseline = value / base["value"]
+            vs_e2e = e2e_value / base["e2e_value"]
+        except Exception as e:  # noqa: BLE001 - the framework's own line must still be printed
+            base = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+
+    if world == 1:
+        parallelism = "single-gpu"
+    elif stage_used == 3:
+        parallelism = f"fsdp{world} (zero-3: layer weights as 1/{world} slices, all-gather and reduce-scatter fused into the GEMM kernels)"
+    else:
+        parallelism = f"zero1-dp{world} (bf16 weights and fp32 gradients whole on every GPU; master weights and Adam moments sliced)"
+    if args.model == "mixtral_ep" and world > 1:
+        parallelism += f"+ep{world}"
     out = {
         "metric": "train tokens/sec (device-timed, max over ranks) Llama-7B FSDP",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights std 0.02",
+        "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline,
+        "vs_baseline_note": "this arm / the stock-PyTorch arm (cuBLAS, library attention, torch FSDP over NCCL, fused AdamW) timed in the same "
+                            "call; the reference publishes no GPU number and cannot be installed offline",
+        "dtype": "bf16", "data": DATA_NAME,
         "impl": "ours",
-        "config": {"model": "Llama-2 7B (32L, hidden 4096, 32 heads MHA, SwiGLU 11008, vocab 32000, RoPE 1e4)" if headline
+        "config": {"model": MODEL_NAME if headline
                    else f"NOT THE HEADLINE CONFIG: model={args.model} layers={args.layers} hidden={args.hidden} seq={S} per_gpu_batch={B} remat={args.remat}",
-                   "global_batch": B * world, "seq_len": S, "parallelism": (f"fsdp{world}" + (f"+ep{world}" if args.model == "mixtral_ep" else "")) if world > 1 else "single-gpu",
+                   "global_batch": B * world, "seq_len": S, "parallelism": parallelism,
                    "microbatch_per_gpu": micro, "optimizer": "AdamW fp32 master + fp32 moments, global-norm clip 1.0",
                    "params": n_params, "l2_note": "inputs (activations + 13.5 GB of weights per pass) far exceed the 126 MB L2",
                    "attention_backend": args.attn or "default",
                    "collectives": comm_used, "expert_exchange": os.environ.get("LEVANTER_B200_EP_COMM", "peer") if args.model == "mixtral_ep" else None},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4, "final_loss": last_loss},
+                "d2h_bytes_per_step": 4, "final_loss": last_loss, "vs_baseline": vs_e2e},
         "gpu_launches": launches,
         "mfu_vs_measured_sustained_cublas": flops_per_token * value / world / (peak_tf * 1e12),
         "mfu_vs_nominal_2.25PF": flops_per_token * value / world / 2.25e15,
         "peak_mem_gib": mem_gb,
+        "torch_baseline_same_call": base,
     }
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
+    if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
     return 0
