@@ -36,7 +36,7 @@ class WatchCallback(JitCallback):
                   group=group, sharded=sharded, all_names=[s.name for s in engine.slots] if sharded else None)
         if "grads" in self.watch_targets:
             # gradients in the accumulator are not yet reduced over data ranks at this point; use local full grads
-            g = {s.name: s.param.main_grad for s in engine.slots}
+            g = {s.name: s.param.main_grad for s in engine.slots if getattr(s.param, "main_grad", None) is not None}
             out.update(summary_statistics_for_tree("grad", g, **{**kw, "group": None, "sharded": False, "all_names": None}))
         if "params" in self.watch_targets:
             out.update(summary_statistics_for_tree("params", engine.master_tree(), **kw))

@@ -327,7 +327,8 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
             if full is None:
                 missing.append(f"model.{s.name}")
                 continue
-            s.param.data.copy_(full.to(device=engine.device, dtype=s.param.dtype))
+            if not s.streamed:  # (a streamed matrix is a view of a staging slot, filled when its layer is assembled)
+                s.param.data.copy_(full.to(device=engine.device, dtype=s.param.dtype))
             seg = engine.segments.get(s.name)
             if seg is not None and not engine.master_is_param:
                 lo, fo, n = seg
@@ -391,6 +392,7 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
                 slot = next(s for s in engine.slots if s.name == name)
                 a = fo - slot.offset
                 leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype))
+    engine.sync_streamed_from_master()  # fully sharded layers: peers gather from the compute-dtype rows, refresh them
     step = tss.read_leaf(checkpoint_path, "step")
     if step is None:
         step = torch.tensor(_load_metadata(checkpoint_path)["step"] + 1)

@@ -62,12 +62,20 @@ struct Params {
   int c_rows_per_rank;    // scattered C: rows [r * c_rows_per_rank, ...) are stored to c_peer[r]
   void* c_peer[kMaxPeers];   // scattered C: this rank's slot in rank r's staging buffer
   int* c_cnt[kMaxPeers];     // scattered C: rank r's per-tile arrival counters (in rank r's memory); they only ever grow
-  int c_target;              // scattered C: value of a counter once all 4 * world parts of this call's tile have arrived
+  int c_target;              // scattered C: value of a counter once all `world` parts of this call's unit have arrived
+  const int* c_m_order;      // scattered C: the raster's i-th row block is block c_m_order[i] (owners dealt round-robin)
+  int rs_accumulate;         // scattered C: the reduced rows are added to rs_out (fp32) instead of stored
   const float* rs_staging;   // scattered C: this rank's own staging buffer [world, slot]
   long long rs_slot;         // elements per slot
   void* rs_out;              // this rank's reduced rows [c_rows_per_rank, N] (bf16, or fp32 if rs_out_f32), row stride rs_ldo
   int rs_ldo;
   int rs_out_f32;
+  // ---- copy job (kModeCopyJob): units [cj_u0, cj_u1) of a table of {source rank, source offset / 16, destination offset / 16,
+  // bytes / 16}; a seventh warp of every CTA moves them (peer or local memory -> shared memory -> cj_dst) beside the GEMM
+  const int4* cj_table;
+  int cj_u0, cj_u1;
+  const uint8_t* cj_src[kMaxPeers];
+  uint8_t* cj_dst;
   // ---- grouped GEMM (see lvb_gemm_grouped)
   const int* g_tile_group;  // K-major A: group of every 128-row block of A, or -1 for a block past the last group (skipped)
   int g_b_rows;             // K-major A: rows (K-major B) or reduction rows (MN-major B) of one group's B inside the stacked B
@@ -79,6 +87,7 @@ constexpr int kModePlain = 0;
 constexpr int kModeGatherA = 1;   // all-gather fused into the A operand
 constexpr int kModeScatterC = 2;  // reduce-scatter fused into the epilogue
 constexpr int kModeGrouped = 3;   // one B matrix (or one K range) per group of rows: the expert GEMMs of a mixture-of-experts layer
+constexpr int kModeCopyJob = 4;   // plain GEMM whose CTAs also carry out a list of bulk copies (the next layer's weight gather)
 constexpr int kCopyUnit = 16384;  // bytes per bulk copy of the gather
 constexpr int kCopyExtra = 256 + 2 * kCopyUnit;  // extra dynamic shared memory of the gather kernel
 constexpr int kGatherThreads = kNumThreads + 32;  // + one copy warp
@@ -120,13 +129,12 @@ __device__ __forceinline__ void tile_coords_rot(int t, int tiles_m, int tiles_n,
   mb += m_rot;
   if (mb >= tiles_m) mb -= tiles_m;
 }
-// Scatter raster: consecutive m-blocks of the raster go to consecutive ranks (next rank first, own rank last of each round),
-// so the peer stores are spread evenly over the kernel's duration and every rank's rows complete at a steady rate.
-__device__ __forceinline__ void tile_coords_interleaved(int t, int tiles_m, int tiles_n, int rank, int world, int& mb, int& nb) {
+// Scatter raster: the host passes a permutation of the row blocks that deals them out to their owners in turn (next rank
+// first, own rank last of each round), so the peer stores are spread evenly over the kernel's duration and every rank's rows
+// complete at a steady rate.
+__device__ __forceinline__ void tile_coords_ordered(int t, int tiles_m, int tiles_n, const int* __restrict__ m_order, int& mb, int& nb) {
   tile_coords(t, tiles_m, tiles_n, mb, nb);
-  int dest = rank + 1 + mb % world;
-  if (dest >= world) dest -= world;
-  mb = dest * (tiles_m / world) + mb / world;
+  mb = __ldg(m_order + mb);
 }
 
 // Grouped mode: what a tile has to do.  K-major A (forward, input gradient): the tile's row block belongs to group g (skip when
@@ -183,7 +191,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 4);  // one arrival per epilogue warp
     }
-    if constexpr (MODE == kModeGatherA) {
+    if constexpr (MODE == kModeGatherA || MODE == kModeCopyJob) {
       mbar_init(&copy_bar[0], 1);
       mbar_init(&copy_bar[1], 1);
     }
@@ -209,8 +217,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       int ready_block = -1;  // gather mode: last m-block whose rows are known to have arrived
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb;
-        if constexpr (MODE == kModePlain || MODE == kModeGrouped) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-        else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
+        if constexpr (MODE == kModePlain || MODE == kModeGrouped || MODE == kModeCopyJob) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        else if constexpr (MODE == kModeScatterC) tile_coords_ordered(t, p.tiles_m, p.tiles_n, p.c_m_order, mb, nb);
         else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
         int a_map = 0, a_row = m0;
@@ -321,8 +329,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
     const float alpha = p.alpha_dev != nullptr ? p.alpha * p.alpha_dev[0] : p.alpha;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      if constexpr (MODE == kModePlain || MODE == kModeGrouped) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-      else if constexpr (MODE == kModeScatterC) tile_coords_interleaved(t, p.tiles_m, p.tiles_n, p.rank, p.world, mb, nb);
+      if constexpr (MODE == kModePlain || MODE == kModeGrouped || MODE == kModeCopyJob) tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      else if constexpr (MODE == kModeScatterC) tile_coords_ordered(t, p.tiles_m, p.tiles_n, p.c_m_order, mb, nb);
       else tile_coords_rot(t, p.tiles_m, p.tiles_n, p.m_rot, mb, nb);
       if constexpr (MODE == kModeGrouped) {
         int group, kb0, kb1;
@@ -337,9 +345,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       void* c_base = p.C;
       size_t c_row = static_cast<size_t>(row);
       int c_dest = 0;
+      bool c_live = true;
       if constexpr (MODE == kModeScatterC) {
-        // the whole tile belongs to one rank (c_rows_per_rank is a multiple of BM): store it into that rank's staging slot
-        c_dest = (mb * BM) / p.c_rows_per_rank;
+        // this warp's 32 rows belong to one rank (c_rows_per_rank and M are multiples of 32): they go to that rank's staging slot
+        const int row0w = mb * BM + quad * 32;
+        c_live = row0w < p.M;
+        c_dest = c_live ? row0w / p.c_rows_per_rank : 0;
         c_base = p.c_peer[c_dest];
         c_row = static_cast<size_t>(row - c_dest * p.c_rows_per_rank);
       }
@@ -353,7 +364,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
         if constexpr (MODE == kModeScatterC) {
           // Peer stores: turn the row-per-lane fragment into row-contiguous 128-byte segments through shared memory, so a
           // store instruction covers 4 rows x 128 B instead of 32 rows x 16 B (NVLink moves short writes poorly).
-          if (col0 < p.N) {  // warp-uniform; every row of the tile is valid (M / world is a multiple of BM)
+          if (col0 < p.N && c_live) {  // warp-uniform; all 32 rows of a live warp are valid
             float* eb = epi_buf + (warp - 2) * (32 * kEpiStride);
             if (out_f32) {
 #pragma unroll
@@ -502,8 +513,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       if (lane == 0) {
         mbar_arrive(&tempty_bar[buf]);
         if constexpr (MODE == kModeScatterC) {
-          const int mb_local = mb - c_dest * (p.c_rows_per_rank / BM);
-          red_release_sys_add(p.c_cnt[c_dest] + mb_local * p.tiles_n + nb, 1);
+          // one arrival per rank and (32-row group, column tile) of the owner's rows
+          if (c_live) {
+            const int grp = (mb * BM + quad * 32 - c_dest * p.c_rows_per_rank) >> 5;
+            red_release_sys_add(p.c_cnt[c_dest] + grp * p.tiles_n + nb, 1);
+          }
         }
       }
       if (++buf == 2) { buf = 0; tphase ^= 1; }
@@ -564,27 +578,68 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       if (ok && prev >= 0) signal(prev);
       if (!ok && pending_load) mbar_wait_quiet(&copy_bar[(j & 1) ^ 1], (j & 1) ? ph0 : ph1);  // let the load in flight land
     }
+  } else if constexpr (MODE == kModeCopyJob) {
+    // ------------------------------------------------------------ copy-job warp (warp 6)
+    // CTA b moves units cj_u0 + b, cj_u0 + b + grid, ... of the table: source (a peer's or this GPU's memory) -> shared
+    // memory -> cj_dst, both legs as bulk copies, one load in flight while the previous unit is stored.  Nothing in this
+    // kernel reads what is copied: the consumer is a later kernel on the same stream, so completion of the stores before
+    // the kernel ends (bulk_wait<0>) is the only ordering needed.
+    if (lane == 0 && p.cj_u1 > p.cj_u0) {
+      auto issue = [&](int u, int b) {
+        const int4 e = __ldg(p.cj_table + u);
+        const uint32_t bytes = static_cast<uint32_t>(e.w) << 4;
+        mbar_expect_tx(&copy_bar[b], bytes);
+        bulk_load(copy_buf + b * kCopyUnit, p.cj_src[e.x] + (static_cast<size_t>(static_cast<uint32_t>(e.y)) << 4), bytes, &copy_bar[b]);
+      };
+      int u = p.cj_u0 + static_cast<int>(blockIdx.x);
+      uint32_t ph0 = 0, ph1 = 0;
+      int j = 0;
+      bool ok = true, pending_load = false;
+      if (u < p.cj_u1) issue(u, 0);
+      while (u < p.cj_u1) {
+        const int un = u + static_cast<int>(gridDim.x);
+        const int b = j & 1;
+        pending_load = false;
+        if (un < p.cj_u1) {
+          bulk_wait_read<0>();  // the store that last read the other buffer has drained it
+          issue(un, b ^ 1);
+          pending_load = true;
+        }
+        ok = mbar_wait(&copy_bar[b], b ? ph1 : ph0, abort_flag, p.status, 410, b);
+        if (!ok) break;
+        if (b) ph1 ^= 1; else ph0 ^= 1;
+        const int4 e = __ldg(p.cj_table + u);
+        bulk_store(p.cj_dst + (static_cast<size_t>(static_cast<uint32_t>(e.z)) << 4), copy_buf + b * kCopyUnit, static_cast<uint32_t>(e.w) << 4);
+        bulk_commit();
+        u = un;
+        ++j;
+      }
+      bulk_wait<0>();
+      if (!ok && pending_load) mbar_wait_quiet(&copy_bar[(j & 1) ^ 1], (j & 1) ? ph0 : ph1);  // let the load in flight land
+    }
   } else if constexpr (MODE == kModeScatterC) {
     // ------------------------------------------------------------ reduce warps (warps 6-9)
-    // This rank's rows, concurrently with the main loop: tile by tile, in the order the raster produces them, wait until all
-    // 4 * world epilogue warps (own and remote) have delivered their part of the tile into the staging slots, then sum the
-    // slots.  Every rank produces the tiles of a given rank at the same steady rate, so these warps trail the tensor cores
+    // This rank's rows, concurrently with the main loop, in units of 32 rows x BN columns in the order the raster produces
+    // them: wait until all `world` ranks (this one included) have delivered the unit into their staging slots, then sum the
+    // slots.  Every rank produces the rows of a given rank at the same steady rate, so these warps trail the tensor cores
     // closely and little is left to reduce when the last tile has been multiplied.
     const int rtid = threadIdx.x - kNumThreads;
-    const int own_tiles = (p.c_rows_per_rank / BM) * p.tiles_n;
+    const int own_units = (p.c_rows_per_rank >> 5) * p.tiles_n;
     const bool out_f32 = p.rs_out_f32 != 0;
-    for (int t = blockIdx.x; t < own_tiles; t += gridDim.x) {
+    const bool acc_out = p.rs_accumulate != 0;
+    constexpr int RU = 32;  // rows per unit
+    for (int t = blockIdx.x; t < own_units; t += gridDim.x) {
       if (rtid == 0 && !*abort_flag)
         flag_wait_ge(p.c_cnt[p.rank] + t, p.c_target, true, abort_flag, p.status, 500, t);
       reduce_bar_sync();
       if (*abort_flag) break;
-      const int mb_local = t / p.tiles_n, nb = t - mb_local * p.tiles_n;
+      const int grp = t / p.tiles_n, nb = t - grp * p.tiles_n;
       if (!(p.flags & kOutF32)) {
         // bf16 staging slots: 8 elements per 16-byte load, fp32 accumulation
         constexpr int kVec8PerRow = BN / 8;
         constexpr int kU = 4;
         const __nv_bfloat16* stg = reinterpret_cast<const __nv_bfloat16*>(p.rs_staging);
-        for (int i0 = rtid; i0 < BM * kVec8PerRow; i0 += kU * kReduceThreads) {
+        for (int i0 = rtid; i0 < RU * kVec8PerRow; i0 += kU * kReduceThreads) {
           float acc[kU][8];
           size_t off[kU];
           bool live[kU];
@@ -593,8 +648,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
             const int i = i0 + u * kReduceThreads;
             const int r = i / kVec8PerRow;
             const int col = nb * BN + (i - r * kVec8PerRow) * 8;
-            live[u] = (i < BM * kVec8PerRow) && (col < p.N);
-            off[u] = (static_cast<size_t>(mb_local) * BM + r) * p.ldc + col;
+            live[u] = (i < RU * kVec8PerRow) && (col < p.N);
+            off[u] = (static_cast<size_t>(grp) * RU + r) * p.ldc + col;
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
           }
@@ -620,11 +675,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
             const int i = i0 + u * kReduceThreads;
             const int r = i / kVec8PerRow;
             const int col = nb * BN + (i - r * kVec8PerRow) * 8;
-            const size_t row = static_cast<size_t>(mb_local) * BM + r;
+            const size_t row = static_cast<size_t>(grp) * RU + r;
             if (out_f32) {
               float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col);
-              o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
-              o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+              if (acc_out) {
+                const float4 a = o[0], b = o[1];
+                o[0] = make_float4(a.x + acc[u][0], a.y + acc[u][1], a.z + acc[u][2], a.w + acc[u][3]);
+                o[1] = make_float4(b.x + acc[u][4], b.y + acc[u][5], b.z + acc[u][6], b.w + acc[u][7]);
+              } else {
+                o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+                o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+              }
             } else {
               *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo + col) =
                   make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
@@ -637,7 +698,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
       }
       constexpr int kVecPerRow = BN / 4;
       constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread and slot
-      for (int i0 = rtid; i0 < BM * kVecPerRow; i0 += kUnroll * kReduceThreads) {
+      for (int i0 = rtid; i0 < RU * kVecPerRow; i0 += kUnroll * kReduceThreads) {
         float4 acc[kUnroll];
         size_t off[kUnroll];
         bool live[kUnroll];
@@ -646,8 +707,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
           const int i = i0 + u * kReduceThreads;
           const int r = i / kVecPerRow;
           const int col = nb * BN + (i - r * kVecPerRow) * 4;
-          live[u] = (i < BM * kVecPerRow) && (col < p.N);
-          off[u] = (static_cast<size_t>(mb_local) * BM + r) * p.ldc + col;
+          live[u] = (i < RU * kVecPerRow) && (col < p.N);
+          off[u] = (static_cast<size_t>(grp) * RU + r) * p.ldc + col;
           acc[u] = live[u] ? __ldcg(reinterpret_cast<const float4*>(p.rs_staging + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         for (int w = 1; w < p.world; ++w) {
@@ -664,9 +725,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_maps, const CUt
           const int i = i0 + u * kReduceThreads;
           const int r = i / kVecPerRow;
           const int col = nb * BN + (i - r * kVecPerRow) * 4;
-          const size_t row = static_cast<size_t>(mb_local) * BM + r;
+          const size_t row = static_cast<size_t>(grp) * RU + r;
           if (out_f32) {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col) = acc[u];
+            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col);
+            if (acc_out) {
+              const float4 a = *o;
+              *o = make_float4(a.x + acc[u].x, a.y + acc[u].y, a.z + acc[u].z, a.w + acc[u].w);
+            } else {
+              *o = acc[u];
+            }
           } else {
             *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo + col) =
                 make_uint2(pack_bf16x2(acc[u].x, acc[u].y), pack_bf16x2(acc[u].z, acc[u].w));
@@ -701,10 +768,18 @@ gemm_gather_a_kernel(const __grid_constant__ PeerMaps tmAs, const __grid_constan
 
 // Reduce-scatter fused into the epilogue: tiles go to the staging slot of the rank that owns their rows, while four more
 // warps of every CTA sum this rank's own rows over the slots as the contributions arrive.
-template <int BN>
+template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kScatterThreads, 1)
 gemm_scatter_c_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
-  gemm_body<BN, false, false, false, kModeScatterC>(&tmA, tmB, p);
+  gemm_body<BN, A_MN, B_MN, false, kModeScatterC>(&tmA, tmB, p);
+}
+
+// Plain GEMM plus a copy job: a seventh warp per CTA moves a list of 16 KB units (the next layer's weight shards, pulled
+// from the peers) while the tensor cores work; bulk copies without any cluster qualifier.
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGatherThreads, 1)
+gemm_copy_job_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_body<BN, A_MN, B_MN, false, kModeCopyJob>(&tmA, tmB, p);
 }
 
 // Grouped GEMM: the same pipeline with a per-tile group look-up (see grouped_tile and lvb_gemm_grouped).
@@ -885,18 +960,21 @@ int launch_gather_a(const void* B, Params p, int ldb, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
 
-template <int BN>
+template <int BN, bool A_MN, bool B_MN>
 int launch_scatter_c(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   constexpr int kSmem = L::kTotal + kEpiExtra;
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_2d_bf16(&tmA, A, p.M, p.K, lda, BM, BK);
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, p.M, p.K, lda, BM, BK);
+  else       rc = make_tmap_2d_bf16(&tmA, A, p.K, p.M, lda, BK, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
+  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
+  else       rc = make_tmap_2d_bf16(&tmB, B, p.K, p.N, ldb, BK, 64);
   if (rc != kErrOk) return rc;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  auto kern = gemm_scatter_c_kernel<BN>;
+  auto kern = gemm_scatter_c_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
@@ -906,6 +984,88 @@ int launch_scatter_c(const void* A, const void* B, Params p, int lda, int ldb, c
   if (grid > num_sms()) grid = num_sms();
   kern<<<grid, kScatterThreads, kSmem, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_copy_job(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  constexpr int kSmem = L::kTotal + kCopyExtra;
+  static_assert(kSmem <= 232448, "copy-job kernel exceeds the shared memory of an SM");
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, p.M, p.K, lda, BM, BK);
+  else       rc = make_tmap_2d_bf16(&tmA, A, p.K, p.M, lda, BK, 64);
+  if (rc != kErrOk) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN, BK);
+  else       rc = make_tmap_2d_bf16(&tmB, B, p.K, p.N, ldb, BK, 64);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_copy_job_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  // one CTA per SM even when there are fewer tiles: every CTA's copy warp moves a share of the units
+  kern<<<num_sms(), kGatherThreads, kSmem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+// Stand-alone form of the copy job (no GEMM to ride on: the first layer of a step): two copy warps per CTA.
+constexpr int kGatherWarps = 4;
+constexpr int kGatherSmem = kGatherWarps * 2 * kCopyUnit + 128;
+__global__ void __launch_bounds__(kGatherWarps * 32, 1)
+copy_job_kernel(const int4* __restrict__ table, int u0, int u1, Params p) {
+  extern __shared__ uint8_t gather_smem_raw[];
+  uint8_t* gs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gather_smem_raw) + 127) & ~uintptr_t(127));
+  auto bufs = reinterpret_cast<uint8_t(*)[2][kCopyUnit]>(gs);
+  __shared__ __align__(8) uint64_t bars[kGatherWarps][2];
+  __shared__ int abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int w = 0; w < kGatherWarps; ++w) {
+      mbar_init(&bars[w][0], 1);
+      mbar_init(&bars[w][1], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_word;
+  if (lane != 0) return;
+  const int stride = static_cast<int>(gridDim.x) * kGatherWarps;
+  auto issue = [&](int u, int b) {
+    const int4 e = __ldg(table + u);
+    const uint32_t bytes = static_cast<uint32_t>(e.w) << 4;
+    mbar_expect_tx(&bars[warp][b], bytes);
+    bulk_load(bufs[warp][b], p.cj_src[e.x] + (static_cast<size_t>(static_cast<uint32_t>(e.y)) << 4), bytes, &bars[warp][b]);
+  };
+  int u = u0 + static_cast<int>(blockIdx.x) * kGatherWarps + warp;
+  uint32_t ph0 = 0, ph1 = 0;
+  int j = 0;
+  bool ok = true, pending_load = false;
+  if (u < u1) issue(u, 0);
+  while (u < u1) {
+    const int un = u + stride;
+    const int b = j & 1;
+    pending_load = false;
+    if (un < u1) {
+      bulk_wait_read<0>();
+      issue(un, b ^ 1);
+      pending_load = true;
+    }
+    ok = mbar_wait(&bars[warp][b], b ? ph1 : ph0, abort_flag, p.status, 420, b);
+    if (!ok) break;
+    if (b) ph1 ^= 1; else ph0 ^= 1;
+    const int4 e = __ldg(table + u);
+    bulk_store(p.cj_dst + (static_cast<size_t>(static_cast<uint32_t>(e.z)) << 4), bufs[warp][b], static_cast<uint32_t>(e.w) << 4);
+    bulk_commit();
+    u = un;
+    ++j;
+  }
+  bulk_wait<0>();
+  if (!ok && pending_load) mbar_wait_quiet(&bars[warp][(j & 1) ^ 1], (j & 1) ? ph0 : ph1);
 }
 
 }  // namespace gemm
@@ -946,26 +1106,30 @@ extern "C" int lvb_gemm_allgather_a(const void* const* a_peers, int rank, int wo
   return N > 128 ? launch_gather_a<256>(B, p, ldb, s) : launch_gather_a<128>(B, p, ldb, s);
 }
 
-// Reduce-scatter fused into a GEMM: out[M / world, N] = rows [rank * M / world, ...) of sum_s A_s[M, K_s] B_s[N, K_s]^T, where
-// every rank s calls this with its own partial operands.  Tile by tile the epilogue stores the partial product (fp32, or
-// bf16 when staging_f32 is 0: half the NVLink traffic, partial sums rounded as in a bf16 NCCL reduce-scatter) into slot
-// `rank` of the staging buffer of the rank that owns the tile's rows (c_slots[r]: a pointer to that slot in rank r's memory;
-// staging layout [world, M / world, ldc] elements) and adds 1 to that rank's arrival counter of the tile (cnt_peers[r]:
-// (M / world / 128) * lvb_gemm_tiles_n(N) ints in rank r's memory).  The raster deals the m-blocks round-robin over the
-// ranks.  Four more warps per CTA sum this rank's own tiles over the slots (`staging`: this rank's own buffer) as soon as a
-// tile's counter reaches `target`.  The counters are never reset: the caller passes target = 4 * world * (number of
-// products, this one included, that have used these counters), and alternates between two staging areas with their own
-// counters from call to call, which makes any cross-rank barrier between calls unnecessary: a rank can only be one call
-// ahead of its slowest peer, because its own call completes only when every peer's parts of that call have arrived.
-// M / world must be a multiple of 128, N of 8.
-extern "C" int lvb_gemm_reduce_scatter(const void* A, const void* B, void* const* c_slots, int* const* cnt_peers, int rank,
-                                       int world, const void* staging, long long slot_elems, int staging_f32, int target,
-                                       void* out, int ldo, int out_f32, int M, int N, int K, int lda, int ldb, int ldc,
-                                       float alpha, int* status, void* stream) {
+// Reduce-scatter fused into a GEMM: out[M / world, N] (+)= rows [rank * M / world, ...) of sum_s op(A_s) op(B_s)^T, where
+// every rank s calls this with its own partial operands (a_mn / b_mn as for lvb_gemm_bf16: the weight-gradient form
+// dW = dY^T X is a_mn = b_mn = 1 with the tokens as the reduction index).  Tile by tile the epilogue stores the partial
+// product (fp32, or bf16 when staging_f32 is 0: half the NVLink traffic, partial sums rounded as in a bf16 NCCL
+// reduce-scatter) into slot `rank` of the staging buffer of the rank that owns the rows (c_slots[r]: a pointer to that slot
+// in rank r's memory; staging layout [world, M / world, ldc] elements), 32 rows (one epilogue warp) at a time, and adds 1 to
+// that rank's arrival counter of the (32-row group, column tile) unit (cnt_peers[r]: lvb_gemm_rs_counters(M / world, N) ints
+// in rank r's memory).  m_order (device, int32[ceil(M / 128)]) is the order in which the row blocks are visited; the
+// caller deals them out to their owners in turn.  Four more warps per CTA sum this rank's own units over the slots
+// (`staging`: this rank's own buffer) as soon as a unit's counter reaches `target`.  The counters are never reset: the
+// caller passes target = world * (number of products, this one included, that have used these counters), and alternates
+// between two staging areas with their own counters from call to call, which makes any cross-rank barrier between calls
+// unnecessary: a rank can only be one call ahead of its slowest peer, because its own call completes only when every
+// peer's parts of that call have arrived.  M / world must be a multiple of 32, N of 8.  With `accumulate` (fp32 out only)
+// the reduced rows are added to `out`.
+extern "C" int lvb_gemm_reduce_scatter(const void* A, const void* B, int a_mn, int b_mn, void* const* c_slots, int* const* cnt_peers,
+                                       int rank, int world, const void* staging, long long slot_elems, int staging_f32, int target,
+                                       const int* m_order, void* out, int ldo, int out_f32, int accumulate, int M, int N, int K,
+                                       int lda, int ldb, int ldc, float alpha, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::gemm;
   if (world <= 0 || world > kMaxPeers || rank < 0 || rank >= world || M <= 0 || N <= 0 || K <= 0) return kErrBadArg;
-  if (M % world != 0 || (M / world) % BM != 0 || (N & 7) || (ldc & 7) || (ldo & 7) || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (M % world != 0 || (M / world) % 32 != 0 || (N & 7) || (ldc & 7) || (ldo & 7) || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (m_order == nullptr || (accumulate && !out_f32) || (a_mn != b_mn)) return kErrBadArg;
   Params p;
   p.C = c_slots[rank]; p.bias = nullptr; p.residual = nullptr;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
@@ -980,8 +1144,66 @@ extern "C" int lvb_gemm_reduce_scatter(const void* A, const void* B, void* const
     p.c_cnt[r] = cnt_peers[r < world ? r : 0];
   }
   p.rs_staging = reinterpret_cast<const float*>(staging); p.rs_slot = slot_elems; p.rs_out = out; p.rs_ldo = ldo; p.rs_out_f32 = out_f32; p.c_target = target;
+  p.c_m_order = m_order; p.rs_accumulate = accumulate;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return N > 128 ? launch_scatter_c<256>(A, B, p, lda, ldb, s) : launch_scatter_c<128>(A, B, p, lda, ldb, s);
+  if (a_mn) return N > 128 ? launch_scatter_c<256, true, true>(A, B, p, lda, ldb, s) : launch_scatter_c<128, true, true>(A, B, p, lda, ldb, s);
+  return N > 128 ? launch_scatter_c<256, false, false>(A, B, p, lda, ldb, s) : launch_scatter_c<128, false, false>(A, B, p, lda, ldb, s);
+}
+
+// Arrival counters of lvb_gemm_reduce_scatter for an owner's [rows, N] slice.
+extern "C" int lvb_gemm_rs_counters(int rows, int N) { return ((rows + 31) / 32) * (N > 128 ? (N + 255) / 256 : 1); }
+
+// lvb_gemm_bf16 whose CTAs also carry out a copy job: units [u0, u1) of `table` (device; int4 {source rank, source byte
+// offset / 16, destination byte offset / 16, bytes / 16}, at most 16 KB per unit, offsets and sizes multiples of 16 bytes)
+// are moved from srcs[rank] + offset (peer or local memory) to dst + offset by a seventh warp of every CTA while the
+// tensor cores multiply.  The GEMM itself does not read what is copied; a later kernel on the same stream may.  N must be
+// larger than 128 (the 256-column tile configuration has the shared memory to spare).
+extern "C" int lvb_gemm_bf16_copy_job(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                      int a_mn, int b_mn, int flags, float alpha, const void* bias, const void* residual, int ldr,
+                                      const void* table, int u0, int u1, const void* const* srcs, int n_srcs, void* dst,
+                                      int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (M <= 0 || N <= 128 || K <= 0 || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (table == nullptr || dst == nullptr || n_srcs <= 0 || n_srcs > kMaxPeers || u1 < u0) return kErrBadArg;
+  Params p;
+  p.C = C; p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
+  p.flags = flags; p.alpha = alpha; p.status = status; p.alpha_dev = nullptr;
+  p.a_fmt = p.b_fmt = 0;
+  p.rank = 0; p.world = 1; p.m_rot = 0; p.a_rows_per_map = 0; p.c_rows_per_rank = 0;
+  p.cj_table = reinterpret_cast<const int4*>(table); p.cj_u0 = u0; p.cj_u1 = u1;
+  for (int r = 0; r < kMaxPeers; ++r) p.cj_src[r] = reinterpret_cast<const uint8_t*>(srcs[r < n_srcs ? r : 0]);
+  p.cj_dst = reinterpret_cast<uint8_t*>(dst);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return launch_copy_job<256, false, false>(A, B, p, lda, ldb, s);
+  if (!a_mn && b_mn) return launch_copy_job<256, false, true>(A, B, p, lda, ldb, s);
+  if (a_mn && b_mn) return launch_copy_job<256, true, true>(A, B, p, lda, ldb, s);
+  return launch_copy_job<256, true, false>(A, B, p, lda, ldb, s);
+}
+
+// The copy job on its own (see lvb_gemm_bf16_copy_job): used when no GEMM precedes the consumer, e.g. for the first layer
+// of a step.  `ctas` <= 0 means one per SM.
+extern "C" int lvb_copy_job(const void* table, int u0, int u1, const void* const* srcs, int n_srcs, void* dst, int ctas, int* status,
+                            void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm;
+  if (table == nullptr || dst == nullptr || n_srcs <= 0 || n_srcs > kMaxPeers || u1 < u0) return kErrBadArg;
+  if (u1 == u0) return kErrOk;
+  Params p;
+  p.status = status;
+  for (int r = 0; r < kMaxPeers; ++r) p.cj_src[r] = reinterpret_cast<const uint8_t*>(srcs[r < n_srcs ? r : 0]);
+  p.cj_dst = reinterpret_cast<uint8_t*>(dst);
+  int grid = ctas > 0 ? ctas : num_sms();
+  const int need = (u1 - u0 + kGatherWarps - 1) / kGatherWarps;
+  if (grid > need) grid = need;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(copy_job_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherSmem) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  copy_job_kernel<<<grid, kGatherWarps * 32, kGatherSmem, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const int4*>(table), u0, u1, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
 
 // Tiles along N of the kernels above for an N-column output (sizes the per-tile counters).

@@ -67,15 +67,55 @@ def all_gather_matmul(x_sym: SymmetricBuffer, rows: int, k: int, w: torch.Tensor
     return out
 
 
+def scatter_m_order(M: int, world: int, rank: int) -> list:
+    """Order in which a reduce-scatter GEMM visits the 128-row blocks of an ``M``-row product: the blocks are dealt out to the
+    ranks that own them in turn (a block belongs to the owner of its first row), next rank first and own rank last in each
+    round, so that every rank's rows are produced at a steady rate by all ranks at once."""
+    rows = M // world
+    per_owner = [[] for _ in range(world)]
+    for b in range((M + 127) // 128):
+        per_owner[min((b * 128) // rows, world - 1)].append(b)
+    owners = [(rank + 1 + i) % world for i in range(world)]
+    order = []
+    for i in range(max(len(x) for x in per_owner)):
+        for d in owners:
+            if i < len(per_owner[d]):
+                order.append(per_owner[d][i])
+    return order
+
+
+_m_order_cache = {}
+
+
+def m_order_tensor(M: int, world: int, rank: int, device) -> torch.Tensor:
+    key = (M, world, rank, str(device))
+    t = _m_order_cache.get(key)
+    if t is None:
+        t = _m_order_cache[key] = torch.tensor(scatter_m_order(M, world, rank), dtype=torch.int32, device=device)
+    return t
+
+
+def rs_counters(rows: int, N: int) -> int:
+    """Arrival counters of one staging area for an owner's ``[rows, N]`` slice (one per 32 rows x column tile)."""
+    return ((rows + 31) // 32) * ((N + 255) // 256 if N > 128 else 1)
+
+
 def reduce_scatter_staging_elems(M: int, N: int, dtype: torch.dtype = torch.float32) -> int:
     """Elements of ``dtype`` (fp32 or bf16) of symmetric staging that :func:`matmul_reduce_scatter` needs for an ``[M, N]``
-    product: two areas (used alternately), each of ``W`` slots plus its int32 per-tile arrival counters."""
+    product: two areas (used alternately), each of ``W`` slots plus its int32 arrival counters."""
     return 2 * _rs_area_elems(M, N, dtype)
 
 
 def _rs_area_elems(M, N, dtype):
-    tiles = ((M + 127) // 128) * lib.fn("lvb_gemm_tiles_n", [lib.c_int], launches=0)(N)
-    return (M * N + tiles * (4 // dtype.itemsize) + 127) // 128 * 128  # keeps the second area 256-byte aligned
+    cnt = rs_counters(M, N)  # an upper bound on the counters of one rank's slice, whatever the number of ranks
+    return (M * N + cnt * (4 // dtype.itemsize) + 127) // 128 * 128  # keeps the second area 256-byte aligned
+
+
+def _rs_fn():
+    c = lib
+    return _fn("lvb_gemm_reduce_scatter", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p,
+                                           c.c_longlong, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int] + [c.c_int] * 6
+               + [c.c_float, c.c_void_p, c.c_void_p])
 
 
 def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBuffer, out: Optional[torch.Tensor] = None,
@@ -87,7 +127,6 @@ def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBu
 
     No barrier and no counter reset happen per call: the kernel alternates between the buffer's two areas and its arrival
     counters only grow (the first call on a buffer clears it and synchronises the ranks once)."""
-    c = lib
     W, r = staging.world, staging.rank
     M, K = x.shape
     N = w.shape[0]
@@ -105,7 +144,7 @@ def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBu
     n = state["calls"]
     state["calls"] = n + 1
     base = (n & 1) * area * es  # byte offset of this call's area
-    target = 4 * W * (n // 2 + 1)
+    target = W * (n // 2 + 1)
     if out is None:
         out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
     slots = _ptr_array([p + base + r * slot * es for p in staging.peer_ptrs])  # this rank's slot in every rank's area
@@ -116,10 +155,8 @@ def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBu
         own = staging.peer_ptrs[r]
         slots = _ptr_array([own + base + d * slot * es for d in range(W)])
         cnts = _ptr_array([own + base + W * slot * es] * W)
-    f = _fn("lvb_gemm_reduce_scatter", [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_longlong,
-                                        c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_int] + [c.c_int] * 6 + [c.c_float, c.c_void_p, c.c_void_p])
-    rc = f(x.data_ptr(), w.data_ptr(), slots, cnts, r, W, st.data_ptr() + base, slot, 1 if st.dtype == torch.float32 else 0, target,
-           out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, M, N, K, x.stride(0), w.stride(0), N, 1.0,
-           lib.status_buffer().data_ptr(), lib.stream_ptr())
+    rc = _rs_fn()(x.data_ptr(), w.data_ptr(), 0, 0, slots, cnts, r, W, st.data_ptr() + base, slot, 1 if st.dtype == torch.float32 else 0, target,
+                  m_order_tensor(M, W, r, x.device).data_ptr(), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, 0,
+                  M, N, K, x.stride(0), w.stride(0), N, 1.0, lib.status_buffer().data_ptr(), lib.stream_ptr())
     lib.check_rc(rc, "lvb_gemm_reduce_scatter")
     return out

@@ -129,6 +129,17 @@ def gemm(
         )
         lib.check_rc(rc, "lvb_gemm_skinny")
         return out
+    if _copy_job_provider is not None and N > 128 and max_ctas == 0:
+        job = _copy_job_provider(2.0 * M * N * K)
+        if job is not None:
+            table, u0, u1, srcs, n_srcs, dst = job
+            rc = _cj_fn()(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr,
+                table, u0, u1, srcs, n_srcs, dst, lib.status_buffer().data_ptr(), lib.stream_ptr(),
+            )
+            lib.check_rc(rc, "lvb_gemm_bf16_copy_job")
+            return out
     rc = _fn()(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr, int(max_ctas),
@@ -136,6 +147,29 @@ def gemm(
     )
     lib.check_rc(rc, "lvb_gemm_bf16")
     return out
+
+
+# A provider of copy jobs (``flops -> (table_ptr, u0, u1, src_ptr_array, n_srcs, dst_ptr) | None``): when one is set, dense
+# GEMMs ask it before every launch and, given a job, run the kernel variant whose extra warp carries out the copies beside
+# the tensor cores (the next layer's weight gather of fully sharded training, ``parallel/zero3.py``).
+_copy_job_provider = None
+_cj = None
+
+
+def set_copy_job_provider(fn) -> None:
+    global _copy_job_provider
+    _copy_job_provider = fn
+
+
+def _cj_fn():
+    global _cj
+    if _cj is None:
+        c = lib
+        _cj = lib.fn("lvb_gemm_bf16_copy_job",
+                     [c.c_void_p, c.c_void_p, c.c_void_p] + [c.c_int] * 9 + [c.c_float, c.c_void_p, c.c_void_p, c.c_int,
+                                                                              c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p,
+                                                                              c.c_void_p, c.c_void_p])
+    return _cj
 
 
 SKINNY_MAX_ROWS = 128
@@ -175,7 +209,8 @@ class _LinearFn(torch.autograd.Function):
 
     If ``weight`` carries a ``main_grad`` attribute (an fp32 buffer of the same shape, owned by the
     sharded-gradient engine) the weight gradient is accumulated straight into it by the GEMM
-    epilogue and autograd sees no dense weight gradient.
+    epilogue and autograd sees no dense weight gradient.  If it carries a ``grad_sink`` (weights that exist only as
+    row slices per rank, ``parallel/zero3.py``) the two operands of the weight-gradient product are handed to it.
     """
 
     @staticmethod
@@ -202,7 +237,11 @@ class _LinearFn(torch.autograd.Function):
             dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(ctx.weight_ref, "main_grad", None)
-            if main_grad is not None:
+            sink = getattr(ctx.weight_ref, "grad_sink", None)
+            if sink is not None:
+                sink(dy2, x2)  # fully sharded weights: the product is reduce-scattered to the rows' owners as it is computed
+                dw = None
+            elif main_grad is not None:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
                 dw = None
             else:

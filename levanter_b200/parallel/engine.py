@@ -16,6 +16,12 @@ over ``data``; XLA all-gathers weights and reduce-scatters gradients, src/levant
   Because weights stay resident, communication is one reduce-scatter plus one all-gather *per step*, not per
   micro-batch and not per layer pass.
 
+With ``zero_stage=3`` (more than one data rank, sharded optimizer) the weight matrices of the decoder layers leave this
+scheme: they are cut by rows, every rank keeps only its rows (compute-dtype copy, fp32 master, moments, fp32 gradient
+accumulator), whole layers are assembled in two staging slots just before use and weight gradients are reduce-scattered as
+they are produced (``parallel/zero3.py``).  Everything else (embeddings, LM head, norms, biases) stays in the flat buffers
+described above.  ``zero_stage=1`` is the scheme above for all parameters.
+
 Optimizers run on ``{param path: 1-D view of the owned slice}`` trees, so any element-wise transformation chain works
 sharded.  Optimizers that need whole matrices (Muon, SOAP, Kron, ...) run with ``shard_optimizer=False``: gradients are
 all-reduced and every rank updates full tensors.  AdamW has a fused CUDA path (``ops/csrc/optim.cu``).
@@ -50,6 +56,7 @@ class ParamSlot:
     offset: int  # in the flat buffers
     bucket: int
     ep_dim: Optional[int] = None  # expert-parallel parameters: the axis the experts are sliced over (each rank holds its slice)
+    streamed: bool = False  # zero-3: lives outside the flat buffers (``offset`` is a virtual position past their end)
 
 
 @dataclass
@@ -87,7 +94,7 @@ def default_bucket_of(model: nn.Module) -> Callable[[str], str]:
 class ShardedEngine:
     def __init__(self, model: nn.Module, mp: Policy, mesh=None, *, device=None, shard_optimizer: bool = True,
                  grad_reduce_dtype: torch.dtype = torch.float32, is_trainable: Optional[Callable[[str], bool]] = None,
-                 bucket_of: Optional[Callable[[str], str]] = None, comm: Optional[str] = None):
+                 bucket_of: Optional[Callable[[str], str]] = None, comm: Optional[str] = None, zero_stage: int = 1):
         """``comm``: ``"nccl"`` (library reduce-scatter / all-gather per bucket) or ``"p2p"`` (gradient pull-reduce and AdamW with
         an all-gather epilogue as two kernels over peer-mapped buffers); ``"multimem"`` is the same through the switch's multicast mapping (one reduced load, one broadcast store per
         element).  Default: ``LEVANTER_B200_COMM`` if set, else ``multimem``, degrading to ``p2p`` and ``nccl`` when the fabric
@@ -107,6 +114,8 @@ class ShardedEngine:
         self.model_group = mesh.model_group if (mesh is not None and mesh.model_size > 1) else None
         self.shard_optimizer = shard_optimizer or self.world == 1
         self.grad_reduce_dtype = grad_reduce_dtype
+        self.stream = None  # zero-3 layer streamer
+        self.zero_stage = 3 if (zero_stage == 3 and self.world > 1 and self.shard_optimizer and mp.param_dtype == torch.float32) else 1
         self._build_layout(is_trainable, bucket_of or default_bucket_of(model))
         self.opt = None
         self.opt_state = None
@@ -141,6 +150,22 @@ class ShardedEngine:
         def bucket_of(name: str) -> str:  # noqa: F811
             return plain_bucket_of(name) + ("#experts" if is_local[name] else "")
 
+        # zero-3: the weight matrices of the layer stack are streamed (see parallel/zero3.py); the rest is laid out below
+        stream_layers: Dict[str, List[Tuple[str, nn.Parameter]]] = {}
+        if self.zero_stage == 3:
+            from .zero3 import eligible
+
+            keep = []
+            for name, p in named:
+                b = plain_bucket_of(name)
+                if b != "root" and not is_local[name] and eligible(p, W):
+                    stream_layers.setdefault(b, []).append((name, p))
+                else:
+                    keep.append((name, p))
+            if stream_layers:
+                named = keep
+            else:
+                self.zero_stage = 1
         order: Dict[str, int] = {}
         for name, _ in named:
             order.setdefault(bucket_of(name), len(order))
@@ -194,6 +219,15 @@ class ShardedEngine:
             self.grad_flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         # owned slices, concatenated bucket by bucket
         self.shard_numel = sum(b.end - b.start if b.local else (b.end - b.start) // W for b in self.buckets) if self.shard_optimizer else self.total
+        self.stream_lo = self.shard_numel  # zero-3: the streamed matrices' rows follow the owned slices in every per-rank buffer
+        if stream_layers:
+            from .zero3 import LayerStreamer
+
+            names = list(stream_layers.keys())
+            modules = [self.model.get_submodule(b) for b in names]
+            self.stream = LayerStreamer([stream_layers[b] for b in names], modules, world=W, rank=self.rank, group=self.data_group,
+                                        device=self.device, compute_dtype=cd, comm=self.comm if use_p2p or self.comm == "nccl" else "nccl")
+            self.shard_numel += self.stream.shard_numel
         self.has_local = any(b.local for b in self.buckets)
         self.master_is_param = (pd == cd and W == 1) or (pd == cd and not self.shard_optimizer)
         if self.master_is_param:
@@ -215,9 +249,29 @@ class ShardedEngine:
                 if a < e:
                     self.segments[s.name] = (local + (a - lo), a, e - a)
             local += hi - lo
+        if self.stream is not None:
+            st = self.stream
+            st.grad_shard = self.grad_shard[self.stream_lo:]
+            virt = self.total
+            with torch.no_grad():
+                for sp in st.params:
+                    slot = ParamSlot(sp.name, sp.param, sp.shape, sp.param.numel(), virt, -1, None, streamed=True)
+                    self.slots.append(slot)
+                    self._shapes[sp.name] = sp.shape
+                    lo = self.stream_lo + sp.shard_off
+                    self.segments[sp.name] = (lo, virt + self.rank * sp.shard_numel, sp.shard_numel)
+                    mine = sp.param.data[self.rank * sp.rows:(self.rank + 1) * sp.rows].reshape(-1)
+                    self.master[lo:lo + sp.shard_numel].copy_(mine)
+                    st.w_shard[sp.shard_off:sp.shard_off + sp.shard_numel].copy_(mine)
+                    virt += sp.param.numel()
+            st.attach()
+            if st.peer:
+                st._sym_w.barrier(1)  # every rank's rows are in place before anyone assembles a layer from them
         # move the data: master slices take the original (param-dtype) values, the flat buffer their compute-dtype cast
         with torch.no_grad():
             for s in self.slots:
+                if s.streamed:
+                    continue
                 src = s.param.data
                 seg = self.segments.get(s.name)
                 if seg is not None and not self.master_is_param:
@@ -240,9 +294,22 @@ class ShardedEngine:
                 if seg is None:
                     continue
                 lo, fo, n = seg
+                if s.streamed and not (source is not None and s.name in source):
+                    continue  # the parameter is a view of a staging slot: the master rows already hold its values
                 src = source[s.name].reshape(-1) if source is not None and s.name in source else s.param.data.reshape(-1)
                 a = fo - s.offset
                 self.master[lo:lo + n].copy_(src[a:a + n].to(self.master.dtype))
+        self.sync_streamed_from_master()
+
+    def sync_streamed_from_master(self) -> None:
+        """zero-3: refresh the compute-dtype rows that peers gather from after the master rows were set from outside (a
+        checkpoint, an initial state)."""
+        if self.stream is not None:
+            with torch.no_grad():
+                self.stream.w_shard.copy_(self.master[self.stream_lo:])
+            self.stream.invalidate()
+            if self.stream.peer:
+                self.stream._sym_w.barrier(1)
 
     # ------------------------------------------------------------------------------------------ trees
     def _shaped(self, name: str, flat: torch.Tensor) -> torch.Tensor:
@@ -286,6 +353,8 @@ class ShardedEngine:
     # ------------------------------------------------------------------------------------------ gradients
     def zero_grad(self) -> None:
         self.grad_flat.zero_()
+        if self.stream is not None:
+            self.grad_shard[self.stream_lo:].zero_()  # the streamed rows accumulate here during the backward passes
         for s in self.slots:
             s.param.grad = None
 
@@ -294,13 +363,15 @@ class ShardedEngine:
         the fp32 accumulator."""
         for s in self.slots:
             g = s.param.grad
-            if g is not None:
+            if g is not None and not s.streamed:  # (a streamed matrix's gradient was reduced the moment autograd produced it)
                 s.param.main_grad.add_(g.to(torch.float32).view(s.shape))
                 s.param.grad = None
 
     def reduce_grads(self, scale: float = 1.0) -> None:
         """Average gradients over the data axis into the owned slices (and over replicas)."""
         W = self.world
+        if self.stream is not None and scale != 1.0:
+            self.grad_shard[self.stream_lo:].mul_(scale)  # already averaged over the ranks, row slice by row slice
         if self._sym_grad is not None:
             self._p2p_reduce_grads(scale)
             if self.replica_group is not None:
@@ -381,6 +452,10 @@ class ShardedEngine:
         if self._sym_grad is not None and getattr(self, "_p2p_sumsq_valid", False) and self.replica_group is None:
             sq = self._p2p_sumsq.clone()
             self._p2p_sumsq_valid = False
+            if self.stream is not None:  # the reduce kernels covered the flat buffers only
+                from ..ops.optim_kernels import sumsq
+
+                sq = sq + sumsq(g[self.stream_lo:])
         elif self.device.type == "cuda" and lib.available():
             from ..ops.optim_kernels import sumsq
 
@@ -411,6 +486,9 @@ class ShardedEngine:
     def step(self, *, grad_scale: float = 1.0, loss: Optional[torch.Tensor] = None, **extra) -> None:
         """collect -> reduce -> optimizer update on owned slices -> refresh compute-dtype parameters everywhere."""
         self.collect_grads()
+        if self.stream is not None and self.stream.peer:
+            # peers may still be pulling this rank's weight rows for their last layers: nobody overwrites rows before all are done
+            self.stream._sym_w.barrier(0)
         self.reduce_grads(grad_scale)
         if self.fused_adam is not None:
             self.fused_adam.step()
@@ -433,6 +511,10 @@ class ShardedEngine:
         if self._sym_grad is not None:
             # peers read this rank's gradients and write this rank's weights: nobody may run ahead into the next step
             self._sym_param.barrier(1)
+        if self.stream is not None:
+            self.stream.invalidate()
+            if self.stream.peer:
+                self.stream._sym_w.barrier(1)  # every rank's new rows are in place before anyone gathers them
         self.zero_grad()
 
     def publish_params(self) -> None:
@@ -440,6 +522,8 @@ class ShardedEngine:
         W = self.world
         if self.master_is_param:
             return
+        if self.stream is not None and (self.fused_adam is None or not self.fused_adam.writes_compute_copy):
+            self.stream.w_shard.copy_(self.master[self.stream_lo:])
         if not self.shard_optimizer or W == 1:
             if self.fused_adam is None or not self.fused_adam.writes_compute_copy:
                 self.param_flat.copy_(self.master)
@@ -473,7 +557,13 @@ class ShardedEngine:
                     continue
                 n = (b.end - b.start) // W
                 dist.all_gather_into_tensor(flat[b.start:b.end], shard[lstart:lstart + n].contiguous(), group=self.data_group)
-            return {s.name: local_full[s.name] if s.ep_dim is not None else flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots}
+            out = {s.name: local_full[s.name] if s.ep_dim is not None else flat[s.offset:s.offset + s.numel].view(s.shape)
+                   for s in self.slots if not s.streamed}
+            if self.stream is not None:
+                for sp in self.stream.params:
+                    lo = self.stream_lo + sp.shard_off
+                    out[sp.name] = self.stream.gather_full(sp, shard[lo:lo + sp.shard_numel])
+            return out
         return {s.name: flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots}
 
     def _gather_local_bucket(self, b: Bucket, mine: torch.Tensor) -> Dict[str, torch.Tensor]:
@@ -527,7 +617,12 @@ class ShardedEngine:
             o = slot.offset - b.start
             return cache["flat"][o:o + slot.numel].view(slot.shape)
 
-        return {s.name: DeferredLeaf(lambda s=s: fetch(s), self._full_shape(s), shard.dtype) for s in self.slots}
+        out = {s.name: DeferredLeaf(lambda s=s: fetch(s), self._full_shape(s), shard.dtype) for s in self.slots if not s.streamed}
+        if self.stream is not None:
+            for sp in self.stream.params:
+                lo = self.stream_lo + sp.shard_off
+                out[sp.name] = DeferredLeaf(lambda sp=sp, lo=lo: self.stream.gather_full(sp, shard[lo:lo + sp.shard_numel]), sp.shape, shard.dtype)
+        return out
 
     def scatter_named(self, full: Dict[str, torch.Tensor], shard: torch.Tensor) -> None:
         """Inverse of :meth:`_gather_named`: copy the owned part of each full tensor into ``shard``."""
@@ -544,10 +639,11 @@ class ShardedEngine:
         """Set parameters (master and compute copies) from full tensors."""
         with torch.no_grad():
             for s in self.slots:
-                if s.name in full:
+                if s.name in full and not s.streamed:
                     s.param.data.copy_(self._own_part(s, full[s.name]).to(device=self.device, dtype=self.param_flat.dtype).reshape(s.shape))
         if not self.master_is_param:
             self.scatter_named({k: v.to(self.device) for k, v in full.items()}, self.master)
+        self.sync_streamed_from_master()
 
     def optimizer_state_tree(self, deferred: bool = False) -> Any:
         """Optimizer state with every tensor leaf at its full parameter shape (for checkpoints).  With ``deferred`` the
@@ -643,6 +739,8 @@ class FusedAdamW:
         # contiguous runs of equal weight decay over the local slice (gaps are padding: no decay, zero grads)
         runs: List[Tuple[int, int, float]] = []
         starts = set(engine._bucket_local_start)
+        if engine.stream is not None:
+            starts.add(engine.stream_lo)  # a run never spans the flat buffers' slices and the streamed rows
         for name in sorted(names, key=lambda k: engine.segments[k][0]):
             lo, fo, n = engine.segments[name]
             wd = cfg.weight_decay if (mask.get(name, True) and cfg.weight_decay > 0) else 0.0
@@ -678,6 +776,9 @@ class FusedAdamW:
             for lo, hi, wd in self.runs:
                 if hi <= lo:
                     continue
+                if e.stream is not None and lo >= e.stream_lo:
+                    self._step_streamed(lo, hi, wd, lr, bc1, bc2)
+                    continue
                 hi8 = lo + ((hi - lo + 7) // 8) * 8  # the tail up to the next 8 is layout padding (zero weights, zero gradients)
                 if e.has_local and self._run_is_local(lo):  # rank-local experts: the new weights go to this rank's buffer only
                     rc = f(e.master[lo:hi8].data_ptr(), self.m[lo:hi8].data_ptr(), self.v[lo:hi8].data_ptr(), e.grad_shard[lo:hi8].data_ptr(),
@@ -703,10 +804,22 @@ class FusedAdamW:
         for lo, hi, wd in self.runs:
             if hi <= lo:
                 continue
+            if e.stream is not None and lo >= e.stream_lo:
+                self._step_streamed(lo, hi, wd, lr, bc1, bc2)
+                continue
             # compute-dtype destination: the owned slice inside param_flat
             dst = self._compute_view(lo, hi)
             adamw(e.master[lo:hi], self.m[lo:hi], self.v[lo:hi], e.grad_shard[lo:hi], dst, lr, c.beta1, c.beta2, c.epsilon,
                   wd, bc1, bc2, self.coef, 1.0, c.nesterov)
+
+    def _step_streamed(self, lo: int, hi: int, wd: float, lr: float, bc1: float, bc2: float) -> None:
+        """zero-3 rows: the new compute-dtype values go to this rank's own rows; peers pull them when they assemble a layer."""
+        from ..ops.optim_kernels import adamw
+
+        e, c = self.e, self.cfg
+        s0 = e.stream_lo
+        adamw(e.master[lo:hi], self.m[lo:hi], self.v[lo:hi], e.grad_shard[lo:hi], e.stream.w_shard[lo - s0:hi - s0], lr, c.beta1, c.beta2,
+              c.epsilon, wd, bc1, bc2, self.coef, 1.0, c.nesterov)
 
     def _run_is_local(self, lo: int) -> bool:
         e = self.e

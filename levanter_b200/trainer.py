@@ -499,7 +499,8 @@ class Trainer:
         needs_full = self.optimizer_config is not None and getattr(self.optimizer_config, "needs_full_tensors", False)
         engine = ShardedEngine(model, cfg.mp, mesh, device=self.device,
                                shard_optimizer=cfg.shard_optimizer and not needs_full,
-                               grad_reduce_dtype=Policy.parse(cfg.grad_reduce_dtype).param_dtype, is_trainable=is_trainable)
+                               grad_reduce_dtype=Policy.parse(cfg.grad_reduce_dtype).param_dtype, is_trainable=is_trainable,
+                               zero_stage=cfg.zero_stage)
         info = ParamInfo(model)
         if self.optimizer is None:
             self.optimizer = self.optimizer_config.build(cfg.num_train_steps, info)

@@ -26,7 +26,7 @@ def _init(rank, world, port, timeout_s=60):
     return dist
 
 
-def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None):
+def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None):
     from levanter_b200 import config as C
     from levanter_b200.data.dataset import ListAsyncDataset
     from levanter_b200.models.llama import LlamaConfig
@@ -40,7 +40,8 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None):
     g = torch.Generator().manual_seed(0)
     starts = torch.randint(0, VOCAB, (64,), generator=g)
     data = ListAsyncDataset([LmExample.causal(((s + torch.arange(16)) % VOCAB).to(torch.int32)) for s in starts], is_complete=True)
-    mcfg = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
+    mcfg = LlamaConfig(seq_len=16, hidden_dim=hidden, intermediate_dim=2 * hidden, num_layers=3 if hidden > 32 else 2, num_heads=2, num_kv_heads=2,
+                       gradient_checkpointing=False)
     opt = AdamConfig(learning_rate=3e-3, warmup=0.0, weight_decay=0.0, lr_schedule="constant", min_lr_ratio=1.0)
     if opt_dict is not None:
         from levanter_b200.optim import OptimizerConfig
@@ -50,14 +51,21 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None):
     with Trainer(cfg, opt, compute_next_token_loss) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(VOCAB, seed=3))
         trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
+        if expect_stage is not None:
+            assert state.engine.zero_stage == expect_stage, state.engine.zero_stage
         info = trainer.train(state, trainer.data_loader(data).iter_from_step(int(state.step)))
+        if expect_stage == 3:
+            st = state.engine.stream
+            assert st is not None and st.stats["library_weight_grads"] > 0
+            full = state.engine.full_master()  # whole matrices again, assembled from every rank's rows
+            return {k: full[k].detach().clone() for k, _ in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
 
 
-def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None):
+def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None):
     dist = _init(rank, world, port)
     try:
-        params, losses = _train(tmp, opt_dict=opt_dict, trainer_extra=trainer_extra)
+        params, losses = _train(tmp, opt_dict=opt_dict, trainer_extra=trainer_extra, hidden=hidden, expect_stage=expect_stage)
         if rank == 0:
             torch.save({"params": params, "losses": losses}, f"{tmp}/dist.pt")
     finally:
@@ -67,6 +75,17 @@ def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None):
 def test_two_rank_sharded_training_matches_single_process(tmp_path):
     single, losses = _train(str(tmp_path / "single"))
     mp.spawn(_sharded_worker, args=(2, 29711, str(tmp_path)), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+def test_two_rank_zero3_layer_streaming_matches_single_process(tmp_path):
+    """zero_stage 3 on two ranks (library transport on gloo): layer matrices live as row slices, are gathered per layer and
+    their gradients reduce-scattered as autograd produces them; losses and final weights equal one process."""
+    single, losses = _train(str(tmp_path / "single"), hidden=64)
+    mp.spawn(_sharded_worker, args=(2, 29723, str(tmp_path), None, {"zero_stage": 3, "per_device_parallelism": 2}, 64, 3), nprocs=2, join=True)
     got = torch.load(tmp_path / "dist.pt")
     assert got["losses"] == pytest.approx(losses, abs=2e-5)
     for k, v in single.items():
@@ -96,12 +115,22 @@ def test_two_replicas_take_the_same_step_as_one_process(tmp_path):
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
 
 
-def _first_half_worker(rank, world, port, tmp):
+def _first_half_worker(rank, world, port, tmp, hidden=32, trainer_extra=None):
     dist = _init(rank, world, port)
     try:
-        _train(tmp, steps=3)
+        _train(tmp, steps=3, hidden=hidden, trainer_extra=trainer_extra)
     finally:
         dist.destroy_process_group()
+
+
+def test_zero3_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
+    """The same with streamed layers: the row slices of weights and moments are gathered into whole tensors on save."""
+    full, losses = _train(str(tmp_path / "full"), steps=6, hidden=64)
+    mp.spawn(_first_half_worker, args=(2, 29716, str(tmp_path / "res"), 64, {"zero_stage": 3}), nprocs=2, join=True)
+    resumed, tail = _train(str(tmp_path / "res"), steps=6, hidden=64)
+    assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=3e-5)
+    for k, v in full.items():
+        assert torch.allclose(v, resumed[k], atol=3e-5), k
 
 
 def test_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
