@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_baseline"])
     ap.add_argument("--zero-stage", type=int, default=3, choices=[1, 3], help="see the module docstring")
+    ap.add_argument("--no-equiv", action="store_true", help="N > 1: skip the one-step comparison of the product path with the NCCL path")
     ap.add_argument("--no-baseline", action="store_true", help="ours: do not time the stock-PyTorch arm in the same call")
     ap.add_argument("--baseline-steps", type=int, default=5, help="timed steps of the in-call stock-PyTorch arm (after 3 warm-up steps)")
     # shape overrides for quick functional checks; a run that uses them is labelled in "config" and is not the headline
@@ -220,6 +221,53 @@ def main_torch_baseline(args):
     return 0
 
 
+def equivalence_check(args, mcfg, vocab, dev, rank) -> dict:
+    """Outside every timed region: one optimizer step of a 2-layer slice of the model (same layer shapes) from the same
+    initial state and batch, once on the library path (zero stage 1, NCCL reduce-scatter / all-gather) and once on the product
+    path (the configured stage and the peer-memory kernels).  Reports how far the two results are apart."""
+    import dataclasses
+
+    import torch
+
+    from levanter_b200.config import Policy
+    from levanter_b200.models.lm_model import LmExample, compute_next_token_loss
+    from levanter_b200.ops import lib
+    from levanter_b200.ops.gemm import set_copy_job_provider
+    from levanter_b200.optim import AdamConfig, ParamInfo
+    from levanter_b200.parallel.engine import ShardedEngine
+    from levanter_b200.parallel.mesh import DeviceMesh
+
+    import torch.distributed as dist
+
+    small = dataclasses.replace(mcfg, num_layers=2)
+    mesh = DeviceMesh(replica=1, data=dist.get_world_size(), model=1)
+    ocfg = AdamConfig(learning_rate=1e-3, weight_decay=0.1, warmup=0.0, max_grad_norm=1.0)
+    tokens = torch.randint(0, vocab, (1, args.seq_len), generator=torch.Generator().manual_seed(77 + rank), dtype=torch.int32).to(dev)
+    out = {}
+    for tag, comm, stage in (("nccl", "nccl", 1), ("product", os.environ.get("LEVANTER_B200_COMM", "multimem"), args.zero_stage)):
+        model = small.build(vocab, seed=0, device=dev)
+        eng = ShardedEngine(model, Policy.parse("p=f32,c=bfloat16"), mesh, device=dev, comm=comm, zero_stage=stage)
+        eng.set_optimizer(ocfg.build(10, ParamInfo(model)), optimizer_config=ocfg, num_train_steps=10)
+        loss = compute_next_token_loss(model, LmExample.causal(tokens))
+        loss.backward()
+        eng.step(loss=loss)
+        torch.cuda.synchronize()
+        lib.check_status()
+        out[tag] = (float(loss.detach()), float(eng.last_grad_norm), {k: v.float() for k, v in eng.full_master().items()}, eng.comm, eng.zero_stage)
+        set_copy_job_provider(None)
+        del eng, model
+    la, na, wa, _, _ = out["nccl"]
+    lb, nb, wb, comm_b, stage_b = out["product"]
+    lr = 1e-3
+    worst = max(float((wa[k] - wb[k]).abs().max()) for k in wa)
+    moved = sum(float(((wa[k] - wb[k]).abs() > 0.1 * lr).sum()) for k in wa) / sum(v.numel() for v in wa.values())
+    res = {"loss_abs_diff": abs(la - lb), "grad_norm_rel_err": abs(na - nb) / max(abs(na), 1e-30), "weights_max_abs_diff_in_steps": worst / lr,
+           "fraction_of_weights_off_by_more_than_a_tenth_of_a_step": moved, "product_path": f"zero{stage_b}/{comm_b}", "layers": 2}
+    del out, wa, wb
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -275,6 +323,10 @@ def main():
                              gradient_checkpointing=bool(args.remat), initializer_range=0.02)
     ocfg = AdamConfig(learning_rate=3e-4, weight_decay=0.1, warmup=100, max_grad_norm=1.0)
     headline = _is_headline(args)
+
+    equiv = None
+    if world > 1 and args.model == "llama" and not args.no_equiv:
+        equiv = equivalence_check(args, mcfg, vocab, dev, rank)
 
     with Trainer(tcfg, ocfg, add_default_hooks=False) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mcfg.build(vocab, seed=0, device=dev))
@@ -332,6 +384,10 @@ def main():
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = float(times[0]), float(times[1])
         mem_gb = torch.cuda.max_memory_allocated() / 2**30
+        from levanter_b200.parallel.symm import SymmetricBuffer
+
+        symm_gb = SymmetricBuffer.total_bytes / 2**30
+        stream_stats = dict(state.engine.stream.stats) if getattr(state.engine, "stream", None) is not None else None
         del state, loader, it, dev_batch, host_batches, info
 
     tokens_per_step = B * world * S
@@ -383,7 +439,11 @@ def main():
         "gpu_launches": launches,
         "mfu_vs_measured_sustained_cublas": flops_per_token * value / world / (peak_tf * 1e12),
         "mfu_vs_nominal_2.25PF": flops_per_token * value / world / 2.25e15,
-        "peak_mem_gib": mem_gb,
+        "peak_mem_gib": mem_gb, "symmetric_mem_gib": symm_gb,
+        "peak_mem_note": "peak_mem_gib is the caching allocator's peak; peer-mapped (symmetric) buffers are allocated outside it and listed "
+                         "separately (cumulative over the process, the equivalence check's small engines included)",
+        "zero3_stats": stream_stats,
+        "equiv_check": equiv,
         "torch_baseline_same_call": base,
     }
     if rank == 0:

@@ -140,13 +140,34 @@ def gemm(
             )
             lib.check_rc(rc, "lvb_gemm_bf16_copy_job")
             return out
-    rc = _fn()(
+    pair = PAIR_ENABLED and N > 128 and M > 128
+    rc = (_pair_fn() if pair else _fn())(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr, int(max_ctas),
         lib.status_buffer().data_ptr(), lib.stream_ptr(),
     )
-    lib.check_rc(rc, "lvb_gemm_bf16")
+    lib.check_rc(rc, "lvb_gemm_bf16_pair" if pair else "lvb_gemm_bf16")
     return out
+
+
+# Large products run on CTA pairs (``csrc/gemm_pair.cu``: 256 x 256 tiles, tcgen05 cta_group::2); ``LEVANTER_B200_GEMM_PAIR=0``
+# keeps everything on the one-CTA kernel.
+import os as _os
+
+PAIR_ENABLED = _os.environ.get("LEVANTER_B200_GEMM_PAIR", "1") != "0"
+_pair = None
+
+
+def _pair_fn():
+    global _pair
+    if _pair is None:
+        c = lib
+        _pair = lib.fn(
+            "lvb_gemm_bf16_pair",
+            [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+             c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p],
+        )
+    return _pair
 
 
 # A provider of copy jobs (``flops -> (table_ptr, u0, u1, src_ptr_array, n_srcs, dst_ptr) | None``): when one is set, dense

@@ -15,7 +15,10 @@ import torch.distributed as dist
 class SymmetricBuffer:
     """``tensor`` is this rank's copy; ``peer_ptrs[r]`` the address of rank ``r``'s copy as seen from this device."""
 
+    total_bytes = 0  # bytes allocated through this class by this process (the caching allocator's statistics do not see them)
+
     def __init__(self, numel: int, dtype: torch.dtype, device, group):
+        SymmetricBuffer.total_bytes += int(numel) * torch.empty((), dtype=dtype).element_size()
         import torch.distributed._symmetric_memory as symm_mem
 
         if group is None:
