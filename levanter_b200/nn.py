@@ -90,7 +90,9 @@ class Embedding(nn.Module):
         self.weight.tp_dim = None
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return F.embedding(ids, self.weight)
+        from .ops.embedding import embedding
+
+        return embedding(ids, self.weight)
 
     embed = forward
 
@@ -165,4 +167,6 @@ class Dropout(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.p == 0.0 or not self.training:
             return x
-        return F.dropout(x, self.p, training=True)
+        from .ops.dropout import dropout
+
+        return dropout(x, self.p, training=True)

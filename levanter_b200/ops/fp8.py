@@ -2,11 +2,13 @@
 delayed scaling, src/levanter/trainer.py:648, config/gpt2_small_fast_fp8.yaml:17-18).
 
 Forward operands are quantised to e4m3, output gradients to e5m2, each with one scale per tensor taken from a rolling
-history of absolute maxima (delayed scaling: the scale used now comes from earlier steps, so quantisation needs no extra
-pass over the tensor; the first step uses the current maximum).  The three GEMMs of a layer run on the tcgen05 fp8 path
-(``kind::f8f6f4``, ``csrc/gemm_bf16.cu``), fp32 accumulation, with the product of the two de-quantisation scales applied in
-the epilogue from a device scalar.  The kernel takes K-contiguous operands only, so the backward pass quantises transposed
-copies of the weight, the input and the output gradient.  Master weights, optimizer state and checkpoints are unchanged:
+history of absolute maxima (delayed scaling: the scale used now is the maximum over earlier steps' recorded maxima, so
+quantisation needs no pass over the tensor beforehand; values that outgrow it saturate, and a tensor's very first use
+takes its current maximum).  On a B200 one kernel (``csrc/fp8_quant.cu``) reads the bf16 tensor once and writes its fp8
+copy, the transposed fp8 copy and the tensor's absolute maximum into the history.  The three GEMMs of a layer run on the
+tcgen05 fp8 path (``kind::f8f6f4``, ``csrc/gemm_bf16.cu``), fp32 accumulation, with the product of the two
+de-quantisation scales applied in the epilogue from a device scalar.  The GEMM takes K-contiguous operands only, which
+is what the transposed copies are for.  Master weights, optimizer state and checkpoints are unchanged:
 ``Fp8Linear`` owns the same ``weight`` / ``bias`` parameters as the ``Linear`` it replaces."""
 from __future__ import annotations
 
@@ -65,39 +67,72 @@ def fp8_gemm(a: torch.Tensor, b: torch.Tensor, scale: torch.Tensor, *, out: Opti
     return out
 
 
+def quantize_with_history(x2: torch.Tensor, dtype: torch.dtype, hist: torch.Tensor, seen: bool, want_t: bool):
+    """Quantise ``x2 [R, C]`` with the scale its history gives and record its own maximum as the newest history entry.
+    Returns ``(q, q_t or None, inv_scale)``.  One pass over ``x2`` on a B200; PyTorch ops elsewhere."""
+    src = hist.max().reshape(1) if seen else x2.detach().abs().amax().float().reshape(1)
+    hist.copy_(torch.roll(hist, 1))
+    hist[0] = 0.0
+    if x2.is_cuda and lib.available() and x2.dtype == torch.bfloat16 and x2.stride(1) == 1:
+        R, C = x2.shape
+        q = torch.empty(R, C, dtype=dtype, device=x2.device)
+        qt = torch.empty(C, R, dtype=dtype, device=x2.device) if want_t else None
+        inv = torch.empty(1, dtype=torch.float32, device=x2.device)
+        c = lib
+        if "q" not in _f:
+            _f["q"] = lib.fn("lvb_fp8_quantize", [c.c_void_p, c.c_longlong, c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p,
+                                                  c.c_void_p, c.c_void_p, c.c_void_p])
+        rc = _f["q"](x2.data_ptr(), x2.stride(0), R, C, src.data_ptr(), _FMT[dtype], q.data_ptr(), lib.ptr(qt), inv.data_ptr(),
+                     hist.data_ptr(), lib.stream_ptr())  # hist[0] (just cleared) receives the maximum: a non-negative float's bits order as integers
+        lib.check_rc(rc, "lvb_fp8_quantize")
+        return q, qt, inv
+    hist[0] = x2.detach().abs().amax().float()
+    q, inv = quantize(x2, dtype, src.reshape(()))
+    return q, (_t(q) if want_t else None), inv
+
+
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, amax_x, amax_w, amax_g):
+    def forward(ctx, x, weight, bias, mod):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
-        xq, sx = quantize(x2, E4M3, amax_x)
-        wq, sw = quantize(weight, E4M3, amax_w)
+        train = torch.is_grad_enabled() or mod.training
+        xq, xq_t, sx = quantize_with_history(x2, E4M3, mod.amax_hist_x, mod._seen["x"], train)
+        wq, wq_t, sw = quantize_with_history(weight, E4M3, mod.amax_hist_w, mod._seen["w"], train)
+        mod._seen["x"] = mod._seen["w"] = True
         y = fp8_gemm(xq, wq, sx * sw, out_dtype=x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16, bias=bias)
-        ctx.save_for_backward(xq, sx, wq, sw, amax_g if amax_g is not None else torch.empty(0))
+        ctx.save_for_backward(xq_t if xq_t is not None else xq, sx, wq_t if wq_t is not None else wq, sw)
+        ctx.has_t = xq_t is not None
         ctx.has_bias = bias is not None
         ctx.weight = weight
+        ctx.mod = mod
         ctx.x_dtype = x.dtype
+        ctx.in_features = x.shape[-1]
         return y.reshape(*lead, weight.shape[0]).to(x.dtype)
 
     @staticmethod
     def backward(ctx, gy):
-        xq, sx, wq, sw, amax_g = ctx.saved_tensors
+        xs, sx, ws, sw = ctx.saved_tensors
+        xq_t, wq_t = (xs, ws) if ctx.has_t else (_t(xs), _t(ws))
+        mod = ctx.mod
         g2 = gy.reshape(-1, gy.shape[-1])
-        gq, sg = quantize(g2, E5M2, amax_g if amax_g.numel() else None)
-        dx = fp8_gemm(gq, _t(wq), sg * sw, out_dtype=torch.bfloat16 if gy.dtype == torch.bfloat16 else torch.float32)
+        gq, gq_t, sg = quantize_with_history(g2, E5M2, mod.amax_hist_g, mod._seen["g"], True)
+        mod._seen["g"] = True
+        dx = fp8_gemm(gq, wq_t, sg * sw, out_dtype=torch.bfloat16 if gy.dtype == torch.bfloat16 else torch.float32)
         w = ctx.weight
         main = getattr(w, "main_grad", None)
         if main is not None:
-            fp8_gemm(_t(gq), _t(xq), sg * sx, out=main, accumulate=True)  # straight into the fp32 gradient accumulator
+            fp8_gemm(gq_t, xq_t, sg * sx, out=main, accumulate=True)  # straight into the fp32 gradient accumulator
             dw = None
         else:
-            dw = fp8_gemm(_t(gq), _t(xq), sg * sx, out_dtype=torch.float32).to(w.dtype)
+            dw = fp8_gemm(gq_t, xq_t, sg * sx, out_dtype=torch.float32).to(w.dtype)
         db = g2.float().sum(0).to(gy.dtype) if ctx.has_bias else None
-        return dx.reshape(*gy.shape[:-1], xq.shape[1]).to(ctx.x_dtype), dw, db, None, None, None
+        return dx.reshape(*gy.shape[:-1], ctx.in_features).to(ctx.x_dtype), dw, db, None
 
 
 class Fp8Linear(nn.Module):
-    """Drop-in for :class:`levanter_b200.nn.Linear` with fp8 GEMMs and delayed per-tensor scaling."""
+    """Drop-in for :class:`levanter_b200.nn.Linear` with fp8 GEMMs and delayed per-tensor scaling (one scale per tensor; a
+    ``block`` argument is accepted for configs that name a block size and is not used)."""
 
     def __init__(self, weight: nn.Parameter, bias: Optional[nn.Parameter], amax_history_length: int = 1024):
         super().__init__()
@@ -106,24 +141,14 @@ class Fp8Linear(nn.Module):
         h = max(int(amax_history_length), 1)
         for name in ("x", "w", "g"):
             self.register_buffer(f"amax_hist_{name}", torch.zeros(h, device=weight.device), persistent=False)
-        self._seen = False
+        self._seen = {"x": False, "w": False, "g": False}
 
     @staticmethod
     def from_linear(linear: nn.Module, block: int = 128, amax_history_length: int = 16) -> "Fp8Linear":
         return Fp8Linear(linear.weight, getattr(linear, "bias", None), amax_history_length)
 
-    def _delayed(self, name: str, current: torch.Tensor) -> torch.Tensor:
-        """Scale source for this step: the maximum over the history (the current value on the first step), then push."""
-        hist = getattr(self, f"amax_hist_{name}")
-        cur = current.detach().abs().amax().float()
-        use = torch.where(hist.max() > 0, hist.max(), cur)
-        hist.copy_(torch.roll(hist, 1))
-        hist[0] = cur
-        # a tensor that outgrew its history would saturate: never use a scale below the current maximum's
-        return torch.maximum(use, cur)
-
     def forward(self, x: torch.Tensor, *, skip_bias: bool = False) -> torch.Tensor:
-        ax = self._delayed("x", x)
-        aw = self._delayed("w", self.weight)
-        ag = self.amax_hist_g.max() if self.training and bool(self._seen) else None
-        return _Fp8LinearFn.apply(x, self.weight, None if skip_bias else self.bias, ax, aw, None)
+        w = self.weight if self.weight.dtype == x.dtype else self.weight.to(x.dtype)
+        if w is not self.weight and hasattr(self.weight, "main_grad"):
+            w.main_grad = self.weight.main_grad
+        return _Fp8LinearFn.apply(x, w, None if skip_bias else self.bias, self)
