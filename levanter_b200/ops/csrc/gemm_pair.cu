@@ -18,6 +18,13 @@
 //   tempty[b] in the leader: the four epilogue warps of each CTA arrive on it (remote arrive from the follower).
 // Operand majorness as in gemm_bf16.cu (K-major / MN-major through the UMMA descriptors).
 //
+// kScatter mode fuses a reduce-scatter over GPUs into the epilogue (the weight-gradient product of fully sharded training,
+// or a row-parallel tensor-parallel output): every epilogue warp stores its 32 rows into the staging slot of the rank that
+// owns them (peer stores over NVLink, row-contiguous 128-byte segments) and bumps that rank's arrival counter of the
+// (32-row group, column tile) unit; four more warps per CTA sum this rank's own units over the slots as they fill.  The
+// protocol (two alternating staging areas, counters that only grow, an ordered raster) is that of lvb_gemm_reduce_scatter
+// in gemm_bf16.cu.
+//
 // Replaces the dense projections that the reference lowers through XLA dots (hnn.Linear -> hax.dot;
 // src/levanter/layers/attention.py:1606-1635, src/levanter/models/llama.py:273-280).
 #include "common.cuh"
@@ -31,6 +38,7 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kNumThreads = 192;  // warp0 TMA, warp1 MMA (leader) / TMEM allocation, warps2-5 epilogue
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared-memory address: the leader's copy
+constexpr int kMaxPeers = 8;
 
 enum EpiFlags : int { kOutF32 = 1, kAccumulate = 2, kBias = 4, kResidual = 8, kBiasF32 = 16 };
 
@@ -44,7 +52,39 @@ struct Params {
   float alpha;
   int tiles_m, tiles_n;
   int* status;
+  // ---- reduce-scatter epilogue (kScatter)
+  int rank, world;
+  int c_rows_per_rank;       // rows [r * c_rows_per_rank, ...) of C belong to rank r (a multiple of 32)
+  void* c_peer[kMaxPeers];   // this rank's slot in rank r's staging area
+  int* c_cnt[kMaxPeers];     // rank r's arrival counters, one per (32-row group, column tile); they only ever grow
+  int c_target;              // value of a counter once all `world` parts of this call's unit have arrived
+  const int* c_m_order;      // the raster's i-th 256-row block is block c_m_order[i]
+  const float* rs_staging;   // this rank's own staging area [world, slot]
+  long long rs_slot;         // elements per slot
+  void* rs_out;              // this rank's reduced rows [c_rows_per_rank, N] (fp32 or bf16), row stride rs_ldo
+  int rs_ldo;
+  int rs_out_f32;
+  int rs_accumulate;         // add to rs_out (fp32 only) instead of storing
+  // ---- copy job (kCopyJob): units [cj_u0, cj_u1) of a table of {source rank, source offset / 16, destination offset / 16,
+  // bytes / 16}; a seventh warp of every CTA moves them (peer or local memory -> shared memory -> cj_dst) beside the GEMM
+  const int4* cj_table;
+  int cj_u0, cj_u1;
+  const uint8_t* cj_src[kMaxPeers];
+  uint8_t* cj_dst;
 };
+
+constexpr int kPlain = 0;
+constexpr int kScatter = 1;
+constexpr int kCopyJob = 2;
+constexpr int kCopyUnit = 16384;                  // bytes per bulk copy of a copy job
+constexpr int kCopyExtra = 256 + 2 * kCopyUnit;  // extra dynamic shared memory of the copy-job kernel
+constexpr int kCopyThreads = kNumThreads + 32;
+constexpr int kReduceThreads = 128;
+constexpr int kScatterThreads = kNumThreads + kReduceThreads;
+constexpr int kEpiStride = 36;  // floats per staged row (144 B: 16-byte aligned, conflict-free for float4 rows)
+constexpr int kEpiExtra = 256 + 4 * 32 * kEpiStride * 4;
+
+__device__ __forceinline__ void reduce_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kReduceThreads) : "memory"); }
 
 template <int BN>
 struct Smem {
@@ -129,9 +169,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   nb = r / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p) {
   using L = Smem<BN>;
   constexpr int kStages = L::kStages;
   constexpr int BNH = BN / 2;  // columns of the B tile held by one CTA
@@ -143,6 +182,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // scatter mode only: a 32 x 32 fp32 transposition buffer per epilogue warp behind the barriers
+  float* epi_buf = reinterpret_cast<float*>(smem + ((L::kTileBytes + L::kBarBytes + 127) & ~127));
+  // copy-job mode only: two copy barriers and two staging buffers in the same place
+  uint64_t* copy_bar = reinterpret_cast<uint64_t*>(epi_buf);
+  uint8_t* copy_buf = reinterpret_cast<uint8_t*>(copy_bar) + 128;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -161,6 +205,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 8);  // one arrival per epilogue warp of either CTA
+    }
+    if constexpr (MODE == kCopyJob) {
+      mbar_init(&copy_bar[0], 1);
+      mbar_init(&copy_bar[1], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -185,6 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int mb, nb;
         tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        if constexpr (MODE == kScatter) mb = __ldg(p.c_m_order + mb);
         const int m0 = mb * BMP + static_cast<int>(cta) * BMC;  // this CTA's rows of the tile
         const int n0 = nb * BN + static_cast<int>(cta) * BNH;   // this CTA's columns of the B tile
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -245,7 +294,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++buf == 2) { buf = 0; tphase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (four warps per CTA, this CTA's 128 rows)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     int buf = 0;
@@ -257,6 +306,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      if constexpr (MODE == kScatter) mb = __ldg(p.c_m_order + mb);
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300, buf);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -264,12 +314,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = mb * BMP + static_cast<int>(cta) * BMC + quad * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      // scatter mode: this warp's 32 rows belong to one rank (rows per rank and M are multiples of 32)
+      const int row0w = row - lane;
+      const bool c_live = row0w < p.M;
+      int c_dest = 0;
+      float* c_dst_row0 = nullptr;
+      if constexpr (MODE == kScatter) {
+        c_dest = c_live ? row0w / p.c_rows_per_rank : 0;
+        c_dst_row0 = reinterpret_cast<float*>(p.c_peer[c_dest]) + static_cast<size_t>(row0w - c_dest * p.c_rows_per_rank) * p.ldc;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col0 = n0 + c;
+        if constexpr (MODE == kScatter) {
+          // Peer stores: turn the row-per-lane fragment into row-contiguous 128-byte segments through shared memory, so a
+          // store instruction covers 4 rows x 128 B instead of 32 rows x 16 B (NVLink moves short writes poorly).
+          if (col0 < p.N && c_live) {  // warp-uniform
+            float* eb = epi_buf + (warp - 2) * (32 * kEpiStride);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(eb + lane * kEpiStride + 4 * q) =
+                  make_float4(__uint_as_float(r[4 * q]) * alpha, __uint_as_float(r[4 * q + 1]) * alpha,
+                              __uint_as_float(r[4 * q + 2]) * alpha, __uint_as_float(r[4 * q + 3]) * alpha);
+            __syncwarp();
+            const int col = col0 + 4 * (lane & 7);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = (lane >> 3) + 4 * i;
+              const float4 val = *reinterpret_cast<const float4*>(eb + rl * kEpiStride + 4 * (lane & 7));
+              if (col < p.N) *reinterpret_cast<float4*>(c_dst_row0 + static_cast<size_t>(rl) * p.ldc + col) = val;
+            }
+            __syncwarp();
+          }
+          continue;
+        }
         if (row < p.M && col0 < p.N) {
           float v[32];
 #pragma unroll
@@ -361,9 +442,117 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // all TMEM reads of this warp are complete (tmem_ld_wait above)
       tc_fence_before();
+      if constexpr (MODE == kScatter) __threadfence_system();  // this lane's stores before the arrival below
       __syncwarp();
-      if (lane == 0) mbar_arrive_leader(&tempty_bar[buf]);
+      if (lane == 0) {
+        mbar_arrive_leader(&tempty_bar[buf]);
+        if constexpr (MODE == kScatter) {
+          if (c_live) {  // one arrival per rank and (32-row group, column tile) of the owner's rows
+            const int grp = (row0w - c_dest * p.c_rows_per_rank) >> 5;
+            red_release_sys_add(p.c_cnt[c_dest] + grp * p.tiles_n + nb, 1);
+          }
+        }
+      }
       if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+  } else if constexpr (MODE == kCopyJob) {
+    // ------------------------------------------------------------ copy-job warp (warp 6 of every CTA)
+    // CTA b moves units cj_u0 + b, cj_u0 + b + grid, ...: source (a peer's or this GPU's memory) -> shared memory -> cj_dst,
+    // both legs as bulk copies without any cluster qualifier, one load in flight while the previous unit is stored.  The
+    // consumer of the copied data is a later kernel on the same stream, so completion of the stores before this kernel ends
+    // is the only ordering needed.
+    if (lane == 0 && p.cj_u1 > p.cj_u0) {
+      auto issue = [&](int u, int b) {
+        const int4 e = __ldg(p.cj_table + u);
+        const uint32_t bytes = static_cast<uint32_t>(e.w) << 4;
+        mbar_expect_tx(&copy_bar[b], bytes);
+        bulk_load(copy_buf + b * kCopyUnit, p.cj_src[e.x] + (static_cast<size_t>(static_cast<uint32_t>(e.y)) << 4), bytes, &copy_bar[b]);
+      };
+      int u = p.cj_u0 + static_cast<int>(blockIdx.x);
+      uint32_t ph0 = 0, ph1 = 0;
+      int j = 0;
+      bool ok = true, pending_load = false;
+      if (u < p.cj_u1) issue(u, 0);
+      while (u < p.cj_u1) {
+        const int un = u + static_cast<int>(gridDim.x);
+        const int b = j & 1;
+        pending_load = false;
+        if (un < p.cj_u1) {
+          bulk_wait_read<0>();  // the store that last read the other buffer has drained it
+          issue(un, b ^ 1);
+          pending_load = true;
+        }
+        ok = mbar_wait(&copy_bar[b], b ? ph1 : ph0, abort_flag, p.status, 410, b);
+        if (!ok) break;
+        if (b) ph1 ^= 1; else ph0 ^= 1;
+        const int4 e = __ldg(p.cj_table + u);
+        bulk_store(p.cj_dst + (static_cast<size_t>(static_cast<uint32_t>(e.z)) << 4), copy_buf + b * kCopyUnit, static_cast<uint32_t>(e.w) << 4);
+        bulk_commit();
+        u = un;
+        ++j;
+      }
+      bulk_wait<0>();
+      if (!ok && pending_load) mbar_wait_quiet(&copy_bar[(j & 1) ^ 1], (j & 1) ? ph0 : ph1);  // let the load in flight land
+    }
+  } else if constexpr (MODE == kScatter) {
+    // ------------------------------------------------------------ reduce warps (warps 6-9 of every CTA)
+    // This rank's rows, concurrently with the main loop, in units of 32 rows x BN columns in the order the raster produces
+    // them: wait until all `world` ranks (this one included) have delivered the unit, then sum the slots.
+    const int rtid = threadIdx.x - kNumThreads;
+    const int own_units = (p.c_rows_per_rank >> 5) * p.tiles_n;
+    const bool out_f32 = p.rs_out_f32 != 0;
+    const bool acc_out = p.rs_accumulate != 0;
+    constexpr int RU = 32;
+    constexpr int kVecPerRow = BN / 4;
+    constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread and slot
+    for (int t = blockIdx.x; t < own_units; t += gridDim.x) {
+      if (rtid == 0 && !*abort_flag) flag_wait_ge(p.c_cnt[p.rank] + t, p.c_target, true, abort_flag, p.status, 500, t);
+      reduce_bar_sync();
+      if (*abort_flag) break;
+      const int grp = t / p.tiles_n, nb = t - grp * p.tiles_n;
+      for (int i0 = rtid; i0 < RU * kVecPerRow; i0 += kUnroll * kReduceThreads) {
+        float4 acc[kUnroll];
+        size_t off[kUnroll];
+        bool live[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int i = i0 + u * kReduceThreads;
+          const int r = i / kVecPerRow;
+          const int col = nb * BN + (i - r * kVecPerRow) * 4;
+          live[u] = (i < RU * kVecPerRow) && (col < p.N);
+          off[u] = (static_cast<size_t>(grp) * RU + r) * p.ldc + col;
+          acc[u] = live[u] ? __ldcg(reinterpret_cast<const float4*>(p.rs_staging + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int w = 1; w < p.world; ++w) {
+          float4 v[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u)
+            v[u] = live[u] ? __ldcg(reinterpret_cast<const float4*>(p.rs_staging + w * p.rs_slot + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (!live[u]) continue;
+          const int i = i0 + u * kReduceThreads;
+          const int r = i / kVecPerRow;
+          const int col = nb * BN + (i - r * kVecPerRow) * 4;
+          const size_t row = static_cast<size_t>(grp) * RU + r;
+          if (out_f32) {
+            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_out) + row * p.rs_ldo + col);
+            if (acc_out) {
+              const float4 a = *o;
+              *o = make_float4(a.x + acc[u].x, a.y + acc[u].y, a.z + acc[u].z, a.w + acc[u].w);
+            } else {
+              *o = acc[u];
+            }
+          } else {
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo + col) =
+                make_uint2(pack_bf16x2(acc[u].x, acc[u].y), pack_bf16x2(acc[u].z, acc[u].w));
+          }
+        }
+      }
+      reduce_bar_sync();  // nobody is still reading the abort flag when thread 0 starts the next wait
     }
   }
 
@@ -377,46 +566,114 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_pair_body<BN, A_MN, B_MN, kPlain>(tmA, tmB, p);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kScatterThreads, 1)
+gemm_pair_scatter_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_pair_body<BN, A_MN, B_MN, kScatter>(tmA, tmB, p);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kCopyThreads, 1)
+gemm_pair_copy_job_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  gemm_pair_body<BN, A_MN, B_MN, kCopyJob>(tmA, tmB, p);
+}
+
+template <typename Kern>
+int max_resident_pairs(Kern kern, int threads, int smem) {
+  // as many pairs as can be resident at once (a GPC with an odd number of free SMs cannot host a pair on the last one)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (num_sms() / 2));
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = num_sms() / 2;
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int make_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, const Params& p, int lda, int ldb) {
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(tmA, A, p.M, p.K, lda, BMC, BK);  // [M,K] rows=M
+  else       rc = make_tmap_2d_bf16(tmA, A, p.K, p.M, lda, BK, 64);   // [K,M] rows=K, box 64 k x 64 m
+  if (rc != kErrOk) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(tmB, B, p.N, p.K, ldb, BN / 2, BK);
+  else       rc = make_tmap_2d_bf16(tmB, B, p.K, p.N, ldb, BK, 64);
+  return rc;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_scatter(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
+  using L = Smem<BN>;
+  constexpr int kSmem = L::kTotal + kEpiExtra;
+  static_assert(kSmem <= 232448, "scatter kernel exceeds the shared memory of an SM");
+  CUtensorMap tmA, tmB;
+  int rc = make_maps<BN, A_MN, B_MN>(&tmA, &tmB, A, B, p, lda, ldb);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BMP - 1) / BMP;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_pair_scatter_kernel<BN, A_MN, B_MN>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
+    max_pairs = max_resident_pairs(kern, kScatterThreads, kSmem);
+  }
+  int pairs = p.tiles_m * p.tiles_n;
+  if (pairs > max_pairs) pairs = max_pairs;
+  kern<<<2 * pairs, kScatterThreads, kSmem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_copy_job(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
+  using L = Smem<BN>;
+  constexpr int kSmem = L::kTotal + kCopyExtra;
+  static_assert(kSmem <= 232448, "copy-job kernel exceeds the shared memory of an SM");
+  CUtensorMap tmA, tmB;
+  int rc = make_maps<BN, A_MN, B_MN>(&tmA, &tmB, A, B, p, lda, ldb);
+  if (rc != kErrOk) return rc;
+  p.tiles_m = (p.M + BMP - 1) / BMP;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  auto kern = gemm_pair_copy_job_kernel<BN, A_MN, B_MN>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return kErrCuda;
+    max_pairs = max_resident_pairs(kern, kCopyThreads, kSmem);
+  }
+  // every resident pair even when there are fewer tiles: every CTA's copy warp moves a share of the units
+  kern<<<2 * max_pairs, kCopyThreads, kSmem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream, int max_ctas) {
   using L = Smem<BN>;
   CUtensorMap tmA, tmB;
-  int rc;
-  if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, p.M, p.K, lda, BMC, BK);  // [M,K] rows=M
-  else       rc = make_tmap_2d_bf16(&tmA, A, p.K, p.M, lda, BK, 64);   // [K,M] rows=K, box 64 k x 64 m
-  if (rc != kErrOk) return rc;
-  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, B, p.N, p.K, ldb, BN / 2, BK);
-  else       rc = make_tmap_2d_bf16(&tmB, B, p.K, p.N, ldb, BK, 64);
+  int rc = make_maps<BN, A_MN, B_MN>(&tmA, &tmB, A, B, p, lda, ldb);
   if (rc != kErrOk) return rc;
   p.tiles_m = (p.M + BMP - 1) / BMP;
   p.tiles_n = (p.N + BN - 1) / BN;
   auto kern = gemm_pair_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
-    attr_set = true;
-  }
-  int pairs = p.tiles_m * p.tiles_n;
-  // as many pairs as can be resident at once (a GPC with an odd number of free SMs cannot host a pair on the last one)
   static int max_pairs = 0;
   if (max_pairs == 0) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (num_sms() / 2));
-    cfg.blockDim = dim3(kNumThreads);
-    cfg.dynamicSmemBytes = L::kTotal;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
-      (void)cudaGetLastError();
-      n = num_sms() / 2;
-    }
-    max_pairs = n;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
+    max_pairs = max_resident_pairs(kern, kNumThreads, L::kTotal);
   }
+  int pairs = p.tiles_m * p.tiles_n;
   int cap = max_pairs;
   if (max_ctas > 0 && max_ctas / 2 < cap) cap = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (pairs > cap) pairs = cap;
@@ -449,4 +706,56 @@ extern "C" int lvb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, 
   if (!a_mn && b_mn) return launch<256, false, true>(A, B, p, lda, ldb, s, max_ctas);
   if (a_mn && b_mn) return launch<256, true, true>(A, B, p, lda, ldb, s, max_ctas);
   return launch<256, true, false>(A, B, p, lda, ldb, s, max_ctas);
+}
+
+// The CTA-pair form of lvb_gemm_reduce_scatter (gemm_bf16.cu) with fp32 staging: same protocol and arguments, except that
+// m_order lists 256-row blocks (int32[ceil(M / 256)]) and N must exceed 128.
+extern "C" int lvb_gemm_reduce_scatter_pair(const void* A, const void* B, int a_mn, int b_mn, void* const* c_slots, int* const* cnt_peers,
+                                            int rank, int world, const void* staging, long long slot_elems, int target,
+                                            const int* m_order, void* out, int ldo, int out_f32, int accumulate, int M, int N, int K,
+                                            int lda, int ldb, int ldc, float alpha, int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm2;
+  if (world <= 0 || world > kMaxPeers || rank < 0 || rank >= world || M <= 0 || N <= 128 || K <= 0) return kErrBadArg;
+  if (M % world != 0 || (M / world) % 32 != 0 || (N & 7) || (ldc & 7) || (ldo & 7) || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (m_order == nullptr || (accumulate && !out_f32) || (a_mn != b_mn)) return kErrBadArg;
+  Params p;
+  p.C = c_slots[rank]; p.bias = nullptr; p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+  p.flags = kOutF32; p.alpha = alpha; p.status = status;
+  p.rank = rank; p.world = world;
+  p.c_rows_per_rank = M / world;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    p.c_peer[r] = c_slots[r < world ? r : 0];
+    p.c_cnt[r] = cnt_peers[r < world ? r : 0];
+  }
+  p.rs_staging = reinterpret_cast<const float*>(staging); p.rs_slot = slot_elems; p.rs_out = out; p.rs_ldo = ldo; p.rs_out_f32 = out_f32;
+  p.c_target = target; p.c_m_order = m_order; p.rs_accumulate = accumulate;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (a_mn) return launch_scatter<256, true, true>(A, B, p, lda, ldb, s);
+  return launch_scatter<256, false, false>(A, B, p, lda, ldb, s);
+}
+
+// The CTA-pair form of lvb_gemm_bf16_copy_job (gemm_bf16.cu): the same arguments; N must exceed 128.
+extern "C" int lvb_gemm_bf16_pair_copy_job(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                           int a_mn, int b_mn, int flags, float alpha, const void* bias, const void* residual, int ldr,
+                                           const void* table, int u0, int u1, const void* const* srcs, int n_srcs, void* dst,
+                                           int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm2;
+  if (M <= 0 || N <= 128 || K <= 0 || (lda & 7) || (ldb & 7)) return kErrBadArg;
+  if (table == nullptr || dst == nullptr || n_srcs <= 0 || n_srcs > kMaxPeers || u1 < u0) return kErrBadArg;
+  Params p;
+  p.C = C; p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
+  p.flags = flags; p.alpha = alpha; p.status = status;
+  p.rank = 0; p.world = 1; p.c_rows_per_rank = 0;
+  p.cj_table = reinterpret_cast<const int4*>(table); p.cj_u0 = u0; p.cj_u1 = u1;
+  for (int r = 0; r < kMaxPeers; ++r) p.cj_src[r] = reinterpret_cast<const uint8_t*>(srcs[r < n_srcs ? r : 0]);
+  p.cj_dst = reinterpret_cast<uint8_t*>(dst);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return launch_copy_job<256, false, false>(A, B, p, lda, ldb, s);
+  if (!a_mn && b_mn) return launch_copy_job<256, false, true>(A, B, p, lda, ldb, s);
+  if (a_mn && b_mn) return launch_copy_job<256, true, true>(A, B, p, lda, ldb, s);
+  return launch_copy_job<256, true, false>(A, B, p, lda, ldb, s);
 }

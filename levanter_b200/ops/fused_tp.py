@@ -67,14 +67,15 @@ def all_gather_matmul(x_sym: SymmetricBuffer, rows: int, k: int, w: torch.Tensor
     return out
 
 
-def scatter_m_order(M: int, world: int, rank: int) -> list:
-    """Order in which a reduce-scatter GEMM visits the 128-row blocks of an ``M``-row product: the blocks are dealt out to the
-    ranks that own them in turn (a block belongs to the owner of its first row), next rank first and own rank last in each
-    round, so that every rank's rows are produced at a steady rate by all ranks at once."""
+def scatter_m_order(M: int, world: int, rank: int, block: int = 128) -> list:
+    """Order in which a reduce-scatter GEMM visits the ``block``-row blocks of an ``M``-row product (128 rows for the one-CTA
+    kernel, 256 for the CTA-pair kernel): the blocks are dealt out to the ranks that own them in turn (a block belongs to
+    the owner of its first row), next rank first and own rank last in each round, so that every rank's rows are produced at a
+    steady rate by all ranks at once."""
     rows = M // world
     per_owner = [[] for _ in range(world)]
-    for b in range((M + 127) // 128):
-        per_owner[min((b * 128) // rows, world - 1)].append(b)
+    for b in range((M + block - 1) // block):
+        per_owner[min((b * block) // rows, world - 1)].append(b)
     owners = [(rank + 1 + i) % world for i in range(world)]
     order = []
     for i in range(max(len(x) for x in per_owner)):
@@ -87,11 +88,11 @@ def scatter_m_order(M: int, world: int, rank: int) -> list:
 _m_order_cache = {}
 
 
-def m_order_tensor(M: int, world: int, rank: int, device) -> torch.Tensor:
-    key = (M, world, rank, str(device))
+def m_order_tensor(M: int, world: int, rank: int, device, block: int = 128) -> torch.Tensor:
+    key = (M, world, rank, str(device), block)
     t = _m_order_cache.get(key)
     if t is None:
-        t = _m_order_cache[key] = torch.tensor(scatter_m_order(M, world, rank), dtype=torch.int32, device=device)
+        t = _m_order_cache[key] = torch.tensor(scatter_m_order(M, world, rank, block), dtype=torch.int32, device=device)
     return t
 
 
@@ -116,6 +117,32 @@ def _rs_fn():
     return _fn("lvb_gemm_reduce_scatter", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p,
                                            c.c_longlong, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int] + [c.c_int] * 6
                + [c.c_float, c.c_void_p, c.c_void_p])
+
+
+def _rs_pair_fn():
+    c = lib
+    return _fn("lvb_gemm_reduce_scatter_pair", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p,
+                                                c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int] + [c.c_int] * 6
+               + [c.c_float, c.c_void_p, c.c_void_p])
+
+
+def reduce_scatter_gemm(a: torch.Tensor, b: torch.Tensor, mn_major: bool, slots, cnts, rank: int, world: int, staging_ptr: int, slot_elems: int,
+                        staging_f32: bool, target: int, out: torch.Tensor, accumulate: bool, M: int, N: int, K: int, alpha: float) -> None:
+    """One launch of the fused GEMM -> reduce-scatter (see ``lvb_gemm_reduce_scatter`` in ``csrc/gemm_bf16.cu`` for the
+    protocol): the CTA-pair kernel for fp32 staging and more than 128 output columns, the one-CTA kernel otherwise."""
+    from .gemm import PAIR_ENABLED
+
+    out_f32 = 1 if out.dtype == torch.float32 else 0
+    if PAIR_ENABLED and staging_f32 and N > 128:
+        rc = _rs_pair_fn()(a.data_ptr(), b.data_ptr(), int(mn_major), int(mn_major), slots, cnts, rank, world, staging_ptr, slot_elems, target,
+                           m_order_tensor(M, world, rank, a.device, 256).data_ptr(), out.data_ptr(), out.stride(0), out_f32, int(accumulate),
+                           M, N, K, a.stride(0), b.stride(0), N, float(alpha), lib.status_buffer().data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_gemm_reduce_scatter_pair")
+        return
+    rc = _rs_fn()(a.data_ptr(), b.data_ptr(), int(mn_major), int(mn_major), slots, cnts, rank, world, staging_ptr, slot_elems,
+                  1 if staging_f32 else 0, target, m_order_tensor(M, world, rank, a.device).data_ptr(), out.data_ptr(), out.stride(0), out_f32,
+                  int(accumulate), M, N, K, a.stride(0), b.stride(0), N, float(alpha), lib.status_buffer().data_ptr(), lib.stream_ptr())
+    lib.check_rc(rc, "lvb_gemm_reduce_scatter")
 
 
 def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBuffer, out: Optional[torch.Tensor] = None,
@@ -155,8 +182,5 @@ def matmul_reduce_scatter(x: torch.Tensor, w: torch.Tensor, staging: SymmetricBu
         own = staging.peer_ptrs[r]
         slots = _ptr_array([own + base + d * slot * es for d in range(W)])
         cnts = _ptr_array([own + base + W * slot * es] * W)
-    rc = _rs_fn()(x.data_ptr(), w.data_ptr(), 0, 0, slots, cnts, r, W, st.data_ptr() + base, slot, 1 if st.dtype == torch.float32 else 0, target,
-                  m_order_tensor(M, W, r, x.device).data_ptr(), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, 0,
-                  M, N, K, x.stride(0), w.stride(0), N, 1.0, lib.status_buffer().data_ptr(), lib.stream_ptr())
-    lib.check_rc(rc, "lvb_gemm_reduce_scatter")
+    reduce_scatter_gemm(x, w, False, slots, cnts, r, W, st.data_ptr() + base, slot, st.dtype == torch.float32, target, out, False, M, N, K, 1.0)
     return out

@@ -133,7 +133,7 @@ def gemm(
         job = _copy_job_provider(2.0 * M * N * K)
         if job is not None:
             table, u0, u1, srcs, n_srcs, dst = job
-            rc = _cj_fn()(
+            rc = (_cj_pair_fn() if (PAIR_ENABLED and M > 128) else _cj_fn())(
                 a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
                 int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr,
                 table, u0, u1, srcs, n_srcs, dst, lib.status_buffer().data_ptr(), lib.stream_ptr(),
@@ -180,6 +180,20 @@ _cj = None
 def set_copy_job_provider(fn) -> None:
     global _copy_job_provider
     _copy_job_provider = fn
+
+
+_cj_pair = None
+
+
+def _cj_pair_fn():
+    global _cj_pair
+    if _cj_pair is None:
+        c = lib
+        _cj_pair = lib.fn("lvb_gemm_bf16_pair_copy_job",
+                          [c.c_void_p, c.c_void_p, c.c_void_p] + [c.c_int] * 9 + [c.c_float, c.c_void_p, c.c_void_p, c.c_int,
+                                                                                   c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p,
+                                                                                   c.c_void_p, c.c_void_p])
+    return _cj_pair
 
 
 def _cj_fn():

@@ -306,8 +306,7 @@ class LayerStreamer:
         self._sym_stage.barrier(0)
 
     def _fused_weight_grad(self, sp: StreamParam, dy2: torch.Tensor, x2: torch.Tensor) -> None:
-        from ..ops import lib
-        from ..ops.fused_tp import _ptr_array, _rs_fn, m_order_tensor
+        from ..ops.fused_tp import _ptr_array, reduce_scatter_gemm
         from ..ops.gemm import _rowmajor_2d
 
         W, r = self.world, self.rank
@@ -329,10 +328,7 @@ class LayerStreamer:
         slots = _ptr_array([p + data_off + r * slot * 4 for p in peers])  # this rank's slot in every rank's area
         cnts = _ptr_array([p + cnt_off for p in peers])
         out = self._grad_rows(sp)
-        rc = _rs_fn()(dy2.data_ptr(), x2.data_ptr(), 1, 1, slots, cnts, r, W, peers[r] + data_off, slot, 1, target,
-                      m_order_tensor(N, W, r, dy2.device).data_ptr(), out.data_ptr(), K, 1, 1, N, K, T, dy2.stride(0), x2.stride(0), K,
-                      1.0 / W, lib.status_buffer().data_ptr(), lib.stream_ptr())
-        lib.check_rc(rc, "lvb_gemm_reduce_scatter")
+        reduce_scatter_gemm(dy2, x2, True, slots, cnts, r, W, peers[r] + data_off, slot, True, target, out, True, N, K, T, 1.0 / W)
         self.stats["fused_weight_grads"] += 1
 
     # ------------------------------------------------------------------------------------------ whole tensors (export, checkpoints)
