@@ -44,6 +44,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                    help="train: the headline; decode: the inference engine serving Llama-3 8B, tensor parallel over the GPUs (a second metric: "
+                         "prefill and decode tokens/s at 256 concurrent requests, prompts U[128, 2048], 256 greedy tokens, 16-token pages)")
+    ap.add_argument("--requests", type=int, default=256, help="decode mode: concurrent requests")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_baseline"])
     ap.add_argument("--zero-stage", type=int, default=3, choices=[1, 3], help="see the module docstring")
     ap.add_argument("--no-equiv", action="store_true", help="N > 1: skip the one-step comparison of the product path with the NCCL path")
@@ -268,10 +272,61 @@ def equivalence_check(args, mcfg, vocab, dev, rank) -> dict:
     return res
 
 
+def main_decode(args):
+    """Inference benchmark (the second metric of the baseline document): Llama-3 8B in bf16, tensor parallel over the N GPUs,
+    paged KV cache with 16-token pages, ``--requests`` concurrent requests with uniform-random prompts of 128..2048 tokens,
+    256 greedy tokens each.  One untimed generate() call (hundreds of decode rounds: kernel attributes, graph capture,
+    allocator), then ``--steps`` timed calls through the public ``InferenceEngine.generate``: prompts enter as host lists,
+    tokens leave as host lists.  Phase times are host clocks after device synchronisation at the phase boundaries, MAX over
+    ranks; the best call is reported."""
+    import argparse as _ap
+
+    import torch
+
+    from levanter_b200.inference import bench_decode
+    from levanter_b200.ops import lib
+
+    world, rank, local_rank = _env()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = lib.launch_count
+    a = _ap.Namespace(model="llama3_8b", seqs=args.requests, prompt_len=0, new_tokens=256, page_size=16, max_rounds=16, cuda_graph=True, layers=None,
+                      repeats=max(1, args.steps), tp=world, prompt_min=128, prompt_max=2048, quiet=True)
+    r = bench_decode.run(a)
+    clocks = sampler.stop()
+    best = min(r["runs"], key=lambda x: x["wall_s"])
+    out = {"metric": "decode tokens/sec (inference engine, Llama-3 8B, paged KV cache)", "value": r["decode_tokens_per_s"], "unit": "tokens/s",
+           "n_gpus": world, "steps": max(1, args.steps), "warmup": 1, "warmup_note": "one whole generate() call of the same workload (about 256 decode rounds)",
+           "ms_per_step": r["ms_per_decode_round"], "step_note": "a step is one decode round (one new token for every running request)",
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic uniform-random prompts, random-init weights", "impl": "ours", "mode": "decode",
+           "prefill_tokens_per_s": r["prefill_tokens_per_s"],
+           "config": {"model": "Llama-3 8B (32L, hidden 4096, 32 query / 8 KV heads, SwiGLU 14336, vocab 128256)", "parallelism": f"tp{world}" if world > 1 else "single-gpu",
+                      "requests": args.requests, "prompt_lengths": "uniform in [128, 2048]", "new_tokens": 256, "page_size": 16, "sampling": "greedy",
+                      "cuda_graph": True, "tp_all_reduce": os.environ.get("LEVANTER_B200_TP_COMM", "auto")},
+           "clocks": clocks,
+           "e2e": {"value": r["end_to_end_generated_tokens_per_s"], "unit": "generated tokens/s over the whole generate() call (prefill included)",
+                   "h2d_bytes_per_step": int(4 * best["prefill_tokens"] / max(best.get("decode_rounds", 1), 1)),
+                   "d2h_bytes_per_step": int(8 * best["decode_tokens"] / max(best.get("decode_rounds", 1), 1)),
+                   "bytes_note": "prompt tokens in (int32) and sampled tokens + log-probabilities out, averaged per decode round"},
+           "gpu_launches": lib.launch_count - launches0, "kernel_all_reduces": r.get("kernel_all_reduces"),
+           "peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30}
+    if rank == 0:
+        print(json.dumps(out))
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.mode == "decode":
+        return main_decode(args)
     if args.impl == "torch_baseline":
         return main_torch_baseline(args)
 

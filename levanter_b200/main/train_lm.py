@@ -95,7 +95,17 @@ def main(config: TrainLmConfig):
         train_dataset = config.data.train_set(Pos, config.trainer.batch_schedule, key=data_key, epochs=config.epoch)
         tagged_eval_datasets = config.data.tagged_eval_sets(Pos)
 
-        state = trainer.initial_state(training_key, model_init=lambda: config.model.build(Vocab, seed=model_key, device=trainer.device))
+        def model_init():
+            tp = trainer.tensor_parallel
+            if tp is None:
+                return config.model.build(Vocab, seed=model_key, device=trainer.device)
+            # model axis > 1 (tensor_parallel_axes): heads and MLP columns are split over the model axis; every rank takes its
+            # slices of the weights an unsharded run with this seed would start from
+            from levanter_b200.parallel.tp import build_sharded_from_seed
+
+            return build_sharded_from_seed(lambda tp: config.model.build(Vocab, seed=model_key, device=trainer.device, tp=tp), tp)
+
+        state = trainer.initial_state(training_key, model_init=model_init)
 
         if int(state.step) == 0 and config.initialize_from_checkpoint_path is not None:
             state = load_checkpoint(state, config.initialize_from_checkpoint_path)

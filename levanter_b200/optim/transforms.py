@@ -64,15 +64,41 @@ def set_norm_reduce_group(group) -> None:
     _dist_group = group
 
 
+_model_group = None
+_model_sharded: Optional[set] = None
+
+
+def set_model_parallel_norm(group, sharded_names) -> None:
+    """Tensor parallelism: ``sharded_names`` are the leaves of which every rank of ``group`` (the model axis) holds a different
+    slice; ``global_norm`` sums their squared norms over the group and counts the replicated leaves once.  ``None`` clears."""
+    global _model_group, _model_sharded
+    _model_group = group
+    _model_sharded = set(sharded_names) if (group is not None and sharded_names is not None) else None
+
+
 def global_norm(tree: Tree) -> torch.Tensor:
     keys = tree_keys(tree)
     if not keys:
         return torch.zeros(())
-    norms = torch._foreach_norm(_leaves(tree, keys))
-    sq = torch.stack([n.float() ** 2 for n in norms]).sum()
-    if _dist_group is not None:
-        import torch.distributed as dist
+    import torch.distributed as dist
 
+    def sumsq(ks):
+        if not ks:
+            return torch.zeros((), dtype=torch.float32, device=tree[keys[0]].device)
+        norms = torch._foreach_norm(_leaves(tree, ks))
+        return torch.stack([n.float() ** 2 for n in norms]).sum()
+
+    if _model_group is not None and _model_sharded is not None:
+        part = sumsq([k for k in keys if k in _model_sharded])
+        rep = sumsq([k for k in keys if k not in _model_sharded])
+        if _dist_group is not None:  # slices over the data axis first: both kinds of leaves are cut there
+            both = torch.stack([part, rep])
+            dist.all_reduce(both, group=_dist_group if _dist_group is not True else None)
+            part, rep = both[0], both[1]
+        dist.all_reduce(part, group=_model_group)
+        return torch.sqrt(part + rep)
+    sq = sumsq(keys)
+    if _dist_group is not None:
         dist.all_reduce(sq, group=_dist_group if _dist_group is not True else None)
     return torch.sqrt(sq)
 

@@ -207,3 +207,31 @@ def shard_full_state_(model: torch.nn.Module, full_state: dict, tp: Optional["Te
             if src.shape != p.shape:
                 raise ValueError(f"{name}: cannot place {tuple(full_state[name].shape)} into {tuple(p.shape)} (tp_dim={dim})")
             p.copy_(src.to(p.dtype))
+
+
+def gather_full_state(model: torch.nn.Module, tp: Optional["TensorParallel"]) -> dict:
+    """Inverse of :func:`shard_full_state_`: name -> unsharded tensor, assembled from every rank's slice along ``tp_dim``
+    (collective over the model axis; parameters without ``tp_dim`` are returned as they are)."""
+    out = {}
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            dim = getattr(p, "tp_dim", None)
+            if tp is None or tp.size <= 1 or dim is None:
+                out[name] = p.detach().clone()
+                continue
+            parts = [torch.empty_like(p) for _ in range(tp.size)]
+            dist.all_gather(parts, p.detach().contiguous(), group=tp.group)
+            out[name] = torch.cat(parts, dim=dim)
+    return out
+
+
+def build_sharded_from_seed(build, tp: Optional["TensorParallel"]):
+    """A tensor-parallel model whose weights are this rank's slices of the model that ``build(tp=None)`` creates, so that a
+    run on a model axis of any size starts from the same weights as an unsharded run with the same seed."""
+    if tp is None or tp.size <= 1:
+        return build(tp=None)
+    full = build(tp=None)
+    model = build(tp=tp)
+    shard_full_state_(model, {n: p.detach() for n, p in full.named_parameters()}, tp)
+    del full
+    return model

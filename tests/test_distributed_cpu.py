@@ -49,7 +49,10 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
         opt = C.decode(OptimizerConfig, opt_dict)
     losses = {}
     with Trainer(cfg, opt, compute_next_token_loss) as trainer:
-        state = trainer.initial_state(0, model_init=lambda: mcfg.build(VOCAB, seed=3))
+        from levanter_b200.parallel.tp import build_sharded_from_seed, gather_full_state
+
+        tp = trainer.tensor_parallel
+        state = trainer.initial_state(0, model_init=lambda: build_sharded_from_seed(lambda tp: mcfg.build(VOCAB, seed=3, tp=tp), tp))
         trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
         if expect_stage is not None:
             assert state.engine.zero_stage == expect_stage, state.engine.zero_stage
@@ -59,6 +62,8 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
             assert st is not None and st.stats["library_weight_grads"] > 0
             full = state.engine.full_master()  # whole matrices again, assembled from every rank's rows
             return {k: full[k].detach().clone() for k, _ in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
+        if tp is not None:
+            return gather_full_state(info.state.model, tp), [losses[k] for k in sorted(losses)]
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
 
 
@@ -86,6 +91,22 @@ def test_two_rank_zero3_layer_streaming_matches_single_process(tmp_path):
     their gradients reduce-scattered as autograd produces them; losses and final weights equal one process."""
     single, losses = _train(str(tmp_path / "single"), hidden=64)
     mp.spawn(_sharded_worker, args=(2, 29723, str(tmp_path), None, {"zero_stage": 3, "per_device_parallelism": 2}, 64, 3), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+def test_two_way_tensor_parallel_training_matches_single_process(tmp_path):
+    """model axis 2 (heads and MLP columns split, all-reduce after the row-parallel projections and of the input gradients of
+    the column-parallel ones): three optimizer steps give the losses and the weights of the unsharded run."""
+    # (a larger Adam epsilon than usual: with 1e-8 the elements whose gradient is rounding noise take full-size steps of random
+    # sign, and the split reductions of tensor parallelism change that noise)
+    opt = {"type": "adam", "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0,
+           "epsilon": 1e-4, "max_grad_norm": 0.5}
+    single, losses = _train(str(tmp_path / "single"), opt_dict=opt)
+    mp.spawn(_sharded_worker, args=(2, 29724, str(tmp_path), opt, {"model_axis_size": 2, "tensor_parallel_axes": ["mlp", "heads"]}), nprocs=2,
+             join=True)
     got = torch.load(tmp_path / "dist.pt")
     assert got["losses"] == pytest.approx(losses, abs=2e-5)
     for k, v in single.items():
