@@ -79,7 +79,16 @@ class LoraLinear(nn.Module):
         return self.wrapped.out_features
 
     def forward(self, x, *, skip_bias: bool = False):
-        return self.wrapped(x, skip_bias=skip_bias) + self.lora(x)
+        base = self.wrapped(x, skip_bias=skip_bias)
+        lo = self.lora
+        if x.is_cuda and x.dtype == torch.bfloat16 and lo.lora_B.weight.dtype == torch.bfloat16 and lo.lora_B.weight.shape[1] % 8 == 0:
+            # y = base + scale * B (A x): the up-projection GEMM adds the base output in its epilogue, so the low-rank branch costs
+            # two skinny GEMMs and no separate scale or add pass over the [tokens, out] activations
+            from .ops.gemm import linear_residual
+
+            t = lo.lora_A(lo.dropout(x))
+            return linear_residual(t * lo.scale, lo.lora_B.weight, None, base)
+        return base + lo(x)
 
     def merge(self) -> Linear:
         with torch.no_grad():

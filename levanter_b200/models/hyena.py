@@ -1,7 +1,8 @@
 """The Hyena operator: gated long convolutions with implicitly parametrised filters
 (src/levanter/models/hyena.py:39-556; Poli et al. 2023).
 
-The long convolution is an FFT convolution in fp32 (cuFFT through ``torch.fft``); the filter is generated once per call from
+The long convolution is a direct causal sum on this library's kernel for sequences up to 4096 (``ops/long_conv.py``) and an
+FFT convolution in fp32 otherwise; the filter is generated once per call from
 a small sine-activated MLP over positional features and is shared by every sequence of the batch.  Sequences may be split
 into ``num_blocks`` independent blocks; filters are generated for one block only."""
 from __future__ import annotations
@@ -120,13 +121,12 @@ class MLPTrainableActivation(nn.Module):
         return self.layers[-1](x)
 
 
-def fft_conv(u: torch.Tensor, k: torch.Tensor) -> torch.Tensor:
-    """Causal convolution along the second-to-last axis: ``u[..., L, C]`` with ``k[L, C]`` (zero-padded FFT of size 2L)."""
-    L = u.shape[-2]
-    n = 2 * L
-    u_f = torch.fft.rfft(u.float(), n=n, dim=-2)
-    k_f = torch.fft.rfft(k.float(), n=n, dim=-2)
-    return torch.fft.irfft(u_f * k_f, n=n, dim=-2)[..., :L, :].to(u.dtype)
+def fft_conv(u: torch.Tensor, k: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal convolution along the second-to-last axis: ``u[..., L, C]`` with ``k[L, C]`` (+ per-channel bias).  On a B200 and
+    for ``L <= 4096`` this is a direct sum in shared memory (``ops/long_conv.py``); otherwise a zero-padded FFT of size 2L."""
+    from ..ops.long_conv import long_conv
+
+    return long_conv(u, k, bias)
 
 
 class HyenaFilter(nn.Module):
@@ -155,9 +155,7 @@ class HyenaFilter(nn.Module):
     def forward(self, x: torch.Tensor, k: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x[..., L, head_size]``, ``k[L, head_size]``."""
         bias = self.bias if bias is None else bias
-        y = fft_conv(x, k)
-        if self.use_bias:
-            y = y + bias.to(y.dtype)
+        y = fft_conv(x, k, bias if self.use_bias else None)
         return self.dropout(y)
 
 

@@ -43,6 +43,34 @@ def stochastic_hessian_diagonal(fn: Callable[[Dict[str, torch.Tensor]], torch.Te
     return {k: product[k] * g[k].to(product[k].dtype) for k in product}
 
 
+def _fused_update_available(updates, state, keys) -> bool:
+    from ..ops import lib
+
+    if not keys:
+        return False
+    t = updates[keys[0]]
+    return bool(t.is_cuda and lib.available() and all(updates[k].dtype == torch.float32 and state.mu[k].dtype == torch.float32
+                                                       and state.h[k].dtype == torch.float32 and updates[k].is_contiguous() for k in keys))
+
+
+_sophia_fn = {}
+
+
+def _fused_update(g, mu, h, param, b1, bc1, gamma, eps, clip, stats):
+    """One pass of ``csrc/sophia.cu`` over a leaf: momentum update, preconditioned and clipped step, statistics."""
+    from ..ops import lib
+
+    if "f" not in _sophia_fn:
+        c = lib
+        _sophia_fn["f"] = lib.fn("lvb_sophia_update", [c.c_void_p] * 5 + [c.c_longlong] + [c.c_float] * 5 + [c.c_void_p, c.c_void_p])
+    u = torch.empty_like(g)
+    pp = param if (param is not None and param.dtype == torch.float32 and param.is_contiguous()) else None
+    rc = _sophia_fn["f"](g.data_ptr(), mu.data_ptr(), h.data_ptr(), lib.ptr(pp), u.data_ptr(), g.numel(), float(b1), float(bc1), float(gamma),
+                         float(eps), float(clip) if clip is not None else 0.0, stats.data_ptr(), lib.stream_ptr())
+    lib.check_rc(rc, "lvb_sophia_update")
+    return u
+
+
 def _sophia_gradient_transform(sophia_hess_fn, update_interval: int, b1: float, b2: float, eps: float, gamma: float,
                                clip_threshold: Optional[float], initial_key: int) -> GradientTransformation:
     def init(params):
@@ -59,7 +87,18 @@ def _sophia_gradient_transform(sophia_hess_fn, update_interval: int, b1: float, 
         mom_sq = torch.zeros((), device=updates[keys[0]].device)
         hess_sq = torch.zeros((), device=updates[keys[0]].device)
         par_sq = torch.zeros((), device=updates[keys[0]].device)
-        for k in keys:
+        fused = _fused_update_available(updates, state, keys)
+        if fused:
+            stats_dev = torch.zeros(4, dtype=torch.float32, device=updates[keys[0]].device)
+            for k in keys:
+                p_k = params.get(k) if params is not None else None
+                out[k] = _fused_update(updates[k], state.mu[k], state.h[k], p_k, b1, 1 - b1 ** count, gamma, eps, clip_threshold, stats_dev)
+                total += updates[k].numel()
+            mom_sq, hess_sq, par_sq, unclipped = stats_dev[0], stats_dev[1], stats_dev[2], stats_dev[3]
+            keys_loop = []
+        else:
+            keys_loop = keys
+        for k in keys_loop:
             mu = state.mu[k]
             mu.mul_(b1).add_(updates[k], alpha=1 - b1)
             mu_hat = mu / (1 - b1 ** count)

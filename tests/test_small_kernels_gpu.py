@@ -103,3 +103,68 @@ def test_fp8_linear_trains_with_delayed_scaling():
         assert ((lin.weight.grad.float() - wref).abs().max() / wref.abs().max()).item() < 0.12
     torch.cuda.synchronize()
     lib.check_status()
+
+
+@pytest.mark.parametrize("L,C", [(256, 48), (1024, 96), (2048, 40)])
+def test_long_conv_matches_fft_convolution(L, C):
+    from levanter_b200.ops.long_conv import fft_conv_reference, long_conv
+
+    torch.manual_seed(4)
+    u = torch.randn(2, 3, L, C, device="cuda").bfloat16().requires_grad_()
+    k = (torch.randn(L, C, device="cuda") * torch.exp(-torch.arange(L, device="cuda").float() / 64)[:, None]).bfloat16().requires_grad_()
+    bias = torch.randn(C, device="cuda").requires_grad_()
+    y = long_conv(u, k, bias)
+    ur, kr, br = u.detach().float().requires_grad_(), k.detach().float().requires_grad_(), bias.detach().clone().requires_grad_()
+    yr = fft_conv_reference(ur, kr, br)
+    scale = yr.abs().max().item()
+    assert (y.float() - yr).abs().max().item() < 2e-2 * scale
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    assert (u.grad.float() - ur.grad).abs().max().item() < 2e-2 * ur.grad.abs().max().item()
+    assert (k.grad.float() - kr.grad).abs().max().item() < 2e-2 * kr.grad.abs().max().item()
+    assert torch.allclose(bias.grad, br.grad, rtol=1e-3, atol=1e-2)
+    torch.cuda.synchronize()
+    lib.check_status()
+
+
+def test_lora_branch_through_the_gemm_epilogue():
+    from levanter_b200.lora import LoraLinear
+    from levanter_b200.nn import Linear
+
+    torch.manual_seed(5)
+    base = Linear(256, 384, device="cuda", dtype=torch.bfloat16)
+    ll = LoraLinear.init(base, r=16, alpha=32.0, dropout_prob=0.0)
+    with torch.no_grad():
+        ll.lora.lora_B.weight.copy_(torch.randn_like(ll.lora.lora_B.weight) * 0.1)
+    x = torch.randn(300, 256, device="cuda").bfloat16().requires_grad_()
+    y = ll(x)
+    ref = x.float() @ base.weight.float().t() + ll.lora.scale * ((x.float() @ ll.lora.lora_A.weight.float().t()) @ ll.lora.lora_B.weight.float().t())
+    assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    A, B = ll.lora.lora_A.weight.detach().float().requires_grad_(), ll.lora.lora_B.weight.detach().float().requires_grad_()
+    (xr @ base.weight.float().t() + ll.lora.scale * ((xr @ A.t()) @ B.t())).backward(g.float())
+    for got, want in ((x.grad, xr.grad), (ll.lora.lora_A.weight.grad, A.grad), (ll.lora.lora_B.weight.grad, B.grad)):
+        assert (got.float() - want).abs().max().item() < 3e-2 * want.abs().max().item()
+
+
+def test_sophia_fused_update_matches_the_reference_statement():
+    from levanter_b200.optim.sophia import _fused_update
+
+    torch.manual_seed(6)
+    n = 100_003
+    g, mu, h, p = (torch.randn(n, device="cuda") for _ in range(4))
+    h = h.abs() * 0.1
+    mu0 = mu.clone()
+    stats = torch.zeros(4, device="cuda")
+    b1, count, gamma, eps, rho = 0.96, 3, 0.01, 1e-12, 1.0
+    u = _fused_update(g, mu, h, p, b1, 1 - b1 ** count, gamma, eps, rho, stats)
+    m_ref = b1 * mu0 + (1 - b1) * g
+    mh = m_ref / (1 - b1 ** count)
+    raw = mh / torch.clamp(gamma * h, min=eps)
+    assert torch.allclose(mu, m_ref, rtol=1e-6, atol=1e-7)
+    assert torch.allclose(u, raw.clamp(-rho, rho), rtol=1e-4, atol=1e-6)  # the kernel divides with the fast-math reciprocal
+    want = torch.stack([(mh ** 2).sum(), (h ** 2).sum(), (p ** 2).sum(), (raw.abs() < rho).float().sum()])
+    assert torch.allclose(stats, want, rtol=1e-3)
