@@ -35,6 +35,21 @@ def _bwd():
     return _f["b"]
 
 
+def _bwd2():
+    if "b2" not in _f:
+        c = lib
+        _f["b2"] = lib.fn("lvb_flash_attn_bwd2", [c.c_void_p] * 12 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p],
+                          launches=2)
+    return _f["b2"]
+
+
+# The backward pass runs on the software-pipelined kernel (``csrc/flash_attn_bwd2.cu``); ``LEVANTER_B200_FLASH_BWD=serial`` selects
+# the one-buffer kernel (``csrc/flash_attn_bwd.cu``).
+import os as _os
+
+BWD_PIPELINED = _os.environ.get("LEVANTER_B200_FLASH_BWD", "pipelined") != "serial"
+
+
 # Activation checkpointing that keeps attention outputs (utils/remat.py:checkpoint_layer): during the first pass of a
 # checkpointed layer the forward below appends (o, lse) to ``_keep``; during the recomputation it takes them back from
 # ``_replay`` in the same order and launches nothing.
@@ -100,7 +115,7 @@ class _FlashFn(torch.autograd.Function):
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-        rc = _bwd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
+        rc = (_bwd2() if BWD_PIPELINED else _bwd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
                     dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
                     float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_flash_attn_bwd")
