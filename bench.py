@@ -54,7 +54,9 @@ def parse_args():
     ap.add_argument("--no-baseline", action="store_true", help="ours: do not time the stock-PyTorch arm in the same call")
     ap.add_argument("--baseline-steps", type=int, default=5, help="timed steps of the in-call stock-PyTorch arm (after 3 warm-up steps)")
     # shape overrides for quick functional checks; a run that uses them is labelled in "config" and is not the headline
-    ap.add_argument("--model", default="llama", choices=["llama", "mixtral_ep"],
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (model axis); the data axis is gpus / tp (a side measurement)")
+    ap.add_argument("--fp8", action="store_true", help="fp8 GEMMs with per-tensor delayed scaling in the Linear layers (a side measurement)")
+    ap.add_argument("--model", default="llama", choices=["llama", "llama3_8b", "mixtral_ep"],
                     help="llama: the headline model; mixtral_ep: Mixtral 8x7B layer shapes with the experts sliced over the GPUs (a side "
                          "measurement, never the headline: give --layers so that it fits)")
     ap.add_argument("--layers", type=int, default=32)
@@ -169,7 +171,7 @@ DATA_NAME = "synthetic uniform-random token ids (fixed seed), random-init weight
 
 def _is_headline(args) -> bool:
     return (args.model == "llama" and args.layers == 32 and args.seq_len == 4096 and args.per_gpu_batch == 8 and args.hidden == 4096
-            and not args.remat)
+            and not args.remat and args.tp == 1 and not args.fp8)
 
 
 def run_torch_baseline(args, steps: int, warmup: int, sample_clocks: bool = True) -> dict:
@@ -360,16 +362,28 @@ def main():
     S, B = args.seq_len, args.per_gpu_batch
     micro = _micro(args, world)
     tmp = tempfile.mkdtemp(prefix="lvb_bench_")
+    data_ranks = world // max(args.tp, 1)
+    quant = None
+    if args.fp8:
+        from levanter_b200.quantization import QuantizationConfig
+
+        quant = QuantizationConfig(fp8=True, amax_history_length=16)
     tcfg = TrainerConfig(
-        seed=0, mp=Policy.parse("p=f32,c=bfloat16"), num_train_steps=1_000_000, train_batch_size=B * world,
+        seed=0, mp=Policy.parse("p=f32,c=bfloat16"), num_train_steps=1_000_000, train_batch_size=B * data_ranks,
         per_device_parallelism=micro, tracker=NoopConfig(), log_dir=os.path.join(tmp, "logs"), id="bench",
         checkpointer=CheckpointerConfig(base_path=os.path.join(tmp, "ckpt"), save_interval=None, keep=[dict(every=10**9)]),
-        load_checkpoint=False, zero_stage=args.zero_stage)
+        load_checkpoint=False, zero_stage=args.zero_stage, model_axis_size=max(args.tp, 1),
+        tensor_parallel_axes=["mlp", "heads"] if args.tp > 1 else None, quantization=quant)
     tcfg.initialize()
     mcfg = LlamaConfig(seq_len=S, hidden_dim=args.hidden, intermediate_dim=11008 if args.hidden == 4096 else args.hidden * 8 // 3 // 128 * 128,
                        num_layers=args.layers, num_heads=args.hidden // 128, num_kv_heads=args.hidden // 128,
                        gradient_checkpointing=bool(args.remat), initializer_range=0.02,
                        attn_backend=AttentionBackend(args.attn) if args.attn else None)
+    if args.model == "llama3_8b":
+        vocab = 128256
+        mcfg = LlamaConfig(seq_len=S, hidden_dim=4096, intermediate_dim=14336, num_layers=args.layers, num_heads=32, num_kv_heads=8,
+                           gradient_checkpointing=bool(args.remat), initializer_range=0.02,
+                           attn_backend=AttentionBackend(args.attn) if args.attn else None)
     if args.model == "mixtral_ep":
         from levanter_b200.models.mixtral import MixtralConfig
 
@@ -380,11 +394,19 @@ def main():
     headline = _is_headline(args)
 
     equiv = None
-    if world > 1 and args.model == "llama" and not args.no_equiv:
+    if world > 1 and args.model == "llama" and not args.no_equiv and args.tp == 1 and not args.fp8:
         equiv = equivalence_check(args, mcfg, vocab, dev, rank)
 
     with Trainer(tcfg, ocfg, add_default_hooks=False) as trainer:
-        state = trainer.initial_state(0, model_init=lambda: mcfg.build(vocab, seed=0, device=dev))
+        def model_init():
+            tp = trainer.tensor_parallel
+            if tp is None:
+                return mcfg.build(vocab, seed=0, device=dev)
+            from levanter_b200.parallel.tp import build_sharded_from_seed
+
+            return build_sharded_from_seed(lambda tp: mcfg.build(vocab, seed=0, device=dev, tp=tp), tp)
+
+        state = trainer.initial_state(0, model_init=model_init)
         n_params = sum(p.numel() for p in state.model.parameters())
         comm_used = state.engine.comm if world > 1 else "none"
         stage_used = getattr(state.engine, "zero_stage", 1) if world > 1 else None
@@ -445,7 +467,7 @@ def main():
         stream_stats = dict(state.engine.stream.stats) if getattr(state.engine, "stream", None) is not None else None
         del state, loader, it, dev_batch, host_batches, info
 
-    tokens_per_step = B * world * S
+    tokens_per_step = B * data_ranks * S
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
     flops_per_token = 3 * mcfg.flops_per_token(vocab)
@@ -453,7 +475,7 @@ def main():
 
     # ---- the stock-PyTorch arm in the same call (same GPUs, same clocks), after this arm's memory is released
     base, vs_baseline, vs_e2e = None, None, None
-    if not args.no_baseline and args.model == "llama":
+    if not args.no_baseline and args.model == "llama" and args.tp == 1 and not args.fp8:
         del trainer
         gc.collect()
         torch.cuda.empty_cache()
@@ -465,14 +487,18 @@ def main():
         except Exception as e:  # noqa: BLE001 - the framework's own line must still be printed
             base = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
 
-    if world == 1:
-        parallelism = "single-gpu"
-    elif stage_used == 3:
-        parallelism = f"fsdp{world} (zero-3: layer weights as 1/{world} slices, all-gather and reduce-scatter fused into the GEMM kernels)"
+    if data_ranks == 1:
+        parallelism = "single-gpu" if world == 1 else "no data parallelism"
+    elif stage_used == 3 and getattr(args, "_stage_effective", 3) == 3:
+        parallelism = f"fsdp{data_ranks} (zero-3: layer weights as 1/{data_ranks} slices, all-gather and reduce-scatter fused into the GEMM kernels)"
     else:
-        parallelism = f"zero1-dp{world} (bf16 weights and fp32 gradients whole on every GPU; master weights and Adam moments sliced)"
+        parallelism = f"zero1-dp{data_ranks} (bf16 weights and fp32 gradients whole on every GPU; master weights and Adam moments sliced)"
     if args.model == "mixtral_ep" and world > 1:
         parallelism += f"+ep{world}"
+    if args.tp > 1:
+        parallelism = f"tp{args.tp} x " + parallelism
+    if args.fp8:
+        parallelism += ", fp8 GEMMs (e4m3 forward, e5m2 gradients, per-tensor delayed scaling)"
     out = {
         "metric": "train tokens/sec (device-timed, max over ranks) Llama-7B FSDP",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -483,7 +509,7 @@ def main():
         "impl": "ours",
         "config": {"model": MODEL_NAME if headline
                    else f"NOT THE HEADLINE CONFIG: model={args.model} layers={args.layers} hidden={args.hidden} seq={S} per_gpu_batch={B} remat={args.remat}",
-                   "global_batch": B * world, "seq_len": S, "parallelism": parallelism,
+                   "global_batch": B * data_ranks, "seq_len": S, "parallelism": parallelism,
                    "microbatch_per_gpu": micro, "optimizer": "AdamW fp32 master + fp32 moments, global-norm clip 1.0",
                    "params": n_params, "l2_note": "inputs (activations + 13.5 GB of weights per pass) far exceed the 126 MB L2",
                    "attention_backend": args.attn or "default",
