@@ -437,6 +437,238 @@ __global__ void __launch_bounds__(kThreads) paged_attention_staged_kernel(Params
   }
 }
 
+// Tensor-core variant for D = 128 and at most 16 query heads per KV head.  The query heads that share a KV head are the M rows
+// of warp-level MMAs (m16n8k16, bf16, fp32 accumulation; rows beyond G are zero), so one pass over a key's K and V rows
+// serves all of them at a sixteenth of the instruction count of the scalar kernels, which were bound by instruction issue
+// and shared-memory reads, not by the cache traffic.  Each of the four warps owns 64 keys of the partition and is its own
+// pipeline: it copies stages of 16 keys (K and V rows are adjacent in the cache: 512 bytes per key, padded to 528 in
+// shared memory so that ldmatrix reads are conflict-free) with cp.async, double-buffered, and needs no CTA-wide barrier
+// inside the loop.  Scores S = Q K^T come from ldmatrix'd K rows, the online softmax runs on the accumulator fragments,
+// P is re-packed in registers as the A operand of O += P V (V rows through ldmatrix.trans), and the four warps' (max, sum,
+// O) are merged through shared memory at the end.
+constexpr int kMmaStageKeys = 16;
+constexpr int kMmaRowBytes = 528;  // K (256 B) + V (256 B) + 16 B padding
+constexpr int kMmaWarpKeys = kPart / (kThreads / 32);  // 64
+constexpr int kMmaStageBytes = kMmaStageKeys * kMmaRowBytes;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kThreads) paged_attention_mma_kernel(Params p) {
+  constexpr int D = 128;
+  const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
+  const int G = p.H / p.KV;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  extern __shared__ __align__(16) uint8_t s_dyn[];
+  uint8_t* s_stage = s_dyn;                                   // [4 warps][2 stages][16 keys][528 B] = 67584 B; reused for the merge
+  int* s_rows = reinterpret_cast<int*>(s_dyn + 4 * 2 * kMmaStageBytes);  // [kPart]
+  float* s_ml = reinterpret_cast<float*>(s_rows + kPart);     // [4 warps][16 rows][2]
+
+  int seq = 0, ctx = 0;
+  const bool live = locate(p, t, seq, ctx);
+  const int k0 = part * kPart;
+  if (!live || k0 >= ctx) {
+    if (part == 0 && !live) {
+      for (int i = threadIdx.x; i < G * D; i += kThreads)
+        p.out[(static_cast<long long>(t) * p.H + kvh * G) * D + i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  const int nk = min(kPart, ctx - k0);
+  for (int i = threadIdx.x; i < kPart; i += kThreads) {
+    int slot = -1;
+    if (i < nk) {
+      const int key = k0 + i;
+      const int page = p.page_indices[seq * p.pages_per_seq + key / p.page_size];
+      slot = (page >= 0 && page < p.num_pages) ? page * p.page_size + key % p.page_size : -1;
+    }
+    s_rows[i] = slot;
+  }
+  __syncthreads();
+
+  // ---- Q as A fragments (rows = query heads of this KV head, zero beyond G): 8 k-steps of 16 dimensions
+  const int row_lo = lane >> 2, row_hi = row_lo + 8, kq = (lane & 3) * 2;
+  uint32_t qa[8][4];
+  {
+    const __nv_bfloat16* qbase = p.q + (static_cast<long long>(t) * p.H + kvh * G) * D;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int d0 = ks * 16 + kq;
+      qa[ks][0] = row_lo < G ? *reinterpret_cast<const uint32_t*>(qbase + row_lo * D + d0) : 0u;
+      qa[ks][1] = row_hi < G ? *reinterpret_cast<const uint32_t*>(qbase + row_hi * D + d0) : 0u;
+      qa[ks][2] = row_lo < G ? *reinterpret_cast<const uint32_t*>(qbase + row_lo * D + d0 + 8) : 0u;
+      qa[ks][3] = row_hi < G ? *reinterpret_cast<const uint32_t*>(qbase + row_hi * D + d0 + 8) : 0u;
+    }
+  }
+
+  const long long tok_stride = 2LL * p.KV * D;
+  const int wk0 = warp * kMmaWarpKeys;                       // this warp's first key inside the partition
+  const int wnk = max(0, min(kMmaWarpKeys, nk - wk0));       // and how many of its 64 are real
+  const int stages = (wnk + kMmaStageKeys - 1) / kMmaStageKeys;
+  uint8_t* my_stage = s_stage + warp * (2 * kMmaStageBytes);
+  // one stage: 16 rows x 32 chunks of 16 bytes, 16 per lane; rows without a key are zero-filled (0 * NaN would poison O)
+  auto issue = [&](int st) {
+    uint8_t* dst = my_stage + (st & 1) * kMmaStageBytes;
+#pragma unroll 4
+    for (int c = lane; c < kMmaStageKeys * 32; c += 32) {
+      const int r = c >> 5, ch = c & 31;
+      const int i = wk0 + st * kMmaStageKeys + r;
+      const int slot = (st * kMmaStageKeys + r < wnk) ? s_rows[i] : -1;
+      uint8_t* d = dst + r * kMmaRowBytes + ch * 16;
+      if (slot >= 0) cp_async_16(d, p.kv_pages + slot * tok_stride + (2LL * kvh) * D + ch * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // running max / sum of rows row_lo and row_hi
+  const float sc_log2 = p.scale * 1.4426950408889634f;
+
+  if (stages > 0) issue(0);
+  for (int st = 0; st < stages; ++st) {
+    if (st + 1 < stages) issue(st + 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncwarp();
+    const uint32_t buf = smem_u32(my_stage + (st & 1) * kMmaStageBytes);
+    // ---- S[16 heads, 16 keys] = Q K^T: two n-tiles of 8 keys
+    float sacc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {  // 32 dimensions per ldmatrix.x4: matrices (d 0-7), (8-15), (16-23), (24-31) of the 8 keys
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = buf + (8 * j + (lane & 7)) * kMmaRowBytes + (kp * 32 + (lane >> 3) * 8) * 2;
+        ldmatrix_x4(addr, b0, b1, b2, b3);
+        mma_16816(sacc[j], qa[2 * kp], b0, b1);
+        mma_16816(sacc[j], qa[2 * kp + 1], b2, b3);
+      }
+    }
+    // ---- online softmax on the fragments: this lane holds keys (lane % 4) * 2 + {0, 1} of each n-tile, rows row_lo / row_hi
+    float rmax_lo = -INFINITY, rmax_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kcol = st * kMmaStageKeys + 8 * j + kq + (e & 1);
+        const bool valid = kcol < wnk && s_rows[wk0 + kcol] >= 0;
+        float v = sacc[j][e];
+        if (p.soft_cap > 0.f) v = p.soft_cap * tanhf(v * p.scale / p.soft_cap) * 1.4426950408889634f;
+        else v *= sc_log2;
+        v = valid ? v : -INFINITY;
+        sacc[j][e] = v;
+        if (e < 2) rmax_lo = fmaxf(rmax_lo, v); else rmax_hi = fmaxf(rmax_hi, v);
+      }
+    }
+    rmax_lo = fmaxf(rmax_lo, __shfl_xor_sync(0xffffffffu, rmax_lo, 1));
+    rmax_lo = fmaxf(rmax_lo, __shfl_xor_sync(0xffffffffu, rmax_lo, 2));
+    rmax_hi = fmaxf(rmax_hi, __shfl_xor_sync(0xffffffffu, rmax_hi, 1));
+    rmax_hi = fmaxf(rmax_hi, __shfl_xor_sync(0xffffffffu, rmax_hi, 2));
+    const float mn_lo = fmaxf(m_lo, rmax_lo), mn_hi = fmaxf(m_hi, rmax_hi);
+    const float a_lo = (m_lo == -INFINITY) ? 0.f : exp2f(m_lo - mn_lo);
+    const float a_hi = (m_hi == -INFINITY) ? 0.f : exp2f(m_hi - mn_hi);
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t pa[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        pv[j][0] = (mn_lo == -INFINITY) ? 0.f : exp2f(sacc[j][0] - mn_lo);
+        pv[j][1] = (mn_lo == -INFINITY) ? 0.f : exp2f(sacc[j][1] - mn_lo);
+        pv[j][2] = (mn_hi == -INFINITY) ? 0.f : exp2f(sacc[j][2] - mn_hi);
+        pv[j][3] = (mn_hi == -INFINITY) ? 0.f : exp2f(sacc[j][3] - mn_hi);
+        sum_lo += pv[j][0] + pv[j][1];
+        sum_hi += pv[j][2] + pv[j][3];
+      }
+      pa[0] = pack_bf16x2(pv[0][0], pv[0][1]);  // (row_lo, keys 0-7 tile)
+      pa[1] = pack_bf16x2(pv[0][2], pv[0][3]);  // (row_hi, keys 0-7 tile)
+      pa[2] = pack_bf16x2(pv[1][0], pv[1][1]);  // (row_lo, keys 8-15 tile)
+      pa[3] = pack_bf16x2(pv[1][2], pv[1][3]);  // (row_hi, keys 8-15 tile)
+    }
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    l_lo = l_lo * a_lo + sum_lo;
+    l_hi = l_hi * a_hi + sum_hi;
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    // ---- O[16 heads, 128 d] = O * alpha + P V: pairs of 8-wide d tiles per ldmatrix.x4.trans
+#pragma unroll
+    for (int np = 0; np < 8; ++np) {
+      uint32_t b0, b1, b2, b3;
+      // matrices: (keys 0-7, d 16 np .. +7), (keys 8-15, same d), (keys 0-7, d 16 np + 8 ..), (keys 8-15, same)
+      const int mi = lane >> 3;
+      const uint32_t addr = buf + ((mi & 1) * 8 + (lane & 7)) * kMmaRowBytes + 256 + (np * 16 + (mi >> 1) * 8) * 2;
+      ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+      float* oa = o[2 * np];
+      float* ob = o[2 * np + 1];
+      oa[0] *= a_lo; oa[1] *= a_lo; oa[2] *= a_hi; oa[3] *= a_hi;
+      ob[0] *= a_lo; ob[1] *= a_lo; ob[2] *= a_hi; ob[3] *= a_hi;
+      mma_16816(o[2 * np], pa, b0, b1);
+      mma_16816(o[2 * np + 1], pa, b2, b3);
+    }
+    __syncwarp();  // every lane is done with this buffer before the copy of stage st + 2 overwrites it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // all warps are out of their pipelines: the stage memory becomes the merge buffer
+
+  // ---- merge the four warps: per row the global max, then the rescaled sums and outputs
+  if ((lane & 3) == 0) {
+    s_ml[(warp * 16 + row_lo) * 2 + 0] = m_lo;
+    s_ml[(warp * 16 + row_lo) * 2 + 1] = l_lo;
+    s_ml[(warp * 16 + row_hi) * 2 + 0] = m_hi;
+    s_ml[(warp * 16 + row_hi) * 2 + 1] = l_hi;
+  }
+  float* s_o = reinterpret_cast<float*>(s_stage);  // [4 warps][16 rows][128] fp32 = 32 KB
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    const int d0 = n * 8 + kq;
+    *reinterpret_cast<float2*>(s_o + (warp * 16 + row_lo) * D + d0) = make_float2(o[n][0], o[n][1]);
+    *reinterpret_cast<float2*>(s_o + (warp * 16 + row_hi) * D + d0) = make_float2(o[n][2], o[n][3]);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kThreads) {
+    const int g = idx / D, d = idx - g * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, s_ml[(w * 16 + g) * 2]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = s_ml[(w * 16 + g) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      acc = fmaf(s_o[(w * 16 + g) * D + d], f, acc);
+      l = fmaf(s_ml[(w * 16 + g) * 2 + 1], f, l);
+    }
+    const long long hrow = static_cast<long long>(t) * p.H + kvh * G + g;
+    if (p.parts == 1) {
+      p.out[hrow * D + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+    } else {
+      p.part_o[(hrow * p.parts + part) * D + d] = acc;
+      if (d == 0) {
+        // the merge kernel works with natural-log maxima: this kernel's are in base 2
+        p.part_ml[(hrow * p.parts + part) * 2 + 0] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f;
+        p.part_ml[(hrow * p.parts + part) * 2 + 1] = l;
+      }
+    }
+  }
+}
+constexpr int kMmaSmem = 4 * 2 * kMmaStageBytes + kPart * 4 + 4 * 16 * 2 * 4;
+
 // One CTA per (token, head): merge the partials of the partitions that were live for this token.
 template <int D>
 __global__ void __launch_bounds__(D <= 128 ? 128 : 256) paged_merge_kernel(Params p) {
@@ -463,22 +695,34 @@ __global__ void __launch_bounds__(D <= 128 ? 128 : 256) paged_merge_kernel(Param
   }
 }
 
-// LVB_PAGED_ATTENTION=direct selects the kernel that reads the cache rows straight from global memory for every shape.
-inline bool staged_enabled() {
-  static const bool on = [] {
-    const char* v = std::getenv("LVB_PAGED_ATTENTION");
-    return !(v != nullptr && std::string(v) == "direct");
+// LVB_PAGED_ATTENTION=direct selects the kernel that reads the cache rows straight from global memory for every shape,
+// LVB_PAGED_ATTENTION=staged the scalar kernel on staged rows; the default for D = 128 is the tensor-core kernel.
+inline int paged_variant() {
+  static const int v = [] {
+    const char* e = std::getenv("LVB_PAGED_ATTENTION");
+    if (e != nullptr && std::string(e) == "direct") return 0;
+    if (e != nullptr && std::string(e) == "staged") return 1;
+    return 2;
   }();
-  return on;
+  return v;
 }
 
 template <int D>
 int launch(const Params& p, cudaStream_t s) {
   dim3 grid(p.T, p.KV, p.parts);
-  if (D == 128 && p.H / p.KV <= kStagedMaxG && staged_enabled())
+  const int variant = paged_variant();
+  if (D == 128 && p.H / p.KV <= 16 && variant == 2) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem) != cudaSuccess) return kErrCuda;
+      attr_set = true;
+    }
+    paged_attention_mma_kernel<<<grid, kThreads, kMmaSmem, s>>>(p);
+  } else if (D == 128 && p.H / p.KV <= kStagedMaxG && variant >= 1) {
     paged_attention_staged_kernel<<<grid, kThreads, 0, s>>>(p);
-  else
+  } else {
     paged_attention_kernel<D><<<grid, kThreads, 0, s>>>(p);
+  }
   if (p.parts > 1) paged_merge_kernel<D><<<dim3(p.T, p.H), D <= 128 ? 128 : 256, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
