@@ -67,6 +67,9 @@ class AttentionMask:
     explicit_mask: Optional[torch.Tensor] = None            # [..., Sq, Sk] bool
     segment_ids: Optional[Tuple[torch.Tensor, torch.Tensor]] = None  # ([B, Sq], [B, Sk])
     sliding_window: Optional[int] = None
+    segments_sorted: bool = False
+    """the segment ids are non-decreasing along the sequence with negative ids (padding) only at the end, as in packed
+    batches: kernels may then skip every key block that lies before a query block's first sequence"""
 
     def __post_init__(self):
         if self.segment_ids is not None and not isinstance(self.segment_ids, tuple):
@@ -80,8 +83,9 @@ class AttentionMask:
     def explicit(mask: torch.Tensor) -> "AttentionMask":
         return AttentionMask(is_causal=False, explicit_mask=mask)
 
-    def with_segment_ids(self, segment_ids, kv_segment_ids=None) -> "AttentionMask":
-        return replace(self, segment_ids=(segment_ids, segment_ids if kv_segment_ids is None else kv_segment_ids))
+    def with_segment_ids(self, segment_ids, kv_segment_ids=None, *, sorted: bool = False) -> "AttentionMask":
+        return replace(self, segment_ids=(segment_ids, segment_ids if kv_segment_ids is None else kv_segment_ids),
+                       segments_sorted=bool(sorted))
 
     def with_sliding_window(self, sliding_window: Optional[int]) -> "AttentionMask":
         return replace(self, sliding_window=sliding_window)
@@ -452,7 +456,7 @@ class Attention(nn.Module):
         if seg is not None and x.is_cuda:
             # pure prefill: nothing to read from the cache, so this is causal attention over the packed tokens with one segment
             # per sequence (the flash kernel), instead of the decode kernel walking pages
-            m = AttentionMask.causal(sliding_window=c.sliding_window).with_segment_ids(seg.unsqueeze(0))
+            m = AttentionMask.causal(sliding_window=c.sliding_window).with_segment_ids(seg.unsqueeze(0), sorted=True)
             out = dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), m, attn_backend=c.attn_backend,
                                         logits_soft_cap=c.logits_soft_cap, scaling_factor=c.scaling_factor, inference=True).squeeze(0)
         else:

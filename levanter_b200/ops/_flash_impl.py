@@ -16,14 +16,14 @@ _FORCE_ONE_TILE = False  # tests flip this to exercise the one-tile forward kern
 def _fwd():
     if "f" not in _f:
         c = lib
-        _f["f"] = lib.fn("lvb_flash_attn_fwd", [c.c_void_p] * 7 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["f"] = lib.fn("lvb_flash_attn_fwd", [c.c_void_p] * 8 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["f"]
 
 
 def _fwd2():
     if "f2" not in _f:
         c = lib
-        _f["f2"] = lib.fn("lvb_flash_attn_fwd2", [c.c_void_p] * 7 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["f2"] = lib.fn("lvb_flash_attn_fwd2", [c.c_void_p] * 8 + [c.c_int] * 4 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["f2"]
 
 
@@ -79,7 +79,7 @@ def replaying_outputs(store: list):
 
 class _FlashFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window):
+    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None):
         B, S, Hq, D = q.shape
         Hkv = k.shape[2]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -92,7 +92,7 @@ class _FlashFn(torch.autograd.Function):
             lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
             # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
             fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
-            rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+            rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), lib.ptr(kblock_lo),
                      B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(),
                      lib.stream_ptr())
             lib.check_rc(rc, "lvb_flash_attn_fwd")
@@ -119,7 +119,7 @@ class _FlashFn(torch.autograd.Function):
                     dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
                     float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_flash_attn_bwd")
-        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None
+        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None
 
 
 def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
@@ -135,4 +135,12 @@ def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = No
             B, S = q.shape[0], q.shape[1]
             q_seg = q_seg.to(torch.int32).expand(B, S).contiguous()
             k_seg = k_seg.to(torch.int32).expand(B, S).contiguous()
-    return _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window)
+    kblock_lo = None
+    if q_seg is not None and getattr(mask, "segments_sorted", False) and not torch.is_grad_enabled():
+        # packed sequences: per block of 128 queries, the first block of 128 keys of the first query's sequence (padding ids < 0
+        # sort last); the forward kernels start their key loop there instead of at the beginning of the packed batch
+        big = torch.iinfo(torch.int32).max
+        ks = torch.where(k_seg < 0, torch.full_like(k_seg, big), k_seg)
+        qs = torch.where(q_seg < 0, torch.full_like(q_seg, big), q_seg)[:, ::128].contiguous()
+        kblock_lo = (torch.searchsorted(ks, qs) // 128).to(torch.int32).contiguous()
+    return _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window, kblock_lo)

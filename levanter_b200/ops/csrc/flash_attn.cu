@@ -32,6 +32,7 @@ struct FwdParams {
   float* lse2;          // [B, Hq, S]
   const int* q_seg;     // [B, S] or null
   const int* k_seg;     // [B, S] or null
+  const int* kblock_lo; // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
   int B, S, Hq, Hkv;
   float scale;          // softmax scale (1/sqrt(D) by default)
   float soft_cap;       // 0 = off
@@ -93,6 +94,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (p.window > 0) {
     const int first_key = q0 - p.window + 1;
     jlo = first_key > 0 ? first_key / BN : 0;
+  }
+  if (p.kblock_lo != nullptr) {
+    // packed sequences (segment ids ascending): key blocks before the first query's sequence hold nothing these rows can see
+    const int lo = p.kblock_lo[b * nqb + qb];
+    jlo = max(jlo, min(lo, jhi));
   }
   const int nblocks = jhi - jlo + 1;
 
@@ -387,7 +393,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // q: [B, S, Hq, 128], k/v: [B, S, Hkv, 128] (bf16, contiguous), o: [B, S, Hq, 128] bf16, lse2: [B, Hq, S] fp32.
 // S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.
 extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                  const int* k_seg, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
+                                  const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                   int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa;
@@ -404,6 +410,7 @@ extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   p.lse2 = lse2;
   p.q_seg = q_seg;
   p.k_seg = k_seg;
+  p.kblock_lo = kblock_lo;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale;
   p.soft_cap = soft_cap;

@@ -29,6 +29,7 @@ struct Params {
   float* lse2;
   const int* q_seg;
   const int* k_seg;
+  const int* kblock_lo;  // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
   int B, S, Hq, Hkv;
   float scale, soft_cap;
   int window;
@@ -81,6 +82,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (p.window > 0) {
     const int first_key = q0 - p.window + 1;
     jlo = first_key > 0 ? first_key / BT : 0;
+  }
+  if (p.kblock_lo != nullptr) {
+    // packed sequences (segment ids ascending): key blocks before the first query's sequence hold nothing these rows can see
+    const int lo = p.kblock_lo[b * (p.S / BT) + jdiagA];
+    jlo = max(jlo, min(lo, jdiagA));
   }
   const int nB = jdiagB - jlo + 1;   // blocks processed by tile B
   const int nA = nB - 1;             // tile A stops one block earlier (its diagonal)
@@ -389,7 +395,7 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
 
 // Same contract as lvb_flash_attn_fwd, but S must be a multiple of 256.
 extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                   const int* k_seg, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
+                                   const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                    int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa2;
@@ -407,6 +413,7 @@ extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   p.lse2 = lse2;
   p.q_seg = q_seg;
   p.k_seg = k_seg;
+  p.kblock_lo = kblock_lo;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.soft_cap = soft_cap; p.window = window;
   p.status = status;

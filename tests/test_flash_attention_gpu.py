@@ -119,3 +119,23 @@ def test_head_sizes_the_kernel_does_not_cover_take_the_fused_library_path():
             out = dot_product_attention(q, k, v, mask)
             ref = simple_attention_with_dropout(q.float(), k.float(), v.float(), mask)
             assert (out.float() - ref).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("S", [384, 1024])
+def test_packed_sequences_skip_foreign_key_blocks(S):
+    """Sorted segment ids (a packed prefill batch, padding at the end): the forward kernels start each query block's key loop
+    at its own sequence; the result equals the kernel without the hint and the fp32 reference."""
+    torch.manual_seed(11)
+    B, H = 1, 4
+    q, k, v = (torch.randn(B, S, H, 128, device="cuda").bfloat16() for _ in range(3))
+    bounds = sorted(set([0, 100, 130, 300, S - 40, S]))
+    seg = torch.full((S,), -1, dtype=torch.int32, device="cuda")
+    for i, (a, b) in enumerate(zip(bounds[:-2], bounds[1:-1])):
+        seg[a:b] = i
+    with torch.no_grad():
+        hint = flash_attention_cuda(q, k, v, AttentionMask.causal().with_segment_ids(seg[None], sorted=True))
+        plain = flash_attention_cuda(q, k, v, AttentionMask.causal().with_segment_ids(seg[None]))
+    torch.cuda.synchronize()
+    lib.check_status()
+    live = seg >= 0
+    assert torch.equal(hint[:, live], plain[:, live])
