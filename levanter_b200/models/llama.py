@@ -167,7 +167,7 @@ class LlamaMlp(nn.Module):
             x = self.tp.copy_to_region(x)
         h = gated_activation(self.gate_proj(x), self.up_proj(x), self.act)
         if self.tp is not None and self.tp.size > 1:
-            out = self.tp.reduce_from_region(self.down_proj(h, skip_bias=True))
+            out = self.tp.row_linear(h, self.down_proj)
             if self.down_proj.bias is not None:
                 out = out + self.down_proj.bias
             return out if residual is None else out + residual

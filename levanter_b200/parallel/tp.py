@@ -47,6 +47,44 @@ class _ReduceFromRegion(torch.autograd.Function):
         return g, None
 
 
+class _RowLinearFn(torch.autograd.Function):
+    """``y = all_reduce(x W^T)`` with the collective split around the product (see ``TensorParallel.matmul_all_reduce``).  The
+    backward pass needs no communication: ``dx = dy W`` stays local to the rank's columns, ``dW = dy^T x`` goes where
+    ``ops.gemm`` puts weight gradients (the engine's fp32 accumulator, a gradient sink, or autograd)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, tp):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).contiguous()
+        y = tp.matmul_all_reduce(x2, weight)
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = shp
+        ctx.weight_ref = weight
+        return y.view(*shp[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            sink = getattr(ctx.weight_ref, "grad_sink", None)
+            main_grad = getattr(ctx.weight_ref, "main_grad", None)
+            if sink is not None:
+                sink(dy2, x2)
+            elif main_grad is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        return dx, dw, None
+
+
 class TensorParallel:
     def __init__(self, group: Optional[dist.ProcessGroup], size: int, rank: int, comm: Optional[str] = None):
         self.group = group
@@ -185,6 +223,88 @@ class TensorParallel:
         x.reshape(-1).copy_(stage[:n])
         self.kernel_all_reduces += 1
         return x
+
+    # -- row-parallel projection with the all-reduce split around the GEMM ------------------------------------------------
+    def fused_row_linear_ok(self, x2: torch.Tensor, w: torch.Tensor) -> bool:
+        from ..ops import lib
+        from ..ops.gemm import PAIR_ENABLED
+
+        T, N = x2.shape[0], w.shape[0]
+        return bool(self.comm in ("auto", "p2p", "multimem") and not self._sym_failed and x2.is_cuda and lib.available() and PAIR_ENABLED
+                    and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 < self.size <= 8 and T % (self.size * 32) == 0
+                    and T >= 2048 and N > 128 and N % 8 == 0 and x2.shape[1] % 8 == 0)
+
+    def matmul_all_reduce(self, x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``sum over ranks of x2 @ w.T`` on every rank (``x2 [T, K_local]``, ``w [N, K_local]``): the row-parallel projection of a
+        tensor-parallel block.  The reduce-scatter half of the all-reduce is fused into the GEMM (tile by tile the epilogue
+        stores partial products into the staging slots of the rank that owns the rows, which sums them as they arrive,
+        ``ops/fused_tp.py``); the all-gather half is one copy kernel that pulls every rank's reduced rows over NVLink."""
+        from ..ops import lib
+        from ..ops.fused_tp import _ptr_array, reduce_scatter_gemm, rs_counters
+        from .symm import SymmetricBuffer
+
+        W, r = self.size, self.rank
+        T, K = x2.shape
+        N = w.shape[0]
+        rows = T // W
+        st = self.__dict__.setdefault("_rs", {"arena": None, "area": 0, "cnt": {}, "calls": 0, "uses": {}, "slice": None, "tables": {}})
+        need = (T * N + 63) // 64 * 64
+        if st["arena"] is None or need > st["area"]:
+            # every rank reaches this with the same shapes, so the allocation is collective; counters of all shapes start over
+            cnt_cap = 8 * ((rs_counters(rows, N) + 63) // 64 * 64) * 2
+            st["area"], st["cnt"], st["uses"], st["cnt_next"] = need, {}, {}, 2 * need
+            st["arena"] = SymmetricBuffer(2 * need + cnt_cap, torch.float32, x2.device, self.group)
+            st["cnt_cap"] = 2 * need + cnt_cap
+            st["arena"].barrier(0)
+        key = (T, N)
+        if key not in st["cnt"]:
+            n = (rs_counters(rows, N) + 63) // 64 * 64
+            assert st["cnt_next"] + 2 * n <= st["cnt_cap"], "too many distinct row-parallel shapes for the staging arena"
+            st["cnt"][key], st["uses"][key] = (st["cnt_next"], n), [0, 0]
+            st["cnt_next"] += 2 * n
+        if st["slice"] is None or st["slice"].tensor.numel() < rows * N:
+            st["slice"] = SymmetricBuffer(rows * N, torch.bfloat16, x2.device, self.group)
+        parity = st["calls"] & 1
+        st["calls"] += 1
+        st["uses"][key][parity] += 1
+        target = (W * st["uses"][key][parity]) & 0xFFFFFFFF
+        if target >= 1 << 31:
+            target -= 1 << 32
+        slot = rows * N
+        data_off = parity * st["area"] * 4
+        cnt_off = (st["cnt"][key][0] + parity * st["cnt"][key][1]) * 4
+        peers = st["arena"].peer_ptrs
+        slots = _ptr_array([p + data_off + r * slot * 4 for p in peers])
+        cnts = _ptr_array([p + cnt_off for p in peers])
+        mine = st["slice"].tensor[:rows * N].view(rows, N)
+        reduce_scatter_gemm(x2, w, False, slots, cnts, r, W, peers[r] + data_off, slot, True, target, mine, False, T, N, K, 1.0)
+        st["slice"].barrier(0)  # every rank's reduced rows are complete; a rank overwrites its rows only inside its next product,
+        #                         whose units need a contribution from every peer, i.e. after every peer's pull below
+        y = torch.empty(T, N, dtype=torch.bfloat16, device=x2.device)
+        tkey = (rows * N, W, r)
+        if tkey not in st["tables"]:
+            nbytes = rows * N * 2
+            tab = []
+            for i in range(W):
+                src = (r + 1 + i) % W
+                for off in range(0, nbytes, 16384):
+                    tab.append((src, off // 16, (src * nbytes + off) // 16, min(16384, nbytes - off) // 16))
+            st["tables"][tkey] = (torch.tensor(tab, dtype=torch.int32, device=x2.device), len(tab))
+        table, n_units = st["tables"][tkey]
+        c = lib
+        f = lib.fn("lvb_copy_job", [c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p])
+        rc = f(table.data_ptr(), 0, n_units, st["slice"].c_ptrs, W, y.data_ptr(), 0, lib.status_buffer().data_ptr(), lib.stream_ptr())
+        lib.check_rc(rc, "lvb_copy_job")
+        self.fused_row_linears = getattr(self, "fused_row_linears", 0) + 1
+        return y
+
+    def row_linear(self, x: torch.Tensor, linear) -> torch.Tensor:
+        """Row-parallel projection without its bias: ``all_reduce(x @ W_local.T)``, on the fused path when the shapes allow."""
+        w = linear.weight
+        x2 = x.reshape(-1, x.shape[-1])
+        if type(linear).__name__ == "Linear" and w.dtype == x.dtype and self.fused_row_linear_ok(x2, w):
+            return _RowLinearFn.apply(x, w, self)
+        return self.reduce_from_region(linear(x, skip_bias=True))
 
     def all_gather_last_dim(self, x: torch.Tensor) -> torch.Tensor:
         parts = [torch.empty_like(x) for _ in range(self.size)]
