@@ -415,7 +415,9 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, mask: Union[None, AttentionMask, torch.Tensor] = None,
                 pos_ids: Optional[torch.Tensor] = None, *, skip_out_bias: bool = False,
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, row_parallel=None) -> torch.Tensor:
+        """``row_parallel``: a ``TensorParallel`` whose ``row_linear`` applies the output projection and sums it over the model
+        axis (the caller then adds the bias once)."""
         c = self.config
         q, k, v = self._compute_qkv(x, pos_ids)
         if c.sliding_window is not None and isinstance(mask, AttentionMask) and mask.is_causal:
@@ -436,6 +438,8 @@ class Attention(nn.Module):
 
                 return linear_residual(attn, self.o_proj.weight, None if skip_out_bias else self.o_proj.bias, residual)
             return self.o_proj(attn, skip_bias=skip_out_bias) + residual  # wrapped projections (LoRA, fp8) add it themselves
+        if row_parallel is not None:
+            return row_parallel.row_linear(attn, self.o_proj)
         return self.o_proj(attn, skip_bias=skip_out_bias)
 
     def forward_with_residual(self, x, mask, pos_ids, residual):

@@ -210,8 +210,7 @@ class LlamaDecoderLayer(nn.Module):
 
     def _tp_attn(self, h, mask, pos_ids):
         a = self.self_attn
-        out = a.forward(h, mask, pos_ids, skip_out_bias=True)
-        out = self.tp.reduce_from_region(out)
+        out = a.forward(h, mask, pos_ids, skip_out_bias=True, row_parallel=self.tp)
         if a.o_proj.bias is not None:
             out = out + a.o_proj.bias
         return out
