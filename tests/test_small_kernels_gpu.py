@@ -156,7 +156,7 @@ def test_sophia_fused_update_matches_the_reference_statement():
     torch.manual_seed(6)
     n = 100_003
     g, mu, h, p = (torch.randn(n, device="cuda") for _ in range(4))
-    h = h.abs() * 0.1
+    h = h.abs() * 100 + 10  # gamma * h around 1: a mix of clipped and unclipped entries
     mu0 = mu.clone()
     stats = torch.zeros(4, device="cuda")
     b1, count, gamma, eps, rho = 0.96, 3, 0.01, 1e-12, 1.0
@@ -165,6 +165,8 @@ def test_sophia_fused_update_matches_the_reference_statement():
     mh = m_ref / (1 - b1 ** count)
     raw = mh / torch.clamp(gamma * h, min=eps)
     assert torch.allclose(mu, m_ref, rtol=1e-6, atol=1e-7)
-    assert torch.allclose(u, raw.clamp(-rho, rho), rtol=1e-4, atol=1e-6)  # the kernel divides with the fast-math reciprocal
+    err = (u - raw.clamp(-rho, rho)).abs().max().item()
+    assert err < 1e-5, err  # the kernel divides with the fast-math reciprocal
     want = torch.stack([(mh ** 2).sum(), (h ** 2).sum(), (p ** 2).sum(), (raw.abs() < rho).float().sum()])
-    assert torch.allclose(stats, want, rtol=1e-3)
+    assert torch.allclose(stats[:3], want[:3], rtol=1e-3)
+    assert abs(stats[3].item() - want[3].item()) <= 5  # entries within rounding of the clipping threshold may count either way
