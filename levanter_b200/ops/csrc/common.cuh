@@ -458,4 +458,9 @@ inline int num_sms() {
   return n;
 }
 
+// Sums the fp32 partial products ws[splits, M, N] of a K-split GEMM in slab order and applies alpha, bias, residual and the
+// output type (flags as in the GEMM entry points); defined in gemm_skinny.cu.
+int launch_splitk_finalize(const float* ws, int splits, int M, int N, float alpha, int flags, const void* bias, const void* residual,
+                           int ldr, void* C, int ldc, cudaStream_t stream);
+
 }  // namespace lvb

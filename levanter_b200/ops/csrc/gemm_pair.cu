@@ -52,6 +52,11 @@ struct Params {
   float alpha;
   int tiles_m, tiles_n;
   int* status;
+  // ---- K split (kPlain): a piece of work is (tile, split); each split stores its raw fp32 partial tile to ws[split, M, N]
+  // and a second kernel sums the slabs in order.  For products with far fewer tiles than SM pairs (decode-size M).
+  int splits = 1;
+  int kb_per_split = 0;
+  float* ws = nullptr;
   // ---- reduce-scatter epilogue (kScatter)
   int rank, world;
   int c_rows_per_rank;       // rows [r * c_rows_per_rank, ...) of C belong to rank r (a multiple of 32)
@@ -193,6 +198,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
   const uint32_t cta = cluster_ctarank();  // 0 = leader
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
+  const int splits = p.splits;
+  const int kbps = splits > 1 ? p.kb_per_split : k_blocks;
+  const int num_work = num_tiles * splits;  // the split index runs fastest
   const int first_tile = static_cast<int>(cluster_id_x());
   const int tile_step = static_cast<int>(n_clusters_x());
 
@@ -230,13 +238,15 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int t = first_tile; t < num_work && ok; t += tile_step) {
         int mb, nb;
-        tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        tile_coords(t / splits, p.tiles_m, p.tiles_n, mb, nb);
         if constexpr (MODE == kScatter) mb = __ldg(p.c_m_order + mb);
         const int m0 = mb * BMP + static_cast<int>(cta) * BMC;  // this CTA's rows of the tile
         const int n0 = nb * BN + static_cast<int>(cta) * BNH;   // this CTA's columns of the B tile
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb0 = (t % splits) * kbps;
+        const int kb1 = min(k_blocks, kb0 + kbps);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100, stage);
           if (!ok) break;
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -268,12 +278,14 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       int buf = 0;
       uint32_t tphase = 0;
       bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int t = first_tile; t < num_work && ok; t += tile_step) {
         ok = mbar_wait(&tempty_bar[buf], tphase ^ 1, abort_flag, p.status, 200, buf);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb0 = (t % splits) * kbps;
+        const int n_kb = min(k_blocks, kb0 + kbps) - kb0;
+        for (int kb = 0; kb < n_kb; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201, stage);
           if (!ok) break;
           tc_fence_after();
@@ -303,9 +315,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
     const bool out_f32 = (p.flags & kOutF32) != 0;
     const bool accum = (p.flags & kAccumulate) != 0;
     const float alpha = p.alpha;
-    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+    for (int t = first_tile; t < num_work && ok; t += tile_step) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      tile_coords(t / splits, p.tiles_m, p.tiles_n, mb, nb);
       if constexpr (MODE == kScatter) mb = __ldg(p.c_m_order + mb);
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300, buf);
       ok = __all_sync(0xffffffffu, ok);
@@ -350,6 +362,20 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
             __syncwarp();
           }
           continue;
+        }
+        if constexpr (MODE == kPlain) {
+          if (splits > 1) {
+            // partial sum of this K split: raw fp32 to the workspace slab (N is a multiple of 4 on this path)
+            if (row < p.M && col0 < p.N) {
+              float* wp = p.ws + (static_cast<size_t>(t % splits) * p.M + row) * p.N + col0;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (col0 + 4 * q < p.N)
+                  reinterpret_cast<float4*>(wp)[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                 __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            }
+            continue;
+          }
         }
         if (row < p.M && col0 < p.N) {
           float v[32];
@@ -673,12 +699,28 @@ int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return kErrCuda;
     max_pairs = max_resident_pairs(kern, kNumThreads, L::kTotal);
   }
-  int pairs = p.tiles_m * p.tiles_n;
   int cap = max_pairs;
   if (max_ctas > 0 && max_ctas / 2 < cap) cap = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  if (p.splits < 0) {
+    // as many (tile, split) pairs as SM pairs, at least 8 k-blocks each
+    int sp = cap / tiles;
+    if (sp > k_blocks / 8) sp = k_blocks / 8;
+    if (sp > 8) sp = 8;
+    p.splits = sp < 1 ? 1 : sp;
+  }
+  if (p.ws == nullptr || (p.N & 3) || (p.flags & kAccumulate)) p.splits = 1;
+  if (p.splits > k_blocks) p.splits = k_blocks;
+  p.kb_per_split = (k_blocks + p.splits - 1) / p.splits;
+  p.splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  int pairs = tiles * p.splits;
   if (pairs > cap) pairs = cap;
   kern<<<2 * pairs, kNumThreads, L::kTotal, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+  if (cudaGetLastError() != cudaSuccess) return kErrCuda;
+  if (p.splits > 1)
+    return launch_splitk_finalize(p.ws, p.splits, p.M, p.N, p.alpha, p.flags, p.bias, p.residual, p.ldr, p.C, p.ldc, stream);
+  return kErrOk;
 }
 
 }  // namespace gemm2
@@ -706,6 +748,24 @@ extern "C" int lvb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, 
   if (!a_mn && b_mn) return launch<256, false, true>(A, B, p, lda, ldb, s, max_ctas);
   if (a_mn && b_mn) return launch<256, true, true>(A, B, p, lda, ldb, s, max_ctas);
   return launch<256, true, false>(A, B, p, lda, ldb, s, max_ctas);
+}
+
+// lvb_gemm_bf16_pair for K-major operands with K split over `splits` CTA pairs per tile (0: chosen by the launcher so that about
+// every SM pair gets a piece; at most 8).  `workspace`: lvb_gemm_skinny_workspace_bytes(M, N) bytes of device memory, contents
+// irrelevant.  N % 4 == 0 and no accumulate flag, else one split is used.  The partial tiles are summed in a fixed order.
+extern "C" int lvb_gemm_bf16_pair_splitk(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int flags,
+                                         float alpha, const void* bias, const void* residual, int ldr, int splits, void* workspace,
+                                         int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::gemm2;
+  if (M <= 0 || N <= 128 || K <= 0 || (lda & 7) || (ldb & 7) || splits < 0 || splits > 8) return kErrBadArg;
+  Params p;
+  p.C = C; p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
+  p.flags = flags; p.alpha = alpha; p.status = status;
+  p.splits = splits == 0 ? -1 : splits;
+  p.ws = reinterpret_cast<float*>(workspace);
+  return launch<256, false, false>(A, B, p, lda, ldb, reinterpret_cast<cudaStream_t>(stream), 0);
 }
 
 // The CTA-pair form of lvb_gemm_reduce_scatter (gemm_bf16.cu) with fp32 staging: same protocol and arguments, except that

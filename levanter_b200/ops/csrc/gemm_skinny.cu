@@ -1,4 +1,4 @@
-// bf16 GEMM for one row block (M <= 128: decode steps, small batches) on sm_100a.
+// bf16 GEMM for a few row blocks (M <= 512: decode steps, small batches) on sm_100a.
 //
 //   C[M,N] = alpha * A[M,K] B[N,K]^T (+ bias[N]) (+ residual[M,N]),   A and B K-major (the forward layout of a Linear).
 //
@@ -17,6 +17,10 @@
 //     MMAs into one accumulator run one after the other, and with a 32-column tile each of them is almost all latency, so
 //     one chain of K/16 dependent MMAs, not the memory system, set the pace (measured: time proportional to K and the same
 //     for 32- and 64-column tiles).  Independent chains overlap.
+//   * takes up to four row blocks of 128 (M <= 512): a piece of work is (column tile, K split, row block) with the row block
+//     fastest, so the CTAs that need the same tile of B run side by side and all but the first read it from L2.  Against the
+//     general kernel's 256 x 256 pair tiles this fills the SMs when N / 256 is far below their number (the attention-output
+//     and MLP-down projections of a 256-request decode round).
 // Roles as in the general kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue; two TMEM accumulators.
 // Every wait is bounded (common.cuh).
 #include "common.cuh"
@@ -42,6 +46,7 @@ struct Params {
   int flags;
   float alpha;
   int tiles_n;
+  int tiles_m;       // row blocks of 128
   int stages;        // ring depth
   int a_bytes;       // bytes of A loaded per stage (a_box_rows * 128)
   int splits;        // CTAs per column tile along K (1: the epilogue writes C itself)
@@ -72,7 +77,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int k_blocks = (p.K + BK - 1) / BK;
-  const int num_work = p.tiles_n * p.splits;  // (column tile, K split) pairs
+  const int num_work = p.tiles_n * p.splits * p.tiles_m;  // (column tile, K split, row block), row block fastest
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -103,15 +108,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_work && ok; t += gridDim.x) {
-        const int n0 = (t / p.splits) * BN;
-        const int kb0 = (t % p.splits) * p.kb_per_split;
+        const int m0 = (t % p.tiles_m) * BM;
+        const int u = t / p.tiles_m;
+        const int n0 = (u / p.splits) * BN;
+        const int kb0 = (u % p.splits) * p.kb_per_split;
         const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100, stage);
           if (!ok) break;
           uint8_t* sa = ring + stage * stride;
           mbar_expect_tx(&full_bar[stage], stride);
-          tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, 0);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m0);
           tma_load_2d(sa + p.a_bytes, &tmB, &full_bar[stage], kb * BK, n0);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
@@ -129,7 +136,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         ok = mbar_wait(&tempty_bar[buf], tphase ^ 1, abort_flag, p.status, 200, buf);
         if (!ok) break;
         tc_fence_after();
-        const int kb0 = (t % p.splits) * p.kb_per_split;
+        const int kb0 = ((t / p.tiles_m) % p.splits) * p.kb_per_split;
         const int n_kb = min(k_blocks, kb0 + p.kb_per_split) - kb0;
         for (int kb = 0; kb < n_kb; ++kb) {
           const uint32_t tmem_acc = tmem_base + (buf * kAcc + (kb % kAcc)) * BN;
@@ -156,20 +163,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t tphase = 0;
     bool ok = true;
     const bool out_f32 = (p.flags & kOutF32) != 0;
-    const int row = quad * 32 + lane;
     for (int t = blockIdx.x; t < num_work && ok; t += gridDim.x) {
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300, buf);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int n0 = (t / p.splits) * BN;
-      const int split = t % p.splits;
+      const int m0 = (t % p.tiles_m) * BM;
+      const int u = t / p.tiles_m;
+      const int n0 = (u / p.splits) * BN;
+      const int split = u % p.splits;
+      const int row = m0 + quad * 32 + lane;
       const int kb0 = split * p.kb_per_split;
       const int n_kb = min(k_blocks, kb0 + p.kb_per_split) - kb0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kAcc * BN;
       const int n_acc = n_kb < kAcc ? n_kb : kAcc;  // accumulators that were written for this piece of work
       // warps whose 32 rows are all beyond M still take part in the barrier protocol but skip the loads
-      const bool warp_has_rows = quad * 32 < p.M;
+      const bool warp_has_rows = m0 + quad * 32 < p.M;
 #pragma unroll 1
       for (int c = 0; c < BN && warp_has_rows; c += 32) {
         float v[32];
@@ -307,7 +316,8 @@ __global__ void splitk_finalize_kernel(const float* __restrict__ ws, int splits,
 template <int BN, int kAcc>
 int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_t stream) {
   constexpr int kBBytes = BN * BK * 2;
-  const int a_rows = ((p.M + 7) / 8) * 8;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  const int a_rows = p.tiles_m > 1 ? BM : ((p.M + 7) / 8) * 8;  // rows past M in the last block are zero-filled by TMA
   p.a_bytes = a_rows * BK * 2;
   const int stride = p.a_bytes + kBBytes;
   int stages = kSmemBudget / stride;
@@ -332,7 +342,7 @@ int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448) != cudaSuccess) return kErrCuda;
     attr_set = true;
   }
-  const int work = p.tiles_n * p.splits;
+  const int work = p.tiles_n * p.splits * p.tiles_m;
   const int grid = work < num_sms() ? work : num_sms();
   kern<<<grid, kThreads, smem_bytes, stream>>>(tmA, tmB, p);
   if (cudaGetLastError() != cudaSuccess) return kErrCuda;
@@ -346,12 +356,21 @@ int launch(const void* A, const void* B, Params p, int lda, int ldb, cudaStream_
 }
 
 }  // namespace skinny
+
+int launch_splitk_finalize(const float* ws, int splits, int M, int N, float alpha, int flags, const void* bias, const void* residual,
+                           int ldr, void* C, int ldc, cudaStream_t stream) {
+  const long long total = static_cast<long long>(M) * (N / 4);
+  const int blocks = static_cast<int>((total + 255) / 256 < 4LL * num_sms() ? (total + 255) / 256 : 4LL * num_sms());
+  skinny::splitk_finalize_kernel<<<blocks, 256, 0, stream>>>(ws, splits, M, N, alpha, flags, bias,
+                                                             reinterpret_cast<const __nv_bfloat16*>(residual), ldr, C, ldc);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
 }  // namespace lvb
 
 // Bytes of fp32 workspace lvb_gemm_skinny may use for an [M, N] product (the most splits it ever picks is 8).
 extern "C" long long lvb_gemm_skinny_workspace_bytes(int M, int N) { return 8LL * M * N * 4; }
 
-// C[M,N] = alpha * A[M,K] B[N,K]^T (+ bias) (+ residual) for M <= 128.  flags: 1 = fp32 output, 4 = bias, 16 = bias is fp32,
+// C[M,N] = alpha * A[M,K] B[N,K]^T (+ bias) (+ residual) for M <= 512.  flags: 1 = fp32 output, 4 = bias, 16 = bias is fp32,
 // 8 = residual (bf16 [M, N], row stride ldr).  bn: tile width (32, 64 or 128), or 0 to let the launcher choose.
 // splits: CTAs per column tile along K, or 0 to let the launcher choose; more than one needs `workspace`
 // (lvb_gemm_skinny_workspace_bytes(M, N) bytes of device memory, contents irrelevant) and N % 4 == 0, else 1 is used.
@@ -360,7 +379,7 @@ extern "C" int lvb_gemm_skinny(const void* A, const void* B, void* C, int M, int
                                int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::skinny;
-  if (M <= 0 || M > BM || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || splits < 0 || splits > 8) return kErrBadArg;
+  if (M <= 0 || M > 4 * BM || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || splits < 0 || splits > 8) return kErrBadArg;
   Params p;
   p.C = C; p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
@@ -371,7 +390,7 @@ extern "C" int lvb_gemm_skinny(const void* A, const void* B, void* C, int M, int
   if (splits == 0) {
     // enough (tile, split) pairs for about one per SM, but keep at least ~12 k-blocks per CTA (the fixed cost of a CTA is
     // worth about 25 k-blocks)
-    const int tiles = (N + bn - 1) / bn;
+    const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     const int k_blocks = (K + BK - 1) / BK;
     splits = num_sms() / tiles;
     if (splits > k_blocks / 12) splits = k_blocks / 12;

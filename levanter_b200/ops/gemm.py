@@ -120,8 +120,8 @@ def gemm(
             residual = residual.to(torch.bfloat16).contiguous()
         residual = residual.view(M, N) if residual.dim() != 2 else residual
         ldr = residual.stride(0)
-    if M <= SKINNY_MAX_ROWS and not a_mn and not b_mn and not accumulate and max_ctas == 0:
-        # one row block (decode steps, small batches): the weight-streaming kernel
+    if _use_skinny(M, N) and not a_mn and not b_mn and not accumulate and max_ctas == 0:
+        # a few row blocks (decode steps, small batches): the weight-streaming kernel
         rc = _skinny_fn()(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), flags, float(alpha),
             lib.ptr(bias), lib.ptr(residual), ldr, 0, 0, _skinny_workspace(a.device, M, N),
@@ -141,6 +141,13 @@ def gemm(
             lib.check_rc(rc, "lvb_gemm_bf16_copy_job")
             return out
     pair = PAIR_ENABLED and N > 128 and M > 128
+    if pair and not a_mn and not b_mn and not accumulate and max_ctas == 0 and _use_pair_splitk(M, N, K):
+        rc = _pair_splitk_fn()(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), flags, float(alpha),
+            lib.ptr(bias), lib.ptr(residual), ldr, 0, _splitk_workspace(a.device), lib.status_buffer().data_ptr(), lib.stream_ptr(),
+        )
+        lib.check_rc(rc, "lvb_gemm_bf16_pair_splitk")
+        return out
     rc = (_pair_fn() if pair else _fn())(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), flags, float(alpha), lib.ptr(bias), lib.ptr(residual), ldr, int(max_ctas),
@@ -168,6 +175,35 @@ def _pair_fn():
              c.c_int, c.c_int, c.c_float, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p],
         )
     return _pair
+
+
+_pair_splitk = None
+SPLITK_MODE = _os.environ.get("LEVANTER_B200_SMALL_M", "splitk")  # what 128 < M products with few tiles run on: splitk | stream | general
+
+
+def _pair_splitk_fn():
+    global _pair_splitk
+    if _pair_splitk is None:
+        c = lib
+        _pair_splitk = lib.fn("lvb_gemm_bf16_pair_splitk",
+                              [c.c_void_p, c.c_void_p, c.c_void_p] + [c.c_int] * 7 + [c.c_float, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                                                                       c.c_void_p, c.c_void_p, c.c_void_p], launches=2)
+    return _pair_splitk
+
+
+def _use_pair_splitk(M: int, N: int, K: int) -> bool:
+    """Few 256 x 256 tiles (at most half the 74 SM pairs) and a K long enough to split, N % 4 == 0: the decode-size
+    projections, where whole-K tiles would leave most SMs idle."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    return SPLITK_MODE == "splitk" and tiles <= 37 and K >= 1024 and N % 4 == 0
+
+
+def _splitk_workspace(device) -> int:
+    """The split-K scratch shared with the streaming kernel (tiles x splits <= 74 pieces of 256 x 256 fp32 fit in it)."""
+    ws = _skinny_ws.get(device)
+    if ws is None:
+        ws = _skinny_ws[device] = torch.empty(8 * _SKINNY_SPLIT_MAX_TILES * 128 * 128 * 4, dtype=torch.uint8, device=device)
+    return ws.data_ptr()
 
 
 # A provider of copy jobs (``flops -> (table_ptr, u0, u1, src_ptr_array, n_srcs, dst_ptr) | None``): when one is set, dense
@@ -207,8 +243,18 @@ def _cj_fn():
     return _cj
 
 
-SKINNY_MAX_ROWS = 128
+SKINNY_MAX_ROWS = 128          # up to here the weight-streaming kernel always runs
+SKINNY_MAX_ROWS_NARROW = 512   # up to here it runs when the general kernel's 256 x 256 tiles would leave most SMs idle
+_SKINNY_NARROW_TILES = int(_os.environ.get("LEVANTER_B200_SKINNY_NARROW_TILES", "48"))
 _skinny = None
+
+
+def _use_skinny(M: int, N: int) -> bool:
+    if M <= SKINNY_MAX_ROWS:
+        return True
+    if M > SKINNY_MAX_ROWS_NARROW or SPLITK_MODE != "stream":
+        return False
+    return ((M + 255) // 256) * ((N + 255) // 256) <= _SKINNY_NARROW_TILES
 
 
 def _skinny_fn():
@@ -228,15 +274,15 @@ def _skinny_workspace(device, M: int, N: int) -> int:
     """Address of the per-device scratch for the split-K partials of the streaming kernel, or 0 when the launcher will not
     split (wide outputs already give every SM a tile).  Successive GEMMs on a stream reuse the scratch safely: each one's
     second kernel has consumed it before the next one's first kernel writes it."""
-    if N > _SKINNY_SPLIT_MAX_N:
+    if ((M + 127) // 128) * ((N + 127) // 128) > _SKINNY_SPLIT_MAX_TILES:
         return 0
     ws = _skinny_ws.get(device)
     if ws is None:
-        ws = _skinny_ws[device] = torch.empty(8 * SKINNY_MAX_ROWS * _SKINNY_SPLIT_MAX_N * 4, dtype=torch.uint8, device=device)
+        ws = _skinny_ws[device] = torch.empty(8 * _SKINNY_SPLIT_MAX_TILES * 128 * 128 * 4, dtype=torch.uint8, device=device)
     return ws.data_ptr()
 
 
-_SKINNY_SPLIT_MAX_N = 128 * 74  # more 128-column tiles than half the SMs: the launcher does not split K
+_SKINNY_SPLIT_MAX_TILES = 74  # more 128 x 128 tiles than half the SMs: the launcher does not split K
 
 
 class _LinearFn(torch.autograd.Function):

@@ -154,3 +154,29 @@ def test_single_row_block_shapes_use_the_streaming_kernel(M, N, K):
     lib.check_status()
     _check(guard[:M], a.float() @ b.float().t() + res.float(), K)
     assert bool((guard[M:] == 7.0).all())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 4096), (200, 1024, 14336), (512, 6144, 1024), (300, 136, 200), (129, 4096, 512)])
+@pytest.mark.parametrize("mode", ["splitk", "stream"])
+def test_a_few_row_blocks_with_a_narrow_output(M, N, K, mode, monkeypatch):
+    """128 < M <= 512 with few 256-column tiles.  "splitk": the pair kernel with K split over several CTA pairs per tile and
+    the partials summed by a second kernel; "stream": the weight-streaming kernel with row blocks of 128 sharing each tile
+    of B.  The last row block is partial in both."""
+    monkeypatch.setattr(G, "SPLITK_MODE", mode)
+    assert G._use_skinny(M, N) == (mode == "stream")
+    torch.manual_seed(3)
+    a, b = _rand(M, K), _rand(N, K)
+    bias = _rand(N)
+    c = G.gemm(a, b, bias=bias)
+    torch.cuda.synchronize()
+    lib.check_status()
+    _check(c, a.float() @ b.float().t() + bias.float(), K)
+    res = _rand(M, N)
+    guard = torch.full((M + 8, N), 7.0, device="cuda")
+    G.gemm(a, b, residual=res, out=guard[:M])
+    torch.cuda.synchronize()
+    lib.check_status()
+    _check(guard[:M], a.float() @ b.float().t() + res.float(), K)
+    assert bool((guard[M:] == 7.0).all())
+    c2 = G.gemm(a, b, bias=bias)
+    assert torch.equal(c, c2)  # split-K partials are summed in a fixed order
