@@ -19,6 +19,7 @@ from torch.utils.checkpoint import checkpoint
 from ..compat.hf_checkpoints import HFCheckpointConverter, HFCompatConfig
 from ..layers.attention import AttentionBackend, AttentionMask, dot_product_attention
 from ..nn import Embedding, LayerNorm, Linear
+from ..ops import conv1d as conv_ops
 from ..utils.activation import ActivationFunctionEnum
 from ..utils.remat import should_recompute
 from .asr_model import ASRConfig, ASRMixin
@@ -198,8 +199,15 @@ class WhisperEncoder(nn.Module):
     def forward(self, mel: torch.Tensor) -> torch.Tensor:
         """``mel[B, n_mels, frames]`` -> ``[B, frames / 2, d_model]``."""
         w = self.conv1.weight
-        x = F.gelu(self.conv1(mel.to(w.dtype)))
-        x = F.gelu(self.conv2(x)).transpose(1, 2)
+        mel = mel.to(w.dtype)
+        if mel.is_cuda and w.dtype == torch.bfloat16 and mel.shape[-1] % 2 == 0 and conv_ops.lib.available():
+            # both stem convolutions as tensor-core GEMMs over channels-last, zero-padded activations (ops/conv1d.py)
+            h = F.gelu(conv_ops.conv1d_k3(conv_ops.pad_channels_last(mel), w, self.conv1.bias, 1))
+            hp = F.pad(h, (0, 0, 1, 1))
+            x = F.gelu(conv_ops.conv1d_k3(hp, self.conv2.weight, self.conv2.bias, 2))
+        else:
+            x = F.gelu(self.conv1(mel))
+            x = F.gelu(self.conv2(x)).transpose(1, 2)
         if x.shape[1] > self.embed_positions.weight.shape[0]:
             raise ValueError(f"audio of {x.shape[1]} positions exceeds max_source_positions={self.embed_positions.weight.shape[0]}")
         x = x + self.embed_positions.weight[: x.shape[1]].to(x.dtype)

@@ -2,8 +2,10 @@
 ``trainer.quantization``, src/levanter/trainer.py:648, config/gpt2_small_fast_fp8.yaml:17-18).
 
 ``fp8: true`` selects fp8 GEMMs for the Linear layers named by ``targets`` (all by default): e4m3 for forward operands,
-e5m2 for output gradients, with one scale per tensor taken from a rolling history of absolute maxima (delayed scaling, as
-in the reference).  ``block_size`` is accepted for configs that name it and is not used: scaling is per tensor.
+e5m2 for output gradients.  ``scaling: tensor`` (default) uses one scale per tensor taken from a rolling history of absolute
+maxima (delayed scaling, as in the reference); ``scaling: block`` uses one power-of-two scale per 32 values along the
+contraction dimension, applied by the tensor core (``tcgen05.mma kind::mxf8f6f4.block_scale``).  ``block_size`` is accepted
+for configs that name it; the hardware's block is 32 whatever it says.
 ``quantize_linear_layers`` swaps matching ``Linear`` modules for ``Fp8Linear``;
 master weights, optimizer state and checkpoints are unchanged."""
 from __future__ import annotations
@@ -24,10 +26,13 @@ class QuantizationConfig:
     fp8: bool = False
     int8: bool = False
     block_size: int = 128
+    scaling: str = "tensor"  # tensor | block
 
     def __post_init__(self):
         if self.fp8 and self.int8:
             raise ValueError("only one of fp8 / int8 can be enabled")
+        if self.scaling not in ("tensor", "block"):
+            raise ValueError(f"scaling must be 'tensor' or 'block', got {self.scaling!r}")
 
     def matches(self, name: str) -> bool:
         if self.targets is None:
@@ -50,5 +55,6 @@ def quantize_linear_layers(model: nn.Module, config: QuantizationConfig) -> nn.M
         for child_name, child in list(mod.named_children()):
             full = f"{name}.{child_name}" if name else child_name
             if type(child) is Linear and config.matches(full) and "lm_head" not in full:
-                setattr(mod, child_name, Fp8Linear.from_linear(child, block=config.block_size))
+                setattr(mod, child_name, Fp8Linear.from_linear(child, block=config.block_size, amax_history_length=config.amax_history_length,
+                                                                     block_scaled=config.scaling == "block"))
     return model

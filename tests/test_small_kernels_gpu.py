@@ -170,3 +170,33 @@ def test_sophia_fused_update_matches_the_reference_statement():
     want = torch.stack([(mh ** 2).sum(), (h ** 2).sum(), (p ** 2).sum(), (raw.abs() < rho).float().sum()])
     assert torch.allclose(stats[:3], want[:3], rtol=1e-3)
     assert abs(stats[3].item() - want[3].item()) <= 5  # entries within rounding of the clipping threshold may count either way
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_three_tap_convolution_as_a_gemm_matches_conv1d(stride):
+    """Whisper's stem convolutions: the im2col matrix is an overlapping-row view of the padded channels-last input."""
+    import torch.nn.functional as F
+    from levanter_b200.ops import conv1d as C
+
+    torch.manual_seed(0)
+    B, Ci, Co, T = 3, 80, 384, 3000 if stride == 1 else 1500
+    x = torch.randn(B, Ci, T, device="cuda").bfloat16()
+    w = (torch.randn(Co, Ci, 3, device="cuda") * 0.05).bfloat16().requires_grad_()
+    b = torch.randn(Co, device="cuda").bfloat16().requires_grad_()
+    xp = C.pad_channels_last(x).requires_grad_()
+    assert C.kernel_ok(xp, w, stride)
+    y = C.conv1d_k3(xp, w, b, stride)
+    xr, wr, br = x.float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    ref = F.conv1d(xr, wr, br, stride=stride, padding=1).transpose(1, 2)
+    assert y.shape == ref.shape
+    assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    g = torch.randn_like(ref)
+    y.backward(g.bfloat16())
+    ref.backward(g)
+    torch.cuda.synchronize()
+    lib.check_status()
+    assert (w.grad.float() - wr.grad).abs().max() <= 2e-2 * wr.grad.abs().max()
+    assert (b.grad.float() - br.grad).abs().max() <= 2e-2 * br.grad.abs().max()
+    dx = xp.grad[:, 1 : T + 1].float().transpose(1, 2)
+    assert (dx - xr.grad).abs().max() <= 2e-2 * xr.grad.abs().max()
+    assert float(xp.grad[:, 0].abs().max()) < 1e30  # padding rows receive a finite (ignored) gradient
