@@ -55,7 +55,9 @@ def parse_args():
     ap.add_argument("--baseline-steps", type=int, default=5, help="timed steps of the in-call stock-PyTorch arm (after 3 warm-up steps)")
     # shape overrides for quick functional checks; a run that uses them is labelled in "config" and is not the headline
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (model axis); the data axis is gpus / tp (a side measurement)")
-    ap.add_argument("--fp8", action="store_true", help="fp8 GEMMs with per-tensor delayed scaling in the Linear layers (a side measurement)")
+    ap.add_argument("--fp8", action="store_true", help="fp8 GEMMs in the Linear layers (a side measurement)")
+    ap.add_argument("--fp8-scaling", choices=["tensor", "block"], default="tensor",
+                    help="tensor: one delayed scale per tensor; block: one scale per 32 values, applied by the tensor core")
     ap.add_argument("--model", default="llama", choices=["llama", "llama3_8b", "mixtral_ep"],
                     help="llama: the headline model; mixtral_ep: Mixtral 8x7B layer shapes with the experts sliced over the GPUs (a side "
                          "measurement, never the headline: give --layers so that it fits)")
@@ -367,7 +369,7 @@ def main():
     if args.fp8:
         from levanter_b200.quantization import QuantizationConfig
 
-        quant = QuantizationConfig(fp8=True, amax_history_length=16)
+        quant = QuantizationConfig(fp8=True, amax_history_length=16, scaling=args.fp8_scaling)
     tcfg = TrainerConfig(
         seed=0, mp=Policy.parse("p=f32,c=bfloat16"), num_train_steps=1_000_000, train_batch_size=B * data_ranks,
         per_device_parallelism=micro, tracker=NoopConfig(), log_dir=os.path.join(tmp, "logs"), id="bench",
@@ -498,7 +500,8 @@ def main():
     if args.tp > 1:
         parallelism = f"tp{args.tp} x " + parallelism
     if args.fp8:
-        parallelism += ", fp8 GEMMs (e4m3 forward, e5m2 gradients, per-tensor delayed scaling)"
+        parallelism += (", fp8 GEMMs (e4m3 forward, e5m2 gradients, "
+                        + ("per-tensor delayed scaling)" if args.fp8_scaling == "tensor" else "one scale per 32 values applied by the tensor core)"))
     out = {
         "metric": "train tokens/sec (device-timed, max over ranks) Llama-7B FSDP",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

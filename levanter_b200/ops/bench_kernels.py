@@ -58,7 +58,7 @@ def _report(name, cfg, ms, ms_min, flops=None, nbytes=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule", "rmsnorm_bwd", "rope", "dwconv", "entropy", "histogram", "gdn_layer"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "gemm_mxfp8", "mxfp8_quant", "flash_fwd", "flash_bwd", "rmsnorm", "cross_entropy", "adamw", "paged_attention", "sampler", "moe_mlp", "delta_rule", "rmsnorm_bwd", "rope", "dwconv", "entropy", "histogram", "gdn_layer"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -102,6 +102,23 @@ def main(argv=None):
         sc = sa * sb
         ms, mn = _time(lambda: fp8_gemm(A, B, sc, out=C), a.iters, a.warmup, flush)
         return _report("gemm_fp8_e4m3", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
+
+    if a.kernel == "gemm_mxfp8":
+        from .fp8 import E4M3, mx_gemm, mx_quantize
+
+        A, sa, _, _ = mx_quantize(torch.randn(a.m, a.k, device=dev, dtype=bf), E4M3)
+        B, sb, _, _ = mx_quantize(torch.randn(a.n, a.k, device=dev, dtype=bf), E4M3)
+        C = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        ms, mn = _time(lambda: mx_gemm(A, sa, B, sb, out=C), a.iters, a.warmup, flush)
+        return _report("gemm_mxfp8_e4m3_block32", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
+
+    if a.kernel == "mxfp8_quant":
+        from .fp8 import E4M3, mx_quantize
+
+        X = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        ms, mn = _time(lambda: mx_quantize(X, E4M3, True, True), a.iters, a.warmup, flush)
+        # read bf16 once, write the fp8 tensor and its transpose (+ 1/16 of that in scales)
+        return _report("mxfp8_quantize_both_directions", {"rows": a.m, "cols": a.k}, ms, mn, nbytes=a.m * a.k * (2 + 2 + 2 / 32))
 
     if a.kernel in ("flash_fwd", "flash_bwd"):
         from ..layers.attention import AttentionMask
