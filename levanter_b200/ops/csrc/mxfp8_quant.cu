@@ -19,7 +19,7 @@ namespace lvb {
 namespace mxq {
 
 constexpr int kTile = 128;
-constexpr int kPitch = kTile + 2;  // bf16 elements per shared-memory row; the odd word count spreads column reads over banks
+constexpr int kPitch = kTile + 8;  // bf16 per shared-memory row: 272 bytes keep rows 16-byte aligned and put row i at bank 4 i
 
 // ceil(log2(amax / fmax)), exactly: the exponent field of the correctly rounded quotient, plus one unless it is a power of two
 __device__ __forceinline__ int block_exponent(float amax, float fmax) {
@@ -38,66 +38,76 @@ __device__ __forceinline__ uint32_t cvt4(float a, float b, float c, float d, int
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, k);
   return lo | (hi << 16);
 }
+__device__ __forceinline__ float amax8(uint4 w, float m) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 f = __bfloat1622float2(h[t]);
+    m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+  }
+  return m;
+}
+__device__ __forceinline__ uint2 cvt8(uint4 w, float inv, int fmt) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+  return make_uint2(cvt4(a.x * inv, a.y * inv, b.x * inv, b.y * inv, fmt), cvt4(c.x * inv, c.y * inv, d.x * inv, d.y * inv, fmt));
+}
 
-__global__ void __launch_bounds__(256)
+// Five CTAs per SM (35 KB of shared memory and at most 48 registers each): the tile is brought in by 16-byte asynchronous copies,
+// and each block of 32 is read from shared memory twice (maximum, then conversion) rather than held in registers, so that
+// enough CTAs are resident for their load phases to keep DRAM busy while others compute.
+__global__ void __launch_bounds__(256, 5)
 mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int C, int fmt, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
-  __shared__ __nv_bfloat16 tile[kTile * kPitch];
+  __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
   const int c0 = blockIdx.x * kTile, r0 = blockIdx.y * kTile;
   const int tid = threadIdx.x;
   const float fmax = fmt ? 57344.f : 448.f;
-  // ---- load: a warp reads one row of 128 values (4 per lane) at a time; outside the matrix the tile is zero
-  for (int r = tid >> 5; r < kTile; r += 8) {
-    const int c = (tid & 31) * 4;
-    uint2 v = make_uint2(0u, 0u);
-    if (r0 + r < R && c0 + c < C) v = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(r0 + r) * ldx + c0 + c);  // C % 4 == 0
-    uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * kPitch + c);
-    dst[0] = v.x;
-    dst[1] = v.y;
+  // ---- load: 128 rows x 16 chunks of 16 bytes, 8 chunks per thread; outside the matrix the tile is zero (C % 8 == 0)
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = it * 256 + tid;
+    const int r = idx >> 4, c = (idx & 15) * 8;
+    const uint32_t dst = smem_u32(tile + r * kPitch + c);
+    const bool in = r0 + r < R && c0 + c < C;
+    const void* src = in ? static_cast<const void*>(x + static_cast<size_t>(r0 + r) * ldx + c0 + c) : static_cast<const void*>(x);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
   }
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   const int cblocks = (C + kTile - 1) / kTile, rblocks = (R + kTile - 1) / kTile;
-  const int i = tid >> 1, half = tid & 1;  // a row (or column) of the tile, and which two of its four blocks of 32
+  const int i = tid & 127, half = tid >> 7;  // a row (or column) of the tile -- consecutive over a warp -- and two of its four blocks
   if (q_row != nullptr) {
     uint8_t* sf = sf_row + (static_cast<size_t>(blockIdx.y) * cblocks + blockIdx.x) * 512 + (i & 31) * 16 + (i >> 5) * 4;
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
       const int j = half * 2 + bb;
-      float v[32];
+      const uint4* src = reinterpret_cast<const uint4*>(tile + i * kPitch + j * 32);
       float amax = 0.f;
 #pragma unroll
-      for (int t = 0; t < 32; t += 2) {
-        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(tile + i * kPitch + j * 32 + t));
-        v[t] = f.x; v[t + 1] = f.y;
-        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
+      for (int t = 0; t < 4; ++t) amax = amax8(src[t], amax);
       const bool live = r0 + i < R && c0 + j * 32 < C;
       const int e = live ? block_exponent(amax, fmax) : 0;
       sf[j] = static_cast<uint8_t>(e + 127);
       if (live) {
         const float inv = exp2_int(-e);
-        uint32_t w[8];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) w[t] = cvt4(v[4 * t] * inv, v[4 * t + 1] * inv, v[4 * t + 2] * inv, v[4 * t + 3] * inv, fmt);
+        const uint2 a = cvt8(src[0], inv, fmt), b = cvt8(src[1], inv, fmt), c = cvt8(src[2], inv, fmt), d = cvt8(src[3], inv, fmt);
         uint4* dst = reinterpret_cast<uint4*>(q_row + static_cast<size_t>(r0 + i) * C + c0 + j * 32);  // C % 32 == 0
-        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        dst[0] = make_uint4(a.x, a.y, b.x, b.y);
+        dst[1] = make_uint4(c.x, c.y, d.x, d.y);
       }
     }
   }
   if (q_col != nullptr) {
-    // operand rows are the columns of x; K runs over the rows of x
+    // operand rows are the columns of x; K runs over the rows of x.  A warp reads 32 consecutive columns of one row at a time.
     uint8_t* sf = sf_col + (static_cast<size_t>(blockIdx.x) * rblocks + blockIdx.y) * 512 + (i & 31) * 16 + (i >> 5) * 4;
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
       const int j = half * 2 + bb;
-      float v[32];
+      const __nv_bfloat16* src = tile + (j * 32) * kPitch + i;
       float amax = 0.f;
 #pragma unroll
-      for (int t = 0; t < 32; ++t) {
-        v[t] = __bfloat162float(tile[(j * 32 + t) * kPitch + i]);
-        amax = fmaxf(amax, fabsf(v[t]));
-      }
+      for (int t = 0; t < 32; ++t) amax = fmaxf(amax, fabsf(__bfloat162float(src[t * kPitch])));
       const bool live = c0 + i < C && r0 + j * 32 < R;
       const int e = live ? block_exponent(amax, fmax) : 0;
       sf[j] = static_cast<uint8_t>(e + 127);
@@ -105,7 +115,9 @@ mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
         const float inv = exp2_int(-e);
         uint32_t w[8];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) w[t] = cvt4(v[4 * t] * inv, v[4 * t + 1] * inv, v[4 * t + 2] * inv, v[4 * t + 3] * inv, fmt);
+        for (int t = 0; t < 8; ++t)
+          w[t] = cvt4(__bfloat162float(src[(4 * t) * kPitch]) * inv, __bfloat162float(src[(4 * t + 1) * kPitch]) * inv,
+                      __bfloat162float(src[(4 * t + 2) * kPitch]) * inv, __bfloat162float(src[(4 * t + 3) * kPitch]) * inv, fmt);
         uint4* dst = reinterpret_cast<uint4*>(q_col + static_cast<size_t>(c0 + i) * R + r0 + j * 32);  // R % 32 == 0
         dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
         dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -117,13 +129,13 @@ mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
 }  // namespace mxq
 }  // namespace lvb
 
-// x [R, C] bf16 (row stride ldx elements, a multiple of 4; 8-byte aligned) -> q_row [R, C] + sf_row and / or q_col [C, R] + sf_col
+// x [R, C] bf16 (C and the row stride ldx multiples of 8 elements; 16-byte aligned) -> q_row [R, C] + sf_row and / or q_col [C, R] + sf_col
 // (either pair may be null).  fmt: 0 = e4m3, 1 = e5m2.  q_row needs C % 32 == 0, q_col needs R % 32 == 0; the scale arrays have
 // lvb_mxfp8_sf_bytes(R, round_up(C, 128)) and lvb_mxfp8_sf_bytes(C, round_up(R, 128)) bytes and are written completely.
 extern "C" int lvb_mxfp8_quantize(const void* x, long long ldx, int R, int C, int fmt, void* q_row, void* sf_row, void* q_col,
                                   void* sf_col, void* stream) {
   using namespace lvb;
-  if (R <= 0 || C <= 0 || (ldx & 3) || (reinterpret_cast<uintptr_t>(x) & 7) || fmt < 0 || fmt > 1) return kErrBadArg;
+  if (R <= 0 || C <= 0 || (ldx & 7) || (C & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || fmt < 0 || fmt > 1) return kErrBadArg;
   if ((q_row == nullptr) != (sf_row == nullptr) || (q_col == nullptr) != (sf_col == nullptr)) return kErrBadArg;
   if ((q_row != nullptr && (C & 31)) || (q_col != nullptr && (R & 31))) return kErrBadArg;
   if ((reinterpret_cast<uintptr_t>(q_row) & 15) || (reinterpret_cast<uintptr_t>(q_col) & 15)) return kErrBadArg;

@@ -134,7 +134,8 @@ def mx_quantize(x2: torch.Tensor, dtype: torch.dtype, want_row: bool = True, wan
     """``x2 [R, C]`` -> ``(q_row [R, C], sf_row, q_col [C, R], sf_col)`` (``None`` for what was not asked): fp8 values with
     one scale per 32 values along C (``q_row``) or along R (``q_col``, the transpose).  One kernel on a B200."""
     R, C = x2.shape
-    if x2.is_cuda and lib.available() and x2.dtype == torch.bfloat16 and x2.stride(1) == 1 and x2.stride(0) % 4 == 0:
+    if (x2.is_cuda and lib.available() and x2.dtype == torch.bfloat16 and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and C % 8 == 0
+            and x2.data_ptr() % 16 == 0):
         c = lib
         if "mxq" not in _f:
             _f["mxq"] = lib.fn("lvb_mxfp8_quantize", [c.c_void_p, c.c_longlong, c.c_int, c.c_int, c.c_int] + [c.c_void_p] * 5)
