@@ -72,6 +72,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--bn", type=int, default=0, help="gemm_mxfp8: tile width 128 or 256 (0: chosen by the launcher)")
     ap.add_argument("--once", action="store_true", help="warm-up plus one launch (for profiler captures)")
     a = ap.parse_args(argv)
     from . import lib
@@ -109,8 +110,8 @@ def main(argv=None):
         A, sa, _, _ = mx_quantize(torch.randn(a.m, a.k, device=dev, dtype=bf), E4M3)
         B, sb, _, _ = mx_quantize(torch.randn(a.n, a.k, device=dev, dtype=bf), E4M3)
         C = torch.empty(a.m, a.n, device=dev, dtype=bf)
-        ms, mn = _time(lambda: mx_gemm(A, sa, B, sb, out=C), a.iters, a.warmup, flush)
-        return _report("gemm_mxfp8_e4m3_block32", {"m": a.m, "n": a.n, "k": a.k}, ms, mn, flops=2.0 * a.m * a.n * a.k)
+        ms, mn = _time(lambda: mx_gemm(A, sa, B, sb, out=C, bn=a.bn), a.iters, a.warmup, flush)
+        return _report("gemm_mxfp8_e4m3_block32", {"m": a.m, "n": a.n, "k": a.k, "bn": a.bn}, ms, mn, flops=2.0 * a.m * a.n * a.k)
 
     if a.kernel == "mxfp8_quant":
         from .fp8 import E4M3, mx_quantize
