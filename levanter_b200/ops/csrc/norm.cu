@@ -30,6 +30,17 @@ __device__ __forceinline__ Vec8 load8(const __nv_bfloat16* p) {
   }
   return o;
 }
+__device__ __forceinline__ Vec8 unpack8(const uint4& w) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+  Vec8 o;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = __bfloat1622float2(h[j]);
+    o.v[2 * j] = f.x;
+    o.v[2 * j + 1] = f.y;
+  }
+  return o;
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const Vec8& a) {
   uint4 o;
   o.x = pack_bf16x2(a.v[0], a.v[1]);
@@ -46,9 +57,12 @@ __device__ __forceinline__ Vec8 loadw8(const void* w, int wf32, int col, float o
     return o;
   }
   if (wf32) {
-    const float* p = reinterpret_cast<const float*>(w) + col;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o.v[j] = p[j] + offset;
+    // two 16-byte loads (col is a multiple of 8 and the array 16-byte aligned): eight scalar loads per vector made the
+    // weight reads, not the activations, the busiest traffic of the load/store unit
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + col);
+    const float4 lo = __ldg(p), hi = __ldg(p + 1);
+    o.v[0] = lo.x + offset; o.v[1] = lo.y + offset; o.v[2] = lo.z + offset; o.v[3] = lo.w + offset;
+    o.v[4] = hi.x + offset; o.v[5] = hi.y + offset; o.v[6] = hi.z + offset; o.v[7] = hi.w + offset;
   } else {
     o = load8(reinterpret_cast<const __nv_bfloat16*>(w) + col);
 #pragma unroll
@@ -146,6 +160,85 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
       for (int j = 0; j < 8; ++j) o.v[j] += bb.v[j];
     }
     store8(y + base + i * 8, o);
+  }
+}
+
+// Forward with one warp per row and the row held in registers (packed bf16: VPL 16-byte vectors per lane): every load of the
+// row is issued before anything waits, the row is read from memory once, and the reduction is five shuffles with no
+// block-wide barrier.  For dim = 256 * VPL, VPL in {1, 2, 4, 8, 16} (256 ... 4096).
+template <bool LN, int VPL, bool RES>
+__global__ void __launch_bounds__(128, 3)
+norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual, const void* __restrict__ w,
+                     const void* __restrict__ b, int wf32, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+                     float* __restrict__ rstd_out, float* __restrict__ mean_out, int rows, float eps, float w_offset) {
+  constexpr int dim = 256 * VPL;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t base = static_cast<size_t>(row) * dim;
+  uint4 v[VPL];
+#pragma unroll
+  for (int s = 0; s < VPL; ++s) v[s] = *reinterpret_cast<const uint4*>(x + base + (lane + 32 * s) * 8);
+  if constexpr (RES) {
+    uint4 r[VPL];
+#pragma unroll
+    for (int s = 0; s < VPL; ++s) r[s] = *reinterpret_cast<const uint4*>(residual + base + (lane + 32 * s) * 8);
+#pragma unroll
+    for (int s = 0; s < VPL; ++s) {
+      const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
+      const __nv_bfloat162* c = reinterpret_cast<const __nv_bfloat162*>(&r[s]);
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __bfloat1622float2(a[j]), fc = __bfloat1622float2(c[j]);
+        ow[j] = pack_bf16x2(fa.x + fc.x, fa.y + fc.y);  // normalise exactly what later layers will read
+      }
+      v[s] = o;
+      if (h_out != nullptr) *reinterpret_cast<uint4*>(h_out + base + (lane + 32 * s) * 8) = o;
+    }
+  }
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int s = 0; s < VPL; ++s) {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(a[j]);
+      s1 += f.x + f.y;
+      s2 += f.x * f.x + f.y * f.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  const float mean = LN ? s1 / dim : 0.f;
+  const float var = LN ? fmaxf(s2 / dim - mean * mean, 0.f) : s2 / dim;
+  const float rstd = rsqrtf(var + eps);
+  if (lane == 0) {
+    if (rstd_out != nullptr) rstd_out[row] = rstd;
+    if (LN && mean_out != nullptr) mean_out[row] = mean;
+  }
+#pragma unroll
+  for (int s = 0; s < VPL; ++s) {
+    const int col = (lane + 32 * s) * 8;
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
+    const Vec8 ww = loadw8(w, wf32, col, w_offset);
+    Vec8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(a[j]);
+      o.v[2 * j] = (f.x - mean) * rstd * ww.v[2 * j];
+      o.v[2 * j + 1] = (f.y - mean) * rstd * ww.v[2 * j + 1];
+    }
+    if (b != nullptr) {
+      const Vec8 bb = loadw8(b, wf32, col, 0.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.v[j] += bb.v[j];
+    }
+    store8(y + base + col, o);
   }
 }
 
@@ -285,6 +378,29 @@ extern "C" int lvb_norm_fwd(const void* x, const void* residual, const void* w, 
   auto R = reinterpret_cast<const __nv_bfloat16*>(residual);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
   auto H = reinterpret_cast<__nv_bfloat16*>(h_out);
+  {
+    const int vpl = dim / 256;
+    if (dim % 256 == 0 && (vpl == 1 || vpl == 2 || vpl == 4 || vpl == 8 || vpl == 16)) {
+      const dim3 wgrid((rows + 3) / 4);
+#define LVB_NORM_WARP(LNV, V)                                                                                                  \
+  if (R != nullptr)                                                                                                            \
+    norm_fwd_warp_kernel<LNV, V, true><<<wgrid, 128, 0, s>>>(X, R, w, b, w_is_f32, Y, H, rstd_out, mean_out, rows, eps, w_offset); \
+  else                                                                                                                         \
+    norm_fwd_warp_kernel<LNV, V, false><<<wgrid, 128, 0, s>>>(X, R, w, b, w_is_f32, Y, H, rstd_out, mean_out, rows, eps, w_offset)
+#define LVB_NORM_WARP_V(LNV)                                                                                                   \
+  switch (vpl) {                                                                                                               \
+    case 1: LVB_NORM_WARP(LNV, 1); break;                                                                                      \
+    case 2: LVB_NORM_WARP(LNV, 2); break;                                                                                      \
+    case 4: LVB_NORM_WARP(LNV, 4); break;                                                                                      \
+    case 8: LVB_NORM_WARP(LNV, 8); break;                                                                                      \
+    default: LVB_NORM_WARP(LNV, 16); break;                                                                                    \
+  }
+      if (layer_norm) { LVB_NORM_WARP_V(true) } else { LVB_NORM_WARP_V(false) }
+#undef LVB_NORM_WARP_V
+#undef LVB_NORM_WARP
+      return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+    }
+  }
   if (layer_norm)
     norm_fwd_kernel<true><<<grid, block, smem, s>>>(X, R, w, b, w_is_f32, Y, H, rstd_out, mean_out, rows, dim, eps, w_offset);
   else

@@ -58,8 +58,8 @@ def _kernel_ok(x, weight, bias) -> bool:
     if dim % 8 != 0 or dim > 16384:
         return False
     for p in (weight, bias):
-        if p is not None and p.dtype not in (torch.float32, torch.bfloat16):
-            return False
+        if p is not None and (p.dtype not in (torch.float32, torch.bfloat16) or not p.is_contiguous() or p.data_ptr() % 16 != 0):
+            return False  # the kernels read weights with 16-byte loads
     if weight is not None and bias is not None and weight.dtype != bias.dtype:
         return False
     return True
