@@ -275,8 +275,8 @@ def dot_product_attention(q, k, v, mask: Union[None, torch.Tensor, AttentionMask
                                  and mask.sliding_window is None and _structured_only(mask))
         if q.is_cuda and plain and bias is None and no_drop and logits_soft_cap is None and q.dtype in (torch.bfloat16, torch.float16) \
                 and q.shape[1] == k.shape[1]:
-            # shapes the tcgen05 kernel does not cover yet (head sizes other than 128): the library's fused attention rather
-            # than the blockwise PyTorch loop
+            # shapes the tcgen05 kernels do not cover (head sizes other than 64 and 128, cross attention): the library's fused
+            # attention rather than the blockwise PyTorch loop
             backend = AttentionBackend.SDPA
         else:
             backend = AttentionBackend.TORCH_FLASH if q.shape[1] > 1 else AttentionBackend.VANILLA

@@ -35,6 +35,22 @@ def _bwd():
     return _f["b"]
 
 
+def _fwd_hd():
+    """Head size 64 or 128, causal or not (one query tile per CTA)."""
+    if "fh" not in _f:
+        c = lib
+        _f["fh"] = lib.fn("lvb_flash_attn_fwd_hd", [c.c_void_p] * 8 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+    return _f["fh"]
+
+
+def _bwd_hd():
+    if "bh" not in _f:
+        c = lib
+        _f["bh"] = lib.fn("lvb_flash_attn_bwd_hd", [c.c_void_p] * 12 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p],
+                          launches=2)
+    return _f["bh"]
+
+
 def _bwd2():
     if "b2" not in _f:
         c = lib
@@ -79,8 +95,9 @@ def replaying_outputs(store: list):
 
 class _FlashFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None):
+    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None, causal=True):
         B, S, Hq, D = q.shape
+        general = D != 128 or not causal  # the kernels templated on the head size; the pipelined ones are causal, 128 only
         Hkv = k.shape[2]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         if _replay:
@@ -91,21 +108,26 @@ class _FlashFn(torch.autograd.Function):
             o = torch.empty_like(q)
             lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
             # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
-            fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
-            rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), lib.ptr(kblock_lo),
-                     B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(),
-                     lib.stream_ptr())
+            if general:
+                rc = _fwd_hd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+                               lib.ptr(kblock_lo) if causal else 0, B, S, Hq, Hkv, D, int(bool(causal)), float(scale), float(soft_cap or 0.0),
+                               int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
+            else:
+                fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
+                rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+                         lib.ptr(kblock_lo), B, S, Hq, Hkv, float(scale), float(soft_cap or 0.0), int(window or 0),
+                         lib.status_buffer().data_ptr(), lib.stream_ptr())
             lib.check_rc(rc, "lvb_flash_attn_fwd")
             if _keep is not None:
                 _keep.append((o, lse2))
         ctx.save_for_backward(q, k, v, o, lse2, q_seg, k_seg)
-        ctx.args = (scale, soft_cap, window)
+        ctx.args = (scale, soft_cap, window, causal, general)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse2, q_seg, k_seg = ctx.saved_tensors
-        scale, soft_cap, window = ctx.args
+        scale, soft_cap, window, causal, general = ctx.args
         B, S, Hq, D = q.shape
         Hkv = k.shape[2]
         do = do.contiguous()
@@ -115,32 +137,51 @@ class _FlashFn(torch.autograd.Function):
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-        rc = (_bwd2() if BWD_PIPELINED else _bwd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
-                    dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
-                    float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
+        if general:
+            rc = _bwd_hd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
+                           dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, D, int(bool(causal)),
+                           float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
+        else:
+            rc = (_bwd2() if BWD_PIPELINED else _bwd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
+                        dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
+                        float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_flash_attn_bwd")
-        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None
+        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None, None
+
+
+PAD_SEGMENT = -2  # segment id of the rows added to bring a sequence to a multiple of 128: they see only one another
 
 
 def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
-    """``q[B,S,Hq,128]``, ``k/v[B,S,Hkv,128]`` bf16; ``mask`` is a causal ``AttentionMask`` (optionally with a sliding
-    window and segment ids)."""
+    """``q[B,S,Hq,D]``, ``k/v[B,S,Hkv,D]`` bf16, D = 64 or 128; ``mask`` is ``None`` (every key visible) or an ``AttentionMask``
+    made of causal / sliding-window / segment-id parts.  A sequence length that is not a multiple of 128 is padded, and the
+    padding rows get a segment id of their own so that no real query sees them."""
     scale = scaling_factor if scaling_factor is not None else 1.0 / math.sqrt(q.shape[-1])
     q_seg = k_seg = None
     window = 0
+    causal = False
+    B, S = q.shape[0], q.shape[1]
     if mask is not None:
+        causal = bool(mask.is_causal)
         window = mask.sliding_window or 0
         if mask.segment_ids is not None:
             q_seg, k_seg = mask.segment_ids
-            B, S = q.shape[0], q.shape[1]
             q_seg = q_seg.to(torch.int32).expand(B, S).contiguous()
             k_seg = k_seg.to(torch.int32).expand(B, S).contiguous()
+    pad = (-S) % 128
+    if pad:
+        if q_seg is None:
+            q_seg = k_seg = torch.zeros(B, S, dtype=torch.int32, device=q.device)
+        q_seg = torch.nn.functional.pad(q_seg, (0, pad), value=PAD_SEGMENT)
+        k_seg = torch.nn.functional.pad(k_seg, (0, pad), value=PAD_SEGMENT)
+        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
     kblock_lo = None
-    if q_seg is not None and getattr(mask, "segments_sorted", False) and not torch.is_grad_enabled():
+    if q_seg is not None and causal and not pad and getattr(mask, "segments_sorted", False) and not torch.is_grad_enabled():
         # packed sequences: per block of 128 queries, the first block of 128 keys of the first query's sequence (padding ids < 0
         # sort last); the forward kernels start their key loop there instead of at the beginning of the packed batch
         big = torch.iinfo(torch.int32).max
         ks = torch.where(k_seg < 0, torch.full_like(k_seg, big), k_seg)
         qs = torch.where(q_seg < 0, torch.full_like(q_seg, big), q_seg)[:, ::128].contiguous()
         kblock_lo = (torch.searchsorted(ks, qs) // 128).to(torch.int32).contiguous()
-    return _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window, kblock_lo)
+    o = _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window, kblock_lo, causal)
+    return o[:, :S] if pad else o

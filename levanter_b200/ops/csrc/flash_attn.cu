@@ -20,7 +20,6 @@ namespace fa {
 
 constexpr int BM = 128;   // query rows per CTA
 constexpr int BN = 128;   // keys per block
-constexpr int D = 128;    // head dim
 constexpr int kThreads = 192;  // warp0 TMA, warp1 MMA, warps2-5 softmax
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KB: two 64-column chunks of [128 rows x 128 B]
 constexpr int kChunkBytes = 128 * 64 * 2;  // 16 KB
@@ -37,15 +36,18 @@ struct FwdParams {
   float scale;          // softmax scale (1/sqrt(D) by default)
   float soft_cap;       // 0 = off
   int window;           // 0 = off
+  int causal;           // 0: every key is visible (subject to segment ids); window must be 0 then
   int* status;
 };
 
-struct Smem {
-  // tiles first (1024-byte aligned), then barriers
+template <int HD>
+struct SmemT {
+  // tiles first (1024-byte aligned), then barriers.  Q, K and V tiles are [128 rows, HD] as HD / 64 chunks of 64 columns.
+  static constexpr int kQKV = 128 * HD * 2;
   static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTileBytes;
-  static constexpr int kV = kK + kKvStages * kTileBytes;
-  static constexpr int kP = kV + kKvStages * kTileBytes;
+  static constexpr int kK = kQ + kQKV;
+  static constexpr int kV = kK + kKvStages * kQKV;
+  static constexpr int kP = kV + kKvStages * kQKV;
   static constexpr int kKseg = kP + kTileBytes;           // per softmax warp: 2 x 128 ints
   static constexpr int kBars = kKseg + 4 * 2 * BN * 4;
   static constexpr int kNumBars = 1 + 4 * kKvStages + 2 + 2 + 1 + 1;
@@ -60,9 +62,14 @@ __device__ __forceinline__ uint32_t swz_off(int r, int c) {
   return chunk * kChunkBytes + r * 128 + unit * 16 + (c & 7) * 2;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+  using Smem = SmemT<HD>;
+  constexpr int D = HD;
+  constexpr int kQKV = Smem::kQKV;
+  const bool causal = p.causal != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
@@ -89,7 +96,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = qb * BM;
   // key blocks [jlo, jhi]
-  const int jhi = qb;
+  const int jhi = causal ? qb : nqb - 1;
   int jlo = 0;
   if (p.window > 0) {
     const int first_key = q0 - p.window + 1;
@@ -137,9 +144,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       const int row_q = b * p.S + q0;
-      mbar_expect_tx(q_full, kTileBytes);
-      tma_load_2d(smem + Smem::kQ, &tmQ, q_full, h * D, row_q);
-      tma_load_2d(smem + Smem::kQ + kChunkBytes, &tmQ, q_full, h * D + 64, row_q);
+      mbar_expect_tx(q_full, kQKV);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + Smem::kQ + c * kChunkBytes, &tmQ, q_full, h * D + 64 * c, row_q);
       bool ok = true;
       for (int it = 0; it < nblocks && ok; ++it) {
         const int j = jlo + it;
@@ -148,16 +155,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int row_k = b * p.S + j * BN;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 600, it);
         if (!ok) break;
-        uint8_t* ks = smem + Smem::kK + st * kTileBytes;
-        mbar_expect_tx(&k_full[st], kTileBytes);
-        tma_load_2d(ks, &tmK, &k_full[st], hkv * D, row_k);
-        tma_load_2d(ks + kChunkBytes, &tmK, &k_full[st], hkv * D + 64, row_k);
+        uint8_t* ks = smem + Smem::kK + st * kQKV;
+        mbar_expect_tx(&k_full[st], kQKV);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(ks + c * kChunkBytes, &tmK, &k_full[st], hkv * D + 64 * c, row_k);
         ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, 601, it);
         if (!ok) break;
-        uint8_t* vs = smem + Smem::kV + st * kTileBytes;
-        mbar_expect_tx(&v_full[st], kTileBytes);
-        tma_load_2d(vs, &tmV, &v_full[st], hkv * D, row_k);
-        tma_load_2d(vs + kChunkBytes, &tmV, &v_full[st], hkv * D + 64, row_k);
+        uint8_t* vs = smem + Smem::kV + st * kQKV;
+        mbar_expect_tx(&v_full[st], kQKV);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(vs + c * kChunkBytes, &tmV, &v_full[st], hkv * D + 64 * c, row_k);
       }
     }
   } else if (warp == 1) {
@@ -177,7 +184,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, 701, it)) return false;
         if (!mbar_wait(&s_empty[sb], sph ^ 1, abort_flag, p.status, 702, it)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + Smem::kK + st * kTileBytes);
+        const uint32_t sk = smem_u32(smem + Smem::kK + st * kQKV);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
@@ -202,7 +209,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = mbar_wait(p_full, it & 1, abort_flag, p.status, 704, it);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sv = smem_u32(smem + Smem::kV + st * kTileBytes);
+        const uint32_t sv = smem_u32(smem + Smem::kV + st * kQKV);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           // A = P: K-major over keys: chunk kk/4, 32 B per 16 keys inside the swizzle row
@@ -247,7 +254,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool need_mask = (j == qb) || use_seg || (p.window > 0 && k0 <= q0 + BM - 1 - p.window);
+      const bool need_mask = (causal && j == qb) || use_seg || (p.window > 0 && k0 <= q0 + BM - 1 - p.window);
       const uint32_t s_addr = tmem_S0 + lane_addr + sb * BN;
 
       // pass 1: row maximum of the scaled (and masked) logits, log2 domain
@@ -264,7 +271,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           else s *= scale_log2;
           if (need_mask) {
             const int kj = k0 + c + t;
-            bool valid = kj <= qi;
+            bool valid = !causal || kj <= qi;
             if (p.window > 0) valid = valid && (qi - kj < p.window);
             if (use_seg) valid = valid && (kseg_w[sb * BN + c + t] == my_seg);
             if (!valid) s = -INFINITY;
@@ -317,7 +324,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           else s *= scale_log2;
           if (need_mask) {
             const int kj = k0 + c + t;
-            bool valid = kj <= qi;
+            bool valid = !causal || kj <= qi;
             if (p.window > 0) valid = valid && (qi - kj < p.window);
             if (use_seg) valid = valid && (kseg_w[sb * BN + c + t] == my_seg);
             if (!valid) s = -INFINITY;
@@ -390,21 +397,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }  // namespace fa
 }  // namespace lvb
 
-// q: [B, S, Hq, 128], k/v: [B, S, Hkv, 128] (bf16, contiguous), o: [B, S, Hq, 128] bf16, lse2: [B, Hq, S] fp32.
-// S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.
-extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                  const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
-                                  int window, int* status, void* stream) {
+namespace lvb {
+namespace fa {
+template <int HD>
+int launch_fwd(const void* q, const void* k, const void* v, FwdParams p, cudaStream_t stream) {
+  using Smem = SmemT<HD>;
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t rows = static_cast<uint64_t>(p.B) * p.S;
+  int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BM, 64);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  if (rc != kErrOk) return rc;
+  auto kern = flash_fwd_kernel<HD>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) != cudaSuccess) return kErrCuda;
+    attr_set = true;
+  }
+  dim3 grid(p.S / BM, p.B * p.Hq);
+  kern<<<grid, kThreads, Smem::kTotal, stream>>>(tmQ, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+}  // namespace fa
+}  // namespace lvb
+
+// q: [B, S, Hq, D], k/v: [B, S, Hkv, D] (bf16, contiguous), o: [B, S, Hq, D] bf16, lse2: [B, Hq, S] fp32; D = head_dim is 64 or 128.
+// S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.  causal: 0 lets
+// every query see every key of its segment (encoders); window must be 0 and kblock_lo null then.
+extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
+                                     const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, int head_dim, int causal,
+                                     float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa;
   if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
-  CUtensorMap tmQ, tmK, tmV;
-  int rc = make_tmap_2d_bf16(&tmQ, q, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(Hq) * D, BM, 64);
-  if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BN, 64);
-  if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BN, 64);
-  if (rc != kErrOk) return rc;
+  if (!causal && (window != 0 || kblock_lo != nullptr)) return kErrBadArg;
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o);
   p.lse2 = lse2;
@@ -415,15 +443,17 @@ extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   p.scale = scale;
   p.soft_cap = soft_cap;
   p.window = window;
+  p.causal = causal ? 1 : 0;
   p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) != cudaSuccess)
-      return kErrCuda;
-    attr_set = true;
-  }
-  dim3 grid(S / BM, B * Hq);
-  flash_fwd_kernel<<<grid, kThreads, Smem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
-  return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 128) return launch_fwd<128>(q, k, v, p, st);
+  if (head_dim == 64) return launch_fwd<64>(q, k, v, p, st);
+  return kErrBadArg;
 }
 
+// Causal, head_dim 128 (the original entry point).
+extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
+                                  const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
+                                  int window, int* status, void* stream) {
+  return lvb_flash_attn_fwd_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
+}

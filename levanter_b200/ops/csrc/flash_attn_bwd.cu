@@ -1,11 +1,10 @@
-// Flash attention backward for sm_100a (head_dim 128, bf16): see the block comment below.
+// Flash attention backward for sm_100a (head_dim 64 or 128, bf16): see the block comment below.
 #include "common.cuh"
 
 namespace lvb {
 namespace fa {
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int D = 128;
 constexpr int kTileBytes = 128 * 128 * 2;
 constexpr int kChunkBytes = 128 * 64 * 2;
 __device__ __forceinline__ uint32_t swz_off(int r, int c) {
@@ -46,25 +45,32 @@ struct BwdParams {
   int B, S, Hq, Hkv;
   float scale, soft_cap;
   int window;
+  int causal;                  // 0: every key is visible (subject to segment ids); window must be 0 then
   int* status;
 };
 
-struct SmemB {
+template <int HD>
+struct SmemBT {
+  static constexpr int kQKV = 128 * HD * 2;  // a [128 rows, HD] tile: HD / 64 chunks of 64 columns
   static constexpr int kK = 0;
-  static constexpr int kV = kK + kTileBytes;
-  static constexpr int kQ = kV + kTileBytes;
-  static constexpr int kDO = kQ + kTileBytes;
-  static constexpr int kP = kDO + kTileBytes;
+  static constexpr int kV = kK + kQKV;
+  static constexpr int kQ = kV + kQKV;
+  static constexpr int kDO = kQ + kQKV;
+  static constexpr int kP = kDO + kQKV;
   static constexpr int kDS = kP + kTileBytes;
   static constexpr int kBars = kDS + kTileBytes;
   static constexpr int kNumBars = 7;
   static constexpr int kTotal = kBars + kNumBars * 8 + 16 + 1024;
 };
 
-template <bool kSeg, bool kCap>
+template <int HD, bool kSeg, bool kCap>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+  using SmemB = SmemBT<HD>;
+  constexpr int D = HD;
+  constexpr int kQKV = SmemB::kQKV;
+  const bool causal = p.causal != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SmemB::kBars);
@@ -86,7 +92,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int hkv = blockIdx.y % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int k0 = jb * BN;
-  const int ilo = jb;
+  const int ilo = causal ? jb : 0;
   int ihi = nqb - 1;
   if (p.window > 0) {
     const int last_q = k0 + BN - 1 + p.window - 1;
@@ -126,11 +132,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       const int row_k = b * p.S + k0;
-      mbar_expect_tx(kv_full, 2 * kTileBytes);
-      tma_load_2d(smem + SmemB::kK, &tmK, kv_full, hkv * D, row_k);
-      tma_load_2d(smem + SmemB::kK + kChunkBytes, &tmK, kv_full, hkv * D + 64, row_k);
-      tma_load_2d(smem + SmemB::kV, &tmV, kv_full, hkv * D, row_k);
-      tma_load_2d(smem + SmemB::kV + kChunkBytes, &tmV, kv_full, hkv * D + 64, row_k);
+      mbar_expect_tx(kv_full, 2 * kQKV);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_2d(smem + SmemB::kK + c * kChunkBytes, &tmK, kv_full, hkv * D + 64 * c, row_k);
+        tma_load_2d(smem + SmemB::kV + c * kChunkBytes, &tmV, kv_full, hkv * D + 64 * c, row_k);
+      }
       bool ok = true;
       for (int t = 0; t < iters && ok; ++t) {
         const int g = t / nq;
@@ -139,18 +146,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int row_q = b * p.S + i * BM;
         ok = mbar_wait(qdo_empty, (t & 1) ^ 1, abort_flag, p.status, 900, t);
         if (!ok) break;
-        mbar_expect_tx(qdo_full, 2 * kTileBytes);
-        tma_load_2d(smem + SmemB::kQ, &tmQ, qdo_full, h * D, row_q);
-        tma_load_2d(smem + SmemB::kQ + kChunkBytes, &tmQ, qdo_full, h * D + 64, row_q);
-        tma_load_2d(smem + SmemB::kDO, &tmDO, qdo_full, h * D, row_q);
-        tma_load_2d(smem + SmemB::kDO + kChunkBytes, &tmDO, qdo_full, h * D + 64, row_q);
+        mbar_expect_tx(qdo_full, 2 * kQKV);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_2d(smem + SmemB::kQ + c * kChunkBytes, &tmQ, qdo_full, h * D + 64 * c, row_q);
+          tma_load_2d(smem + SmemB::kDO + c * kChunkBytes, &tmDO, qdo_full, h * D + 64 * c, row_q);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, false, false);  // S, dP
-      constexpr uint32_t idesc_mm = make_idesc_bf16(128, 128, true, true);    // dV, dK
-      constexpr uint32_t idesc_km = make_idesc_bf16(128, 128, false, true);   // dQ
+      constexpr uint32_t idesc_mm = make_idesc_bf16(128, D, true, true);      // dV, dK: [128 keys, D]
+      constexpr uint32_t idesc_km = make_idesc_bf16(128, D, false, true);     // dQ: [128 queries, D]
       const uint32_t sK = smem_u32(smem + SmemB::kK), sV = smem_u32(smem + SmemB::kV);
       const uint32_t sQ = smem_u32(smem + SmemB::kQ), sDO = smem_u32(smem + SmemB::kDO);
       const uint32_t sP = smem_u32(smem + SmemB::kP), sDS = smem_u32(smem + SmemB::kDS);
@@ -204,9 +212,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ P / dS producers, dQ readout, dK/dV epilogue
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;      // which 64 key columns (and which 64 d columns of dQ / dK / dV)
+    const int half = (warp - 2) >> 2;      // which 64 key columns (and which D / 2 columns of dQ / dK / dV)
     const int r = quad * 32 + lane;
     const int cbase = half * 64;
+    const int dbase = half * (D / 2);
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const int* kseg_g = kSeg ? p.k_seg + b * p.S + k0 : nullptr;
@@ -228,7 +237,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool need_mask = (i == jb) || kSeg || (p.window > 0 && k0 <= i * BM + BM - 1 - p.window);
+      const bool need_mask = (causal && i == jb) || kSeg || (p.window > 0 && k0 <= i * BM + BM - 1 - p.window);
 #pragma unroll 1
       for (int c = cbase; c < cbase + 64; c += 32) {
         uint32_t sv[32], dv[32];
@@ -249,7 +258,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           float pv = exp2f(x);
           if (need_mask) {
             const int kj = k0 + c + u;
-            bool valid = kj <= qi;
+            bool valid = !causal || kj <= qi;
             if (p.window > 0) valid = valid && (qi - kj < p.window);
             if (kSeg) valid = valid && (kseg_g[c + u] == my_seg);
             pv = valid ? pv : 0.f;
@@ -278,14 +287,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
 
-      // dQ tile of this (head, query block): TMEM -> fp32 accumulator in global memory (this warp's 64 d columns)
+      // dQ tile of this (head, query block): TMEM -> fp32 accumulator in global memory (this warp's D / 2 columns)
       ok = mbar_wait(mma_done, ph, abort_flag, p.status, 1101, t);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       float* dq = p.dQ32 + (static_cast<size_t>(b) * p.S + qi) * (static_cast<size_t>(p.Hq) * D) + static_cast<size_t>(h) * D;
 #pragma unroll 1
-      for (int c = cbase; c < cbase + 64; c += 32) {
+      for (int c = dbase; c < dbase + D / 2; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_S + lane_addr + c, v);
         tmem_ld_wait();
@@ -302,7 +311,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) mbar_arrive(s_free);
     }
 
-    // epilogue: dK, dV -> bf16 (this warp's 64 d columns)
+    // epilogue: dK, dV -> bf16 (this warp's D / 2 columns)
     if (ok) {
       tc_fence_after();
       const size_t row = (static_cast<size_t>(b) * p.S + k0 + r) * (static_cast<size_t>(p.Hkv) * D) + static_cast<size_t>(hkv) * D;
@@ -311,7 +320,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + row;
         const uint32_t src = (which == 0 ? tmem_dV : tmem_dK) + lane_addr;
 #pragma unroll 1
-        for (int c = cbase; c < cbase + 64; c += 32) {
+        for (int c = dbase; c < dbase + D / 2; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(src + c, v);
           tmem_ld_wait();
@@ -337,22 +346,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h) row of 128 values
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h) row of D values
+template <int D>
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                    float* __restrict__ delta, int B, int S, int H) {
   const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long rows = static_cast<long long>(B) * S * H;
   if (row >= rows) return;
-  const uint2 a = reinterpret_cast<const uint2*>(O + row * D)[lane];
-  const uint2 g = reinterpret_cast<const uint2*>(dO + row * D)[lane];
-  const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+  constexpr int kPairs = D / 64;  // bf16 pairs per lane
   float acc = 0.f;
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    float2 x = __bfloat1622float2(ah[t]);
-    float2 y = __bfloat1622float2(gh[t]);
+  for (int t = 0; t < kPairs; ++t) {
+    const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(O + row * D)[lane * kPairs + t]);
+    const float2 y = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dO + row * D)[lane * kPairs + t]);
     acc += x.x * y.x + x.y * y.y;
   }
   acc = warp_sum(acc);
@@ -365,52 +372,34 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ O, const __
   }
 }
 
-}  // namespace fa
-}  // namespace lvb
 
-// Backward of lvb_flash_attn_fwd.  dq32: fp32 [B,S,Hq,128], must be zero on entry.  delta: fp32 [B,Hq,S] scratch.
-extern "C" int lvb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                                  const float* lse2, float* delta, float* dq32, void* dk, void* dv, const int* q_seg,
-                                  const int* k_seg, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
-                                  int window, int* status, void* stream) {
-  using namespace lvb;
-  using namespace lvb::fa;
-  if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+template <int HD>
+int launch_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, BwdParams p, cudaStream_t st) {
+  using SmemB = SmemBT<HD>;
   {
-    const long long rows = static_cast<long long>(B) * S * Hq;
+    const long long rows = static_cast<long long>(p.B) * p.S * p.Hq;
     const int block = 256;
     const long long grid = (rows * 32 + block - 1) / block;
-    flash_delta_kernel<<<static_cast<unsigned>(grid), block, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(o),
-                                                                      reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, Hq);
+    flash_delta_kernel<HD><<<static_cast<unsigned>(grid), block, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(o),
+                                                                          reinterpret_cast<const __nv_bfloat16*>(d_o),
+                                                                          const_cast<float*>(p.delta), p.B, p.S, p.Hq);
   }
   CUtensorMap tmQ, tmK, tmV, tmDO;
-  const uint64_t rows = static_cast<uint64_t>(B) * S;
-  int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(Hq) * D, BM, 64);
+  const uint64_t rows = static_cast<uint64_t>(p.B) * p.S;
+  int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BM, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmDO, d_o, rows, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(Hq) * D, BM, 64);
+  rc = make_tmap_2d_bf16(&tmDO, d_o, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BM, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BN, 64);
+  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BN, 64);
+  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
-  BwdParams p;
-  p.dQ32 = dq32;
-  p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
-  p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
-  p.lse2 = lse2;
-  p.delta = delta;
-  p.q_seg = q_seg;
-  p.k_seg = k_seg;
-  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
-  p.scale = scale; p.soft_cap = soft_cap; p.window = window;
-  p.status = status;
-  dim3 grid(S / BN, B * Hkv);
-  const bool seg = q_seg != nullptr;
-  const bool cap = soft_cap > 0.f;
+  dim3 grid(p.S / BN, p.B * p.Hkv);
+  const bool seg = p.q_seg != nullptr;
+  const bool cap = p.soft_cap > 0.f;
 #define LVB_LAUNCH_BWD(SEG, CAP)                                                                                      \
   do {                                                                                                                \
-    auto kern = flash_bwd_kernel<SEG, CAP>;                                                                           \
+    auto kern = flash_bwd_kernel<HD, SEG, CAP>;                                                                       \
     static bool attr_set = false;                                                                                     \
     if (!attr_set) {                                                                                                  \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kTotal) != cudaSuccess)      \
@@ -425,4 +414,44 @@ extern "C" int lvb_flash_attn_bwd(const void* q, const void* k, const void* v, c
   else LVB_LAUNCH_BWD(false, false);
 #undef LVB_LAUNCH_BWD
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
+}
+
+}  // namespace fa
+}  // namespace lvb
+
+// Backward of lvb_flash_attn_fwd_hd.  dq32: fp32 [B,S,Hq,D], must be zero on entry.  delta: fp32 [B,Hq,S] scratch.  D = head_dim
+// is 64 or 128; causal as in the forward.
+extern "C" int lvb_flash_attn_bwd_hd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                     const float* lse2, float* delta, float* dq32, void* dk, void* dv, const int* q_seg,
+                                     const int* k_seg, int B, int S, int Hq, int Hkv, int head_dim, int causal, float scale,
+                                     float soft_cap, int window, int* status, void* stream) {
+  using namespace lvb;
+  using namespace lvb::fa;
+  if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
+  if (!causal && window != 0) return kErrBadArg;
+  BwdParams p;
+  p.dQ32 = dq32;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.lse2 = lse2;
+  p.delta = delta;
+  p.q_seg = q_seg;
+  p.k_seg = k_seg;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale = scale; p.soft_cap = soft_cap; p.window = window;
+  p.causal = causal ? 1 : 0;
+  p.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 128) return launch_bwd<128>(q, k, v, o, d_o, p, st);
+  if (head_dim == 64) return launch_bwd<64>(q, k, v, o, d_o, p, st);
+  return kErrBadArg;
+}
+
+// Causal, head_dim 128 (the original entry point).
+extern "C" int lvb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                  const float* lse2, float* delta, float* dq32, void* dk, void* dv, const int* q_seg,
+                                  const int* k_seg, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
+                                  int window, int* status, void* stream) {
+  return lvb_flash_attn_bwd_hd(q, k, v, o, d_o, lse2, delta, dq32, dk, dv, q_seg, k_seg, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window,
+                               status, stream);
 }

@@ -1,4 +1,5 @@
-"""Causal flash attention on tcgen05 tensor cores (``csrc/flash_attn.cu``): GQA, sliding window, segment ids.
+"""Flash attention on tcgen05 tensor cores (``csrc/flash_attn*.cu``): head sizes 64 and 128, causal (with sliding window) or
+not, GQA, segment ids, any sequence length (padded to a multiple of 128 behind a segment id of its own).
 
 Replaces the reference's fused-attention call sites (TransformerEngine/cuDNN on GPU, src/levanter/layers/attention.py:
 533-544; pure-JAX flash attention, src/levanter/models/flash_attention.py:143-385)."""
@@ -30,15 +31,13 @@ def supported(q, k, v, mask, bias, no_dropout: bool, attention_dtype) -> bool:
         return False
     if attention_dtype is not None and attention_dtype not in (torch.float32, torch.bfloat16):
         return False
-    if q.shape[-1] != 128 or v.shape[-1] != 128:
+    if q.shape[-1] not in (64, 128) or v.shape[-1] != q.shape[-1] or k.shape[-1] != q.shape[-1]:
         return False
-    if q.shape[1] != k.shape[1] or q.shape[1] % 128 != 0:
-        return False
+    if q.shape[1] != k.shape[1]:
+        return False  # cross attention (different query and key lengths) is not on the kernel path
     if mask is not None and not isinstance(mask, AttentionMask):
         return False
-    if isinstance(mask, AttentionMask) and not mask.is_causal:
-        return False
-    if mask is None:
+    if isinstance(mask, AttentionMask) and not mask.is_causal and mask.sliding_window:
         return False
     return _structured_only(mask)
 

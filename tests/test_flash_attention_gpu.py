@@ -18,10 +18,10 @@ def _close(a, b, tol):
     assert err / scale < tol, f"rel err {err / scale}"
 
 
-def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0, growing=False):
+def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0, growing=False, D=128):
     torch.manual_seed(seed)
-    q = torch.randn(B, S, Hq, 128, device="cuda")
-    k = torch.randn(B, S, Hkv, 128, device="cuda")
+    q = torch.randn(B, S, Hq, D, device="cuda")
+    k = torch.randn(B, S, Hkv, D, device="cuda")
     if growing:
         # logits whose row maximum jumps by far more than the lazy-rescale threshold in later key blocks, and only for
         # some rows of a warp: the running output must be rescaled mid-row, row by row
@@ -29,7 +29,7 @@ def _run(B, S, Hq, Hkv, mask, soft_cap=None, seed=0, growing=False):
         k[:, 256:] *= 2.0
         q[:, 1::3] *= 4.0
     q, k = q.bfloat16().requires_grad_(), k.bfloat16().requires_grad_()
-    v = torch.randn(B, S, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
     o = flash_attention_cuda(q, k, v, mask, logits_soft_cap=soft_cap)
     g = torch.randn_like(o)
     o.backward(g)
@@ -139,3 +139,43 @@ def test_packed_sequences_skip_foreign_key_blocks(S):
     lib.check_status()
     live = seg >= 0
     assert torch.equal(hint[:, live], plain[:, live])
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 12, 12), (1, 1024, 4, 1), (2, 384, 4, 2)])
+def test_head_size_64_causal(B, S, Hq, Hkv):
+    """GPT-2's and Whisper's head size on the kernels templated on the head dimension."""
+    _run(B, S, Hq, Hkv, AttentionMask.causal(), D=64)
+
+
+def test_head_size_64_running_max_sliding_window_soft_cap_segments():
+    _run(1, 512, 2, 2, AttentionMask.causal(), growing=True, D=64)
+    _run(1, 640, 2, 1, AttentionMask.causal(sliding_window=200), D=64)
+    _run(1, 256, 2, 2, AttentionMask.causal(), soft_cap=30.0, D=64)
+    seg = torch.tensor([[0] * 100 + [1] * 200 + [2] * 84], device="cuda")
+    _run(1, 384, 2, 2, AttentionMask.causal().with_segment_ids(seg), D=64)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 2, 2), (2, 512, 4, 2), (1, 384, 6, 6)])
+def test_not_causal(B, S, Hq, Hkv, D):
+    """Encoder attention: every query sees every key (``mask=None``), or every key of its own segment."""
+    _run(B, S, Hq, Hkv, None, D=D)
+    seg = torch.arange(S, device="cuda").div(S // 3 + 1, rounding_mode="floor").expand(B, S)
+    _run(B, S, Hq, Hkv, AttentionMask(is_causal=False).with_segment_ids(seg), D=D, seed=1)
+
+
+@pytest.mark.parametrize("D,S,causal", [(64, 1500, False), (64, 200, True), (128, 200, True), (128, 333, False), (64, 77, False)])
+def test_lengths_that_are_not_a_multiple_of_128_are_padded_behind_their_own_segment(D, S, causal):
+    """Whisper's encoder runs 1500 positions: the rows added to reach 1536 must be invisible to the real ones."""
+    _run(1, S, 2, 2, AttentionMask.causal() if causal else None, D=D)
+
+
+def test_dispatch_takes_head_size_64_and_encoder_masks():
+    from levanter_b200.ops import flash_attention as KFA
+
+    q = torch.randn(1, 256, 2, 64, device="cuda").bfloat16()
+    assert KFA.supported(q, q, q, None, None, True, None)
+    assert KFA.supported(q, q, q, AttentionMask.causal(), None, True, None)
+    assert not KFA.supported(q, q[:, :128], q[:, :128], None, None, True, None)  # cross attention
+    q96 = torch.randn(1, 256, 2, 96, device="cuda").bfloat16()
+    assert not KFA.supported(q96, q96, q96, None, None, True, None)
