@@ -72,6 +72,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--head-dim", type=int, default=128, help="flash attention: 64 or 128")
+    ap.add_argument("--not-causal", action="store_true", help="flash attention: every key visible (encoder attention)")
+    ap.add_argument("--sdpa", action="store_true", help="flash attention: time the library's fused attention instead (comparison row)")
     ap.add_argument("--bn", type=int, default=0, help="gemm_mxfp8: tile width 128 or 256 (0: chosen by the launcher)")
     ap.add_argument("--once", action="store_true", help="warm-up plus one launch (for profiler captures)")
     a = ap.parse_args(argv)
@@ -126,17 +129,31 @@ def main(argv=None):
         from ._flash_impl import flash_attention_cuda
 
         kvh = a.kv_heads or a.heads
-        q = torch.randn(a.batch, a.seq, a.heads, 128, device=dev, dtype=bf, requires_grad=True)
-        k = torch.randn(a.batch, a.seq, kvh, 128, device=dev, dtype=bf, requires_grad=True)
-        v = torch.randn(a.batch, a.seq, kvh, 128, device=dev, dtype=bf, requires_grad=True)
-        mask = AttentionMask.causal()
-        causal_flops = 4.0 * a.batch * a.heads * a.seq * a.seq * 128 / 2
-        cfg = {"batch": a.batch, "seq": a.seq, "heads": a.heads, "kv_heads": kvh, "head_dim": 128, "causal": True}
+        hd = a.head_dim
+        q = torch.randn(a.batch, a.seq, a.heads, hd, device=dev, dtype=bf, requires_grad=True)
+        k = torch.randn(a.batch, a.seq, kvh, hd, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(a.batch, a.seq, kvh, hd, device=dev, dtype=bf, requires_grad=True)
+        causal = not a.not_causal
+        mask = AttentionMask.causal() if causal else None
+        causal_flops = 4.0 * a.batch * a.heads * a.seq * a.seq * hd / (2 if causal else 1)
+        cfg = {"batch": a.batch, "seq": a.seq, "heads": a.heads, "kv_heads": kvh, "head_dim": hd, "causal": causal, "impl": "library sdpa" if a.sdpa else "own"}
+        if a.sdpa:
+            # the library's fused attention on the same tensors (the comparison row; not this framework's kernel)
+            import torch.nn.functional as F
+
+            rep = a.heads // kvh
+
+            def attn(q, k, v):
+                kk, vv = (k.repeat_interleave(rep, 2), v.repeat_interleave(rep, 2)) if rep > 1 else (k, v)
+                return F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=causal).transpose(1, 2)
+        else:
+            def attn(q, k, v):
+                return flash_attention_cuda(q, k, v, mask)
         if a.kernel == "flash_fwd":
             with torch.no_grad():
-                ms, mn = _time(lambda: flash_attention_cuda(q, k, v, mask), a.iters, a.warmup, flush)
+                ms, mn = _time(lambda: attn(q, k, v), a.iters, a.warmup, flush)
             return _report("flash_attention_fwd", cfg, ms, mn, flops=causal_flops)
-        o = flash_attention_cuda(q, k, v, mask)
+        o = attn(q, k, v)
         g = torch.randn_like(o)
         ms, mn = _time(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), a.iters, a.warmup, flush)
         return _report("flash_attention_bwd", cfg, ms, mn, flops=2.5 * causal_flops)

@@ -63,8 +63,11 @@ def test_mixtral_block_uses_the_grouped_path_and_matches_cpu():
         mg = m.to("cuda").to(torch.bfloat16)
         got = mg.activations(ids.cuda())
         got = got[0] if isinstance(got, tuple) else got
-    err = (got.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
-    assert err < 5e-2, err
+    # per token: bf16 rounding in attention can flip a near-tie of the router for an odd token, which changes that token's
+    # output wholesale; every other token must agree closely
+    tok_err = (got.float().cpu() - ref).abs().amax(-1) / ref.abs().max().item()
+    assert tok_err.median().item() < 1e-2, tok_err.median().item()
+    assert (tok_err > 5e-2).float().mean().item() <= 0.05, tok_err
 
 
 @pytest.mark.parametrize("T,E,k", [(1000, 8, 2), (77, 16, 4), (5, 3, 1)])
