@@ -43,6 +43,14 @@ def _fwd_hd():
     return _f["fh"]
 
 
+def _fwd2_hd():
+    """Head size 64 or 128, causal or not, two query tiles per CTA (S a multiple of 256)."""
+    if "f2h" not in _f:
+        c = lib
+        _f["f2h"] = lib.fn("lvb_flash_attn_fwd2_hd", [c.c_void_p] * 8 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+    return _f["f2h"]
+
+
 def _bwd_hd():
     if "bh" not in _f:
         c = lib
@@ -109,7 +117,7 @@ class _FlashFn(torch.autograd.Function):
             lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
             # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
             if general:
-                rc = _fwd_hd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
+                rc = (_fwd2_hd() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd_hd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
                                lib.ptr(kblock_lo) if causal else 0, B, S, Hq, Hkv, D, int(bool(causal)), float(scale), float(soft_cap or 0.0),
                                int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
             else:
@@ -149,12 +157,12 @@ class _FlashFn(torch.autograd.Function):
         return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None, None
 
 
-PAD_SEGMENT = -2  # segment id of the rows added to bring a sequence to a multiple of 128: they see only one another
+PAD_SEGMENT = -2  # segment id of the rows added to bring a sequence to a multiple of 256: they see only one another
 
 
 def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
     """``q[B,S,Hq,D]``, ``k/v[B,S,Hkv,D]`` bf16, D = 64 or 128; ``mask`` is ``None`` (every key visible) or an ``AttentionMask``
-    made of causal / sliding-window / segment-id parts.  A sequence length that is not a multiple of 128 is padded, and the
+    made of causal / sliding-window / segment-id parts.  A sequence length that is not a multiple of 256 is padded, and the
     padding rows get a segment id of their own so that no real query sees them."""
     scale = scaling_factor if scaling_factor is not None else 1.0 / math.sqrt(q.shape[-1])
     q_seg = k_seg = None
@@ -168,7 +176,7 @@ def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = No
             q_seg, k_seg = mask.segment_ids
             q_seg = q_seg.to(torch.int32).expand(B, S).contiguous()
             k_seg = k_seg.to(torch.int32).expand(B, S).contiguous()
-    pad = (-S) % 128
+    pad = (-S) % 256  # the two-tile forward kernel wants 256; the one-tile kernel (any multiple of 128) is far slower
     if pad:
         if q_seg is None:
             q_seg = k_seg = torch.zeros(B, S, dtype=torch.int32, device=q.device)

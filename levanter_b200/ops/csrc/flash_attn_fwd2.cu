@@ -16,7 +16,6 @@ namespace lvb {
 namespace fa2 {
 
 constexpr int BT = 128;            // rows per query tile, keys per block
-constexpr int D = 128;
 constexpr int kThreads = 320;      // warp0 TMA, warp1 MMA, warps 2-5 tile A, warps 6-9 tile B
 constexpr int kTileBytes = 128 * 128 * 2;
 constexpr int kChunkBytes = 128 * 64 * 2;
@@ -33,14 +32,17 @@ struct Params {
   int B, S, Hq, Hkv;
   float scale, soft_cap;
   int window;
+  int causal;  // 0: every key is visible (subject to segment ids); window must be 0 and kblock_lo null then
   int* status;
 };
 
-struct Smem {
+template <int HD>
+struct SmemT {
+  static constexpr int kQKV = 128 * HD * 2;                   // a [128 rows, HD] tile: HD / 64 chunks of 64 columns
   static constexpr int kQ = 0;                                // 2 tiles
-  static constexpr int kK = kQ + 2 * kTileBytes;
-  static constexpr int kV = kK + kStages * kTileBytes;
-  static constexpr int kBars = kV + kStages * kTileBytes;
+  static constexpr int kK = kQ + 2 * kQKV;
+  static constexpr int kV = kK + kStages * kQKV;
+  static constexpr int kBars = kV + kStages * kQKV;
   static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2;
   static constexpr int kTotal = kBars + kNumBars * 8 + 16 + 1024;
 };
@@ -51,10 +53,14 @@ __device__ __forceinline__ float to_log2(float s, float scale_log2, float scale,
   else return s * scale_log2;
 }
 
-template <bool kSeg, bool kCap>
+template <int HD, bool kSeg, bool kCap>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, Params p) {
+  using Smem = SmemT<HD>;
+  constexpr int D = HD;
+  constexpr int kQKV = Smem::kQKV;
+  const bool causal = p.causal != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
@@ -77,7 +83,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int h = blockIdx.y % p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = cb * 2 * BT;
-  const int jdiagA = 2 * cb, jdiagB = 2 * cb + 1;
+  // without the causal part there is no diagonal block (the mask test below never matches -1) and both tiles see every block
+  const int jdiagA = causal ? 2 * cb : -1, jdiagB = causal ? 2 * cb + 1 : -1;
   int jlo = 0;
   if (p.window > 0) {
     const int first_key = q0 - p.window + 1;
@@ -88,8 +95,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int lo = p.kblock_lo[b * (p.S / BT) + jdiagA];
     jlo = max(jlo, min(lo, jdiagA));
   }
-  const int nB = jdiagB - jlo + 1;   // blocks processed by tile B
-  const int nA = nB - 1;             // tile A stops one block earlier (its diagonal)
+  const int nB = (causal ? jdiagB : p.S / BT - 1) - jlo + 1;  // blocks processed by tile B
+  const int nA = causal ? nB - 1 : nB;                        // causal: tile A stops one block earlier (its diagonal)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -123,12 +130,12 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const int row_q = b * p.S + q0;
-      mbar_expect_tx(q_full, 2 * kTileBytes);
+      mbar_expect_tx(q_full, 2 * kQKV);
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        tma_load_2d(smem + Smem::kQ + t * kTileBytes, &tmQ, q_full, h * D, row_q + t * BT);
-        tma_load_2d(smem + Smem::kQ + t * kTileBytes + kChunkBytes, &tmQ, q_full, h * D + 64, row_q + t * BT);
-      }
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(smem + Smem::kQ + t * kQKV + c * kChunkBytes, &tmQ, q_full, h * D + 64 * c, row_q + t * BT);
       bool ok = true;
       for (int it = 0; it < nB && ok; ++it) {
         const int st = it % kStages;
@@ -136,16 +143,16 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int row_k = b * p.S + (jlo + it) * BT;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 1200, it);
         if (!ok) break;
-        uint8_t* ks = smem + Smem::kK + st * kTileBytes;
-        mbar_expect_tx(&k_full[st], kTileBytes);
-        tma_load_2d(ks, &tmK, &k_full[st], hkv * D, row_k);
-        tma_load_2d(ks + kChunkBytes, &tmK, &k_full[st], hkv * D + 64, row_k);
+        uint8_t* ks = smem + Smem::kK + st * kQKV;
+        mbar_expect_tx(&k_full[st], kQKV);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(ks + c * kChunkBytes, &tmK, &k_full[st], hkv * D + 64 * c, row_k);
         ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, 1201, it);
         if (!ok) break;
-        uint8_t* vs = smem + Smem::kV + st * kTileBytes;
-        mbar_expect_tx(&v_full[st], kTileBytes);
-        tma_load_2d(vs, &tmV, &v_full[st], hkv * D, row_k);
-        tma_load_2d(vs + kChunkBytes, &tmV, &v_full[st], hkv * D + 64, row_k);
+        uint8_t* vs = smem + Smem::kV + st * kQKV;
+        mbar_expect_tx(&v_full[st], kQKV);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(vs + c * kChunkBytes, &tmV, &v_full[st], hkv * D + 64 * c, row_k);
       }
     }
   } else if (warp == 1) {
@@ -158,8 +165,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
       auto qk = [&](int tile, int it) {
         const int st = it % kStages;
-        const uint32_t sk = smem_u32(smem + Smem::kK + st * kTileBytes);
-        const uint32_t sqt = sq + tile * kTileBytes;
+        const uint32_t sk = smem_u32(smem + Smem::kK + st * kQKV);
+        const uint32_t sqt = sq + tile * kQKV;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
@@ -170,7 +177,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       };
       auto pv = [&](int tile, int it) {
         const int st = it % kStages;
-        const uint32_t sv = smem_u32(smem + Smem::kV + st * kTileBytes);
+        const uint32_t sv = smem_u32(smem + Smem::kV + st * kQKV);
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk) {
           // 16 keys of P = 8 TMEM columns; 16 keys of V = two 8-row groups = 2048 B
@@ -255,7 +262,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
             const int kj = k0 + c + t;
-            bool valid = kj <= qi;
+            bool valid = !causal || kj <= qi;
             if (p.window > 0) valid = valid && (qi - kj < p.window);
             if (kSeg) valid = valid && (kseg_row[kj] == my_seg);
             if (!valid) v[t] = __float_as_uint(-INFINITY);
@@ -308,7 +315,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
             const int kj = k0 + c + t;
-            bool valid = kj <= qi;
+            bool valid = !causal || kj <= qi;
             if (p.window > 0) valid = valid && (qi - kj < p.window);
             if (kSeg) valid = valid && (kseg_row[kj] == my_seg);
             const float x = kCap ? to_log2<kCap>(__uint_as_float(v[t]), scale_log2, p.scale, p.soft_cap) + neg_m
@@ -377,9 +384,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
 }
 
-template <bool kSeg, bool kCap>
+template <int HD, bool kSeg, bool kCap>
 int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const Params& p, cudaStream_t st) {
-  auto kern = flash_fwd2_kernel<kSeg, kCap>;
+  using Smem = SmemT<HD>;
+  auto kern = flash_fwd2_kernel<HD, kSeg, kCap>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) != cudaSuccess) return kErrCuda;
@@ -393,21 +401,37 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
 }  // namespace fa2
 }  // namespace lvb
 
-// Same contract as lvb_flash_attn_fwd, but S must be a multiple of 256.
-extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                   const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
-                                   int window, int* status, void* stream) {
+namespace lvb {
+namespace fa2 {
+template <int HD>
+int launch_hd(const void* q, const void* k, const void* v, const Params& p, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t rows = static_cast<uint64_t>(p.B) * p.S;
+  int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BT, 64);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
+  if (rc != kErrOk) return rc;
+  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
+  if (rc != kErrOk) return rc;
+  const bool seg = p.q_seg != nullptr;
+  const bool cap = p.soft_cap > 0.f;
+  if (seg && cap) return launch<HD, true, true>(tmQ, tmK, tmV, p, st);
+  if (seg) return launch<HD, true, false>(tmQ, tmK, tmV, p, st);
+  if (cap) return launch<HD, false, true>(tmQ, tmK, tmV, p, st);
+  return launch<HD, false, false>(tmQ, tmK, tmV, p, st);
+}
+}  // namespace fa2
+}  // namespace lvb
+
+// Same contract as lvb_flash_attn_fwd_hd (head_dim 64 or 128, causal or not), but S must be a multiple of 256: two query
+// tiles per CTA.
+extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
+                                      const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, int head_dim, int causal,
+                                      float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa2;
   if (B <= 0 || S <= 0 || (S % (2 * BT)) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
-  CUtensorMap tmQ, tmK, tmV;
-  const uint64_t rows = static_cast<uint64_t>(B) * S;
-  int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(Hq) * D, BT, 64);
-  if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BT, 64);
-  if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, BT, 64);
-  if (rc != kErrOk) return rc;
+  if (!causal && (window != 0 || kblock_lo != nullptr)) return kErrBadArg;
   Params p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o);
   p.lse2 = lse2;
@@ -416,12 +440,17 @@ extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   p.kblock_lo = kblock_lo;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.soft_cap = soft_cap; p.window = window;
+  p.causal = causal ? 1 : 0;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool seg = q_seg != nullptr;
-  const bool cap = soft_cap > 0.f;
-  if (seg && cap) return launch<true, true>(tmQ, tmK, tmV, p, st);
-  if (seg) return launch<true, false>(tmQ, tmK, tmV, p, st);
-  if (cap) return launch<false, true>(tmQ, tmK, tmV, p, st);
-  return launch<false, false>(tmQ, tmK, tmV, p, st);
+  if (head_dim == 128) return launch_hd<128>(q, k, v, p, st);
+  if (head_dim == 64) return launch_hd<64>(q, k, v, p, st);
+  return kErrBadArg;
+}
+
+// Causal, head_dim 128 (the original entry point).
+extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
+                                   const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
+                                   int window, int* status, void* stream) {
+  return lvb_flash_attn_fwd2_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
 }

@@ -165,7 +165,7 @@ def test_not_causal(B, S, Hq, Hkv, D):
 
 
 @pytest.mark.parametrize("D,S,causal", [(64, 1500, False), (64, 200, True), (128, 200, True), (128, 333, False), (64, 77, False)])
-def test_lengths_that_are_not_a_multiple_of_128_are_padded_behind_their_own_segment(D, S, causal):
+def test_lengths_that_are_not_a_multiple_of_256_are_padded_behind_their_own_segment(D, S, causal):
     """Whisper's encoder runs 1500 positions: the rows added to reach 1536 must be invisible to the real ones."""
     _run(1, S, 2, 2, AttentionMask.causal() if causal else None, D=D)
 
@@ -179,3 +179,14 @@ def test_dispatch_takes_head_size_64_and_encoder_masks():
     assert not KFA.supported(q, q[:, :128], q[:, :128], None, None, True, None)  # cross attention
     q96 = torch.randn(1, 256, 2, 96, device="cuda").bfloat16()
     assert not KFA.supported(q96, q96, q96, None, None, True, None)
+
+
+@pytest.mark.parametrize("D,causal", [(64, True), (64, False), (128, False)])
+def test_one_tile_forward_kernel_covers_the_same_cases(D, causal):
+    from levanter_b200.ops import _flash_impl
+
+    _flash_impl._FORCE_ONE_TILE = True
+    try:
+        _run(1, 512, 2, 1, AttentionMask.causal() if causal else None, D=D)
+    finally:
+        _flash_impl._FORCE_ONE_TILE = False
