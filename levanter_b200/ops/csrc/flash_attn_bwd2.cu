@@ -269,6 +269,19 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sDST = sPT + kPTile;
     const uint32_t tmem_ST = tmem_base + wg * 128, tmem_dPT = tmem_ST + 64;
     bool ok = true;
+    // The per-query statistics of a step (64 x {-lse, delta, segment id}) are fetched one step of this warpgroup ahead into a
+    // register per thread, so the global-memory latency is not paid between the two barriers that open a step.
+    float pre_stat = 0.f;
+    int pre_seg = 0;
+    auto fetch_stats = [&](int tt) {
+      if (tt >= iters) return;
+      const int hh = hkv * G + tt / nq;
+      const int qq = (ilo + (tt % nq)) * BQ;
+      const size_t stat = (static_cast<size_t>(b) * p.Hq + hh) * p.S + qq;
+      pre_stat = (wtid < 64) ? p.lse2[stat + wtid] : p.delta[stat + wtid - 64];
+      if (kSeg && wtid < 64) pre_seg = p.q_seg[b * p.S + qq + wtid];
+    };
+    fetch_stats(wg);
     for (int t = wg; t < iters; t += 2) {
       const uint32_t n = static_cast<uint32_t>(t >> 1);
       const int g = t / nq;
@@ -279,14 +292,15 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // ran out clears `ok` and the work is skipped), or the others would wait for it for ever.
       wg_bar_sync(wg);  // the previous step no longer reads the statistics, and its dQ tile has been handed to the TMA unit
       if (ok) {
-        const size_t stat = (static_cast<size_t>(b) * p.Hq + h) * p.S + q0;
         if (wtid < 64) {
-          const float l = p.lse2[stat + wtid];
-          s_lse[wtid] = (l == -INFINITY) ? -INFINITY : -l;
+          s_lse[wtid] = (pre_stat == -INFINITY) ? -INFINITY : -pre_stat;
         } else {
-          s_dlt[wtid - 64] = p.delta[stat + wtid - 64];
+          s_dlt[wtid - 64] = pre_stat;
         }
-        if (kSeg && wtid < 64) s_qseg[wtid] = p.q_seg[b * p.S + q0 + wtid];
+        if (kSeg && wtid < 64) s_qseg[wtid] = pre_seg;
+        fetch_stats(t + 2);
+        // the bulk reduction of the previous step must have read its tile before this step's P^T / dS^T overwrite it
+        if (wtid == 0) bulk_wait_read<0>();
       }
       wg_bar_sync(wg);
       if (ok) {
@@ -373,8 +387,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                          reinterpret_cast<uint64_t>(&tmDQ)),
                      "r"(smem_u32(sPT)), "r"(h * D), "r"(b * p.S + q0)
                      : "memory");
-        bulk_commit();
-        bulk_wait_read<0>();  // the tile is overwritten two steps later, after the barrier at the top of the loop
+        bulk_commit();  // waited for (read side) at the top of this warpgroup's next step
       }
     }
     if (wtid == 0) bulk_wait<0>();  // every reduction of this warpgroup has been performed before the CTA leaves

@@ -30,14 +30,19 @@ def zeropower_via_newtonschulz5(X: torch.Tensor, steps: int = 5, eps: float = 1e
         X = X.t()
     use_kernel = X.is_cuda and lib.available() and X.shape[0] % 8 == 0 and X.shape[1] % 8 == 0
     if use_kernel:
-        Xb = X.contiguous().to(torch.bfloat16)
+        # Three GEMMs per iteration and nothing between them: the polynomial's coefficients ride in the epilogues (alpha and
+        # the residual operand).  With the iterate kept as X = s Xs:
+        #   A   = s^2 Xs Xs^T                       alpha = s^2
+        #   B'  = A + (c / b) A A                   alpha = c / b, residual A          (the true B is b B')
+        #   Xs' = Xs + (b / a) B' Xs                alpha = b / a, residual Xs         (a X + B X = a s Xs'),   s' = a s
+        Xs = X.contiguous().to(torch.bfloat16)
+        s = 1.0
         for _ in range(steps):
-            A = gemm(Xb, Xb)                                   # X X^T   [m, m]
-            A2 = gemm(A, A, b_mn=True, out_dtype=torch.float32)  # A A (A is symmetric; read as [K, N])
-            Bm = (_B * A.float() + _C * A2).to(torch.bfloat16)
-            BX = gemm(Bm, Xb, b_mn=True, out_dtype=torch.float32)  # B X
-            Xb = (_A * Xb.float() + BX).to(torch.bfloat16)
-        X = Xb.float()
+            A = gemm(Xs, Xs, alpha=s * s)                                 # [m, m]
+            Bp = gemm(A, A, b_mn=True, alpha=_C / _B, residual=A)         # A is symmetric; read as [K, N]
+            Xs = gemm(Bp, Xs, b_mn=True, alpha=_B / _A, residual=Xs)      # [m, n]
+            s *= _A
+        X = Xs.float() * s
     else:
         for _ in range(steps):
             A = X @ X.t()
