@@ -230,9 +230,21 @@ class TensorParallel:
         from ..ops.gemm import PAIR_ENABLED
 
         T, N = x2.shape[0], w.shape[0]
-        return bool(self.comm in ("auto", "p2p", "multimem") and not self._sym_failed and x2.is_cuda and lib.available() and PAIR_ENABLED
-                    and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 < self.size <= 8 and T % (self.size * 32) == 0
-                    and T >= 2048 and N > 128 and N % 8 == 0 and x2.shape[1] % 8 == 0)
+        if not torch.is_grad_enabled():
+            # inference: prefill batches come in ever-changing token counts, and the staging arena keeps arrival counters
+            # per distinct shape; those calls take the all-reduce after a plain GEMM
+            return False
+        ok = bool(self.comm in ("auto", "p2p", "multimem") and not self._sym_failed and x2.is_cuda and lib.available() and PAIR_ENABLED
+                  and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 < self.size <= 8 and T % (self.size * 32) == 0
+                  and T >= 2048 and N > 128 and N % 8 == 0 and x2.shape[1] % 8 == 0)
+        if ok:
+            st = self.__dict__.get("_rs")
+            if st is not None and st["arena"] is not None and (T, N) not in st["cnt"] and (T * N + 63) // 64 * 64 <= st["area"]:
+                from ..ops.fused_tp import rs_counters
+
+                n = (rs_counters(T // self.size, N) + 63) // 64 * 64
+                ok = st["cnt_next"] + 2 * n <= st["cnt_cap"]  # no room for another shape's counters: the plain path
+        return ok
 
     def matmul_all_reduce(self, x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """``sum over ranks of x2 @ w.T`` on every rank (``x2 [T, K_local]``, ``w [N, K_local]``): the row-parallel projection of a
