@@ -69,7 +69,11 @@ def _kernel_worker(rank, world, port, out_dir):
         lib.check_status()
         res["gather_on_gemm"] = all(torch.equal(sp.param.data, full0[sp.name]) for sp in st.by_layer[2])
         res["units_on_gemms"] = st.stats["units_on_gemms"]
+        from levanter_b200.ops import gemm as G
+
+        G.SPLITK_MODE = "general"  # the product that carried the job ran whole-K tiles: compare with the same tiling, bit for bit
         res["gemm_with_job_ok"] = bool(torch.equal(c, gemm(a, b)))
+        G.SPLITK_MODE = "splitk"
         # ---- weight gradients: dy^T x summed over the ranks, this rank's rows, accumulated over two calls
         g = torch.Generator(device=dev).manual_seed(10 + rank)
         errs = []
