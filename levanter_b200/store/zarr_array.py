@@ -187,6 +187,10 @@ class ZarrArray:
     @staticmethod
     def open(path: str) -> "ZarrArray":
         fs, root = url_to_fs(path.rstrip("/"))
+        if not fs.exists(f"{root}/.zarray") and fs.exists(f"{root}/zarr.json"):
+            from .zarr3_array import Zarr3Array  # an array written by the reference (zarr v3, sharded, blosc): read-only
+
+            return Zarr3Array.open(path)
         meta = None
         for attempt in range(50):  # a writer on a file system without atomic rename may be in the middle of rewriting the file
             try:
@@ -204,7 +208,7 @@ class ZarrArray:
     @staticmethod
     def exists(path: str) -> bool:
         fs, root = url_to_fs(path.rstrip("/"))
-        return fs.exists(f"{root}/.zarray")
+        return fs.exists(f"{root}/.zarray") or fs.exists(f"{root}/zarr.json")
 
     def _write_chunk(self, key: str, blob: bytes) -> None:
         """Chunk files are replaced, never rewritten in place: a concurrent reader sees the old chunk or the new one."""

@@ -1,0 +1,170 @@
+"""Reading the reference's cache arrays: zarr v3, ``sharding_indexed`` shards of blosc-compressed inner chunks.
+
+No zarr / blosc / tensorstore library is installed, so the test writes the bytes itself from the formats' specifications:
+blosc frames (header, block offsets, split streams, byte shuffle) around LZ4 blocks and zstd frames produced by pyarrow's
+codecs (an encoder this framework does not share), shard files with their index and CRC-32C, and ``zarr.json``."""
+import json
+import math
+import os
+import struct
+
+import numpy as np
+import pyarrow as pa
+import pytest
+
+from levanter_b200.store.zarr3_array import Zarr3Array, blosc_decompress_many, crc32c
+from levanter_b200.store.zarr_array import ZarrArray
+
+
+def _blosc_frame(data: bytes, typesize: int, blocksize: int, *, shuffle=True, codec="lz4", split=True, stored=False) -> bytes:
+    nbytes = len(data)
+    flags = (1 if shuffle else 0) | ((0 if split else 1) << 4) | ({"lz4": 1, "zstd": 4}[codec] << 5)
+    if stored:
+        return struct.pack("<BBBBIII", 2, 1, flags | 2, typesize, nbytes, blocksize, 16 + nbytes) + data
+    nblocks = math.ceil(nbytes / blocksize)
+    bodies = []
+    for i in range(nblocks):
+        b = data[i * blocksize:(i + 1) * blocksize]
+        leftover = len(b) != blocksize
+        if shuffle and typesize > 1:
+            nel = len(b) // typesize
+            b = np.frombuffer(b[:nel * typesize], np.uint8).reshape(nel, typesize).T.copy().tobytes() + b[nel * typesize:]
+        nsplits = typesize if (split and typesize <= 16 and blocksize // typesize >= 128 and not leftover) else 1
+        ne = len(b) // nsplits
+        out = b""
+        for s in range(nsplits):
+            stream = b[s * ne:(s + 1) * ne]
+            c = pa.compress(stream, codec="lz4_raw" if codec == "lz4" else "zstd", asbytes=True)
+            out += struct.pack("<I", ne) + stream if len(c) >= ne else struct.pack("<I", len(c)) + c
+        bodies.append(out)
+    starts, pos = [], 16 + 4 * nblocks
+    for b in bodies:
+        starts.append(pos)
+        pos += len(b)
+    return struct.pack("<BBBBIII", 2, 1, flags, typesize, nbytes, blocksize, pos) + struct.pack(f"<{nblocks}I", *starts) + b"".join(bodies)
+
+
+def test_crc32c_known_vector():
+    assert crc32c(b"123456789") == 0xE3069283
+    assert crc32c(b"") == 0
+
+
+@pytest.mark.parametrize("codec", ["lz4", "zstd"])
+@pytest.mark.parametrize("typesize,blocksize,n", [(4, 4096, 10000), (8, 1024, 1024), (2, 512, 3001), (1, 256, 1000), (4, 64, 300)])
+def test_blosc_frames_decode(codec, typesize, blocksize, n):
+    rng = np.random.default_rng(n)
+    data = (rng.integers(0, 50, n) * 3).astype({1: np.uint8, 2: np.uint16, 4: np.int32, 8: np.int64}[typesize]).tobytes()
+    data = data[: len(data) - (len(data) % 3 if typesize > 1 and n == 3001 else 0)]  # a tail shorter than an element
+    frames = [_blosc_frame(data, typesize, blocksize, codec=codec),
+              _blosc_frame(data, typesize, blocksize, codec=codec, shuffle=False),
+              _blosc_frame(data, typesize, blocksize, codec=codec, split=False),
+              _blosc_frame(data, typesize, blocksize, codec=codec, stored=True)]
+    for got in blosc_decompress_many(frames):
+        assert got.tobytes() == data
+    with pytest.raises(ValueError):
+        blosc_decompress_many([frames[0][:40]])
+
+
+def _write_sharded(path, arr: np.ndarray, nominal_shape, shard, inner, *, skip=(), codec="lz4"):
+    os.makedirs(path, exist_ok=True)
+    meta = {"zarr_format": 3, "node_type": "array", "shape": list(nominal_shape), "data_type": str(arr.dtype),
+            "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": list(shard)}},
+            "chunk_key_encoding": {"name": "default"}, "fill_value": 0, "attributes": {},
+            "codecs": [{"name": "sharding_indexed", "configuration": {
+                "chunk_shape": list(inner),
+                "codecs": [{"name": "bytes", "configuration": {"endian": "little"}},
+                           {"name": "blosc", "configuration": {"cname": codec, "clevel": 5, "shuffle": "shuffle",
+                                                               "typesize": arr.dtype.itemsize, "blocksize": 0}}],
+                "index_codecs": [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "crc32c"}],
+                "index_location": "end"}}]}
+    with open(os.path.join(path, "zarr.json"), "w") as f:
+        json.dump(meta, f)
+    per = [s // i for s, i in zip(shard, inner)]
+    n_shards = [math.ceil(a / s) for a, s in zip(arr.shape, shard)]
+    for sidx in np.ndindex(*n_shards):
+        body, index = b"", []
+        for iidx in np.ndindex(*per):
+            lo = [si * s + ii * i for si, s, ii, i in zip(sidx, shard, iidx, inner)]
+            if any(l >= a for l, a in zip(lo, arr.shape)) or (tuple(sidx), tuple(iidx)) in skip:
+                index.append((2 ** 64 - 1, 2 ** 64 - 1))
+                continue
+            chunk = np.zeros(inner, dtype=arr.dtype)
+            sl = tuple(slice(l, min(l + i, a)) for l, i, a in zip(lo, inner, arr.shape))
+            part = arr[sl]
+            chunk[tuple(slice(0, p) for p in part.shape)] = part
+            frame = _blosc_frame(chunk.tobytes(), arr.dtype.itemsize, 2048, codec=codec)
+            index.append((len(body), len(frame)))
+            body += frame
+        raw = b"".join(struct.pack("<QQ", o, n) for o, n in index)
+        key = os.path.join(path, "c", *[str(i) for i in sidx])
+        os.makedirs(os.path.dirname(key), exist_ok=True)
+        with open(key, "wb") as f:
+            f.write(body + raw + struct.pack("<I", crc32c(raw)))
+
+
+def test_sharded_blosc_array_reads_regions_and_missing_chunks(tmp_path):
+    rng = np.random.default_rng(0)
+    arr = rng.integers(0, 1000, (5000, 3), dtype=np.int32)
+    p = str(tmp_path / "a")
+    _write_sharded(p, arr, (2 ** 54, 3), shard=(2048, 3), inner=(512, 3), skip={((1,  0), (2, 0))})
+    z = ZarrArray.open(p)  # the common entry point recognises the v3 metadata
+    assert isinstance(z, Zarr3Array) and z.shape == [2 ** 54, 3] and z.chunks == [2048, 3] and z.inner == [512, 3]
+    want = arr.copy()
+    want[2048 + 1024: 2048 + 1536] = 0  # the inner chunk that was never written reads as the fill value
+    for lo, hi in [(0, 5000), (100, 700), (2040, 2060), (3000, 3700), (4999, 5000), (5000, 5600)]:
+        got = z.read([lo, 0], [hi, 3])
+        ref = np.zeros((hi - lo, 3), np.int32)
+        n = max(0, min(hi, 5000) - lo)
+        ref[:n] = want[lo:lo + n]
+        assert np.array_equal(got, ref), (lo, hi)
+    assert np.array_equal(z.read([10, 1], [20, 2]), want[10:20, 1:2])
+    with pytest.raises(NotImplementedError):
+        z.write(np.zeros((1, 3), np.int32), [0, 0])
+    # a flipped byte in the index is caught by its checksum
+    shard = os.path.join(p, "c", "0", "0")
+    raw = bytearray(open(shard, "rb").read())
+    raw[-10] ^= 1
+    open(shard, "wb").write(bytes(raw))
+    with pytest.raises(ValueError):
+        z.read([0, 0], [10, 3])
+
+
+def test_jagged_store_opens_a_cache_in_the_reference_layout(tmp_path):
+    """``offsets`` (``offsets[0]`` = number of rows, then the end of every row) and ``data`` as sharded zarr v3 arrays."""
+    from levanter_b200.store.jagged_array import JaggedArrayStore
+
+    rng = np.random.default_rng(1)
+    rows = [rng.integers(0, 50000, int(n), dtype=np.int32) for n in rng.integers(1, 400, 300)]
+    data = np.concatenate(rows)
+    offsets = np.concatenate([[len(rows)], np.cumsum([len(r) for r in rows])]).astype(np.int64)
+    _write_sharded(str(tmp_path / "offsets"), offsets, (2 ** 54,), shard=(1024,), inner=(256,), codec="lz4")
+    _write_sharded(str(tmp_path / "data"), data, (2 ** 54,), shard=(16384,), inner=(4096,), codec="zstd")
+    store = JaggedArrayStore.open(str(tmp_path), mode="r", dtype=np.int32)
+    assert store.num_rows == 300 and store.data_size == len(data)
+    for i in (0, 1, 17, 299):
+        assert np.array_equal(store[i], rows[i])
+    batch = store.get_batch_sync([5, 250, 6]) if hasattr(store, "get_batch_sync") else [store[j] for j in (5, 250, 6)]
+    for got, j in zip(batch, (5, 250, 6)):
+        assert np.array_equal(got, rows[j])
+
+
+def test_tree_cache_loads_a_finished_cache_in_the_reference_layout(tmp_path):
+    """A whole cache directory as the reference leaves it: ``shard_ledger.json`` plus ``<field>/{offsets,data}`` in zarr v3."""
+    from levanter_b200.store.cache import TreeCache
+
+    rng = np.random.default_rng(2)
+    rows = [rng.integers(0, 32000, int(n), dtype=np.int32) for n in rng.integers(5, 200, 64)]
+    data = np.concatenate(rows)
+    offsets = np.concatenate([[len(rows)], np.cumsum([len(r) for r in rows])]).astype(np.int64)
+    cache_dir = tmp_path / "cache" / "train"
+    _write_sharded(str(cache_dir / "input_ids" / "offsets"), offsets, (2 ** 54,), shard=(1024,), inner=(256,))
+    _write_sharded(str(cache_dir / "input_ids" / "data"), data, (2 ** 54,), shard=(8192,), inner=(2048,))
+    ledger = {"total_num_rows": len(rows), "shard_rows": {"shard_0": len(rows)}, "is_finished": True, "finished_shards": ["shard_0"],
+              "field_counts": {"input_ids": len(data)}, "metadata": {"preprocessor_metadata": {"tokenizer": "x"}}}
+    with open(cache_dir / "shard_ledger.json", "w") as f:
+        json.dump(ledger, f)
+    cache = TreeCache.load(str(cache_dir), {"input_ids": np.zeros((0,), dtype=np.int32)})
+    assert len(cache) == len(rows)
+    got = cache.get_batch_sync([0, 63, 31])
+    for g, j in zip(got, (0, 63, 31)):
+        assert np.array_equal(g["input_ids"], rows[j])
