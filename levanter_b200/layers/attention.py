@@ -306,6 +306,12 @@ def dot_product_attention_with_sink(q, k, v, sink: torch.Tensor, mask=None, bias
     the bias at that column (src/levanter/layers/attention.py:244-326).  ``sink``: ``[Hq]``."""
     B, Sq, H, D = q.shape
     Sk = k.shape[1]
+    from ..ops import flash_attention as KFA
+
+    if (kw.get("dropout", 0.0) == 0.0 or kw.get("inference", False)) and KFA.supported(q, k, v, mask, bias, True, kw.get("attention_dtype")):
+        # the fused kernel takes the sink as one more term of the softmax denominator
+        return KFA.flash_attention(q, k, v, mask, logits_soft_cap=kw.get("logits_soft_cap"), scaling_factor=kw.get("scaling_factor"),
+                                   sink=sink)
     zk = torch.zeros(B, 1, k.shape[2], D, dtype=k.dtype, device=k.device)
     k2 = torch.cat([k, zk], dim=1)
     v2 = torch.cat([v, torch.zeros_like(zk)], dim=1)

@@ -39,7 +39,7 @@ def _fwd_hd():
     """Head size 64 or 128, causal or not (one query tile per CTA)."""
     if "fh" not in _f:
         c = lib
-        _f["fh"] = lib.fn("lvb_flash_attn_fwd_hd", [c.c_void_p] * 8 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["fh"] = lib.fn("lvb_flash_attn_fwd_hd", [c.c_void_p] * 9 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["fh"]
 
 
@@ -47,7 +47,7 @@ def _fwd2_hd():
     """Head size 64 or 128, causal or not, two query tiles per CTA (S a multiple of 256)."""
     if "f2h" not in _f:
         c = lib
-        _f["f2h"] = lib.fn("lvb_flash_attn_fwd2_hd", [c.c_void_p] * 8 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["f2h"] = lib.fn("lvb_flash_attn_fwd2_hd", [c.c_void_p] * 9 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["f2h"]
 
 
@@ -103,9 +103,11 @@ def replaying_outputs(store: list):
 
 class _FlashFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None, causal=True):
+    def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None, causal=True, sink=None):
         B, S, Hq, D = q.shape
-        general = D != 128 or not causal  # the kernels templated on the head size; the pipelined ones are causal, 128 only
+        general = D != 128 or not causal  # the kernels templated on the head size; the pipelined backward is causal, 128 only
+        if sink is not None:
+            sink = sink.detach().float().contiguous()
         Hkv = k.shape[2]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         if _replay:
@@ -116,10 +118,10 @@ class _FlashFn(torch.autograd.Function):
             o = torch.empty_like(q)
             lse2 = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
             # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
-            if general:
+            if general or sink is not None:
                 rc = (_fwd2_hd() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd_hd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
-                               lib.ptr(kblock_lo) if causal else 0, B, S, Hq, Hkv, D, int(bool(causal)), float(scale), float(soft_cap or 0.0),
-                               int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
+                               lib.ptr(kblock_lo) if causal else 0, lib.ptr(sink), B, S, Hq, Hkv, D, int(bool(causal)), float(scale),
+                               float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
             else:
                 fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
                 rc = fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
@@ -128,13 +130,13 @@ class _FlashFn(torch.autograd.Function):
             lib.check_rc(rc, "lvb_flash_attn_fwd")
             if _keep is not None:
                 _keep.append((o, lse2))
-        ctx.save_for_backward(q, k, v, o, lse2, q_seg, k_seg)
+        ctx.save_for_backward(q, k, v, o, lse2, q_seg, k_seg, sink)
         ctx.args = (scale, soft_cap, window, causal, general)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse2, q_seg, k_seg = ctx.saved_tensors
+        q, k, v, o, lse2, q_seg, k_seg, sink = ctx.saved_tensors
         scale, soft_cap, window, causal, general = ctx.args
         B, S, Hq, D = q.shape
         Hkv = k.shape[2]
@@ -154,16 +156,23 @@ class _FlashFn(torch.autograd.Function):
                         dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, float(scale),
                         float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
         lib.check_rc(rc, "lvb_flash_attn_bwd")
-        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None, None
+        dsink = None
+        if sink is not None and ctx.needs_input_grad[10]:
+            # the sink column's probability is 2^(sink log2 e - lse2); its value row is zero, so its logit's gradient is
+            # -p_sink * delta summed over batch and queries (delta = rowsum(dO * O), left in the scratch by the kernel)
+            dsink = -(torch.exp2(sink.view(1, Hq, 1) * 1.4426950408889634 - lse2) * delta).sum(dim=(0, 2))
+        return dq32.to(torch.bfloat16), dk, dv, None, None, None, None, None, None, None, dsink
 
 
 PAD_SEGMENT = -2  # segment id of the rows added to bring a sequence to a multiple of 256: they see only one another
 
 
-def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
+def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None,
+                         sink: Optional[torch.Tensor] = None):
     """``q[B,S,Hq,D]``, ``k/v[B,S,Hkv,D]`` bf16, D = 64 or 128; ``mask`` is ``None`` (every key visible) or an ``AttentionMask``
     made of causal / sliding-window / segment-id parts.  A sequence length that is not a multiple of 256 is padded, and the
-    padding rows get a segment id of their own so that no real query sees them."""
+    padding rows get a segment id of their own so that no real query sees them.  ``sink [Hq]``: a learned logit per head that
+    joins the softmax denominator (a key column whose value row is zero)."""
     scale = scaling_factor if scaling_factor is not None else 1.0 / math.sqrt(q.shape[-1])
     q_seg = k_seg = None
     window = 0
@@ -191,5 +200,5 @@ def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = No
         ks = torch.where(k_seg < 0, torch.full_like(k_seg, big), k_seg)
         qs = torch.where(q_seg < 0, torch.full_like(q_seg, big), q_seg)[:, ::128].contiguous()
         kblock_lo = (torch.searchsorted(ks, qs) // 128).to(torch.int32).contiguous()
-    o = _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window, kblock_lo, causal)
+    o = _FlashFn.apply(q, k, v, q_seg, k_seg, scale, logits_soft_cap, window, kblock_lo, causal, sink)
     return o[:, :S] if pad else o

@@ -32,6 +32,7 @@ struct FwdParams {
   const int* q_seg;     // [B, S] or null
   const int* k_seg;     // [B, S] or null
   const int* kblock_lo; // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
+  const float* sink;    // optional [Hq]: a learned logit per head that takes part in the softmax denominator only
   int B, S, Hq, Hkv;
   float scale;          // softmax scale (1/sqrt(D) by default)
   float soft_cap;       // 0 = off
@@ -365,7 +366,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (ok) {
       tc_fence_after();
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      float o_scale = 1.f;
+      if (p.sink != nullptr) {  // one more softmax column with a zero value row: see flash_attn_fwd2.cu
+        const float s2 = p.sink[h] * 1.4426950408889634f;
+        const float m_new = fmaxf(m_used, s2);
+        o_scale = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        l_sum = l_sum * o_scale + exp2f(s2 - m_new);
+        m_used = m_new;
+      }
+      const float inv = l_sum > 0.f ? o_scale / l_sum : 0.f;
       __nv_bfloat16* orow = p.O + (static_cast<size_t>(b) * p.S + qi) * (static_cast<size_t>(p.Hq) * D) + static_cast<size_t>(h) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
@@ -424,11 +433,12 @@ int launch_fwd(const void* q, const void* k, const void* v, FwdParams p, cudaStr
 }  // namespace lvb
 
 // q: [B, S, Hq, D], k/v: [B, S, Hkv, D] (bf16, contiguous), o: [B, S, Hq, D] bf16, lse2: [B, Hq, S] fp32; D = head_dim is 64 or 128.
-// S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.  causal: 0 lets
+// S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.  sink: fp32 [Hq] or
+// null (a learned logit per head added to the softmax denominator).  causal: 0 lets
 // every query see every key of its segment (encoders); window must be 0 and kblock_lo null then.
 extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                     const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, int head_dim, int causal,
-                                     float scale, float soft_cap, int window, int* status, void* stream) {
+                                     const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Hq, int Hkv,
+                                     int head_dim, int causal, float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa;
   if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
@@ -439,6 +449,7 @@ extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v
   p.q_seg = q_seg;
   p.k_seg = k_seg;
   p.kblock_lo = kblock_lo;
+  p.sink = sink;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale;
   p.soft_cap = soft_cap;
@@ -455,5 +466,5 @@ extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v
 extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
                                   const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                   int window, int* status, void* stream) {
-  return lvb_flash_attn_fwd_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
+  return lvb_flash_attn_fwd_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
 }

@@ -29,6 +29,7 @@ struct Params {
   const int* q_seg;
   const int* k_seg;
   const int* kblock_lo;  // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
+  const float* sink;     // optional [Hq]: a learned logit per head that takes part in the softmax denominator only
   int B, S, Hq, Hkv;
   float scale, soft_cap;
   int window;
@@ -355,7 +356,18 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     if (ok) {
       tc_fence_after();
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      float o_scale = 1.f;
+      if (p.sink != nullptr) {
+        // The sink is one more column of the softmax whose value row is zero: it enters the denominator (and the saved
+        // log-sum-exp) and nothing else.  If it raises the reference maximum from m to m', the accumulated output and sum
+        // (both relative to m) shrink by a = 2^(m - m').
+        const float s2 = p.sink[h] * kLog2e;
+        const float m_new = fmaxf(m_used, s2);
+        o_scale = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        l_sum = l_sum * o_scale + exp2f(s2 - m_new);
+        m_used = m_new;
+      }
+      const float inv = l_sum > 0.f ? o_scale / l_sum : 0.f;
       __nv_bfloat16* orow = p.O + (static_cast<size_t>(b) * p.S + qi) * (static_cast<size_t>(p.Hq) * D) + static_cast<size_t>(h) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
@@ -423,11 +435,11 @@ int launch_hd(const void* q, const void* k, const void* v, const Params& p, cuda
 }  // namespace fa2
 }  // namespace lvb
 
-// Same contract as lvb_flash_attn_fwd_hd (head_dim 64 or 128, causal or not), but S must be a multiple of 256: two query
-// tiles per CTA.
+// Same contract as lvb_flash_attn_fwd_hd (head_dim 64 or 128, causal or not, optional sink logits [Hq]), but S must be a
+// multiple of 256: two query tiles per CTA.
 extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                      const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, int head_dim, int causal,
-                                      float scale, float soft_cap, int window, int* status, void* stream) {
+                                      const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Hq, int Hkv,
+                                      int head_dim, int causal, float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa2;
   if (B <= 0 || S <= 0 || (S % (2 * BT)) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
@@ -438,6 +450,7 @@ extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* 
   p.q_seg = q_seg;
   p.k_seg = k_seg;
   p.kblock_lo = kblock_lo;
+  p.sink = sink;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.soft_cap = soft_cap; p.window = window;
   p.causal = causal ? 1 : 0;
@@ -452,5 +465,5 @@ extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* 
 extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
                                    const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                    int window, int* status, void* stream) {
-  return lvb_flash_attn_fwd2_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
+  return lvb_flash_attn_fwd2_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
 }

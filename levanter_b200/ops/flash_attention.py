@@ -42,7 +42,7 @@ def supported(q, k, v, mask, bias, no_dropout: bool, attention_dtype) -> bool:
     return _structured_only(mask)
 
 
-def flash_attention(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None):
+def flash_attention(q, k, v, mask, *, logits_soft_cap: Optional[float] = None, scaling_factor: Optional[float] = None, sink=None):
     from ._flash_impl import flash_attention_cuda
 
-    return flash_attention_cuda(q, k, v, mask, logits_soft_cap=logits_soft_cap, scaling_factor=scaling_factor)
+    return flash_attention_cuda(q, k, v, mask, logits_soft_cap=logits_soft_cap, scaling_factor=scaling_factor, sink=sink)

@@ -190,3 +190,33 @@ def test_one_tile_forward_kernel_covers_the_same_cases(D, causal):
         _run(1, 512, 2, 1, AttentionMask.causal() if causal else None, D=D)
     finally:
         _flash_impl._FORCE_ONE_TILE = False
+
+
+@pytest.mark.parametrize("D,S,causal,Hq,Hkv", [(128, 512, True, 4, 2), (64, 256, True, 2, 2), (128, 200, False, 2, 1)])
+def test_sink_logits_join_the_denominator(D, S, causal, Hq, Hkv):
+    from levanter_b200.layers.attention import dot_product_attention_with_sink
+
+    torch.manual_seed(0)
+    q = torch.randn(2, S, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(2, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(2, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    sink = (torch.randn(Hq, device="cuda") * 2).requires_grad_()
+    mask = AttentionMask.causal() if causal else None
+    o = flash_attention_cuda(q, k, v, mask, sink=sink)
+    g = torch.randn_like(o)
+    o.backward(g)
+    torch.cuda.synchronize()
+    lib.check_status()
+    qr, kr, vr = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    sr = sink.detach().clone().requires_grad_()
+    with lib.reference_ops():
+        orf = dot_product_attention_with_sink(qr, kr, vr, sr, mask, attention_dtype=torch.float32)
+    orf.backward(g.float())
+    _close(o, orf, 2e-2)
+    _close(q.grad, qr.grad, 4e-2)
+    _close(k.grad, kr.grad, 4e-2)
+    _close(v.grad, vr.grad, 4e-2)
+    _close(sink.grad, sr.grad, 4e-2)
+    # the module-level entry point takes the kernel path
+    o2 = dot_product_attention_with_sink(q, k, v, sink, mask)
+    assert torch.equal(o2, o)
