@@ -339,13 +339,33 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
   }
 }
 
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int nparts, int dim,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
-  float s = 0.f;
-  for (int r = 0; r < nparts; ++r) s += part[static_cast<size_t>(r) * dim + c];
-  out[c] = accumulate ? out[c] + s : s;
+// out[c] (+)= sum over the partial rows.  A block owns 32 columns; its 8 thread rows each sum every 8th partial row (four
+// independent accumulators, so the loads overlap) and are then added in a fixed order: deterministic, and a few hundred
+// partial rows cost tens of loads per thread instead of one dependent chain of all of them.
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int nparts, int dim, int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < dim) {
+    int r = ty;
+    for (; r + 24 < nparts; r += 32) {
+      a0 += part[static_cast<size_t>(r) * dim + c];
+      a1 += part[static_cast<size_t>(r + 8) * dim + c];
+      a2 += part[static_cast<size_t>(r + 16) * dim + c];
+      a3 += part[static_cast<size_t>(r + 24) * dim + c];
+    }
+    for (; r < nparts; r += 8) a0 += part[static_cast<size_t>(r) * dim + c];
+  }
+  sm[ty][tx] = (a0 + a1) + (a2 + a3);
+  __syncthreads();
+  if (ty == 0 && c < dim) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += sm[j][tx];
+    out[c] = accumulate ? out[c] + s : s;
+  }
 }
 
 inline void pick_block(int dim, int& TX, int& TY) {
@@ -452,8 +472,7 @@ extern "C" int lvb_norm_bwd(const void* dy, const void* x, const void* w, int w_
     else if (vpt <= 4) LVB_NORM_BWD(false, 4); else LVB_NORM_BWD(false, 8);
   }
 #undef LVB_NORM_BWD
-  const int rb = 256;
-  if (dw != nullptr) norm_bwd_reduce_kernel<<<(dim + rb - 1) / rb, rb, 0, s>>>(dw_part, dw, nparts, dim, accumulate);
-  if (db != nullptr) norm_bwd_reduce_kernel<<<(dim + rb - 1) / rb, rb, 0, s>>>(db_part, db, nparts, dim, accumulate);
+  if (dw != nullptr) norm_bwd_reduce_kernel<<<(dim + 31) / 32, 256, 0, s>>>(dw_part, dw, nparts, dim, accumulate);
+  if (db != nullptr) norm_bwd_reduce_kernel<<<(dim + 31) / 32, 256, 0, s>>>(db_part, db, nparts, dim, accumulate);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
