@@ -39,7 +39,7 @@ def _fwd_hd():
     """Head size 64 or 128, causal or not (one query tile per CTA)."""
     if "fh" not in _f:
         c = lib
-        _f["fh"] = lib.fn("lvb_flash_attn_fwd_hd", [c.c_void_p] * 9 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["fh"] = lib.fn("lvb_flash_attn_fwd_hd", [c.c_void_p] * 9 + [c.c_int] * 7 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["fh"]
 
 
@@ -47,14 +47,14 @@ def _fwd2_hd():
     """Head size 64 or 128, causal or not, two query tiles per CTA (S a multiple of 256)."""
     if "f2h" not in _f:
         c = lib
-        _f["f2h"] = lib.fn("lvb_flash_attn_fwd2_hd", [c.c_void_p] * 9 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
+        _f["f2h"] = lib.fn("lvb_flash_attn_fwd2_hd", [c.c_void_p] * 9 + [c.c_int] * 7 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p])
     return _f["f2h"]
 
 
 def _bwd_hd():
     if "bh" not in _f:
         c = lib
-        _f["bh"] = lib.fn("lvb_flash_attn_bwd_hd", [c.c_void_p] * 12 + [c.c_int] * 6 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p],
+        _f["bh"] = lib.fn("lvb_flash_attn_bwd_hd", [c.c_void_p] * 12 + [c.c_int] * 7 + [c.c_float, c.c_float, c.c_int, c.c_void_p, c.c_void_p],
                           launches=2)
     return _f["bh"]
 
@@ -105,6 +105,7 @@ class _FlashFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, q_seg, k_seg, scale, soft_cap, window, kblock_lo=None, causal=True, sink=None):
         B, S, Hq, D = q.shape
+        Sk = k.shape[1]  # differs from S only for cross attention (no causal part)
         general = D != 128 or not causal  # the kernels templated on the head size; the pipelined backward is causal, 128 only
         if sink is not None:
             sink = sink.detach().float().contiguous()
@@ -120,7 +121,7 @@ class _FlashFn(torch.autograd.Function):
             # two query tiles per CTA when the sequence allows it; the one-tile kernel covers the remaining lengths
             if general or sink is not None:
                 rc = (_fwd2_hd() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd_hd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg),
-                               lib.ptr(kblock_lo) if causal else 0, lib.ptr(sink), B, S, Hq, Hkv, D, int(bool(causal)), float(scale),
+                               lib.ptr(kblock_lo) if causal else 0, lib.ptr(sink), B, S, Sk, Hq, Hkv, D, int(bool(causal)), float(scale),
                                float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
             else:
                 fwd = _fwd2() if (S % 256 == 0 and not _FORCE_ONE_TILE) else _fwd()
@@ -149,7 +150,7 @@ class _FlashFn(torch.autograd.Function):
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
         if general:
             rc = _bwd_hd()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
-                           dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, Hq, Hkv, D, int(bool(causal)),
+                           dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), lib.ptr(q_seg), lib.ptr(k_seg), B, S, k.shape[1], Hq, Hkv, D, int(bool(causal)),
                            float(scale), float(soft_cap or 0.0), int(window or 0), lib.status_buffer().data_ptr(), lib.stream_ptr())
         else:
             rc = (_bwd2() if BWD_PIPELINED else _bwd())(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(), delta.data_ptr(),
@@ -177,21 +178,28 @@ def flash_attention_cuda(q, k, v, mask, *, logits_soft_cap: Optional[float] = No
     q_seg = k_seg = None
     window = 0
     causal = False
-    B, S = q.shape[0], q.shape[1]
+    B, S, Sk = q.shape[0], q.shape[1], k.shape[1]
     if mask is not None:
         causal = bool(mask.is_causal)
         window = mask.sliding_window or 0
         if mask.segment_ids is not None:
             q_seg, k_seg = mask.segment_ids
             q_seg = q_seg.to(torch.int32).expand(B, S).contiguous()
-            k_seg = k_seg.to(torch.int32).expand(B, S).contiguous()
-    pad = (-S) % 256  # the two-tile forward kernel wants 256; the one-tile kernel (any multiple of 128) is far slower
-    if pad:
+            k_seg = k_seg.to(torch.int32).expand(B, Sk).contiguous()
+    if causal and Sk != S:
+        raise ValueError("a causal mask needs as many keys as queries")
+    # queries to a multiple of 256 (the two-tile forward kernel; the one-tile kernel takes any multiple of 128 but is far slower),
+    # keys to a multiple of 128, or of 256 with the queries when the lengths are tied by a causal mask
+    pad = (-S) % 256
+    pad_k = pad if Sk == S else (-Sk) % 128
+    if pad or pad_k:
         if q_seg is None:
-            q_seg = k_seg = torch.zeros(B, S, dtype=torch.int32, device=q.device)
+            q_seg = torch.zeros(B, S, dtype=torch.int32, device=q.device)
+            k_seg = torch.zeros(B, Sk, dtype=torch.int32, device=q.device)
         q_seg = torch.nn.functional.pad(q_seg, (0, pad), value=PAD_SEGMENT)
-        k_seg = torch.nn.functional.pad(k_seg, (0, pad), value=PAD_SEGMENT)
-        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        k_seg = torch.nn.functional.pad(k_seg, (0, pad_k), value=PAD_SEGMENT)
+        q = torch.nn.functional.pad(q, (0, 0, 0, 0, 0, pad))
+        k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad_k)) for t in (k, v))
     kblock_lo = None
     if q_seg is not None and causal and not pad and getattr(mask, "segments_sorted", False) and not torch.is_grad_enabled():
         # packed sequences: per block of 128 queries, the first block of 128 keys of the first query's sequence (padding ids < 0

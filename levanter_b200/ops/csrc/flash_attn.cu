@@ -33,7 +33,8 @@ struct FwdParams {
   const int* k_seg;     // [B, S] or null
   const int* kblock_lo; // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
   const float* sink;    // optional [Hq]: a learned logit per head that takes part in the softmax denominator only
-  int B, S, Hq, Hkv;
+  int B, S, Hq, Hkv;    // S: query positions per sequence
+  int Sk;               // key positions per sequence (= S unless the mask has no causal part)
   float scale;          // softmax scale (1/sqrt(D) by default)
   float soft_cap;       // 0 = off
   int window;           // 0 = off
@@ -97,7 +98,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = qb * BM;
   // key blocks [jlo, jhi]
-  const int jhi = causal ? qb : nqb - 1;
+  const int jhi = causal ? qb : p.Sk / BN - 1;
   int jlo = 0;
   if (p.window > 0) {
     const int first_key = q0 - p.window + 1;
@@ -153,7 +154,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int j = jlo + it;
         const int st = it % kKvStages;
         const uint32_t ph = (it / kKvStages) & 1;
-        const int row_k = b * p.S + j * BN;
+        const int row_k = b * p.Sk + j * BN;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 600, it);
         if (!ok) break;
         uint8_t* ks = smem + Smem::kK + st * kQKV;
@@ -248,7 +249,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (use_seg) {
         // stage this block's key segment ids (double-buffered by block parity)
 #pragma unroll
-        for (int t = 0; t < BN / 32; ++t) kseg_w[sb * BN + t * 32 + lane] = p.k_seg[b * p.S + k0 + t * 32 + lane];
+        for (int t = 0; t < BN / 32; ++t) kseg_w[sb * BN + t * 32 + lane] = p.k_seg[b * p.Sk + k0 + t * 32 + lane];
         __syncwarp();
       }
       ok = mbar_wait(&s_full[sb], sph, abort_flag, p.status, 800, it);
@@ -415,9 +416,10 @@ int launch_fwd(const void* q, const void* k, const void* v, FwdParams p, cudaStr
   const uint64_t rows = static_cast<uint64_t>(p.B) * p.S;
   int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BM, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  const uint64_t rows_k = static_cast<uint64_t>(p.B) * p.Sk;
+  rc = make_tmap_2d_bf16(&tmK, k, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  rc = make_tmap_2d_bf16(&tmV, v, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
   auto kern = flash_fwd_kernel<HD>;
   static bool attr_set = false;
@@ -434,15 +436,17 @@ int launch_fwd(const void* q, const void* k, const void* v, FwdParams p, cudaStr
 
 // q: [B, S, Hq, D], k/v: [B, S, Hkv, D] (bf16, contiguous), o: [B, S, Hq, D] bf16, lse2: [B, Hq, S] fp32; D = head_dim is 64 or 128.
 // S must be a multiple of 128.  q_seg/k_seg: int32 [B, S] or null.  window: 0 = none.  soft_cap: 0 = none.  sink: fp32 [Hq] or
-// null (a learned logit per head added to the softmax denominator).  causal: 0 lets
+// null (a learned logit per head added to the softmax denominator).  Sk: keys per sequence, a multiple of 128 (k / v are
+// [B, Sk, Hkv, D], k_seg [B, Sk]); equal to S when causal.  causal: 0 lets
 // every query see every key of its segment (encoders); window must be 0 and kblock_lo null then.
 extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                     const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Hq, int Hkv,
+                                     const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Sk, int Hq, int Hkv,
                                      int head_dim, int causal, float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa;
   if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
   if (!causal && (window != 0 || kblock_lo != nullptr)) return kErrBadArg;
+  if (Sk <= 0 || (Sk % BN) != 0 || (causal && Sk != S)) return kErrBadArg;
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o);
   p.lse2 = lse2;
@@ -450,7 +454,7 @@ extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v
   p.k_seg = k_seg;
   p.kblock_lo = kblock_lo;
   p.sink = sink;
-  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.B = B; p.S = S; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale;
   p.soft_cap = soft_cap;
   p.window = window;
@@ -466,5 +470,5 @@ extern "C" int lvb_flash_attn_fwd_hd(const void* q, const void* k, const void* v
 extern "C" int lvb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
                                   const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                   int window, int* status, void* stream) {
-  return lvb_flash_attn_fwd_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
+  return lvb_flash_attn_fwd_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
 }

@@ -42,7 +42,8 @@ struct BwdParams {
   const float* delta;          // [B, Hq, S]
   const int* q_seg;
   const int* k_seg;
-  int B, S, Hq, Hkv;
+  int B, S, Hq, Hkv;           // S: query positions per sequence
+  int Sk;                      // key positions per sequence (= S unless the mask has no causal part)
   float scale, soft_cap;
   int window;
   int causal;                  // 0: every key is visible (subject to segment ids); window must be 0 then
@@ -131,7 +132,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      const int row_k = b * p.S + k0;
+      const int row_k = b * p.Sk + k0;
       mbar_expect_tx(kv_full, 2 * kQKV);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
@@ -218,7 +219,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int dbase = half * (D / 2);
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const int* kseg_g = kSeg ? p.k_seg + b * p.S + k0 : nullptr;
+    const int* kseg_g = kSeg ? p.k_seg + b * p.Sk + k0 : nullptr;
     uint8_t* sPp = smem + SmemB::kP;
     uint8_t* sDSp = smem + SmemB::kDS;
     bool ok = true;
@@ -314,7 +315,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // epilogue: dK, dV -> bf16 (this warp's D / 2 columns)
     if (ok) {
       tc_fence_after();
-      const size_t row = (static_cast<size_t>(b) * p.S + k0 + r) * (static_cast<size_t>(p.Hkv) * D) + static_cast<size_t>(hkv) * D;
+      const size_t row = (static_cast<size_t>(b) * p.Sk + k0 + r) * (static_cast<size_t>(p.Hkv) * D) + static_cast<size_t>(hkv) * D;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + row;
@@ -390,11 +391,12 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
   if (rc != kErrOk) return rc;
   rc = make_tmap_2d_bf16(&tmDO, d_o, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BM, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  const uint64_t rows_k = static_cast<uint64_t>(p.B) * p.Sk;
+  rc = make_tmap_2d_bf16(&tmK, k, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
+  rc = make_tmap_2d_bf16(&tmV, v, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BN, 64);
   if (rc != kErrOk) return rc;
-  dim3 grid(p.S / BN, p.B * p.Hkv);
+  dim3 grid(p.Sk / BN, p.B * p.Hkv);
   const bool seg = p.q_seg != nullptr;
   const bool cap = p.soft_cap > 0.f;
 #define LVB_LAUNCH_BWD(SEG, CAP)                                                                                      \
@@ -420,15 +422,16 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
 }  // namespace lvb
 
 // Backward of lvb_flash_attn_fwd_hd.  dq32: fp32 [B,S,Hq,D], must be zero on entry.  delta: fp32 [B,Hq,S] scratch.  D = head_dim
-// is 64 or 128; causal as in the forward.
+// is 64 or 128; causal and Sk (keys per sequence: k / v / dk / dv are [B, Sk, Hkv, D]) as in the forward.
 extern "C" int lvb_flash_attn_bwd_hd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                                      const float* lse2, float* delta, float* dq32, void* dk, void* dv, const int* q_seg,
-                                     const int* k_seg, int B, int S, int Hq, int Hkv, int head_dim, int causal, float scale,
+                                     const int* k_seg, int B, int S, int Sk, int Hq, int Hkv, int head_dim, int causal, float scale,
                                      float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa;
   if (B <= 0 || S <= 0 || (S % BM) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
   if (!causal && window != 0) return kErrBadArg;
+  if (Sk <= 0 || (Sk % BN) != 0 || (causal && Sk != S)) return kErrBadArg;
   BwdParams p;
   p.dQ32 = dq32;
   p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
@@ -437,7 +440,7 @@ extern "C" int lvb_flash_attn_bwd_hd(const void* q, const void* k, const void* v
   p.delta = delta;
   p.q_seg = q_seg;
   p.k_seg = k_seg;
-  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.B = B; p.S = S; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.soft_cap = soft_cap; p.window = window;
   p.causal = causal ? 1 : 0;
   p.status = status;
@@ -452,6 +455,6 @@ extern "C" int lvb_flash_attn_bwd(const void* q, const void* k, const void* v, c
                                   const float* lse2, float* delta, float* dq32, void* dk, void* dv, const int* q_seg,
                                   const int* k_seg, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                   int window, int* status, void* stream) {
-  return lvb_flash_attn_bwd_hd(q, k, v, o, d_o, lse2, delta, dq32, dk, dv, q_seg, k_seg, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window,
+  return lvb_flash_attn_bwd_hd(q, k, v, o, d_o, lse2, delta, dq32, dk, dv, q_seg, k_seg, B, S, S, Hq, Hkv, 128, 1, scale, soft_cap, window,
                                status, stream);
 }

@@ -30,7 +30,8 @@ struct Params {
   const int* k_seg;
   const int* kblock_lo;  // optional [B, S / 128]: first block of 128 keys that a query of this 128-row block can attend to
   const float* sink;     // optional [Hq]: a learned logit per head that takes part in the softmax denominator only
-  int B, S, Hq, Hkv;
+  int B, S, Hq, Hkv;  // S: query positions per sequence
+  int Sk;             // key positions per sequence (= S unless the mask has no causal part: cross attention)
   float scale, soft_cap;
   int window;
   int causal;  // 0: every key is visible (subject to segment ids); window must be 0 and kblock_lo null then
@@ -96,7 +97,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int lo = p.kblock_lo[b * (p.S / BT) + jdiagA];
     jlo = max(jlo, min(lo, jdiagA));
   }
-  const int nB = (causal ? jdiagB : p.S / BT - 1) - jlo + 1;  // blocks processed by tile B
+  const int nB = (causal ? jdiagB : p.Sk / BT - 1) - jlo + 1;  // blocks processed by tile B
   const int nA = causal ? nB - 1 : nB;                        // causal: tile A stops one block earlier (its diagonal)
 
   if (threadIdx.x == 0) {
@@ -141,7 +142,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       for (int it = 0; it < nB && ok; ++it) {
         const int st = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
-        const int row_k = b * p.S + (jlo + it) * BT;
+        const int row_k = b * p.Sk + (jlo + it) * BT;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 1200, it);
         if (!ok) break;
         uint8_t* ks = smem + Smem::kK + st * kQKV;
@@ -239,7 +240,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tO = tmem_base + 2 * BT + tile * D + lane_addr;
     const float scale_log2 = p.scale * kLog2e;
     const int my_seg = kSeg ? p.q_seg[b * p.S + qi] : 0;
-    const int* kseg_row = kSeg ? p.k_seg + b * p.S : nullptr;
+    const int* kseg_row = kSeg ? p.k_seg + b * p.Sk : nullptr;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
 
@@ -421,9 +422,10 @@ int launch_hd(const void* q, const void* k, const void* v, const Params& p, cuda
   const uint64_t rows = static_cast<uint64_t>(p.B) * p.S;
   int rc = make_tmap_2d_bf16(&tmQ, q, rows, static_cast<uint64_t>(p.Hq) * HD, static_cast<uint64_t>(p.Hq) * HD, BT, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmK, k, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
+  const uint64_t rows_k = static_cast<uint64_t>(p.B) * p.Sk;
+  rc = make_tmap_2d_bf16(&tmK, k, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
   if (rc != kErrOk) return rc;
-  rc = make_tmap_2d_bf16(&tmV, v, rows, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
+  rc = make_tmap_2d_bf16(&tmV, v, rows_k, static_cast<uint64_t>(p.Hkv) * HD, static_cast<uint64_t>(p.Hkv) * HD, BT, 64);
   if (rc != kErrOk) return rc;
   const bool seg = p.q_seg != nullptr;
   const bool cap = p.soft_cap > 0.f;
@@ -436,14 +438,16 @@ int launch_hd(const void* q, const void* k, const void* v, const Params& p, cuda
 }  // namespace lvb
 
 // Same contract as lvb_flash_attn_fwd_hd (head_dim 64 or 128, causal or not, optional sink logits [Hq]), but S must be a
-// multiple of 256: two query tiles per CTA.
+// multiple of 256: two query tiles per CTA.  Sk: keys per sequence, a multiple of 128 (k / v are [B, Sk, Hkv, D], k_seg [B, Sk]);
+// Sk must equal S when causal.
 extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
-                                      const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Hq, int Hkv,
+                                      const int* k_seg, const int* kblock_lo, const float* sink, int B, int S, int Sk, int Hq, int Hkv,
                                       int head_dim, int causal, float scale, float soft_cap, int window, int* status, void* stream) {
   using namespace lvb;
   using namespace lvb::fa2;
   if (B <= 0 || S <= 0 || (S % (2 * BT)) != 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv) != 0) return kErrBadArg;
   if (!causal && (window != 0 || kblock_lo != nullptr)) return kErrBadArg;
+  if (Sk <= 0 || (Sk % BT) != 0 || (causal && Sk != S)) return kErrBadArg;
   Params p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o);
   p.lse2 = lse2;
@@ -451,7 +455,7 @@ extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* 
   p.k_seg = k_seg;
   p.kblock_lo = kblock_lo;
   p.sink = sink;
-  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.B = B; p.S = S; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.soft_cap = soft_cap; p.window = window;
   p.causal = causal ? 1 : 0;
   p.status = status;
@@ -465,5 +469,5 @@ extern "C" int lvb_flash_attn_fwd2_hd(const void* q, const void* k, const void* 
 extern "C" int lvb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse2, const int* q_seg,
                                    const int* k_seg, const int* kblock_lo, int B, int S, int Hq, int Hkv, float scale, float soft_cap,
                                    int window, int* status, void* stream) {
-  return lvb_flash_attn_fwd2_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
+  return lvb_flash_attn_fwd2_hd(q, k, v, o, lse2, q_seg, k_seg, kblock_lo, nullptr, B, S, S, Hq, Hkv, 128, 1, scale, soft_cap, window, status, stream);
 }

@@ -33,10 +33,10 @@ def supported(q, k, v, mask, bias, no_dropout: bool, attention_dtype) -> bool:
         return False
     if q.shape[-1] not in (64, 128) or v.shape[-1] != q.shape[-1] or k.shape[-1] != q.shape[-1]:
         return False
-    if q.shape[1] != k.shape[1]:
-        return False  # cross attention (different query and key lengths) is not on the kernel path
     if mask is not None and not isinstance(mask, AttentionMask):
         return False
+    if q.shape[1] != k.shape[1] and (q.shape[1] == 1 or (isinstance(mask, AttentionMask) and mask.is_causal)):
+        return False  # different query and key lengths: cross attention only (no causal part); single-token decode steps stay off
     if isinstance(mask, AttentionMask) and not mask.is_causal and mask.sliding_window:
         return False
     return _structured_only(mask)

@@ -176,7 +176,7 @@ def test_dispatch_takes_head_size_64_and_encoder_masks():
     q = torch.randn(1, 256, 2, 64, device="cuda").bfloat16()
     assert KFA.supported(q, q, q, None, None, True, None)
     assert KFA.supported(q, q, q, AttentionMask.causal(), None, True, None)
-    assert not KFA.supported(q, q[:, :128], q[:, :128], None, None, True, None)  # cross attention
+    assert not KFA.supported(q, q[:, :128], q[:, :128], AttentionMask.causal(), None, True, None)  # causal needs equal lengths
     q96 = torch.randn(1, 256, 2, 96, device="cuda").bfloat16()
     assert not KFA.supported(q96, q96, q96, None, None, True, None)
 
@@ -220,3 +220,30 @@ def test_sink_logits_join_the_denominator(D, S, causal, Hq, Hkv):
     # the module-level entry point takes the kernel path
     o2 = dot_product_attention_with_sink(q, k, v, sink, mask)
     assert torch.equal(o2, o)
+
+
+@pytest.mark.parametrize("D,Sq,Sk,Hq,Hkv", [(64, 448, 1500, 6, 6), (128, 256, 384, 4, 2), (64, 100, 640, 2, 1), (128, 300, 128, 2, 2)])
+def test_cross_attention_with_different_query_and_key_lengths(D, Sq, Sk, Hq, Hkv):
+    """Whisper's decoder attends from 448 text positions to 1500 audio positions: no causal part, two lengths, both padded."""
+    torch.manual_seed(0)
+    q = torch.randn(2, Sq, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(2, Sk, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(2, Sk, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    o = flash_attention_cuda(q, k, v, None)
+    assert o.shape == q.shape
+    g = torch.randn_like(o)
+    o.backward(g)
+    torch.cuda.synchronize()
+    lib.check_status()
+    qr, kr, vr = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    orf = simple_attention_with_dropout(qr, kr, vr, None, attention_dtype=torch.float32)
+    orf.backward(g.float())
+    _close(o, orf, 2e-2)
+    _close(q.grad, qr.grad, 4e-2)
+    _close(k.grad, kr.grad, 4e-2)
+    _close(v.grad, vr.grad, 4e-2)
+    from levanter_b200.ops import flash_attention as KFA
+
+    assert KFA.supported(q, k, v, None, None, True, None)
+    assert not KFA.supported(q, k, v, AttentionMask.causal(), None, True, None)
+    assert not KFA.supported(q[:, :1], k, v, None, None, True, None)
