@@ -57,29 +57,58 @@ __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm
   coef[0] = (max_norm > 0.f && norm > max_norm) ? max_norm / (norm + 1e-6f) : 1.f;
 }
 
+__device__ __forceinline__ void adamw_one(float& pi, float& mi, float& vi, float gi, float lr, float b1, float b2, float eps, float wd,
+                                          float bc1, float bc2, int nesterov) {
+  mi = b1 * mi + (1.f - b1) * gi;
+  vi = b2 * vi + (1.f - b2) * gi * gi;
+  // optax scale_by_adam: nesterov uses b1 * m_hat(t+1 correction) + (1 - b1) * g / bc1
+  float mhat = mi / bc1;
+  if (nesterov) mhat = b1 * (mi / (1.f - (1.f - bc1) * b1)) + (1.f - b1) * gi / bc1;
+  const float vhat = vi / bc2;
+  float u = mhat / (sqrtf(vhat) + eps);
+  u += wd * pi;
+  pi = pi - lr * u;
+}
+
+// Four elements per thread and iteration through 16-byte accesses (every array 16-byte aligned: checked by the launcher, which
+// otherwise passes vec = 0); the last n % 4 elements, or everything when vec = 0, go one by one.
 template <typename G>
 __global__ void __launch_bounds__(kBlock)
 adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, const G* __restrict__ g,
              __nv_bfloat16* __restrict__ p_bf16, long long n, float lr, float b1, float b2, float eps, float wd,
-             float bc1, float bc2, const float* __restrict__ grad_scale, float grad_mul, int nesterov) {
+             float bc1, float bc2, const float* __restrict__ grad_scale, float grad_mul, int nesterov, int vec) {
   const float gs = (grad_scale != nullptr ? grad_scale[0] : 1.f) * grad_mul;
-  for (long long i = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * kBlock) {
-    const float gi = ldf<G>(g, i) * gs;
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  const long long tid = blockIdx.x * static_cast<long long>(kBlock) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * kBlock;
+  const long long n4 = vec ? n / 4 : 0;
+  for (long long q = tid; q < n4; q += stride) {
+    float4 pp = reinterpret_cast<float4*>(p)[q], mm = reinterpret_cast<float4*>(m)[q], vv = reinterpret_cast<float4*>(v)[q];
+    float gg[4];
+    if constexpr (sizeof(G) == 4) {
+      const float4 t = reinterpret_cast<const float4*>(g)[q];
+      gg[0] = t.x; gg[1] = t.y; gg[2] = t.z; gg[3] = t.w;
+    } else {
+      const uint2 t = reinterpret_cast<const uint2*>(g)[q];
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+      gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
+    }
+    adamw_one(pp.x, mm.x, vv.x, gg[0] * gs, lr, b1, b2, eps, wd, bc1, bc2, nesterov);
+    adamw_one(pp.y, mm.y, vv.y, gg[1] * gs, lr, b1, b2, eps, wd, bc1, bc2, nesterov);
+    adamw_one(pp.z, mm.z, vv.z, gg[2] * gs, lr, b1, b2, eps, wd, bc1, bc2, nesterov);
+    adamw_one(pp.w, mm.w, vv.w, gg[3] * gs, lr, b1, b2, eps, wd, bc1, bc2, nesterov);
+    reinterpret_cast<float4*>(p)[q] = pp;
+    reinterpret_cast<float4*>(m)[q] = mm;
+    reinterpret_cast<float4*>(v)[q] = vv;
+    if (p_bf16 != nullptr) reinterpret_cast<uint2*>(p_bf16)[q] = make_uint2(pack_bf16x2(pp.x, pp.y), pack_bf16x2(pp.z, pp.w));
+  }
+  for (long long i = 4 * n4 + tid; i < n; i += stride) {
+    float pi = p[i], mi = m[i], vi = v[i];
+    adamw_one(pi, mi, vi, ldf<G>(g, i) * gs, lr, b1, b2, eps, wd, bc1, bc2, nesterov);
+    p[i] = pi;
     m[i] = mi;
     v[i] = vi;
-    // optax scale_by_adam: nesterov uses b1 * m_hat(t+1 correction) + (1 - b1) * g / bc1
-    float mhat = mi / bc1;
-    if (nesterov) mhat = b1 * (mi / (1.f - (1.f - bc1) * b1)) + (1.f - b1) * gi / bc1;
-    const float vhat = vi / bc2;
-    float u = mhat / (sqrtf(vhat) + eps);
-    const float pi = p[i];
-    u += wd * pi;
-    const float np = pi - lr * u;
-    p[i] = np;
-    if (p_bf16 != nullptr) p_bf16[i] = __float2bfloat16(np);
+    if (p_bf16 != nullptr) p_bf16[i] = __float2bfloat16(pi);
   }
 }
 
@@ -127,14 +156,18 @@ extern "C" int lvb_adamw(float* p, float* m, float* v, const void* g, int g_is_b
   long long gl = (n + kBlock - 1) / kBlock;
   long long cap = static_cast<long long>(num_sms()) * 16;
   const int grid = static_cast<int>(gl < cap ? gl : cap);
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(g) | (reinterpret_cast<uintptr_t>(p_bf16) << 1);  // bf16: 8-byte accesses
+  const int vec = (bits & 15) == 0 ? 1 : 0;
   if (g_is_bf16)
     adamw_kernel<__nv_bfloat16><<<grid, kBlock, 0, s>>>(p, m, v, reinterpret_cast<const __nv_bfloat16*>(g),
                                                         reinterpret_cast<__nv_bfloat16*>(p_bf16), n, lr, b1, b2, eps, wd,
-                                                        bc1, bc2, grad_scale, grad_mul, nesterov);
+                                                        bc1, bc2, grad_scale, grad_mul, nesterov,
+                                                        vec && (reinterpret_cast<uintptr_t>(g) & 7) == 0);
   else
     adamw_kernel<float><<<grid, kBlock, 0, s>>>(p, m, v, reinterpret_cast<const float*>(g),
                                                 reinterpret_cast<__nv_bfloat16*>(p_bf16), n, lr, b1, b2, eps, wd, bc1,
-                                                bc2, grad_scale, grad_mul, nesterov);
+                                                bc2, grad_scale, grad_mul, nesterov, vec);
   return cudaGetLastError() == cudaSuccess ? kErrOk : kErrCuda;
 }
 
