@@ -180,6 +180,7 @@ class MixtralDecoderLayer(nn.Module):
     def __init__(self, config: MixtralConfig, *, tp=None, ep=None):
         super().__init__()
         self.config = config
+        self.tp = tp
         self.self_attn = Attention(config.attention_config(), init_std=config.initializer_range, tp=tp)
         self.block_sparse_moe = MixtralSparseMoeBlock(config, ep=ep)
         self.input_layernorm = config.mk_LayerNorm(config.hidden_dim)
@@ -191,7 +192,17 @@ class MixtralDecoderLayer(nn.Module):
             self.shared_mlp = None
 
     def forward(self, x, mask=None, pos_ids=None):
-        x = self.self_attn(self.input_layernorm(x), mask, pos_ids, residual=x)
+        if self.tp is not None and self.tp.size > 1:
+            # heads split over the model axis: the block's input enters the tensor-parallel region (its gradient is summed over the
+            # axis on the way back) and the output projection's partial products are summed before the bias and the residual.
+            # The expert block below runs replicated on the model axis (experts are sliced over the data axis only).
+            a = self.self_attn
+            out = a.forward(self.tp.copy_to_region(self.input_layernorm(x)), mask, pos_ids, skip_out_bias=True, row_parallel=self.tp)
+            if a.o_proj.bias is not None:
+                out = out + a.o_proj.bias
+            x = x + out
+        else:
+            x = self.self_attn(self.input_layernorm(x), mask, pos_ids, residual=x)
         h = self.post_attention_layernorm(x)
         moe_out, extras = self.block_sparse_moe(h)
         if self.shared_mlp is not None:
@@ -248,9 +259,12 @@ class MixtralLMHeadModel(LmHeadModel):
         if ep is None and getattr(config, "expert_parallel", False):
             import torch.distributed as dist
 
-            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-                from ..parallel.expert import ExpertParallel
+            from ..parallel.expert import ExpertParallel
 
+            mesh = getattr(tp, "mesh", None)
+            if mesh is not None:
+                ep = ExpertParallel.from_mesh(mesh)  # with a model axis the experts are sliced over the data axis only
+            elif dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
                 ep = ExpertParallel(None)
         return cls(vocab_size, config, tp=tp, ep=ep)
 

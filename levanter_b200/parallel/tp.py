@@ -102,7 +102,9 @@ class TensorParallel:
         ax = mesh.axes["model"]
         if ax.size <= 1:
             return None
-        return TensorParallel(ax.group, ax.size, ax.rank)
+        tp = TensorParallel(ax.group, ax.size, ax.rank)
+        tp.mesh = mesh  # models that also slice experts over the data axis find that axis's group here
+        return tp
 
     def copy_to_region(self, x: torch.Tensor) -> torch.Tensor:
         return _CopyToRegion.apply(x, self)
@@ -324,14 +326,19 @@ class TensorParallel:
         return torch.cat(parts, dim=-1)
 
 
-def shard_full_state_(model: torch.nn.Module, full_state: dict, tp: Optional["TensorParallel"]) -> None:
+def shard_full_state_(model: torch.nn.Module, full_state: dict, tp: Optional["TensorParallel"], ep=None) -> None:
     """Fill a tensor-parallel ``model`` from the tensors of the unsharded model: every parameter marked ``tp_dim`` takes
     this rank's slice along that dimension (heads and MLP columns are contiguous per rank), the others are copied whole.
+    Parameters marked ``ep_dim`` (experts sliced over the ranks of ``ep``) take that group's slice of the expert axis.
     Used to serve (or continue training) a checkpoint on a model axis of any size."""
     rank = tp.rank if tp is not None else 0
     with torch.no_grad():
         for name, p in model.named_parameters():
             src = full_state[name]
+            edim = getattr(p, "ep_dim", None)
+            if edim is not None and ep is not None and src.shape[edim] != p.shape[edim]:
+                n = p.shape[edim]
+                src = src.narrow(edim, ep.rank * n, n)
             dim = getattr(p, "tp_dim", None)
             if dim is not None and src.shape != p.shape:
                 n = p.shape[dim]
@@ -357,13 +364,14 @@ def gather_full_state(model: torch.nn.Module, tp: Optional["TensorParallel"]) ->
     return out
 
 
-def build_sharded_from_seed(build, tp: Optional["TensorParallel"]):
+def build_sharded_from_seed(build, tp: Optional["TensorParallel"], ep=None):
     """A tensor-parallel model whose weights are this rank's slices of the model that ``build(tp=None)`` creates, so that a
-    run on a model axis of any size starts from the same weights as an unsharded run with the same seed."""
+    run on a model axis of any size starts from the same weights as an unsharded run with the same seed.  ``ep``: the
+    expert-parallel group of a model built with sliced experts (its ``ep_dim`` parameters take their slice as well)."""
     if tp is None or tp.size <= 1:
         return build(tp=None)
     full = build(tp=None)
     model = build(tp=tp)
-    shard_full_state_(model, {n: p.detach() for n, p in full.named_parameters()}, tp)
+    shard_full_state_(model, {n: p.detach() for n, p in full.named_parameters()}, tp, ep)
     del full
     return model
