@@ -372,6 +372,8 @@ def build_sharded_from_seed(build, tp: Optional["TensorParallel"], ep=None):
         return build(tp=None)
     full = build(tp=None)
     model = build(tp=tp)
+    if ep is None:  # a model that sliced its experts by itself carries the group on its expert blocks
+        ep = next((m.ep for m in model.modules() if getattr(m, "ep", None) is not None), None)
     shard_full_state_(model, {n: p.detach() for n, p in full.named_parameters()}, tp, ep)
     del full
     return model

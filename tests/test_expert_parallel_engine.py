@@ -135,7 +135,9 @@ def _train_ep_tp(tmp, steps, rank=0, world=1):
             ep = ExpertParallel.from_mesh(tp.mesh)
             assert ep is not None and ep.size == 2 and tp.size == 2
             sliced_cfg = dataclasses.replace(full_cfg, expert_parallel=True)
-            return build_sharded_from_seed(lambda tp: (sliced_cfg if tp is not None else full_cfg).build(VOCAB, seed=3, tp=tp), tp, ep)
+            # (the group is also found on the model's expert blocks when it is not passed)
+            return build_sharded_from_seed(lambda tp: (sliced_cfg if tp is not None else full_cfg).build(VOCAB, seed=3, tp=tp), tp,
+                                           ep if rank % 2 == 0 else None)
 
         state = trainer.initial_state(0, model_init=model_init)
         trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
