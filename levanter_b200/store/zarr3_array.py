@@ -42,13 +42,16 @@ def crc32c(data: bytes) -> int:
     return int(_native().lvb_crc32c(data, len(data)))
 
 
-def blosc_decompress_many(blobs: List[bytes], threads: int = 8) -> List[np.ndarray]:
-    """Decode blosc frames (lz4 / zstd / stored, byte shuffle) in parallel on the native thread pool."""
+def blosc_decompress_many(blobs: List[bytes], threads: int = 8, expect: Optional[int] = None) -> List[np.ndarray]:
+    """Decode blosc frames (lz4 / zstd / stored, byte shuffle) in parallel on the native thread pool.  ``expect``: the decoded
+    size every frame must declare (a chunk's byte count), checked before any buffer is allocated from a frame's own header."""
     l = _native()
     n = len(blobs)
     sizes = [int(l.lvb_blosc_nbytes(b, len(b))) for b in blobs]
     if any(s < 0 for s in sizes):
         raise ValueError("not a blosc frame")
+    if expect is not None and any(s != expect for s in sizes):
+        raise ValueError(f"a blosc frame declares {[s for s in sizes if s != expect][0]} decoded bytes where the chunk has {expect}")
     outs = [np.empty(max(s, 1), dtype=np.uint8) for s in sizes]
     P, LL = ctypes.c_void_p, ctypes.c_longlong
     keep = [ctypes.create_string_buffer(b, len(b)) for b in blobs]
@@ -84,9 +87,12 @@ class _Pipeline:
                 raise NotImplementedError(f"{where}: codec {name!r} is not supported")
         del seen_bytes
 
-    def decode_many(self, blobs: List[bytes]) -> List[np.ndarray]:
+    def decode_many(self, blobs: List[bytes], expect: Optional[int] = None) -> List[np.ndarray]:
+        """``expect``: byte count of a decoded chunk (known from the chunk shape), enforced on the innermost compressor."""
         cur: List = list(blobs)
-        for name, _ in reversed(self.steps):
+        for pos in range(len(self.steps) - 1, -1, -1):
+            name = self.steps[pos][0]
+            innermost = pos == 0
             if name == "crc32c":
                 nxt = []
                 for b in cur:
@@ -97,7 +103,7 @@ class _Pipeline:
                     nxt.append(body)
                 cur = nxt
             elif name == "blosc":
-                cur = blosc_decompress_many([bytes(b) for b in cur])
+                cur = blosc_decompress_many([bytes(b) for b in cur], expect=expect if innermost else None)
             elif name == "gzip":
                 cur = [zlib.decompress(bytes(b), 15 + 32) for b in cur]
             elif name == "zstd":
@@ -257,7 +263,8 @@ class Zarr3Array:
                 todo.append((tuple(so + i * ic for so, i, ic in zip(s_origin, ii, self.inner)), list(self.inner)))
         if not blobs:
             return
-        decoded = self.pipe.decode_many(blobs)
+        same = {self._chunk_elems(shape) for _, shape in todo}
+        decoded = self.pipe.decode_many(blobs, expect=same.pop() * self.np_dtype.itemsize if len(same) == 1 else None)
         for (origin, shape), d in zip(todo, decoded):
             n = self._chunk_elems(shape) * self.np_dtype.itemsize
             if d.nbytes != n:

@@ -168,3 +168,27 @@ def test_tree_cache_loads_a_finished_cache_in_the_reference_layout(tmp_path):
     got = cache.get_batch_sync([0, 63, 31])
     for g, j in zip(got, (0, 63, 31)):
         assert np.array_equal(g["input_ids"], rows[j])
+
+
+def test_mutated_frames_are_rejected_or_decoded_but_never_trusted_for_sizes():
+    """Bytes from a file are not trusted: a damaged frame is refused (or decodes to the declared size), and a frame that
+    declares another size than its chunk is refused before anything is allocated for it."""
+    import random
+
+    rng = np.random.default_rng(3)
+    data = (rng.integers(0, 50, 3000) * 3).astype(np.int32).tobytes()
+    frames = [_blosc_frame(data, 4, 2048, codec=c, split=sp) for c in ("lz4", "zstd") for sp in (True, False)]
+    random.seed(0)
+    for _ in range(400):
+        f = bytearray(random.choice(frames))
+        for _ in range(random.randint(1, 4)):
+            f[random.randrange(len(f))] = random.randrange(256)
+        try:
+            out = blosc_decompress_many([bytes(f)], expect=len(data))
+            assert out[0].nbytes == len(data)
+        except ValueError:
+            pass
+    big = bytearray(frames[0])
+    big[4:8] = struct.pack("<I", 1 << 31)
+    with pytest.raises(ValueError):
+        blosc_decompress_many([bytes(big)], expect=len(data))
