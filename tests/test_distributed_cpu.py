@@ -62,6 +62,21 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
             assert st is not None and st.stats["library_weight_grads"] > 0
             full = state.engine.full_master()  # whole matrices again, assembled from every rank's rows
             return {k: full[k].detach().clone() for k, _ in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
+        if tp is not None and state.engine.zero_stage == 3:
+            # the module's parameters are views of staging slots here: take the master rows of every data rank, then join the
+            # model-axis slices
+            import torch.distributed as dist
+
+            full = state.engine.full_master()
+            out = {}
+            for name, p in info.state.model.named_parameters():
+                t, dim = full[name].detach().clone(), getattr(p, "tp_dim", None)
+                if dim is not None:
+                    parts = [torch.empty_like(t) for _ in range(tp.size)]
+                    dist.all_gather(parts, t.contiguous(), group=tp.group)
+                    t = torch.cat(parts, dim=dim)
+                out[name] = t
+            return out, [losses[k] for k in sorted(losses)]
         if tp is not None:
             return gather_full_state(info.state.model, tp), [losses[k] for k in sorted(losses)]
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
@@ -97,6 +112,17 @@ def test_two_rank_zero3_layer_streaming_matches_single_process(tmp_path):
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
 
 
+def test_zero3_under_two_replicas_matches_single_process(tmp_path):
+    """Four ranks: replica 2 x data 2.  Layer matrices are row-sliced over the data axis inside each replica, and the gradient
+    rows a rank owns are averaged over the replicas before its optimizer step."""
+    single, losses = _train(str(tmp_path / "single"), hidden=64)
+    mp.spawn(_sharded_worker, args=(4, 29727, str(tmp_path), None, {"zero_stage": 3, "replica_ici_axis_size": 2}, 64, 3), nprocs=4, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
 def test_two_way_tensor_parallel_training_matches_single_process(tmp_path):
     """model axis 2 (heads and MLP columns split, all-reduce after the row-parallel projections and of the input gradients of
     the column-parallel ones): three optimizer steps give the losses and the weights of the unsharded run."""
@@ -111,6 +137,20 @@ def test_two_way_tensor_parallel_training_matches_single_process(tmp_path):
     assert got["losses"] == pytest.approx(losses, abs=2e-5)
     for k, v in single.items():
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+def test_tensor_parallel_with_zero3_over_the_data_axis_matches_single_process(tmp_path):
+    """Four ranks: data 2 x model 2.  Heads and MLP columns are split over the model axis; each model rank's slices are
+    row-sliced again over the data axis (zero stage 3), gathered per layer and their gradients reduce-scattered."""
+    opt = {"type": "adam", "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0,
+           "epsilon": 1e-4, "max_grad_norm": 0.5}
+    single, losses = _train(str(tmp_path / "single"), opt_dict=opt, hidden=128)
+    extra = {"model_axis_size": 2, "tensor_parallel_axes": ["mlp", "heads"], "zero_stage": 3}
+    mp.spawn(_sharded_worker, args=(4, 29728, str(tmp_path), opt, extra, 128), nprocs=4, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=3e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=3e-5), k
 
 
 MUON = {"type": "muon", "learning_rate": 2e-2, "adam_lr": 3e-3, "warmup": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0}
