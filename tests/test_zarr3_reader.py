@@ -226,3 +226,42 @@ def test_exported_cache_reads_back_through_the_v3_reader(tmp_path, cname):
     noise = rng.integers(0, 2 ** 31, 1000, dtype=np.int64)
     for arr in (noise, np.zeros(1000, np.int64)):
         assert blosc_decompress_many([blosc_frame(arr, cname)])[0].tobytes() == arr.tobytes()
+
+
+@pytest.mark.parametrize("codec,key_style", [("zstd", "default"), ("gzip", "v2"), ("none", "default")])
+def test_plain_chunked_v3_arrays_with_other_codecs_and_key_encodings(tmp_path, codec, key_style):
+    """Arrays without the sharding codec (how array checkpoints may be stored): one file per chunk, ``bytes`` + a compressor,
+    either chunk-key encoding, a fill value for chunks that were never written."""
+    import gzip
+
+    rng = np.random.default_rng(7)
+    arr = rng.standard_normal((70, 50)).astype(np.float32)
+    p = tmp_path / "a"
+    p.mkdir()
+    codecs = [{"name": "bytes", "configuration": {"endian": "little"}}]
+    if codec != "none":
+        codecs.append({"name": codec, "configuration": {"level": 3}})
+    enc = {"name": "default", "configuration": {"separator": "/"}} if key_style == "default" else {"name": "v2", "configuration": {"separator": "."}}
+    meta = {"zarr_format": 3, "node_type": "array", "shape": [70, 50], "data_type": "float32",
+            "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": [32, 32]}}, "chunk_key_encoding": enc,
+            "fill_value": 1.5, "codecs": codecs, "attributes": {}}
+    (p / "zarr.json").write_text(json.dumps(meta))
+    for i in range(3):
+        for j in range(2):
+            if (i, j) == (2, 1):
+                continue  # never written: reads as the fill value
+            chunk = np.full((32, 32), 1.5, np.float32)
+            part = arr[i * 32:(i + 1) * 32, j * 32:(j + 1) * 32]
+            chunk[:part.shape[0], :part.shape[1]] = part
+            raw = chunk.tobytes()
+            blob = {"zstd": lambda b: pa.compress(b, codec="zstd", asbytes=True), "gzip": gzip.compress, "none": lambda b: b}[codec](raw)
+            key = p / "c" / str(i) / str(j) if key_style == "default" else p / f"{i}.{j}"
+            key.parent.mkdir(parents=True, exist_ok=True)
+            key.write_bytes(blob)
+    z = ZarrArray.open(str(p))
+    want = arr.copy()
+    want[64:, 32:] = 1.5
+    assert np.array_equal(z.read(), want)
+    assert np.array_equal(z.read([10, 20], [66, 45]), want[10:66, 20:45])
+    t = z.read_tensor([0, 0], [4, 4])
+    assert t.dtype.is_floating_point and t.shape == (4, 4)
