@@ -265,3 +265,30 @@ def test_plain_chunked_v3_arrays_with_other_codecs_and_key_encodings(tmp_path, c
     assert np.array_equal(z.read([10, 20], [66, 45]), want[10:66, 20:45])
     t = z.read_tensor([0, 0], [4, 4])
     assert t.dtype.is_floating_point and t.shape == (4, 4)
+
+
+def test_checkpoint_leaf_stored_as_a_v3_array_loads(tmp_path):
+    """The checkpoint loader opens leaves through the same entry point, so a leaf written as a zarr v3 array (here: a stacked
+    per-layer weight, bf16) loads, including the one-layer slice the loader takes from stacked arrays."""
+    import torch
+
+    from levanter_b200.store.zarr3_export import export_array
+    from levanter_b200.tensorstore_serialization import _fs_path, read_leaf
+
+    w = torch.randn(4, 6, 8).bfloat16()
+
+    class Src:
+        shape, np_dtype, dtype_str = list(w.shape), np.dtype("uint16"), "bfloat16"
+
+        def read(self, lo, hi):
+            return w.view(torch.int16).numpy().view(np.uint16)[tuple(slice(a, b) for a, b in zip(lo, hi))]
+
+    p = _fs_path(str(tmp_path), "model.transformer.layers.stacked.weight")
+    export_array(Src(), p, 4, shard_rows=4, inner_rows=2)
+    meta = json.load(open(os.path.join(p, "zarr.json")))
+    meta["shape"] = [4, 6, 8]  # a checkpoint array has its true shape, not the caches' nominal one
+    json.dump(meta, open(os.path.join(p, "zarr.json"), "w"))
+    got = read_leaf(str(tmp_path), "model.transformer.layers.stacked.weight")
+    assert got.dtype == torch.bfloat16 and torch.equal(got, w)
+    z = ZarrArray.open(p)
+    assert torch.equal(z.read_tensor([2, 0, 0], [3, 6, 8])[0], w[2])
