@@ -605,11 +605,13 @@ def main(fn=None, *, args: Optional[List[str]] = None, config_dir: Optional[str]
 
     @functools.wraps(fn)
     def wrapper(*a, **kw):
-        argv = list(sys.argv[1:] if cmd_args is None else cmd_args)
-        paths, rest = split_config_args(argv)
         spec = inspect.getfullargspec(fn)
         hints = typing.get_type_hints(fn)
         cfg_type = hints[spec.args[0]]
+        if a and isinstance(a[0], cfg_type):
+            return fn(*a, **kw)  # called from Python with a ready configuration: nothing to parse
+        argv = list(sys.argv[1:] if cmd_args is None else cmd_args)
+        paths, rest = split_config_args(argv)
         cfg = parse(cfg_type, paths, rest, config_dir)
         return fn(cfg, *a, **kw)
 

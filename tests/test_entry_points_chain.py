@@ -1,0 +1,126 @@
+"""The other entry points, end to end on a CPU with a tokenizer trained in memory: cache_dataset, train_lm with a Hugging Face
+export, export_lm_to_hf / export_hf_to_lm, sample_lm, viz_logprobs and lora_lm chained on the artefacts of one tiny run."""
+import json
+import os
+
+import numpy as np
+import pytest
+import yaml
+
+from levanter_b200 import config as C
+
+pytestmark = pytest.mark.entry
+
+
+@pytest.fixture(scope="module")
+def workdir(tmp_path_factory):
+    pytest.importorskip("tokenizers")
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    d = tmp_path_factory.mktemp("chain")
+    words = "the quick brown fox jumps over the lazy dog while seven small birds sing near a quiet river at dawn".split()
+    rng = np.random.default_rng(0)
+    docs = [" ".join(rng.choice(words, size=int(rng.integers(12, 40)))) + "." for _ in range(240)]
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(docs, trainers.BpeTrainer(vocab_size=300, special_tokens=["<s>", "</s>", "<pad>"],
+                                                      initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>", pad_token="<pad>")
+    fast.save_pretrained(str(d / "tok"))
+    for s in range(2):
+        with open(d / f"shard{s}.jsonl", "w") as f:
+            for t in docs[s * 120:(s + 1) * 120]:
+                f.write(json.dumps({"text": t}) + "\n")
+    return d
+
+
+def _base(d, steps=3):
+    return yaml.safe_load(f"""
+data:
+  tokenizer: {d}/tok
+  cache_dir: {d}/cache
+  train_urls: ["{d}/shard0.jsonl"]
+  validation_urls: ["{d}/shard1.jsonl"]
+model:
+  type: llama
+  seq_len: 32
+  hidden_dim: 32
+  intermediate_dim: 64
+  num_layers: 2
+  num_heads: 2
+  num_kv_heads: 2
+  gradient_checkpointing: false
+trainer:
+  id: chain
+  num_train_steps: {steps}
+  train_batch_size: 8
+  require_accelerator: false
+  tracker: {{type: noop}}
+  log_dir: {d}/logs
+  steps_per_eval: 100
+  max_eval_batches: 1
+  checkpointer:
+    base_path: {d}/ckpt
+    save_interval: 10h
+optimizer:
+  learning_rate: 1.0e-3
+  warmup: 0.0
+""")
+
+
+def test_chain(workdir, monkeypatch, capsys):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import cache_dataset, export_hf_to_lm, export_lm_to_hf, lora_lm, sample_lm, train_lm, viz_logprobs
+
+    # ---- cache_dataset builds the token cache that training then finds
+    ccfg = C.decode(cache_dataset.RayCachedLMDatasetConfig, _base(d)["data"])
+    cache_dataset.main(ccfg)
+    assert os.path.exists(f"{d}/cache/train/shard_ledger.json") and json.load(open(f"{d}/cache/train/shard_ledger.json"))["is_finished"]
+
+    # ---- train_lm, exporting Hugging Face weights at the end
+    tcfg = _base(d)
+    tcfg["hf_save_path"] = f"{d}/hf_from_training"
+    tcfg["hf_save_steps"] = 3
+    train_lm.main(C.decode(train_lm.TrainLmConfig, tcfg))
+    ck = discover_latest_checkpoint(f"{d}/ckpt/chain")
+    assert ck is not None
+
+    # ---- export_lm_to_hf, then back with export_hf_to_lm
+    export_lm_to_hf.main(C.decode(export_lm_to_hf.ConvertLmConfig, {"checkpoint_path": ck, "output_dir": f"{d}/hf", "model": _base(d)["model"],
+                                                                    "tokenizer": f"{d}/tok", "use_cpu": True,
+                                                                    "trainer": {"require_accelerator": False}}))
+    assert os.path.exists(f"{d}/hf/config.json") and any(f.endswith(".safetensors") for f in os.listdir(f"{d}/hf"))
+    assert json.load(open(f"{d}/hf/config.json"))["hidden_size"] == 32
+    export_hf_to_lm.main(C.decode(export_hf_to_lm.ImportHfConfig, {"hf_checkpoint": f"{d}/hf", "output_path": f"{d}/imported", "dtype": "float32",
+                                                                   "tokenizer": f"{d}/tok"}))
+    assert os.path.exists(f"{d}/imported/metadata.json")
+
+    # ---- sample_lm from the exported directory
+    capsys.readouterr()
+    sample_lm.main(C.decode(sample_lm.SampleLmConfig, {"hf_checkpoint": f"{d}/hf", "tokenizer": f"{d}/tok", "model": _base(d)["model"],
+                                                       "prompts": ["the quick brown", "seven small"], "max_new_tokens": 6, "n_rounds": 1,
+                                                       "stop_sequence": None, "temperature": 0.0,
+                                                       "engine": {"max_seqs": 4, "page_size": 8, "max_pages": 32, "max_pages_per_seq": 4, "max_rounds": 4},
+                                                       "trainer": {"require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": f"{d}/logs",
+                                                                   "mp": "f32"}}))
+    out = capsys.readouterr().out
+    assert "Generated text for 0" in out and "Generated text for 1" in out
+
+    # ---- viz_logprobs writes the page
+    vcfg = {"checkpoint_path": ck, "path": f"{d}/lp.html", "data": _base(d)["data"], "model": _base(d)["model"], "num_docs": 4,
+            "trainer": {"require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": f"{d}/logs", "per_device_eval_parallelism": 4}}
+    viz_logprobs.main(C.decode(viz_logprobs.VizLmConfig, vcfg))
+    assert "<span" in open(f"{d}/lp.html").read()
+
+    # ---- lora_lm on the exported weights, writing an adapter
+    lcfg = {"initialize_from_hf": f"{d}/hf", "data": _base(d)["data"], "lora": {"r": 4, "alpha": 8.0},
+            "trainer": dict(_base(d, 2)["trainer"], id="lora"), "optimizer": {"learning_rate": 1e-3, "warmup": 0.0},
+            "peft_save_path": f"{d}/peft", "hf_save_steps": 2}
+    lora_lm.main(C.decode(lora_lm.LoraLmConfig, lcfg))
+    saved = [os.path.join(r, f) for r, _, fs in os.walk(f"{d}/peft") for f in fs]
+    assert any(f.endswith("adapter_config.json") for f in saved), saved
