@@ -124,3 +124,27 @@ def test_chain(workdir, monkeypatch, capsys):
     lora_lm.main(C.decode(lora_lm.LoraLmConfig, lcfg))
     saved = [os.path.join(r, f) for r, _, fs in os.walk(f"{d}/peft") for f in fs]
     assert any(f.endswith("adapter_config.json") for f in saved), saved
+
+
+def test_sft_on_chat_data_from_the_exported_weights(workdir, monkeypatch):
+    """Runs after ``test_chain`` (it fine-tunes the Hugging Face directory that test exported)."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json"):
+        pytest.skip("needs the export of test_chain")
+    from levanter_b200.main import sft
+
+    rng = np.random.default_rng(1)
+    words = "the quick brown fox jumps over the lazy dog".split()
+    with open(f"{d}/chat.jsonl", "w") as f:
+        for _ in range(64):
+            q, a = " ".join(rng.choice(words, 5)), " ".join(rng.choice(words, 6))
+            f.write(json.dumps({"messages": [{"role": "user", "content": q}, {"role": "assistant", "content": a}]}) + "\n")
+    cfg = {"initialize_from_hf": f"{d}/hf", "model_name_or_path": f"{d}/hf", "tokenizer": f"{d}/tok", "max_seq_len": 32,
+           "dataset_type": "chat_jsonl", "chat_train_urls": [f"{d}/chat.jsonl"], "supervised_data": {"cache_dir": f"{d}/sft_cache"},
+           "trainer": dict(_base(d, 2)["trainer"], id="sft"), "optimizer": {"learning_rate": 1e-4, "warmup": 0.0},
+           "hf_save_path": f"{d}/sft_hf", "hf_save_steps": 2}
+    sft.train(C.decode(sft.SFTConfig, cfg))
+    saved = [os.path.join(r, f) for r, _, fs in os.walk(f"{d}/sft_hf") for f in fs]
+    assert any(f.endswith(".safetensors") for f in saved), saved
