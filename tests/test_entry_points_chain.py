@@ -148,3 +148,27 @@ def test_sft_on_chat_data_from_the_exported_weights(workdir, monkeypatch):
     sft.train(C.decode(sft.SFTConfig, cfg))
     saved = [os.path.join(r, f) for r, _, fs in os.walk(f"{d}/sft_hf") for f in fs]
     assert any(f.endswith(".safetensors") for f in saved), saved
+
+
+def test_sft_mixture_of_two_chat_sets(workdir, monkeypatch):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json"):
+        pytest.skip("needs the export of test_chain")
+    from levanter_b200.main import sft_mixture
+
+    rng = np.random.default_rng(2)
+    words = "seven small birds sing near a quiet river at dawn".split()
+    for name in ("a", "b"):
+        with open(f"{d}/chat_{name}.jsonl", "w") as f:
+            for _ in range(40):
+                q, a = " ".join(rng.choice(words, 4)), " ".join(rng.choice(words, 5))
+                f.write(json.dumps({"messages": [{"role": "user", "content": q}, {"role": "assistant", "content": a}]}) + "\n")
+    cfg = {"initialize_from_hf": f"{d}/hf", "model_name_or_path": f"{d}/hf", "tokenizer": f"{d}/tok", "max_seq_len": 32,
+           "dataset_type": "chat_jsonl", "mixture_block_size": 16, "mixture_weights": {"a": 0.75, "b": 0.25},
+           "supervised_data": {"a": {"cache_dir": f"{d}/mix_cache_a", "train_urls": [f"{d}/chat_a.jsonl"]},
+                               "b": {"cache_dir": f"{d}/mix_cache_b", "train_urls": [f"{d}/chat_b.jsonl"]}},
+           "trainer": dict(_base(d, 2)["trainer"], id="sftmix"), "optimizer": {"learning_rate": 1e-4, "warmup": 0.0}}
+    sft_mixture.train(C.decode(sft_mixture.SFTMixtureConfig, cfg))
+    assert os.path.isdir(f"{d}/mix_cache_a") and os.path.isdir(f"{d}/mix_cache_b")
