@@ -327,8 +327,9 @@ async def _create_chat_completion(ctx: InferenceContext, request: ChatCompletion
         logger.warning(f"chat template failed ({e}); using a plain transcript")
         text = "".join(f"{m['role']}: {m.get('content', '')}\n" for m in messages) + "assistant: "
         prompt_tokens = ctx.tokenizer(text)["input_ids"]
-    if isinstance(prompt_tokens, dict):
+    if hasattr(prompt_tokens, "keys"):  # a dict, or the tokenizer's mapping class (not a dict subclass) in newer releases
         prompt_tokens = prompt_tokens["input_ids"]
+    prompt_tokens = [int(t) for t in prompt_tokens]
     n = request.n or 1
     responses = await _await_responses(ctx, list(prompt_tokens), request, n, request.logprobs)
     choices = []

@@ -172,3 +172,38 @@ def test_sft_mixture_of_two_chat_sets(workdir, monkeypatch):
            "trainer": dict(_base(d, 2)["trainer"], id="sftmix"), "optimizer": {"learning_rate": 1e-4, "warmup": 0.0}}
     sft_mixture.train(C.decode(sft_mixture.SFTMixtureConfig, cfg))
     assert os.path.isdir(f"{d}/mix_cache_a") and os.path.isdir(f"{d}/mix_cache_b")
+
+
+def test_inference_repl_loads_chats_and_runs_a_batch_file(workdir, monkeypatch, capsys):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json"):
+        pytest.skip("needs the export of test_chain")
+    import transformers
+
+    from levanter_b200.main import inference_repl as R
+
+    # the chat routes need a chat template; give the tiny tokenizer a minimal one
+    tok = transformers.AutoTokenizer.from_pretrained(f"{d}/tok")
+    tok.chat_template = "{% for m in messages %}{{ m['role'] }}: {{ m['content'] }}\n{% endfor %}{% if add_generation_prompt %}assistant:{% endif %}"
+    tok.save_pretrained(f"{d}/tok_chat")
+    cfg = C.decode(R.InferenceReplConfig, {"model": _base(d)["model"], "tokenizer": f"{d}/tok_chat", "max_tokens": 5, "temperature": 0.0,
+                                          "trainer": {"require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": f"{d}/logs", "mp": "f32"}})
+    cfg.trainer.initialize()
+    ctx = R.ReplContext(cfg)
+    try:
+        ctx.execute("load", f"{d}/hf")
+        resp = ctx.execute("chat", "the quick brown")
+        assert resp["usage"]["completion_tokens"] >= 1 and isinstance(resp["choices"][0]["message"]["content"], str)
+        with open(f"{d}/batch.jsonl", "w") as f:
+            f.write(json.dumps({"prompt": "seven small birds"}) + "\n")
+            f.write(json.dumps({"messages": [{"role": "user", "content": "a quiet river"}]}) + "\n")
+        outs = ctx.execute("batch", f"{d}/batch.jsonl")
+        assert len(outs) == 2 and all(o["choices"] for o in outs)
+        ctx.execute("nonsense")
+        assert "Unknown command" in capsys.readouterr().out
+    finally:
+        ctx.execute("unload")
+        if ctx.server is not None:
+            ctx.server.shutdown() if hasattr(ctx.server, "shutdown") else None
