@@ -207,3 +207,59 @@ def test_inference_repl_loads_chats_and_runs_a_batch_file(workdir, monkeypatch, 
         ctx.execute("unload")
         if ctx.server is not None:
             ctx.server.shutdown() if hasattr(ctx.server, "shutdown") else None
+
+
+def test_train_lm_on_a_staged_mixture_with_ema_skip_step_and_gpt2(workdir, monkeypatch):
+    """A second training configuration end to end: GPT-2 family, a two-source mixture whose weights change at a step boundary,
+    exponential moving average of the weights, the skip-step guard, tagged evaluation during the run."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import train_lm
+
+    cfg = yaml.safe_load(f"""
+data:
+  tokenizer: {d}/tok
+  cache_dir: {d}/mix_lm_cache
+  mixture_block_size: 8
+  configs:
+    first:
+      train_urls: ["{d}/shard0.jsonl"]
+      validation_urls: ["{d}/shard1.jsonl"]
+      tags: [alpha]
+    second:
+      train_urls: ["{d}/shard1.jsonl"]
+      validation_urls: ["{d}/shard0.jsonl"]
+      tags: [beta]
+  train_weights:
+    - [0, {{first: 1.0, second: 0.0}}]
+    - [2, {{first: 0.25, second: 0.75}}]
+model:
+  type: gpt2
+  seq_len: 32
+  hidden_dim: 32
+  num_layers: 2
+  num_heads: 2
+  gradient_checkpointing: false
+trainer:
+  id: mixrun
+  num_train_steps: 4
+  train_batch_size: 8
+  require_accelerator: false
+  tracker: {{type: noop}}
+  log_dir: {d}/logs
+  steps_per_eval: 2
+  max_eval_batches: 1
+  model_averaging: {{type: ema, beta: 0.9}}
+  checkpointer:
+    base_path: {d}/ckpt
+    save_interval: 10h
+optimizer:
+  learning_rate: 1.0e-3
+  warmup: 0.0
+  skip_bad_steps: true
+""")
+    train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
+    assert discover_latest_checkpoint(f"{d}/ckpt/mixrun") is not None
+    assert os.path.isdir(f"{d}/mix_lm_cache/first/train") and os.path.isdir(f"{d}/mix_lm_cache/second/train")
