@@ -263,3 +263,35 @@ optimizer:
     train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
     assert discover_latest_checkpoint(f"{d}/ckpt/mixrun") is not None
     assert os.path.isdir(f"{d}/mix_lm_cache/first/train") and os.path.isdir(f"{d}/mix_lm_cache/second/train")
+
+
+_FAMILIES = {
+    "mistral": {"type": "mistral", "seq_len": 32, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 2, "num_heads": 2, "num_kv_heads": 1},
+    "mixtral": {"type": "mixtral", "seq_len": 32, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 2, "num_heads": 2, "num_kv_heads": 2,
+                "n_routed_experts": 4, "num_experts_per_tok": 2},
+    "gemma2": {"type": "gemma2", "seq_len": 32, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 2, "num_heads": 2, "num_kv_heads": 1,
+               "head_dim": 16},
+    "qwen3": {"type": "qwen3", "seq_len": 32, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 2, "num_heads": 2, "num_kv_heads": 1,
+              "head_dim": 16},
+    "olmo2": {"type": "olmo2", "seq_len": 32, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 2, "num_heads": 2, "num_kv_heads": 2},
+    "gated_deltanet": {"type": "gated_deltanet", "seq_len": 32, "hidden_dim": 32, "num_layers": 2, "num_heads": 2, "head_k_dim": 16, "head_v_dim": 16},
+    "gpt2_hyena": {"type": "gpt2_hyena", "num_layers": 2, "hyena": {"seq_len": 32, "hidden_dim": 32, "filter_order": 8}},
+}
+
+
+@pytest.mark.parametrize("family", sorted(_FAMILIES))
+def test_every_model_family_trains_through_the_entry_point(workdir, monkeypatch, family):
+    """Two optimizer steps and an evaluation of each family through ``train_lm`` (configuration decoding, the trainer, the
+    sharded engine's single-process path, checkpointing)."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import train_lm
+
+    cfg = _base(d, 2)
+    cfg["model"] = dict(_FAMILIES[family], gradient_checkpointing=False)
+    cfg["trainer"]["id"] = f"fam_{family}"
+    cfg["trainer"]["steps_per_eval"] = 2
+    train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
+    assert discover_latest_checkpoint(f"{d}/ckpt/fam_{family}") is not None
