@@ -318,3 +318,51 @@ def test_every_optimizer_trains_through_the_entry_point(workdir, monkeypatch, op
     monkeypatch.setattr(train_lm.Trainer, "train", spy)
     train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
     assert len(losses) >= 3 and all(np.isfinite(losses)), losses  # (hooks also run once more, forced, after the last step)
+
+
+def test_two_process_launch_through_torchrun_and_resume_on_one(workdir):
+    """The documented launch line on a CPU host: two processes (gloo), sharded state, one checkpoint; then the same run continues
+    as a single process from that checkpoint."""
+    import subprocess
+    import sys
+
+    d = str(workdir)
+    cfg = _base(d, 3)
+    cfg["trainer"]["id"] = "launch2"
+    path = f"{d}/launch2.yaml"
+    yaml.safe_dump(cfg, open(path, "w"))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29611",
+           "-m", "levanter_b200.main.train_lm", "--config_path", path]
+    r = subprocess.run(cmd, env=env, cwd=d, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+
+    ck = discover_latest_checkpoint(f"{d}/ckpt/launch2")
+    assert ck is not None and ck.endswith("step-2"), ck
+    r = subprocess.run([sys.executable, "-m", "levanter_b200.main.train_lm", "--config_path", path, "--trainer.num_train_steps", "5"], env=env, cwd=d,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert discover_latest_checkpoint(f"{d}/ckpt/launch2").endswith("step-4")
+    assert "Resuming" in r.stderr or "esum" in r.stderr or "step-2" in r.stderr
+
+
+def test_train_lm_starts_from_hugging_face_weights_and_from_a_checkpoint(workdir, monkeypatch):
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json"):
+        pytest.skip("needs the export of test_chain")
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import train_lm
+
+    cfg = _base(d, 2)
+    cfg["trainer"]["id"] = "from_hf"
+    cfg.update(initialize_from_hf=f"{d}/hf", use_hf_model_config=True)
+    train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
+    assert discover_latest_checkpoint(f"{d}/ckpt/from_hf") is not None
+    cfg = _base(d, 2)
+    cfg["trainer"]["id"] = "warm"
+    cfg["trainer"]["initialize_from"] = discover_latest_checkpoint(f"{d}/ckpt/chain")
+    train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
+    assert discover_latest_checkpoint(f"{d}/ckpt/warm") is not None
