@@ -366,3 +366,36 @@ def test_train_lm_starts_from_hugging_face_weights_and_from_a_checkpoint(workdir
     cfg["trainer"]["initialize_from"] = discover_latest_checkpoint(f"{d}/ckpt/chain")
     train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
     assert discover_latest_checkpoint(f"{d}/ckpt/warm") is not None
+
+
+@pytest.mark.parametrize("fmt", ["chat", "supervised"])
+def test_train_lm_on_chat_and_supervised_formats_with_packing(workdir, monkeypatch, fmt):
+    """The two other dataset formats through ``train_lm``: chat transcripts (assistant turns carry the loss, a template with a
+    generation block) and prompt / response pairs, both packed several examples to a sequence."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    import transformers
+
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import train_lm
+
+    tok = transformers.AutoTokenizer.from_pretrained(f"{d}/tok")
+    tok.chat_template = ("{% for m in messages %}{% if m['role'] == 'assistant' %}{% generation %}{{ m['content'] }}</s>{% endgeneration %}"
+                         "{% else %}{{ m['role'] }}: {{ m['content'] }}\n{% endif %}{% endfor %}")
+    tok.save_pretrained(f"{d}/tok_gen")
+    rng = np.random.default_rng(3)
+    words = "the quick brown fox jumps over the lazy dog".split()
+    for split in ("train", "val"):
+        with open(f"{d}/{fmt}_{split}.jsonl", "w") as f:
+            for _ in range(96):
+                q, a = " ".join(rng.choice(words, 4)), " ".join(rng.choice(words, 5))
+                row = {"messages": [{"role": "user", "content": q}, {"role": "assistant", "content": a}]} if fmt == "chat" else {"prompt": q, "response": a}
+                f.write(json.dumps(row) + "\n")
+    cfg = _base(d, 2)
+    cfg["trainer"]["id"] = f"fmt_{fmt}"
+    cfg["data"] = {"tokenizer": f"{d}/tok_gen", "cache_dir": f"{d}/cache_{fmt}", "train_urls": [f"{d}/{fmt}_train.jsonl"],
+                   "validation_urls": [f"{d}/{fmt}_val.jsonl"],
+                   "format": {"type": "chat"} if fmt == "chat" else {"type": "supervised", "input_field": "prompt", "output_field": "response"}}
+    train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
+    assert discover_latest_checkpoint(f"{d}/ckpt/fmt_{fmt}") is not None
