@@ -105,17 +105,20 @@ def _sniff_format_for_dataset(url: str) -> str:
     for comp in (".gz", ".zst", ".zstd", ".bz2", ".xz"):
         if base.endswith(comp):
             base = base[: -len(comp)]
-    for ext, fmt in ((".jsonl", "jsonl"), (".ndjson", "jsonl"), (".json", "json"), (".txt", "txt"), (".parquet", "parquet")):
+    for ext, fmt in ((".jsonl", "jsonl"), (".ndjson", "jsonl"), (".txt", "txt"), (".parquet", "parquet")):
         if base.endswith(ext):
             return fmt
-    # look at the content: one JSON object per line, or one JSON array
+    # ".json" is used for both one JSON document and one object per line, and a file without a known extension may be
+    # either: look at the content.  "[" or "{" + newline starts a (pretty-printed) document, "{" + anything else a line.
     with _open_text(url) as f:
-        head = f.read(2048).lstrip()
-    if head.startswith("["):
+        head = f.read(2048).lstrip(" \t")
+    if head.startswith("[") or head.startswith("{\n") or head.startswith("{\r"):
         return "json"
     if head.startswith("{"):
         return "jsonl"
-    return "txt"
+    if base.endswith(".json"):
+        return "json"
+    raise ValueError(f"Unknown format for {url}: expected .jsonl, .json, .txt or .parquet (optionally compressed)")
 
 
 def _iter_rows(url: str, row: int, columns=None) -> Iterator[dict]:

@@ -265,6 +265,9 @@ class TreeCache(AsyncDataset[T_co]):
                 raise FileNotFoundError(f"no cache data under {self.cache_dir}")
         return self._store  # type: ignore
 
+    async def store_async(self) -> TreeStore:
+        return await asyncio.get_running_loop().run_in_executor(None, lambda: self.store)
+
     @property
     def is_finished(self) -> bool:
         return self.ledger is not None and self.ledger.is_finished
@@ -421,7 +424,12 @@ class _CacheBuilder:
 
     def raise_if_failed(self) -> None:
         if self._error is not None:
-            raise RuntimeError(f"cache build at {self.cache_dir} failed") from self._error
+            # the builder's own exception, so that callers can catch what the source or the processor raised
+            err = self._error
+            note = f"raised by the cache build at {self.cache_dir}"
+            if isinstance(err, Exception) and note not in getattr(err, "__notes__", ()):
+                err.add_note(note)
+            raise err
 
     # -- threads ------------------------------------------------------------------------------------------------
     def _take_shard(self) -> Optional[str]:

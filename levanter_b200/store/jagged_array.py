@@ -91,6 +91,10 @@ class JaggedArrayStore:
         shapes = _open("shapes", [0, item_rank - 1], [DEFAULT_CHUNK_SIZE, item_rank - 1], np.int64) if item_rank > 1 else None
         return JaggedArrayStore(offsets, data, shapes, item_rank, cache_metadata and mode == "r")
 
+    @staticmethod
+    async def open_async(path: str, *, mode: str = "a", item_rank: int = 1, dtype, cache_metadata: bool = False) -> "JaggedArrayStore":
+        return JaggedArrayStore.open(path, mode=mode, item_rank=item_rank, dtype=dtype, cache_metadata=cache_metadata)
+
     # -- sizes ---------------------------------------------------------------------------------------------------
     @property
     def num_rows(self) -> int:
@@ -230,6 +234,9 @@ class JaggedArrayStore:
 
     async def get_batch(self, indices: Sequence[int]) -> List[np.ndarray]:
         return self.get_batch_sync(indices)
+
+    async def get_item_async(self, item):
+        return self[item]
 
     def __getitem__(self, item):
         if isinstance(item, slice):

@@ -88,6 +88,9 @@ class TreeStore(Generic[T]):
         for store in self.tree.values():
             store.trim_to_size(size)
 
+    async def trim_to_size_async(self, size: int) -> None:
+        self.trim_to_size(size)
+
     def reload(self) -> "TreeStore":
         return TreeStore({p: s.reload() for p, s in self.tree.items()}, self.exemplar, self.path, self.mode)
 
@@ -99,6 +102,7 @@ class TreeStore(Generic[T]):
         return len(self)
 
     def get_batch_sync(self, indices) -> List[T]:
+        indices = list(indices)
         cols = {p: s.get_batch_sync(indices) for p, s in self.tree.items()}
         return [_unflatten(self.exemplar, {p: c[i] for p, c in cols.items()}) for i in range(len(indices))]
 

@@ -122,7 +122,7 @@ def test_builder_error_reaches_reader(tmp_path):
     with open(f"{d}/bad.jsonl", "w") as f:
         f.write(json.dumps({"text": "1 2 x"}) + "\n")
     proc = BatchTokenizer(PassthroughTokenizer(10), enforce_bos=False, enforce_eos=False)
-    with pytest.raises(RuntimeError):
+    with pytest.raises(ValueError, match="whitespace-separated integers"):
         build_or_load_cache(d + "/c", UrlDataSource([f"{d}/bad.jsonl"]), proc)
 
 
