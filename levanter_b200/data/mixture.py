@@ -106,12 +106,12 @@ class MixtureDataset(AsyncDataset[T]):
         return st
 
     def _block_assignments(self, block: int) -> np.ndarray:
-        """Packed ids ``(dataset << 16) + position-in-block`` for every slot of ``block`` (position counts per source)."""
+        """Packed ids ``(dataset << 32) + position-in-block`` for every slot of ``block`` (position counts per source)."""
         stage = self._stage_of_block(block)
         counts = self._counts_per_block[stage]
         ids = np.concatenate([np.full(c, d, dtype=np.int64) for d, c in enumerate(counts)])
         pos = np.concatenate([np.arange(c, dtype=np.int64) for c in counts])
-        packed = (ids << 16) + pos
+        packed = (ids << 32) + pos
         if self.randomize_blocks:
             perm = Permutation.make("feistel", len(packed), _fold_in(self.key, block))
             packed = packed[perm(np.arange(len(packed)))]
@@ -163,7 +163,7 @@ class MixtureDataset(AsyncDataset[T]):
             if block not in cache:
                 cache[block] = self._block_assignments(block)
             packed = int(cache[block][off])
-            ds, pos = packed >> 16, packed & 0xFFFF
+            ds, pos = packed >> 32, packed & 0xFFFFFFFF
             per_ds.setdefault(ds, []).append((out_pos, self._index_into_dataset(block, ds, pos)))
         names = list(self.datasets.keys())
         out: List[Optional[T]] = [None] * len(indices)
