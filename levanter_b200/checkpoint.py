@@ -284,6 +284,8 @@ def load_model_params(model: torch.nn.Module, checkpoint_path: str, prefix: str 
                 missing.append(name)
                 continue
             p.data.copy_(t.to(device=p.device, dtype=p.dtype))
+    # a checkpoint written without the skip-step wrapper has no window: it starts empty
+    missing = [m for m in missing if not m.rsplit(".", 1)[-1].startswith("_skipstep_")]
     if missing and not allow_partial:
         raise FileNotFoundError(f"Missing parameters in checkpoint {checkpoint_path}: {missing[:5]}{'...' if len(missing) > 5 else ''}")
     return missing
@@ -358,15 +360,9 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
                         a = fo - slot.offset
                         leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype).reshape(leaf.shape))
                     return x
-                j = (lambda k: f"{p}.{k}" if p else str(k))
-                if isinstance(x, tuple) and hasattr(x, "_fields"):
-                    return type(x)(*[rec(getattr(x, f), j(f)) for f in x._fields])
-                if isinstance(x, dict):
-                    return {k: rec(v, j(k)) for k, v in x.items()}
-                if isinstance(x, tuple):
-                    return tuple(rec(v, j(i)) for i, v in enumerate(x))
-                if isinstance(x, list):
-                    return [rec(v, j(i)) for i, v in enumerate(x)]
+                children = tss.keyed_children(x)
+                if children is not None:
+                    return tss.rebuild_from_children(x, [rec(v, f"{p}.{k}" if p else str(k)) for k, v in children])
                 if isinstance(x, (int, float, bool)) or isinstance(x, torch.Tensor):
                     t = tss.read_leaf(checkpoint_path, p)
                     if t is None:
@@ -400,6 +396,8 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
     key = tss.read_leaf(checkpoint_path, "training_key")
     if key is not None:
         state.training_key = key.to(torch.int64).reshape(-1)[:2]
+    # a checkpoint written without the skip-step wrapper has no window: it starts empty
+    missing = [m for m in missing if not m.rsplit(".", 1)[-1].startswith("_skipstep_")]
     if missing and not allow_partial:
         raise FileNotFoundError(f"Checkpoint {checkpoint_path} is missing leaves: {missing[:5]}{'...' if len(missing) > 5 else ''}")
     if missing:

@@ -16,6 +16,9 @@ from . import transforms as T
 from .transforms import GradientTransformation
 
 
+_SKIP_FIELDS = ("losses", "grad_norms", "valid_mask", "current_idx", "count")
+
+
 class SkipStepState(NamedTuple):
     inner_opt_state: Any
     losses: torch.Tensor
@@ -23,6 +26,24 @@ class SkipStepState(NamedTuple):
     valid_mask: torch.Tensor
     current_idx: int
     count: int
+
+    # Checkpoint layout: the children of the inner state keep the key paths they have without this wrapper and the window
+    # sits beside them as ``_skipstep_*`` leaves, so either kind of run can start from the other kind's checkpoint.
+    def checkpoint_children(self):
+        from ..tensorstore_serialization import keyed_children
+
+        inner = keyed_children(self.inner_opt_state)
+        if inner is None:  # the inner state is one leaf (or nothing): it has no children to splice in
+            inner = [("inner_opt_state", self.inner_opt_state)]
+        return list(inner) + [(f"_skipstep_{f}", getattr(self, f)) for f in _SKIP_FIELDS]
+
+    def with_checkpoint_children(self, values):
+        from ..tensorstore_serialization import keyed_children, rebuild_from_children
+
+        values = list(values)
+        n = len(values) - len(_SKIP_FIELDS)
+        inner = values[0] if keyed_children(self.inner_opt_state) is None else rebuild_from_children(self.inner_opt_state, values[:n])
+        return SkipStepState(inner, *values[n:])
 
 
 def _masked_mean_std(x: torch.Tensor, mask: torch.Tensor):

@@ -60,32 +60,62 @@ def layouts_of(model: torch.nn.Module) -> Dict[str, ParamLayout]:
 
 
 # ------------------------------------------------------------------------------------------------ key paths
+_LEAF_TYPES = (torch.Tensor, np.ndarray, int, float, bool, np.generic)
+
+
+def keyed_children(x) -> Optional[List[Tuple[Any, Any]]]:
+    """``[(key, child)]`` of a container node of a state tree, ``None`` for leaves and static values.  Keys are NamedTuple /
+    dataclass field names, dict keys and sequence indices; an object with ``checkpoint_children()`` chooses its own keys."""
+    if x is None or isinstance(x, _LEAF_TYPES) or isinstance(x, DeferredLeaf):
+        return None
+    if hasattr(x, "checkpoint_children"):
+        return list(x.checkpoint_children())
+    if isinstance(x, tuple) and hasattr(x, "_fields"):
+        return [(f, getattr(x, f)) for f in x._fields]
+    if is_dataclass(x) and not isinstance(x, type):
+        return [(f.name, getattr(x, f.name)) for f in fields(x)]
+    if isinstance(x, dict):
+        return list(x.items())
+    if isinstance(x, (list, tuple)):
+        return list(enumerate(x))
+    return None
+
+
+def rebuild_from_children(x, values: Sequence[Any]):
+    """The container ``x`` with its children (in :func:`keyed_children` order) replaced by ``values``."""
+    values = list(values)
+    if hasattr(x, "with_checkpoint_children"):
+        return x.with_checkpoint_children(values)
+    if isinstance(x, tuple) and hasattr(x, "_fields"):
+        return type(x)(*values)
+    if is_dataclass(x) and not isinstance(x, type):
+        import dataclasses
+
+        return dataclasses.replace(x, **{f.name: v for f, v in zip(fields(x), values)})
+    if isinstance(x, dict):
+        return {k: v for k, v in zip(x.keys(), values)}
+    if isinstance(x, tuple):
+        return tuple(values)
+    if isinstance(x, list):
+        return values
+    raise TypeError(f"not a container: {type(x)}")
+
+
 def leaf_key_paths(tree: Any, prefix: str = "") -> List[Tuple[str, Any]]:
     """Flatten ``tree`` into ``(dotted key path, leaf)`` pairs; ``None`` leaves are skipped
     (src/levanter/utils/jax_utils.py:150-223)."""
     out: List[Tuple[str, Any]] = []
 
-    def join(p, k):
-        return f"{p}.{k}" if p else str(k)
-
     def rec(x, p):
         if x is None:
             return
-        if isinstance(x, (torch.Tensor, np.ndarray, DeferredLeaf, int, float, bool, np.generic)):
+        if isinstance(x, _LEAF_TYPES) or isinstance(x, DeferredLeaf):
             out.append((p, x))
-        elif isinstance(x, tuple) and hasattr(x, "_fields"):
-            for f in x._fields:
-                rec(getattr(x, f), join(p, f))
-        elif is_dataclass(x) and not isinstance(x, type):
-            for f in fields(x):
-                rec(getattr(x, f.name), join(p, f.name))
-        elif isinstance(x, dict):
-            for k, v in x.items():
-                rec(v, join(p, k))
-        elif isinstance(x, (list, tuple)):
-            for i, v in enumerate(x):
-                rec(v, join(p, i))
+            return
+        children = keyed_children(x)
         # anything else (callables, strings) is static configuration, not state
+        for k, v in children or ():
+            rec(v, f"{p}.{k}" if p else str(k))
 
     rec(tree, prefix)
     return out
@@ -382,15 +412,9 @@ def tree_deserialize_leaves_tensorstore(checkpoint_dir: str, tree: Any, *, allow
             if isinstance(x, torch.Tensor):
                 return t.to(dtype=x.dtype).reshape(x.shape).to(x.device)
             return t.numpy()
-        j = (lambda k: f"{p}.{k}" if p else str(k))
-        if isinstance(x, tuple) and hasattr(x, "_fields"):
-            return type(x)(*[rec(getattr(x, f), j(f)) for f in x._fields])
-        if isinstance(x, dict):
-            return {k: rec(v, j(k)) for k, v in x.items()}
-        if isinstance(x, tuple):
-            return tuple(rec(v, j(i)) for i, v in enumerate(x))
-        if isinstance(x, list):
-            return [rec(v, j(i)) for i, v in enumerate(x)]
-        return x
+        children = keyed_children(x)
+        if children is None:
+            return x
+        return rebuild_from_children(x, [rec(v, f"{p}.{k}" if p else str(k)) for k, v in children])
 
     return rec(tree, "")
