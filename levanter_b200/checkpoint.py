@@ -284,8 +284,6 @@ def load_model_params(model: torch.nn.Module, checkpoint_path: str, prefix: str 
                 missing.append(name)
                 continue
             p.data.copy_(t.to(device=p.device, dtype=p.dtype))
-    # a checkpoint written without the skip-step wrapper has no window: it starts empty
-    missing = [m for m in missing if not m.rsplit(".", 1)[-1].startswith("_skipstep_")]
     if missing and not allow_partial:
         raise FileNotFoundError(f"Missing parameters in checkpoint {checkpoint_path}: {missing[:5]}{'...' if len(missing) > 5 else ''}")
     return missing
