@@ -255,7 +255,9 @@ def load_checkpoint(state, checkpoint_path: PathLike, *, subpath: Optional[str] 
                     allow_partial: bool = False):
     """Restore a ``TrainerState`` (or, with ``subpath="model"``, just a model) in place from a checkpoint directory.
 
-    ``state`` may be a ``TrainerState`` or an ``nn.Module``.  Raises ``FileNotFoundError`` when nothing is found."""
+    ``state`` may be a ``TrainerState``, an ``nn.Module``, or any tree of tensors and scalars written by
+    :func:`save_checkpoint` (returned as a new tree; with ``allow_partial`` leaves that are not in the checkpoint keep their
+    value).  Raises ``FileNotFoundError`` when nothing is found."""
     checkpoint_path = str(checkpoint_path)
     if discover_latest:
         found = discover_latest_checkpoint(checkpoint_path)
@@ -267,6 +269,9 @@ def load_checkpoint(state, checkpoint_path: PathLike, *, subpath: Optional[str] 
         prefix = subpath or ""
         load_model_params(state, checkpoint_path, prefix, allow_partial=allow_partial)
         return state
+    if not hasattr(state, "engine"):
+        where = checkpoint_path if not subpath else fsspec_utils.join_path(checkpoint_path, subpath.replace(".", "/"))
+        return tss.tree_deserialize_leaves_tensorstore(where, state, allow_missing=allow_partial)
     return _load_trainer_state(state, checkpoint_path, allow_partial=allow_partial)
 
 
