@@ -384,7 +384,14 @@ class HFCheckpointConverter:
 
                 fs, plain = fsspec.core.url_to_fs(str(path))
                 fs.makedirs(plain, exist_ok=True)
-                fs.put(local, plain, recursive=True)
+                # file by file: a recursive put of a directory into an existing one nests it under its own name
+                for root, _, files in os.walk(local):
+                    rel = os.path.relpath(root, local)
+                    dest = plain.rstrip("/") if rel == "." else f"{plain.rstrip('/')}/{rel}"
+                    if rel != ".":
+                        fs.makedirs(dest, exist_ok=True)
+                    for name in files:
+                        fs.put_file(os.path.join(root, name), f"{dest}/{name}")
                 shutil.rmtree(local, ignore_errors=True)
             if upload_to_hf:
                 try:
