@@ -87,3 +87,52 @@ def test_stacked_reference_layout_for_layer_parameters(tmp_path):
     assert torch.equal(got, params[name])
     stacked = ZarrArray.open(tss._fs_path(str(tmp_path), f"model.{key}"))
     assert stacked.shape[0] == 3
+
+
+def test_model_optimizer_state_key_and_step_after_a_few_updates(tmp_path):
+    """A tuple of (parameters, optimizer state, key, step) after three Adam steps comes back exactly, into a tree built from
+    another seed."""
+    from levanter_b200.optim import transforms as T
+
+    def make(seed):
+        g = torch.Generator().manual_seed(seed)
+        params = {"l1.weight": torch.randn(4, 2, generator=g), "l1.bias": torch.randn(4, generator=g), "l2.weight": torch.randn(1, 4, generator=g)}
+        opt = T.chain(T.scale_by_adam(0.9, 0.95, 1e-8), T.scale(-1e-2))
+        return params, opt, opt.init(params), torch.tensor([0, seed], dtype=torch.int64)
+
+    params, opt, state, key = make(0)
+    first = {k: v.clone() for k, v in params.items()}
+    for i in range(3):
+        grads = {k: torch.full_like(v, 0.1 * (i + 1)) for k, v in params.items()}
+        updates, state = opt.update(grads, state, params)
+        params = {k: params[k] + updates[k] for k in params}
+    assert not torch.equal(params["l1.weight"], first["l1.weight"])
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path), (params, state, key, 3))
+    other_params, _, other_state, other_key = make(1)
+    r_params, r_state, r_key, r_step = tss.tree_deserialize_leaves_tensorstore(str(tmp_path), (other_params, other_state, other_key, 0))
+    assert r_step == 3 and torch.equal(r_key, key)
+    for k in params:
+        assert torch.equal(r_params[k], params[k])
+    for (pa, a), (pb, b) in zip(tss.leaf_key_paths(r_state), tss.leaf_key_paths(state)):
+        assert pa == pb and torch.equal(torch.as_tensor(a), torch.as_tensor(b))
+    assert type(r_state) is type(state)
+
+
+def test_dataclass_nodes_none_leaves_and_leaves_missing_on_disk(tmp_path):
+    import dataclasses
+    from typing import Any
+
+    @dataclasses.dataclass
+    class Module:
+        a: Any
+        b: Any
+
+    tss.tree_serialize_leaves_tensorstore(str(tmp_path / "m"), Module(a=None, b=torch.zeros(10)))
+    assert sorted(os.listdir(tmp_path / "m")) == ["b"]  # nothing is written for a None leaf
+    back = tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "m"), Module(a=None, b=torch.ones(10)))
+    assert isinstance(back, Module) and back.a is None and torch.equal(back.b, torch.zeros(10))
+    wants_a = Module(a=torch.full((10,), 4.0), b=torch.ones(10))
+    with pytest.raises(FileNotFoundError):
+        tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "m"), wants_a)
+    partial = tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "m"), wants_a, allow_missing=True)
+    assert torch.equal(partial.a, torch.full((10,), 4.0)) and torch.equal(partial.b, torch.zeros(10))
