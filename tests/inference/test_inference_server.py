@@ -71,6 +71,47 @@ def test_logprobs_n_and_chat(server):
         assert len(cb["choices"][0]["logprobs"]["content"]) == cb["usage"]["completion_tokens"]
 
 
+def test_logprobs_are_reproducible_and_differ_between_generations(server):
+    with TestClient(server.app) as client:
+        req = {"model": "m", "prompt": "Once upon a time", "max_tokens": 4, "temperature": 0.0, "logprobs": True, "seed": 12345}
+        a, b = (client.post("/v1/completions", json=req).json()["choices"][0]["logprobs"] for _ in range(2))
+        assert a["tokens"] == b["tokens"] and len(a["tokens"]) == len(a["token_logprobs"]) > 0
+        assert all(abs(x - y) < 1e-6 for x, y in zip(a["token_logprobs"], b["token_logprobs"]))
+        two = client.post("/v1/completions", json={"model": "m", "prompt": "One plus one is", "max_tokens": 10, "temperature": 0.7,
+                                                   "logprobs": True, "n": 2, "seed": 42}).json()["choices"]
+        assert [c["index"] for c in two] == [0, 1]
+        assert two[0]["logprobs"]["token_logprobs"] != two[1]["logprobs"]["token_logprobs"]  # the clones sample independently
+
+
+def test_reload_with_zeroed_weights_and_back(server):
+    import copy
+
+    with TestClient(server.app) as client:
+        req = {"model": "m", "prompt": "The quick brown fox", "max_tokens": 16, "temperature": 0.0, "seed": 42}
+        original = client.post("/v1/completions", json=req).json()
+        kept = {}
+
+        def zero(model):
+            kept["state"] = copy.deepcopy(model.state_dict())
+            with torch.no_grad():
+                for p in model.parameters():
+                    p.zero_()
+            return model
+
+        server.reload(zero)
+        zeroed = client.post("/v1/completions", json=req).json()
+        assert zeroed["usage"]["completion_tokens"] > 0
+        # all logits equal: greedy decoding picks token 0 = end of sequence at once, or at least something else than before
+        assert zeroed["choices"][0]["text"] != original["choices"][0]["text"] or original["usage"]["completion_tokens"] == 1
+
+        def restore(model):
+            model.load_state_dict(kept["state"])
+            return model
+
+        server.reload(restore)
+        assert client.post("/v1/completions", json=req).json()["choices"][0]["text"] == original["choices"][0]["text"]
+
+
 def test_too_long_request_is_a_400(server):
     with TestClient(server.app) as client:
         r = client.post("/v1/completions", json={"model": "m", "prompt": "x" * 60, "max_tokens": 50})
