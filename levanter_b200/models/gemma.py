@@ -271,7 +271,7 @@ class Gemma2Config(GemmaConfig):
 
     def to_hf_config(self, vocab_size: int, config_overrides: Optional[Dict] = None) -> dict:
         cfg = dict(model_type=self.hf_model_type, architectures=[self.hf_architecture], **self._common_to_hf(vocab_size),
-                   query_pre_attn_scalar=self.query_pre_attn_scalar or self.head_dim,
+                   query_pre_attn_scalar=_int_if_whole(self.query_pre_attn_scalar or self.head_dim),
                    final_logit_softcapping=self.final_logit_softcapping, attn_logit_softcapping=self.attn_logit_softcapping,
                    sliding_window=self.sliding_window if self.sliding_window is not None else self.seq_len)
         cfg.update({k: v for k, v in rope_to_hf_dict(self.rope).items() if k == "rope_parameters"})
@@ -287,6 +287,11 @@ class Gemma2Config(GemmaConfig):
 
 class Gemma2LMHeadModel(GemmaLMHeadModel):
     layer_cls = Gemma2DecoderLayer
+
+
+def _int_if_whole(x):
+    """transformers types this field as an integer and refuses ``256.0``."""
+    return int(x) if float(x).is_integer() else x
 
 
 @LmConfig.register_subclass("gemma3")

@@ -60,6 +60,11 @@ class QwenConfig(LlamaConfig):
         cfg = super().attention_config()
         return dataclasses.replace(cfg, use_bias=True, use_output_bias=False)
 
+    def total_trainable_params(self, vocab_size):
+        hs = self.actual_head_size
+        qkv_biases = hs * (self.num_heads + 2 * self.num_kv_heads)
+        return super().total_trainable_params(vocab_size) + self.num_layers * qkv_biases
+
 
 class QwenDecoderLayer(LlamaDecoderLayer):
     def __init__(self, config: QwenConfig, *, tp=None, layer_idx: int = 0):
@@ -122,6 +127,11 @@ class Qwen3Config(LlamaConfig):
     def attention_config(self) -> AttentionConfig:
         cfg = super().attention_config()
         return dataclasses.replace(cfg, qk_norm=self.norm_config)
+
+    def total_trainable_params(self, vocab_size):
+        hs = self.actual_head_size
+        biases = hs * (2 * self.num_heads + 2 * self.num_kv_heads) if self.use_bias else 0
+        return super().total_trainable_params(vocab_size) + self.num_layers * (2 * hs + biases)  # q and k norms per layer
 
 
 class Qwen3LMHeadModel(LlamaLMHeadModel):
