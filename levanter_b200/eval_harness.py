@@ -132,6 +132,42 @@ class EvalHarnessMainConfig:
         return load_tokenizer(self.tokenizer)
 
 
+# ------------------------------------------------------------------------------------------------------- requests
+def _encode_pair(tokenizer, context: str, continuation: str, move_trailing_space: bool = True) -> Tuple[List[int], List[int]]:
+    """Token ids of the context and of the continuation, split where the context's own encoding ends.  Trailing spaces of a
+    plain context go with the continuation, so that the token boundary is where free-running text has it."""
+    if move_trailing_space:
+        n_spaces = len(context) - len(context.rstrip())
+        if n_spaces > 0:
+            continuation = context[-n_spaces:] + continuation
+            context = context[:-n_spaces]
+    whole = tokenizer(context + continuation)["input_ids"]
+    ctx = tokenizer(context)["input_ids"] if context else []
+    return list(whole[:len(ctx)]), list(whole[len(ctx):])
+
+
+def _iterate_tokenized_requests(requests, tokenizer, max_len: int, batch_size: int = 128,
+                                apply_chat_template: bool = False) -> Iterator[PromptCompletion]:
+    """``(context, continuation)`` requests as :class:`PromptCompletion` s for packing; ``segment_id`` is the request's position
+    (src/levanter/eval_harness.py:821-866).  With ``apply_chat_template`` the context becomes a user turn followed by the
+    generation prompt, kept exactly as the template writes it.  A request longer than ``max_len`` loses tokens from the left:
+    the continuation is what is scored.  An empty context is replaced by the beginning-of-text token."""
+    chat = apply_chat_template and getattr(tokenizer, "chat_template", None)
+    for i, r in enumerate(requests):
+        context, continuation = r.args if hasattr(r, "args") else r
+        if chat:
+            context = tokenizer.apply_chat_template([{"role": "user", "content": context}], tokenize=False, add_generation_prompt=True)
+        ctx, cont = _encode_pair(tokenizer, context, continuation, move_trailing_space=not chat)
+        if not ctx:
+            ctx = [tokenizer.bos_token_id if tokenizer.bos_token_id is not None else tokenizer.eos_token_id]
+        ids, prompt_len = ctx + cont, len(ctx)
+        if len(ids) > max_len:
+            logger.warning(f"Request {i} is too long. Truncating.")
+            prompt_len -= len(ids) - max_len
+            ids = ids[-max_len:]
+        yield PromptCompletion(ids=ids, prompt_length=max(prompt_len, 1), segment_id=i)
+
+
 # ------------------------------------------------------------------------------------------------------- scoring
 class LoglikelihoodScorer:
     """Scores ``(context ids, continuation ids)`` pairs: returns ``(sum log p(continuation | context), greedy?)`` each."""
@@ -268,31 +304,15 @@ class LevanterHarnessLM(LM):
         self.leader = leader
         self.tokenizer = leader.tokenizer
 
-    def _encode_pair(self, context: str, continuation: str) -> Tuple[List[int], List[int]]:
-        # trailing spaces of the context belong to the continuation so the token boundary matches free-running text
-        n_spaces = len(context) - len(context.rstrip())
-        if n_spaces > 0:
-            continuation = context[-n_spaces:] + continuation
-            context = context[:-n_spaces]
-        whole = self.tokenizer(context + continuation)["input_ids"]
-        ctx = self.tokenizer(context)["input_ids"]
-        return list(whole[:len(ctx)]), list(whole[len(ctx):])
+    def _encode_pair(self, context: str, continuation: str, move_trailing_space: bool = True) -> Tuple[List[int], List[int]]:
+        return _encode_pair(self.tokenizer, context, continuation, move_trailing_space)
 
     def loglikelihood(self, requests) -> List[Tuple[float, bool]]:
-        pairs = []
-        for r in requests:
-            context, continuation = r.args if hasattr(r, "args") else r
-            if self.leader.apply_chat_template and getattr(self.tokenizer, "chat_template", None):
-                context = self.tokenizer.apply_chat_template([{"role": "user", "content": context}], tokenize=False,
-                                                             add_generation_prompt=True)
-            ctx, cont = self._encode_pair(context, continuation)
-            if not ctx:
-                ctx = [self.tokenizer.bos_token_id if self.tokenizer.bos_token_id is not None else self.tokenizer.eos_token_id]
-            pairs.append((ctx, cont))
         scorer = self.leader.scorer
-        packed = scorer.pack(pairs)
-        ll = np.zeros(len(pairs))
-        ok = np.zeros(len(pairs), dtype=bool)
+        seqs = list(_iterate_tokenized_requests(requests, self.tokenizer, scorer.eval_pos, 128, self.leader.apply_chat_template))
+        packed = greedy_pack_prompt_completions(scorer.eval_pos, seqs, scorer.pad_token_id, scorer.max_packed_segments)
+        ll = np.zeros(len(seqs))
+        ok = np.zeros(len(seqs), dtype=bool)
         for i in range(0, len(packed), scorer.eval_batch):
             ids, lls, oks = self.leader.dispatch_loglikelihood(LmExample.stack(packed[i:i + scorer.eval_batch]))
             ids, lls, oks = ids.cpu().numpy(), lls.cpu().numpy(), oks.cpu().numpy()
