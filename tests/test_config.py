@@ -126,3 +126,92 @@ def test_main_decorator_finds_config_path(tmp_path):
 def test_negative_numbers_and_lists_on_command_line():
     over = C.parse_overrides(["--a.b", "-3", "--c", "[1, 2]", "--flag", "true", "--name", "x y"])
     assert over == {"a": {"b": -3}, "c": [1, 2], "flag": True, "name": "x y"}
+
+
+# ---------------------------------------------------------------- scenarios after the reference's tests/test_config.py
+def test_main_decorator_reads_a_config_from_an_fsspec_url_with_overrides():
+    import dataclasses as dc
+
+    import fsspec
+
+    from levanter_b200 import config as C
+
+    with fsspec.open("memory://lvb_cfg/test.yaml", "w") as f:
+        f.write("project: test\n")
+
+    @dc.dataclass
+    class Config:
+        project: str
+        x: int = 1
+
+    seen = {}
+
+    @C.main(args=["--config_path", "memory://lvb_cfg/test.yaml", "--x", "2"])
+    def main(config: Config):
+        seen["cfg"] = config
+
+    main()
+    assert seen["cfg"].project == "test" and seen["cfg"].x == 2
+
+
+def test_trainer_axis_mappings_follow_tensor_parallel_axes():
+    from levanter_b200.trainer import TrainerConfig
+
+    cfg = TrainerConfig(tensor_parallel_axes=["a1", "a2"])
+    assert cfg.tensor_parallel_axes == ["a1", "a2"]
+    assert cfg.compute_axis_mapping == {"batch": ("replica", "data"), "a1": "model", "a2": "model"}
+    assert cfg.parameter_axis_mapping == {"embed": "data", "a1": "model", "a2": "model", "batch": ("replica", "data")}
+
+
+def test_dataset_configs_decode_from_yaml_through_the_main_decorator():
+    import dataclasses as dc
+
+    import fsspec
+
+    from levanter_b200 import config as C
+    from levanter_b200.data.text import HfDatasetSourceConfig, HfSingleDatasetLMConfig, LMMixtureDatasetConfig, UrlDatasetSourceConfig
+
+    @dc.dataclass
+    class Single:
+        data: HfSingleDatasetLMConfig = dc.field(default_factory=HfSingleDatasetLMConfig)
+
+    @dc.dataclass
+    class Mixture:
+        data: LMMixtureDatasetConfig = dc.field(default_factory=LMMixtureDatasetConfig)
+
+    with fsspec.open("memory://lvb_cfg/single.yaml", "w") as f:
+        f.write('data:\n  id: dlwh/wikitext_103_detokenized\n  cache_dir: "gs://levanter-data/tokenized/wikitext"\n')
+    with fsspec.open("memory://lvb_cfg/mixture.yaml", "w") as f:
+        f.write("""
+data:
+  configs:
+    owt:
+      train_urls:
+        - "gs://pubmed-mosaic/openwebtext-sharded/openwebtext_train.{1..128}-of-128.jsonl.gz"
+      validation_urls:
+        - "gs://pubmed-mosaic/openwebtext-sharded/openwebtext_val.{1..8}-of-8.jsonl.gz"
+    wikitext:
+      id: dlwh/wikitext_103_detokenized
+  train_weights:
+    owt: 0.6
+    wikitext: 0.4
+  tokenizer: gpt2
+  cache_dir: "gs://levanter-data/tokenized/mixture"
+""")
+    seen = {}
+
+    @C.main(args=["--config_path", "memory://lvb_cfg/single.yaml"])
+    def one(config: Single):
+        seen["single"] = config
+
+    @C.main(args=["--config_path", "memory://lvb_cfg/mixture.yaml"])
+    def two(config: Mixture):
+        seen["mixture"] = config
+
+    one()
+    two()
+    assert seen["single"].data.id == "dlwh/wikitext_103_detokenized" and seen["single"].data.cache_dir == "gs://levanter-data/tokenized/wikitext"
+    mix = seen["mixture"].data
+    assert mix.train_weights == {"owt": 0.6, "wikitext": 0.4} and mix.tokenizer == "gpt2"
+    assert isinstance(mix.configs["owt"], UrlDatasetSourceConfig) and isinstance(mix.configs["wikitext"], HfDatasetSourceConfig)
+    assert len(mix.configs["owt"].urls_for_split("validation")) == 1 and mix.configs["wikitext"].id == "dlwh/wikitext_103_detokenized"
