@@ -81,3 +81,66 @@ def test_background_prefetch_gives_the_same_batches_and_surfaces_errors():
     with pytest.raises(RuntimeError, match="shard went away"):  # batches are fetched ahead in groups, so it may surface early
         for _ in range(3):
             next(it)
+
+
+# ---------------------------------------------------------------- more scenarios after the reference's tests/test_new_loader.py
+SCHEDULE = [ScheduleStep(start=0, value=8), ScheduleStep(start=10, value=16), ScheduleStep(start=20, value=32)]
+
+
+def _token_rows(n, seq_len=16):
+    return ListAsyncDataset([torch.full((seq_len,), i + 1, dtype=torch.int32) for i in range(n)], is_complete=True)
+
+
+@pytest.mark.parametrize("model_axis", [1, 2])
+def test_batch_size_schedule_without_padding_drops_the_short_last_batch(model_axis):
+    mesh = _mesh(1, 2, model_axis, 0)
+    dl = DataLoader(_token_rows(1000), BatchSchedule(SCHEDULE), mesh=mesh, max_buffered_batches=10, pad_final_batch=False, pin_memory=False)
+    sizes = [b.shape[0] for b in dl]
+    # this rank loads half of every batch; 10 * 8 + 10 * 16 = 240 rows in the first 20 steps, (1000 - 240) // 32 = 23 whole batches after
+    assert sizes == [4] * 10 + [8] * 10 + [16] * 23
+
+
+@pytest.mark.parametrize("model_axis", [1, 2])
+def test_batch_size_schedule_with_a_padded_last_batch(model_axis):
+    world = 2 * model_axis
+    last = []
+    for rank in range(world):
+        mesh = _mesh(1, 2, model_axis, rank)
+        dl = DataLoader(_token_rows(1007), BatchSchedule(SCHEDULE), mesh=mesh, max_buffered_batches=10, pad_final_batch=True, pin_memory=False)
+        batches = list(dl)
+        assert [b.shape[0] for b in batches] == [4] * 10 + [8] * 10 + [16] * 24
+        last.append((mesh.batch_index, batches[-1]))
+    # the 24th large batch holds the last (1007 - 240) % 32 = 31 rows and one row of zeros, at the end of the last shard
+    by_shard = dict(last)
+    whole = torch.cat([by_shard[0], by_shard[1]])
+    assert whole.shape[0] == 32 and (whole[:31, 0] == torch.arange(1007 - 30, 1008)).all() and whole[31].abs().sum() == 0
+
+
+def test_examples_that_are_trees_are_stacked_leaf_by_leaf():
+    def example(i):
+        image = torch.arange(16 * 16, dtype=torch.int32).reshape(16, 16) + i * 1000
+        return {"input_ids": image, "labels": image.clone(), "extra": {"input_ids": image.clone(), "mask": torch.arange(16) + i * 1000}}
+
+    ds = ListAsyncDataset([example(i) for i in range(40)], is_complete=True)
+    per_rank = {}
+    for rank in range(4):
+        mesh = _mesh(1, 4, 1, rank)
+        batches = list(DataLoader(ds, 8, mesh=mesh, max_buffered_batches=0, pin_memory=False))
+        assert len(batches) == 5
+        per_rank[rank] = batches
+        for b in batches:
+            assert b["input_ids"].shape == (2, 16, 16) and b["extra"]["mask"].shape == (2, 16)
+            assert torch.equal(b["input_ids"], b["labels"]) and torch.equal(b["input_ids"], b["extra"]["input_ids"])
+            assert torch.equal(b["extra"]["mask"][:, 0], b["input_ids"][:, 0, 0])  # leaves of one example stay together
+    # ranks hold different rows of a batch, and together every row once
+    step2 = torch.cat([per_rank[r][2]["input_ids"][:, 0, 0] for r in range(4)])
+    assert sorted((step2 // 1000).tolist()) == list(range(16, 24))
+
+
+def test_a_dataclass_example_keeps_its_type():
+    from levanter_b200.models.lm_model import LmExample
+
+    ds = ListAsyncDataset([LmExample.causal(torch.full((8,), i, dtype=torch.int32)) for i in range(12)], is_complete=True)
+    (first, *_rest) = list(DataLoader(ds, 4, max_buffered_batches=0, pin_memory=False))
+    assert isinstance(first, LmExample) and first.tokens.shape == (4, 8) and first.loss_mask.shape == (4, 8)
+    assert first.tokens[:, 0].tolist() == [0, 1, 2, 3] and first.attn_mask.is_causal
