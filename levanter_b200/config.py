@@ -34,6 +34,13 @@ class ConfigError(ValueError):
     pass
 
 
+class UnknownChoiceError(ConfigError, KeyError):
+    """A ``type:`` name that no class is registered under (a ``KeyError`` too: a registry is looked up like a mapping)."""
+
+    def __str__(self) -> str:  # KeyError would print the repr of the message
+        return str(self.args[0]) if self.args else ""
+
+
 # --------------------------------------------------------------------------- plugin registries
 class ChoiceRegistry:
     """Base for config classes selected by a ``type:`` key (model, optimizer, tracker, rope, ...).
@@ -64,7 +71,7 @@ class ChoiceRegistry:
     def get_choice_class(cls, name: str) -> type:
         reg = cls._registry_root._choice_registry
         if name not in reg:
-            raise ConfigError(f"unknown {cls._registry_root.__name__} type {name!r}; known: {sorted(reg)}")
+            raise UnknownChoiceError(f"unknown {cls._registry_root.__name__} type {name!r}; known: {sorted(reg)}")
         return reg[name]
 
     @classmethod

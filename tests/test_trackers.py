@@ -65,3 +65,63 @@ def test_histogram_matches_numpy():
     assert h.num == 1000 and abs(h.sum - float(x.sum())) < 1e-3 and abs(h.sum_squares - float((x * x).sum())) < 1e-2
     assert np.allclose(h.bucket_limits, edges, atol=1e-5) and np.abs(h.bucket_counts - counts).sum() <= 2
     assert h.min == float(x.min()) and h.max == float(x.max())
+
+
+# ---------------------------------------------------------------- scenarios after the reference's tests/test_tracker.py
+import pytest  # noqa: E402
+
+
+def test_tracker_registry_default_choice_and_unknown_names():
+    import dataclasses as dc
+
+    import yaml
+
+    from levanter_b200 import config as C
+    from levanter_b200.tracker import TrackerConfig
+
+    assert TrackerConfig.get_choice_class("wandb") is not None
+    with pytest.raises(KeyError):
+        TrackerConfig.get_choice_class("foo")
+    with pytest.raises(C.ConfigError, match="known:.*noop"):
+        TrackerConfig.get_choice_class("foo")
+
+    @dc.dataclass
+    class Holder:
+        tracker: TrackerConfig
+
+    t = C.decode(Holder, yaml.safe_load("tracker:\n  entity: foo\n")).tracker  # no type: the default choice
+    assert isinstance(t, TrackerConfig.get_choice_class("wandb")) and t.entity == "foo"
+
+
+def test_one_tracker_or_a_list_of_trackers_in_a_config():
+    import dataclasses as dc
+    from typing import Tuple, Union
+
+    import yaml
+
+    from levanter_b200 import config as C
+    from levanter_b200.tracker import TrackerConfig
+    from levanter_b200.tracker.tracker import NoopConfig
+
+    @dc.dataclass
+    class Holder:
+        tracker: Union[TrackerConfig, Tuple[TrackerConfig, ...]]
+
+    assert isinstance(C.decode(Holder, yaml.safe_load("tracker:\n  type: noop\n")).tracker, NoopConfig)
+    both = C.decode(Holder, yaml.safe_load("tracker:\n  - type: noop\n  - type: wandb\n")).tracker
+    assert both == (NoopConfig(), TrackerConfig.get_choice_class("wandb")())
+
+
+def test_trackers_are_found_by_name_inside_a_composite():
+    import levanter_b200.tracker as T
+    from levanter_b200.tracker import CompositeTracker, NoopTracker
+    from levanter_b200.tracker.json_logger import JsonLoggerTracker
+
+    import logging
+
+    inner = JsonLoggerTracker(logging.getLogger("test-json-tracker"))
+    with CompositeTracker([inner, NoopTracker()]):
+        assert T.get_tracker("json_logger") is inner
+        assert T.get_tracker("noop") is not None
+        with pytest.raises(KeyError):
+            T.get_tracker("foo")
