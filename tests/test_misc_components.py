@@ -49,6 +49,67 @@ def test_background_iterable_stop_unblocks_a_full_queue():
     assert time.time() - t0 < 5
 
 
+def test_background_iterable_over_async_producers():
+    import asyncio
+
+    async def numbers():
+        for i in range(20):
+            await asyncio.sleep(0)
+            yield i
+
+    it = BackgroundIterable(numbers, max_capacity=3)
+    assert list(it) == list(range(20)) and list(it) == list(range(20))
+
+    async def nothing():
+        return
+        yield  # pragma: no cover
+
+    assert list(BackgroundIterable(nothing, max_capacity=2)) == []
+
+    async def failing():
+        yield 1
+        raise ValueError("boom in async producer")
+
+    got = []
+    with pytest.raises(ValueError, match="boom in async producer"):
+        for x in BackgroundIterable(failing, max_capacity=2):
+            got.append(x)
+    assert got == [1]
+
+    async def endless():
+        i = 0
+        while True:
+            yield i
+            i += 1
+            await asyncio.sleep(0)
+
+    run = iter(BackgroundIterable(endless, max_capacity=2))
+    assert next(run) == 0 and next(run) == 1
+    t0 = time.time()
+    run.stop()
+    assert time.time() - t0 < 5
+    with pytest.raises(StopIteration):
+        while True:
+            next(run)
+
+
+def test_background_iterable_without_a_capacity_limit_runs_ahead():
+    produced = []
+
+    def gen():
+        for i in range(100):
+            produced.append(i)
+            yield i
+
+    it = iter(BackgroundIterable(gen, max_capacity=None))
+    assert next(it) == 0
+    deadline = time.time() + 5
+    while len(produced) < 100 and time.time() < deadline:
+        time.sleep(0.01)
+    assert len(produced) == 100  # the producer did not wait for the consumer
+    assert list(it) == list(range(1, 100))
+
+
 # ------------------------------------------------------------------------------------------------ time deltas
 @pytest.mark.parametrize("text,seconds", [("30m", 1800), ("1h30m", 5400), ("1d2h3m4.5s", 93784.5), ("15", 15), ("2 hours", 7200), ("90s", 90)])
 def test_parse_timedelta(text, seconds):
