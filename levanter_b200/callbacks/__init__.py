@@ -18,7 +18,7 @@ import torch.distributed as dist
 from .. import tracker as trk
 from ..utils.flop_utils import device_hardware_flops, device_kind
 from ._core import Callback, JitCallback, LambdaCallback, StepInfo  # noqa: F401
-from ._metrics import log_epoch_progress, log_performance_stats, log_step_info, pbar_logger  # noqa: F401
+from ._metrics import get_total_dataset_tokens, log_epoch_progress, log_performance_stats, log_step_info, pbar_logger  # noqa: F401
 
 logger = pylogging.getLogger(__name__)
 

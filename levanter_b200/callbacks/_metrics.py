@@ -14,13 +14,36 @@ from ._core import StepInfo
 logger = pylogging.getLogger(__name__)
 
 
+def get_total_dataset_tokens(ds, seq_length: int):
+    """A future for ``len(ds) * seq_length``, computed on a helper thread (the length of a cache that is still being built is
+    slow to get) and logged as the summary ``dataset/total_tokens``.  ``ds`` may be an epoch wrapper: its ``dataset`` is counted."""
+    import asyncio
+    from concurrent.futures import ThreadPoolExecutor
+
+    inner = getattr(ds, "dataset", ds)
+
+    def log_length():
+        total = asyncio.run(inner.async_len()) * seq_length
+        trk.log_summary({"dataset/total_tokens": total})
+        return total
+
+    executor = ThreadPoolExecutor(max_workers=1)
+    future = executor.submit(log_length)
+    executor.shutdown(wait=False)
+    return future
+
+
 def log_epoch_progress(total_tokens_future, tokens_per_example: int, batch_size: int, max_epochs: Optional[int] = None):
-    """Log ``train/current_epoch`` once the dataset's total token count is known."""
+    """Log ``train/current_epoch`` once the dataset's total token count is known (a number, a callable returning one or None,
+    or a future as returned by :func:`get_total_dataset_tokens`)."""
     total = {"v": None}
 
     def log_epoch(step_info: StepInfo):
         if total["v"] is None:
-            v = total_tokens_future() if callable(total_tokens_future) else total_tokens_future
+            if hasattr(total_tokens_future, "done"):
+                v = total_tokens_future.result() if total_tokens_future.done() else None
+            else:
+                v = total_tokens_future() if callable(total_tokens_future) else total_tokens_future
             if v is None:
                 return
             total["v"] = v

@@ -188,6 +188,39 @@ def load_tokenizer(model_name_or_path, revision=None, local_cache_dir=None, trus
     return AutoTokenizer.from_pretrained(path, revision=revision, trust_remote_code=trust_remote_code)
 
 
+def load_processor(model_name_or_path, revision=None, local_cache_dir=None, trust_remote_code=True):
+    """``AutoProcessor`` (feature extractor + tokenizer of an audio model) from a local directory, an fsspec URL (copied to a
+    temp dir) or the hub (:1075)."""
+    from transformers import AutoProcessor
+
+    path = str(model_name_or_path)
+    if "://" in path:
+        import fsspec
+
+        fs, plain = fsspec.core.url_to_fs(path)
+        tmp = local_cache_dir or tempfile.mkdtemp(prefix="lvb_proc_")
+        for f in fs.ls(plain, detail=False):
+            base = os.path.basename(f)
+            if not base.endswith((".safetensors", ".bin", ".pt")):  # everything but the weights
+                fs.get(f, os.path.join(tmp, base))
+        return AutoProcessor.from_pretrained(tmp, trust_remote_code=trust_remote_code)
+    return AutoProcessor.from_pretrained(path, revision=revision, cache_dir=local_cache_dir, trust_remote_code=trust_remote_code)
+
+
+def upload_to_hub(local_path: str, repo_ref, **hf_upload_kwargs) -> None:
+    """Upload a saved directory to the hub from process 0; the other processes wait for it (:1086)."""
+    import torch.distributed as dist
+
+    ref = _coerce_ref(repo_ref)
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0:
+        from huggingface_hub import upload_folder
+
+        logger.info(f"Uploading HF-compatible checkpoint to {ref.model_name_or_path}")
+        upload_folder(folder_path=local_path, repo_id=ref.model_name_or_path, revision=ref.revision, **hf_upload_kwargs)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
 # ------------------------------------------------------------------------------------------------ converter
 class HFCheckpointConverter:
     def __init__(self, config_class, reference_checkpoint: Optional[Union[str, RepoRef]] = None, tokenizer=None,
@@ -397,8 +430,8 @@ class HFCheckpointConverter:
                 try:
                     from huggingface_hub import upload_folder
 
-                    repo = str(upload_to_hf.model_name_or_path if isinstance(upload_to_hf, RepoRef) else upload_to_hf)
-                    upload_folder(repo_id=repo, folder_path=local, **hf_upload_kwargs)
+                    ref = _coerce_ref(upload_to_hf)
+                    upload_folder(repo_id=ref.model_name_or_path, revision=ref.revision, folder_path=local, **hf_upload_kwargs)
                 except Exception as e:  # noqa: BLE001
                     logger.warning(f"upload to the hub failed: {e}")
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:

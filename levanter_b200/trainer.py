@@ -510,10 +510,27 @@ class Trainer:
         avg = cfg.model_averaging.create(engine.master_tree()) if cfg.model_averaging is not None else None
         state = TrainerState(step=0, model=model, engine=engine, training_key=key, mp=cfg.mp, model_averaging=avg,
                              is_trainable=is_trainable)
-        load_path = cfg.load_checkpoint_path or cfg.checkpointer.expanded_path(self.run_id)
-        state = load_checkpoint_or_initialize(state, load_path, force_load=cfg.load_checkpoint,
+        state = load_checkpoint_or_initialize(state, self.checkpoint_path, force_load=cfg.load_checkpoint,
                                               allow_partial=cfg.allow_partial_checkpoint, initialize_from=cfg.initialize_from)
         return state
+
+    @property
+    def checkpoint_path(self) -> str:
+        """Where this run looks for a checkpoint to resume from: ``load_checkpoint_path`` or the checkpointer's run directory."""
+        return self.config.load_checkpoint_path or self.config.checkpointer.expanded_path(self.run_id)
+
+    def write_artifact(self, name: str, artifact, type: Optional[str] = None) -> str:
+        """Write ``artifact`` (text or bytes) to ``<log_dir>/<run id>/artifacts/<name>`` and hand the file to the tracker
+        (src/levanter/trainer.py:600-615).  A name ending in ``.gz`` / ``.zst`` is compressed on the way."""
+        import fsspec
+
+        directory = os.path.join(str(self.config.log_dir), self.run_id, "artifacts")
+        os.makedirs(directory, exist_ok=True)
+        path = os.path.join(directory, name)
+        with fsspec.open(path, "w" if isinstance(artifact, str) else "wb", compression="infer") as f:
+            f.write(artifact)
+        trk.current_tracker().log_artifact(path, name=name, type=type)
+        return path
 
     # -- data ----------------------------------------------------------------------------------------------------
     def data_loader(self, dataset, batch=None, **kw):

@@ -66,3 +66,75 @@ def test_default_ragged_paged_attention_is_the_oracle():
     a = default_ragged_paged_attention(q, pages, kv_lens, page_idx, cu, 2, 0.35)
     b = ragged_paged_attention_reference(q, pages, kv_lens, page_idx, cu, 2, 0.35)
     assert torch.equal(a, b)
+
+
+def test_trainer_checkpoint_path_and_artifacts(tmp_path):
+    import gzip
+
+    from levanter_b200 import config as C
+    from levanter_b200.models.lm_model import compute_next_token_loss
+    from levanter_b200.optim import AdamConfig
+    from levanter_b200.trainer import Trainer, TrainerConfig
+
+    def cfg(**kw):
+        d = {"num_train_steps": 1, "train_batch_size": 2, "require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": f"{tmp_path}/logs",
+             "id": "run7", "checkpointer": {"base_path": f"{tmp_path}/ckpt"}}
+        d.update(kw)
+        return C.decode(TrainerConfig, d)
+
+    with Trainer(cfg(), AdamConfig(), compute_next_token_loss) as trainer:
+        assert trainer.checkpoint_path == f"{tmp_path}/ckpt/run7"
+        text = trainer.write_artifact("notes.txt", "hello", type="text")
+        blob = trainer.write_artifact("blob.bin.gz", b"\\x00\\x01\\x02")
+        assert text == f"{tmp_path}/logs/run7/artifacts/notes.txt" and open(text).read() == "hello"
+        assert gzip.open(blob, "rb").read() == b"\\x00\\x01\\x02"
+    with Trainer(cfg(load_checkpoint_path="/some/other/run"), AdamConfig(), compute_next_token_loss) as trainer:
+        assert trainer.checkpoint_path == "/some/other/run"
+
+
+def test_total_dataset_tokens_future_feeds_the_epoch_progress_hook():
+    import levanter_b200.tracker as T
+    from levanter_b200.callbacks import get_total_dataset_tokens, log_epoch_progress
+    from levanter_b200.data.dataset import EpochDataset, ListAsyncDataset
+
+    class Recorder(T.NoopTracker):
+        def __init__(self):
+            self.logged, self.summary = [], {}
+
+        def log(self, metrics, *, step, commit=None):
+            self.logged.append((step, dict(metrics)))
+
+        def log_summary(self, metrics):
+            self.summary.update(metrics)
+
+    rec = Recorder()
+    with T.current_tracker(rec):
+        ds = EpochDataset(ListAsyncDataset(list(range(50)), is_complete=True))
+        fut = get_total_dataset_tokens(ds, 16)
+        assert fut.result(timeout=10) == 800 and rec.summary == {"dataset/total_tokens": 800}
+        hook = log_epoch_progress(fut, tokens_per_example=16, batch_size=5, max_epochs=2)
+
+        class Info:
+            def __init__(self, step):
+                self.step, self.next_step = step, step + 1
+
+        hook(Info(4))
+        hook(Info(99))
+    assert rec.logged[0] == (4, {"train/current_epoch": 16 * 5 * 5 / 800})
+    assert rec.logged[1] == (99, {"train/current_epoch": 2})  # capped at max_epochs
+
+
+def test_upload_to_hub_passes_the_repository_and_revision(monkeypatch, tmp_path):
+    import sys
+    import types
+
+    from levanter_b200.compat.hf_checkpoints import RepoRef, upload_to_hub
+
+    calls = []
+    fake = types.ModuleType("huggingface_hub")
+    fake.upload_folder = lambda **kw: calls.append(kw)
+    monkeypatch.setitem(sys.modules, "huggingface_hub", fake)
+    upload_to_hub(str(tmp_path), "org/model@dev", commit_message="step 10")
+    upload_to_hub(str(tmp_path), RepoRef("org/other"))
+    assert calls[0] == {"folder_path": str(tmp_path), "repo_id": "org/model", "revision": "dev", "commit_message": "step 10"}
+    assert calls[1]["repo_id"] == "org/other" and calls[1]["revision"] is None
