@@ -119,3 +119,35 @@ def take_train_step(optimizer, params: Dict[str, torch.Tensor], opt_state, grads
     updates, opt_state = optimizer.update(train_grads, opt_state, train_params, obj_fn=obj_fun, loss=loss)
     T.apply_updates(train_params, updates)
     return params, opt_state, updates
+
+
+# ------------------------------------------------------------------------------------------------ trainable subsets
+def make_floating_point_trainable_filter(model: torch.nn.Module, is_trainable: Optional[Callable[[str], bool]] = None) -> Callable[[str], bool]:
+    """``name -> bool``: ``is_trainable(name)`` and the parameter is a floating-point tensor that asks for gradients
+    (src/levanter/trainer_state.py:278-292; integer tables and frozen weights are never trained)."""
+    keep = is_trainable or (lambda name: True)
+    ok = {name for name, p in model.named_parameters() if p.is_floating_point() and p.requires_grad}
+    return lambda name: name in ok and bool(keep(name))
+
+
+def trainables_only(model: torch.nn.Module, is_trainable: Optional[Callable[[str], bool]] = None) -> Dict[str, torch.Tensor]:
+    """The trainable parameters of ``model`` by name (:207-213): what the optimizer state is built for and what a training
+    checkpoint holds."""
+    f = make_floating_point_trainable_filter(model, is_trainable)
+    return {name: p for name, p in model.named_parameters() if f(name)}
+
+
+def init_optimizer_for_trainables(optimizer, trainable_params: Dict[str, torch.Tensor]):
+    """Optimizer state for the trainable parameters only (:180-186)."""
+    return optimizer.init(trainable_params)
+
+
+def cast_params_by_trainability(model: torch.nn.Module, mp, is_trainable: Optional[Callable[[str], bool]] = None) -> torch.nn.Module:
+    """Trainable parameters to the policy's parameter dtype, frozen floating-point ones to its compute dtype, in place
+    (:216-226): a frozen base model under LoRA costs two bytes per weight, not four."""
+    f = make_floating_point_trainable_filter(model, is_trainable)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.is_floating_point():
+                p.data = p.data.to(mp.param_dtype if f(name) else mp.compute_dtype)
+    return model

@@ -138,3 +138,31 @@ def test_upload_to_hub_passes_the_repository_and_revision(monkeypatch, tmp_path)
     upload_to_hub(str(tmp_path), RepoRef("org/other"))
     assert calls[0] == {"folder_path": str(tmp_path), "repo_id": "org/model", "revision": "dev", "commit_message": "step 10"}
     assert calls[1]["repo_id"] == "org/other" and calls[1]["revision"] is None
+
+
+def test_trainable_subsets_and_casting_by_trainability():
+    from levanter_b200.lora import LoraConfig, lora_trainable_params_filter, loraize
+    from levanter_b200.models.llama import LlamaConfig
+    from levanter_b200.optim import transforms as T
+    from levanter_b200.trainer_state import (cast_params_by_trainability, init_optimizer_for_trainables, make_floating_point_trainable_filter,
+                                             trainables_only)
+    from levanter_b200.config import Policy
+
+    model = loraize(LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=1, num_heads=2, num_kv_heads=2).build(40, seed=0),
+                    LoraConfig(r=2, target_modules=["q_proj"]), seed=0)
+    model.register_parameter("table", torch.nn.Parameter(torch.arange(4), requires_grad=False))
+    is_lora = lora_trainable_params_filter(model)
+    train = trainables_only(model, is_lora)
+    assert train and all("lora" in n for n in train) and len(train) == 2
+    everything = trainables_only(model)
+    assert "table" not in everything and len(everything) == sum(1 for _ in model.parameters()) - 1
+    f = make_floating_point_trainable_filter(model, is_lora)
+    assert f(next(iter(train))) and not f("table") and not f("embeddings.token_embeddings.weight")
+    state = init_optimizer_for_trainables(T.scale_by_adam(0.9, 0.95, 1e-8), train)
+    assert set(state.mu) == set(train)
+    cast_params_by_trainability(model, Policy.parse("p=f32,c=bf16"), is_lora)
+    for n, p in model.named_parameters():
+        if n == "table":
+            assert p.dtype == torch.int64
+        else:
+            assert p.dtype == (torch.float32 if n in train else torch.bfloat16), n
