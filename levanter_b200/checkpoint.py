@@ -83,6 +83,10 @@ class Checkpointer:
     def load_checkpoint(self, state, path: Optional[str] = None, *, discover_latest: bool = True, **kw):
         return load_checkpoint(state, path or self.base_path, discover_latest=discover_latest, **kw)
 
+    def load_model(self, model: torch.nn.Module, path: Optional[str] = None, *, discover_latest: bool = True, **kw):
+        """Only the model, from the ``model`` sub-tree of the (newest) checkpoint under ``path`` (src/levanter/checkpoint.py:150-168)."""
+        return load_checkpoint(model, path or self.base_path, subpath="model", discover_latest=discover_latest, **kw)
+
     def on_step(self, info, force: bool = False):
         step = info.step
         self._manager.drain()  # surface an error from a commit that finished in the background

@@ -189,3 +189,17 @@ def test_trees_load_fully_or_partially(tmp_path):
     assert torch.equal(got["model"]["a.bias"], torch.ones(2)) and torch.equal(got["model"]["b.weight"], torch.full((2,), 7.0))
     with pytest.raises(FileNotFoundError):
         load_checkpoint(like, str(tmp_path / "nothing-here"))
+
+
+def test_checkpointer_loads_just_the_model_of_the_newest_checkpoint(tmp_path):
+    ck = Checkpointer(str(tmp_path), None, [CheckpointInterval(every=1)])
+    infos = [_Info(1), _Info(2)]
+    for info in infos:
+        ck.on_step(info)
+    ck.wait_until_finished()
+    fresh = torch.nn.Linear(2, 2)
+    assert not torch.equal(fresh.weight, infos[1].state.model.weight)
+    ck.load_model(fresh)
+    assert torch.equal(fresh.weight, infos[1].state.model.weight) and torch.equal(fresh.bias, infos[1].state.model.bias)
+    ck.load_model(fresh, str(tmp_path / "step-1"), discover_latest=False)
+    assert torch.equal(fresh.weight, infos[0].state.model.weight)
