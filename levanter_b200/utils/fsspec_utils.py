@@ -59,8 +59,13 @@ def expand_glob(url: str):
         fs, path = url_to_fs(candidate)
         if any(ch in path for ch in "*?["):
             protocol = candidate.split("://")[0] + "://" if "://" in candidate else ""
+            rooted = candidate[len(protocol):].startswith("/")
             for p in sorted(fs.glob(path)):
-                yield f"{protocol}{p}" if protocol and not str(p).startswith(protocol) else str(p)
+                p = str(p)
+                if protocol and not p.startswith(protocol):
+                    # (some filesystems list "/bucket/key" for "proto://bucket/key": give back the form that was asked for)
+                    p = protocol + (p.lstrip("/") if not rooted else p)
+                yield p
         else:
             yield candidate
 
