@@ -125,8 +125,9 @@ def pbar_logger(iterable=None, desc: str = "train", **tqdm_mkwargs) -> Callable[
         return lambda step: None
     import torch.distributed as dist
 
-    disable = dist.is_available() and dist.is_initialized() and dist.get_rank() != 0
     kwargs = dict(tqdm_mkwargs)
+    not_rank0 = dist.is_available() and dist.is_initialized() and dist.get_rank() != 0
+    disable = bool(kwargs.pop("disable", False)) or not_rank0  # only process 0 draws; a caller may silence it too
     kwargs.setdefault("mininterval", 10.0)
     pbar = tqdm(iterable, desc=desc, disable=disable, **kwargs)
     last = {"t": 0.0}
