@@ -186,3 +186,32 @@ def test_git_root_of_the_experiment_is_found():
 
     root = infer_experiment_git_root()
     assert root is not None and os.path.isdir(os.path.join(root, ".git"))
+
+
+def test_slurm_environment_gives_coordinator_ranks_and_local_devices(monkeypatch):
+    from levanter_b200.distributed import LevanterSlurmCluster as S
+
+    for k in list(__import__("os").environ):
+        if k.startswith("SLURM"):
+            monkeypatch.delenv(k)
+    assert not S.is_env_present()
+    env = {"SLURM_JOB_ID": "123456", "SLURM_PROCID": "5", "SLURM_NTASKS": "8", "SLURM_LOCALID": "1", "SLURM_STEP_NODELIST": "gpu[07-08,11]",
+           "SLURM_STEP_TASKS_PER_NODE": "4(x2)", "SLURMD_NODENAME": "gpu08", "CUDA_VISIBLE_DEVICES": "0,1,2,3,4,5,6,7"}
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    assert S.is_env_present()
+    host, port = S.get_coordinator_address().split(":")
+    assert host == "gpu07" and 61440 <= int(port) <= 65535 and int(port) == 123456 % 4096 + 61440  # a port every task derives alike
+    assert S.get_process_count() == 8 and S.get_process_id() == 5 and S.get_local_process_id() == 1
+    assert S.get_tasks_per_node() == [4, 4]
+    assert S.get_local_device_ids_for_process() == [2, 3]  # eight visible devices over four local tasks
+    monkeypatch.setenv("SLURM_STEP_TASKS_PER_NODE", "2(x3),1")
+    assert S.get_tasks_per_node() == [2, 2, 2, 1]
+    monkeypatch.setenv("SLURM_STEP_TASKS_PER_NODE", "3")
+    monkeypatch.setenv("SLURM_LOCALID", "0")
+    assert S.get_local_device_ids_for_process() is None  # 8 devices do not divide over 3 tasks
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES")
+    assert S.get_local_device_ids_for_process() is None
+    monkeypatch.setenv("SLURM_STEP_TASKS_PER_NODE", "two")
+    with pytest.raises(ValueError):
+        S.get_tasks_per_node()
