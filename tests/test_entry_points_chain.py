@@ -399,3 +399,45 @@ def test_train_lm_on_chat_and_supervised_formats_with_packing(workdir, monkeypat
                    "format": {"type": "chat"} if fmt == "chat" else {"type": "supervised", "input_field": "prompt", "output_field": "response"}}
     train_lm.main(C.decode(train_lm.TrainLmConfig, cfg))
     assert discover_latest_checkpoint(f"{d}/ckpt/fmt_{fmt}") is not None
+
+
+def test_eval_lm_on_the_exported_hugging_face_weights_with_every_analysis(workdir, monkeypatch, capsys):
+    """Runs after ``test_chain``: the exported directory gives the same validation loss as the checkpoint it came from, and the
+    entropy / top-2 gap / parameter statistics options log their histograms."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json"):
+        pytest.skip("needs the export of test_chain")
+    import levanter_b200.tracker as T
+    from levanter_b200.checkpoint import discover_latest_checkpoint
+    from levanter_b200.main import eval_lm
+    from levanter_b200.tracker.histogram import Histogram
+
+    class Recorder(T.NoopTracker):
+        def __init__(self):
+            self.logged = {}
+
+        def log(self, metrics, *, step, commit=None):
+            self.logged.update(metrics)
+
+    base = _base(d, 4)
+    common = {"data": base["data"], "model": base["model"], "trainer": dict(base["trainer"], id="evalhf", max_eval_batches=2, per_device_eval_parallelism=4)}
+    rec = Recorder()
+    from levanter_b200.trainer import TrainerConfig
+
+    monkeypatch.setattr(TrainerConfig, "_make_tracker", lambda self: rec)  # the entry point installs the configured tracker
+    from_hf = eval_lm.main(C.decode(eval_lm.EvalLmConfig, dict(common, hf_checkpoint=f"{d}/hf", log_entropy=True, log_top2_gap=True, log_param_stats=True)))
+    assert from_hf["eval/loss"] > 0 and "Loss:" in capsys.readouterr().out
+    assert any(k.startswith("eval/") and k.endswith("bpb") for k in from_hf), sorted(from_hf)
+    ent = [v for k, v in rec.logged.items() if k.startswith("analysis/") and k.endswith("/entropy")]
+    gap = [v for k, v in rec.logged.items() if k.endswith("/top2_gap")]
+    assert ent and gap and all(isinstance(h, Histogram) and float(h.num) > 0 for h in ent + gap)
+    assert float(ent[0].min) >= 0 and float(ent[0].max) <= np.log(300) + 1e-3  # an entropy is within [0, log(vocabulary)]
+    assert any(k.startswith("params/norm/") for k in rec.logged) and any(k.startswith("params/hist/") for k in rec.logged)
+
+    ck = discover_latest_checkpoint(f"{d}/ckpt/chain")
+    from_ckpt = eval_lm.main(C.decode(eval_lm.EvalLmConfig, dict(common, checkpoint_path=ck)))
+    assert from_ckpt["eval/loss"] == pytest.approx(from_hf["eval/loss"], rel=1e-4)
+    on_train = eval_lm.main(C.decode(eval_lm.EvalLmConfig, dict(common, checkpoint_path=ck, eval_on_train=True)))
+    assert on_train["eval/loss"] > 0 and on_train["eval/loss"] != pytest.approx(from_ckpt["eval/loss"], rel=1e-6)
