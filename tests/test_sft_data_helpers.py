@@ -49,9 +49,10 @@ def test_cached_chat_examples_are_padded_and_masked_to_the_response(tmp_path):
     assert ex.tokens.shape == (12,) and ex.tokens.tolist()[:n] == first["input_ids"].tolist()
     pad = tok.pad_token_id if tok.pad_token_id is not None else eos
     assert ex.tokens.tolist()[n:] == [pad] * (12 - n)
-    # loss where the next token is a response token (and not padding): positions src_len - 1 .. n - 2
+    # loss where the next token is a response token and not the padding token: positions src_len - 1 .. n - 3 here, because this
+    # tokenizer pads with its end-of-sequence token, so the final token is not told apart from padding (as in the reference)
     want = np.zeros(12, dtype=np.int32)
-    want[1:n - 1] = 1
+    want[1:n - 2] = 1
     assert ex.loss_mask.tolist() == want.tolist()
 
 
