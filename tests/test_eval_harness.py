@@ -168,3 +168,64 @@ def test_report_averages_are_macro_and_sample_weighted():
     assert avg["macro_avg_f1,none"] == pytest.approx(0.25) and avg["micro_avg_f1,none"] == pytest.approx(0.25)
     assert not any("stderr" in k or "alias" in k for k in avg)
     assert np.isfinite(list(avg.values())).all()
+
+
+class _FakeEvaluator:
+    """Stands in for ``lm_eval.evaluator``: asks the adapter for the log-likelihoods of every task's requests and reports the
+    share of requests whose continuation is the greedy one, in the harness's result layout."""
+
+    def __init__(self):
+        self.calls = []
+
+    def evaluate(self, lm, task_dict, limit=None, log_samples=False, bootstrap_iters=0):
+        self.calls.append({"limit": limit, "log_samples": log_samples, "bootstrap_iters": bootstrap_iters})
+        results, n = {}, {}
+        for name, requests in task_dict.items():
+            reqs = requests[:limit] if limit else requests
+            out = lm.loglikelihood(_requests(reqs))
+            results[name] = {"acc,none": float(np.mean([g for _, g in out])), "acc_stderr,none": 0.0, "ll,none": float(np.mean([l for l, _ in out])),
+                             "alias": name}
+            n[name] = {"original": len(requests), "effective": len(reqs)}
+        return {"results": results, "n-samples": n}
+
+
+def test_harness_run_reports_results_averages_and_an_artifact(tokenizer, monkeypatch):
+    import levanter_b200.eval_harness as H
+    import levanter_b200.tracker as T
+
+    fake = _FakeEvaluator()
+    monkeypatch.setattr(H, "_evaluator", fake)
+    monkeypatch.setattr(LmEvalHarnessConfig, "to_task_dict", lambda self: {"capitals": PAIRS[:1] * 3, "sayings": PAIRS[1:]})
+    _, model = _lm(tokenizer)
+    cfg = LmEvalHarnessConfig(task_spec=["capitals", "sayings"], max_examples=2, max_eval_length=64)
+    out = H.run_lm_eval_harness(cfg, model, tokenizer, 2)
+    assert fake.calls == [{"limit": 2, "log_samples": False, "bootstrap_iters": 0}]
+    assert set(out["results"]) == {"capitals", "sayings"} and out["n-samples"]["capitals"] == {"original": 3, "effective": 2}
+    assert out["averages"]["macro_avg_ll,none"] == pytest.approx(np.mean([out["results"][t]["ll,none"] for t in out["results"]]))
+    assert out["results"]["capitals"]["ll,none"] < 0
+
+    class Recorder(T.NoopTracker):
+        def __init__(self):
+            self.logged, self.artifacts = {}, []
+
+        def log(self, metrics, *, step, commit=None):
+            self.logged.update(metrics)
+
+        def log_artifact(self, artifact_path, *, name=None, type=None):
+            self.artifacts.append((name, type, open(artifact_path).read()))
+
+    rec = Recorder()
+    with T.current_tracker(rec):
+        hook = H.lm_eval_harness(cfg, tokenizer, 2, None, None)
+        hook(SimpleNamespace(step=0, eval_model=model))  # nothing at step 0
+        assert rec.logged == {}
+        hook(SimpleNamespace(step=10, eval_model=model))
+    assert rec.logged["lm_eval/capitals/ll"] == pytest.approx(out["results"]["capitals"]["ll,none"])
+    assert "lm_eval/sayings/acc" in rec.logged and "lm_eval/averages/macro_avg_acc" in rec.logged
+    assert not any("stderr" in k and "averages" in k for k in rec.logged)
+    (name, kind, text), = rec.artifacts
+    assert name == "lm_eval_harness_results.10.json" and kind == "lm_eval_output" and "n-samples" in text
+
+    monkeypatch.setattr(H, "_evaluator", None)
+    with pytest.raises(ImportError, match="lm_eval"):
+        H.run_lm_eval_harness(cfg, model, tokenizer, 2)
