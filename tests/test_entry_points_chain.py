@@ -441,3 +441,37 @@ def test_eval_lm_on_the_exported_hugging_face_weights_with_every_analysis(workdi
     assert from_ckpt["eval/loss"] == pytest.approx(from_hf["eval/loss"], rel=1e-4)
     on_train = eval_lm.main(C.decode(eval_lm.EvalLmConfig, dict(common, checkpoint_path=ck, eval_on_train=True)))
     assert on_train["eval/loss"] > 0 and on_train["eval/loss"] != pytest.approx(from_ckpt["eval/loss"], rel=1e-6)
+
+
+def test_inference_repl_command_line_mode_and_interactive_session(workdir, monkeypatch, capsys):
+    """Runs after the REPL test above (it uses the tokenizer with a chat template saved there)."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    if not os.path.exists(f"{d}/hf/config.json") or not os.path.exists(f"{d}/tok_chat"):
+        pytest.skip("needs the export of test_chain and the chat tokenizer")
+    from levanter_b200.main import inference_repl as R
+
+    base = {"model": _base(d)["model"], "tokenizer": f"{d}/tok_chat", "max_tokens": 4, "temperature": 0.0,
+            "trainer": {"require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": f"{d}/logs", "mp": "f32"}}
+    # one command from the command line: load the checkpoint, run it, exit
+    R.main(C.decode(R.InferenceReplConfig, dict(base, checkpoint=f"{d}/hf", command="chat", args="'the quick brown fox'")))
+    out = capsys.readouterr().out
+    assert f"Loaded {d}/hf" in out and "tokens]" in out
+
+    # an interactive session: help, a failing command that must not end it, load, a two-turn chat, unload, quit
+    lines = iter(["help", "", "load /does/not/exist", f"load {d}/hf", "chat", "the lazy dog", "seven small birds", "", "chat 'a quiet river'",
+                  "unload", "chat hello", "quit", "never reached"])
+    monkeypatch.setattr("builtins.input", lambda prompt="": next(lines))
+    R.main(C.decode(R.InferenceReplConfig, base))
+    out = capsys.readouterr().out
+    assert out.count("Commands:") >= 2 and "error:" in out and f"Loaded {d}/hf" in out
+    assert out.count("tokens]") == 3 and "Model unloaded" in out and "Load a model first" in out
+    assert next(lines) == "never reached"
+
+    # end of input ends the session too
+    def eof(prompt=""):
+        raise EOFError
+
+    monkeypatch.setattr("builtins.input", eof)
+    R.main(C.decode(R.InferenceReplConfig, base))
