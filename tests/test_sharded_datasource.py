@@ -77,3 +77,84 @@ def test_mapped_sources_keep_shards_and_row_offsets(tmp_path):
     name = src.shard_names[0]
     assert list(src.open_shard_at_row(name, 3)) == [6, 8, 10]
     assert list(src) == [0, 2, 4, 6, 8, 10]
+
+
+def test_hugging_face_dataset_source_with_a_stand_in_datasets_package(monkeypatch):
+    import sys
+    import types
+
+    from levanter_b200.data.sharded_datasource import datasource_from_hf
+
+    class Fake:
+        def __init__(self, rows, n_shards=1):
+            self.rows, self.n_shards = rows, n_shards
+
+        def shard(self, num_shards, index):
+            return Fake(self.rows[index::num_shards])
+
+        def skip(self, n):
+            return Fake(self.rows[n:])
+
+        def __iter__(self):
+            return iter(self.rows)
+
+    calls = []
+
+    def load_dataset(id, split, streaming, **kw):
+        calls.append((id, split, streaming, kw))
+        return Fake([{"text": f"doc {i}"} for i in range(10)], n_shards=2 if id == "two" else 1)
+
+    fake = types.ModuleType("datasets")
+    fake.load_dataset = load_dataset
+    monkeypatch.setitem(sys.modules, "datasets", fake)
+    one = datasource_from_hf("one", split="train", name="cfg")
+    assert one.shard_names == ["data"] and [r["text"] for r in one.open_shard_at_row("data", 7)] == ["doc 7", "doc 8", "doc 9"]
+    assert calls[0] == ("one", "train", True, {"name": "cfg"})
+    two = datasource_from_hf("two", split="validation", streaming=False)
+    assert two.shard_names == ["shard_0", "shard_1"] and two.num_shards == 2
+    assert [r["text"] for r in two.open_shard_at_row("shard_1", 3)] == ["doc 7", "doc 9"]
+    assert len(list(two)) == 10 and calls[-1][:3] == ("two", "validation", False)
+    monkeypatch.setitem(sys.modules, "datasets", None)
+    with pytest.raises(ImportError, match="datasets"):
+        datasource_from_hf("x", split="train").shard_names
+
+
+def test_audio_pointers_arrays_mappings_bytes_and_paths(tmp_path):
+    import io
+    import wave
+
+    import numpy as np
+
+    from levanter_b200.data.sharded_datasource import AudioTextUrlDataSource
+
+    R = AudioTextUrlDataSource.resolve_audio_pointer
+    a = R([0.0, 0.5, -0.5], 16000)
+    assert a["array"].dtype == np.float32 and a["sampling_rate"] == 16000 and a["array"].tolist() == [0.0, 0.5, -0.5]
+    b = R({"array": np.ones(4), "sampling_rate": 8000}, 16000)
+    assert b["sampling_rate"] == 8000 and b["array"].shape == (4,)
+
+    def wav(rate, channels, samples):
+        buf = io.BytesIO()
+        with wave.open(buf, "wb") as w:
+            w.setnchannels(channels), w.setsampwidth(2), w.setframerate(rate)
+            w.writeframes((np.asarray(samples) * 32767).astype(np.int16).tobytes())
+        return buf.getvalue()
+
+    t = np.sin(np.linspace(0, 20, 800))
+    mono = R(wav(16000, 1, t), 16000)
+    assert mono["array"].shape == (800,) and np.abs(mono["array"] - t).max() < 1e-3
+    stereo = R({"bytes": wav(16000, 2, np.stack([t, -t], axis=1).reshape(-1))}, 16000)
+    assert stereo["array"].shape == (800,) and np.abs(stereo["array"]).max() < 1e-3  # the channels cancel
+    half = R(wav(8000, 1, t), 16000)
+    assert half["array"].shape == (1600,) and half["sampling_rate"] == 16000  # resampled
+    (tmp_path / "clip.wav").write_bytes(wav(16000, 1, t))
+    assert R(str(tmp_path / "clip.wav"), 16000)["array"].shape == (800,)
+    assert R({"path": str(tmp_path / "clip.wav")}, 16000)["array"].shape == (800,)
+    with pytest.raises(ValueError, match="Unsupported"):
+        R(12345, 16000)
+
+    (tmp_path / "speech.jsonl").write_text(json.dumps({"audio": {"path": str(tmp_path / "clip.wav")}, "sentence": "hello"}) + "\n"
+                                           + json.dumps({"audio": [0.1, 0.2], "sentence": "again"}) + "\n")
+    src = AudioTextUrlDataSource([str(tmp_path / "speech.jsonl")])
+    rows = list(src)
+    assert rows[0][0].shape == (800,) and rows[0][1:] == (16000, "hello") and rows[1][2] == "again"
