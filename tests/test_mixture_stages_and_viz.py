@@ -77,3 +77,62 @@ def test_log_probability_pages_are_written(tmp_path):
     out2 = tmp_path / "diff.html"
     visualize_log_prob_diff(toks, lps, lps[::-1].copy(), str(out2))
     assert "diff" in out2.read_text()
+
+
+def test_log_probability_pages_from_models_and_the_training_hook(tmp_path):
+    """Per-token log-probabilities of a model over a loader end up in a page (position t shows the probability OF token t);
+    a second model gives a difference page; the hook form writes one page per call and logs it as an artifact."""
+    import torch
+
+    import levanter_b200.tracker as T
+    from levanter_b200.analysis.visualization import (cb_compute_and_visualize_log_probs, compute_and_diff_log_probs,
+                                                      compute_and_visualize_log_probs)
+    from levanter_b200.data.loader import DataLoader
+    from levanter_b200.data.passthrough_tokenizer import PassthroughTokenizer
+    from levanter_b200.models.llama import LlamaConfig
+    from levanter_b200.models.lm_model import LmExample
+
+    cfg = LlamaConfig(seq_len=8, hidden_dim=16, intermediate_dim=32, num_layers=1, num_heads=2, num_kv_heads=2)
+    a, b = cfg.build(50, seed=0).eval(), cfg.build(50, seed=1).eval()
+    data = ListAsyncDataset([LmExample.causal(torch.arange(i, i + 8, dtype=torch.int32)) for i in range(6)], is_complete=True)
+    loader = DataLoader(data, 2, max_buffered_batches=0, pin_memory=False)
+    tok = PassthroughTokenizer(50)
+
+    def log_prob_fn(model, batch):
+        logits = model(batch.tokens, batch.attn_mask).float()
+        lp = torch.log_softmax(logits, -1)
+        targets = torch.roll(batch.tokens, -1, dims=-1).long()
+        return lp.gather(-1, targets.unsqueeze(-1)).squeeze(-1), logits.argmax(-1)
+
+    page = tmp_path / "lp.html"
+    compute_and_visualize_log_probs(str(page), a, tok, log_prob_fn, loader, max_docs=5)
+    html = page.read_text()
+    assert html.count("<br><br>") == 5 and html.count("<span") == 5 * 8 and "data-argmax" in html
+    assert html.count("data-lp='0.000'") >= 5  # the first token of a document has nothing before it
+    with torch.no_grad():
+        first = LmExample.stack([data.as_sync_dataset()[0]])
+        want = float(log_prob_fn(a, first)[0][0, 0])
+    assert f"data-lp='{want:.3f}'" in html  # shown under token 1, which position 0 predicts
+
+    diff = tmp_path / "diff.html"
+    compute_and_diff_log_probs(str(diff), a, b, tok, log_prob_fn, loader, max_docs=4)
+    assert diff.read_text().count("<br><br>") == 4 and "diff" in diff.read_text()
+    same = tmp_path / "same.html"
+    compute_and_diff_log_probs(str(same), a, a, tok, log_prob_fn, loader, max_docs=2)
+    assert "diff 0.000" in same.read_text() and "diff 0.5" not in same.read_text()
+
+    class Recorder(T.NoopTracker):
+        def __init__(self):
+            self.artifacts = []
+
+        def log_artifact(self, artifact_path, *, name=None, type=None):
+            self.artifacts.append((os.path.basename(str(artifact_path)), name, type))
+
+    import os
+    from types import SimpleNamespace
+
+    rec = Recorder()
+    hook = cb_compute_and_visualize_log_probs(loader, tok, log_prob_fn, str(tmp_path / "pages"), max_docs=2)
+    with T.current_tracker(rec):
+        hook(SimpleNamespace(step=7, eval_model=a))
+    assert os.path.exists(tmp_path / "pages" / "step_7.html") and rec.artifacts == [("step_7.html", "log_probs_step_7.html", "html")]
