@@ -189,3 +189,51 @@ def test_yarn_ramp_follows_the_reference_formula():
     assert r.temperature == pytest.approx(math.sqrt(0.1 * math.log(4.0) + 1.0)) and r.position_scale == 0.25
     theta, d = cfg.to_hf_config()
     assert YarnRotaryEmbeddingsConfig.make_from_hf_config(theta, d) == cfg
+
+
+def test_attention_with_sink_module_and_window_helper():
+    """The module form: zero sinks lower every attention weight by the sink's share; very negative sinks give plain attention
+    back.  ``with_sliding_window`` changes only the window of a mask."""
+    import dataclasses
+
+    from levanter_b200.layers.attention import Attention, AttentionConfig, AttentionMask, AttentionWithSink
+
+    torch.manual_seed(0)
+    cfg = AttentionConfig(hidden_dim=32, num_heads=4, num_kv_heads=2)
+    plain = Attention(cfg).eval()
+    sink = AttentionWithSink(cfg).eval()
+    sink.load_state_dict({**plain.state_dict(), "sinks": torch.zeros(2, 2)})
+    assert sink.sinks.shape == (2, 2)  # one logit per query head, grouped by key/value head
+    x = torch.randn(2, 10, 32)
+    mask = AttentionMask.causal()
+    with torch.no_grad():
+        base = plain(x, mask)
+        with_sink = sink(x, mask)
+        assert not torch.allclose(with_sink, base, atol=1e-4)
+        sink.sinks.fill_(-1e4)
+        assert torch.allclose(sink(x, mask), base, atol=1e-5)
+        assert sink(x[0], mask).shape == (10, 32)  # unbatched input
+    loss = sink(x, mask).sum()
+    sink.sinks.data.zero_()
+    sink(x, mask).sum().backward()
+    assert sink.sinks.grad is not None and float(sink.sinks.grad.abs().sum()) > 0
+
+    m = AttentionMask.causal().with_sliding_window(3)
+    assert m.is_causal and m.sliding_window == 3
+    dense = m.materialize(6, 6)
+    assert dense.reshape(6, 6)[5].tolist() == [False, False, False, True, True, True]
+    assert dataclasses.replace(m, sliding_window=None) == AttentionMask.causal()
+
+
+def test_passthrough_tokenizer_is_enough_of_a_tokenizer():
+    from levanter_b200.data.passthrough_tokenizer import PassthroughTokenizer
+
+    tok = PassthroughTokenizer(100, bos_token_id=1)
+    assert len(tok) == tok.vocab_size == 100 and tok.eos_token_id == 99 and tok.eos_token == "99" and tok.bos_token == "1"
+    assert PassthroughTokenizer(10).bos_token is None and tok.pad_token_id == 99
+    assert tok.encode("3 4 5") == [3, 4, 5] and tok.decode([3, 4, 5]) == "3 4 5"
+    assert tok(["1 2", "3"])["input_ids"] == [[1, 2], [3]] and tok("7 8")["input_ids"] == [7, 8]
+    assert tok.convert_ids_to_tokens([3, 4]) == ["3", "4"] and tok.convert_tokens_to_ids(["3", "4"]) == [3, 4] and tok.convert_tokens_to_ids("9") == 9
+    assert tok.get_vocab()["42"] == 42 and tok.save_vocabulary("/nowhere") == ()
+    with pytest.raises(ValueError, match="integers"):
+        tok.encode("3 x")
