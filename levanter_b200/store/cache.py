@@ -389,6 +389,8 @@ class TreeCache(AsyncDataset[T_co]):
 
 
 _SENTINEL = object()
+_BUILDERS: Dict[str, "_CacheBuilder"] = {}  # running builds of this process by cache directory
+_BUILDERS_LOCK = threading.Lock()
 
 
 class _CacheBuilder:
@@ -521,6 +523,11 @@ class _CacheBuilder:
                 self._error = e
             self._stop.set()
             logger.exception(f"cache build at {self.cache_dir} failed")
+        finally:
+            with _BUILDERS_LOCK:  # finished or failed: the next request starts from the ledger on disk
+                for k, b in list(_BUILDERS.items()):
+                    if b is self:
+                        del _BUILDERS[k]
 
 
 def build_or_load_cache(cache_dir: str, source, processor: BatchProcessor, await_finished: bool = True,
@@ -540,11 +547,19 @@ def build_or_load_cache(cache_dir: str, source, processor: BatchProcessor, await
     if process_index() != 0:
         cache = TreeCache(cache_dir, processor.output_exemplar, None, None)  # follows the ledger rank 0 writes
     else:
-        ledger = CacheLedger.load_or_initialize(cache_dir, source, processor)
-        for s in source.shard_names:
-            ledger.shard_rows.setdefault(s, 0)
-        builder = _CacheBuilder(cache_dir, source, processor, options, ledger)
-        cache = TreeCache(cache_dir, processor.output_exemplar, ledger, builder)
+        # one builder per directory and process: a second request while a build is running reads along with it (the
+        # reference gets this from a named actor per cache directory)
+        key = os.path.abspath(cache_dir) if "://" not in cache_dir else cache_dir
+        with _BUILDERS_LOCK:
+            builder = _BUILDERS.get(key)
+            if builder is not None and (not builder._thread.is_alive() or builder._error is not None):
+                builder = None
+            if builder is None:
+                ledger = CacheLedger.load_or_initialize(cache_dir, source, processor)
+                for s in source.shard_names:
+                    ledger.shard_rows.setdefault(s, 0)
+                builder = _BUILDERS[key] = _CacheBuilder(cache_dir, source, processor, options, ledger)
+        cache = TreeCache(cache_dir, processor.output_exemplar, builder.ledger_snapshot(), builder)
     for m in monitors or []:
         cache.attach_metrics_monitor(m)
     if await_finished:

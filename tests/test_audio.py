@@ -104,3 +104,35 @@ def test_train_asr_tiny(tmp_path, monkeypatch):
         "optimizer": {"learning_rate": 1e-3, "warmup": 0.0},
     }
     train_asr.main(C.decode(train_asr.TrainASRConfig, cfg))
+
+
+def test_audio_mixture_of_two_sources(tmp_path):
+    import asyncio
+
+    from levanter_b200.data.audio import AudioDatasetSourceConfig, AudioMixtureDatasetConfig
+    from levanter_b200.data.mixture import MixtureDataset
+
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    url_a, url_b = _write_corpus(tmp_path / "a", n=6), _write_corpus(tmp_path / "b", n=4)
+    common = dict(cache_dir=f"{tmp_path}/cache", tokenizer="passthrough", vocab_size=100, processor="builtin", max_length=8)
+    cfg = AudioMixtureDatasetConfig(configs={"a": AudioDatasetSourceConfig(train_urls=[url_a], validation_urls=[url_a]),
+                                             "b": AudioDatasetSourceConfig(train_urls=[url_b]),
+                                             "unused": AudioDatasetSourceConfig(train_urls=[url_b])},
+                                    train_weights={"a": 0.75, "b": 0.25, "unused": 0.0}, mixture_block_size=4, shuffle=True, **common)
+    caches = cfg.build_caches("train")
+    assert set(caches) == {"a", "b"}  # a source with weight zero is not even built
+    train = cfg.train_set(key=3)
+    assert isinstance(train, MixtureDataset)
+    rows = asyncio.run(train.get_batch(list(range(8))))
+    assert all(r["input_features"].shape[0] == 80 and r["input_ids"].shape == (8,) for r in rows)
+    val = cfg.validation_sets()
+    assert set(val) == {"a"} and asyncio.run(val["a"].async_len()) == 6  # only the source that names validation data
+    assert asyncio.run(caches["a"].async_len()) == 6 and asyncio.run(caches["b"].async_len()) == 4
+
+    with pytest.raises(ValueError, match="At least one dataset"):
+        AudioMixtureDatasetConfig(configs={}, train_weights={})
+    with pytest.raises(ValueError, match="must be the same"):
+        AudioMixtureDatasetConfig(configs={"a": AudioDatasetSourceConfig(train_urls=[url_a])}, train_weights={"b": 1.0})
+    by_yaml = C.decode(AudioMixtureDatasetConfig, {"configs": {"a": {"train_urls": [url_a]}}, "train_weights": {"a": 1.0}, "shuffle": 16, **common})
+    assert by_yaml.shuffle == 16 and asyncio.run(by_yaml.train_set(key=0).get_batch([0]))[0]["input_ids"].shape == (8,)

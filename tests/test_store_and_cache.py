@@ -413,3 +413,32 @@ def test_serial_writer_drops_an_unfinished_cache_on_error(tmp_path):
             raise _Boom()
     with pytest.raises(FileNotFoundError):
         TreeCache.load(str(tmp_path / "c"), ex)
+
+
+def test_two_requests_for_a_cache_that_is_being_built_share_one_builder(tmp_path):
+    gate = threading.Event()
+    opened = []
+
+    class Gated(ShardedDataSource):
+        @property
+        def shard_names(self):
+            return ["shard_0"]
+
+        def open_shard_at_row(self, shard_name, row):
+            opened.append(row)
+            for i in range(row, 12):
+                if i == 6:
+                    assert gate.wait(30)
+                yield [i] * 4
+
+    opts = CacheOptions(target_size_per_flush=1, batch_size=2)
+    first = build_or_load_cache(str(tmp_path), Gated(), _Processor(), await_finished=False, options=opts)
+    first.get_batch_sync([0])
+    second = build_or_load_cache(str(tmp_path), Gated(), _Processor(), await_finished=False, options=opts)
+    assert second._builder is first._builder and opened == [0]  # the source was opened once
+    gate.set()
+    first.await_finished(timeout=30)
+    second.await_finished(timeout=30)
+    _check(second, [np.asarray([i] * 4, np.int64) for i in range(12)])
+    third = build_or_load_cache(str(tmp_path), Gated(), _Processor(), options=opts)  # finished: no builder at all
+    assert third._builder is None and len(third) == 12
