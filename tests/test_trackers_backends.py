@@ -1,4 +1,6 @@
 """The tensorboard and trackio trackers against fake back ends (neither service is contacted), and the flat packing of trees."""
+import pytest
+import os
 import numpy as np
 import torch
 
@@ -87,3 +89,79 @@ def test_pack_and_unpack_trees():
     assert int(back["b"][1]) == 5 and back["b"][1].dtype == torch.int32 and back["b"][1].shape == ()
     offsets, flat = pack_pytree({})
     assert flat.numel() == 0 and unpack_pytree(offsets, flat) == {}
+
+
+class _FakeWandbRun:
+    def __init__(self):
+        self.step, self.logged, self.summary, self.artifacts, self.finished, self.code = 0, [], {}, [], False, None
+        self.config = self
+
+    def update(self, values, allow_val_change=False):  # run.config.update
+        self.hparams = dict(values)
+
+    def log(self, metrics, step=None, commit=None):
+        self.logged.append((step, dict(metrics), commit))
+        if step is not None:
+            self.step = step
+
+    def log_artifact(self, path, name=None, type=None):
+        self.artifacts.append((os.path.basename(path), name, type))
+
+    def log_code(self, root):
+        self.code = root
+
+    def finish(self):
+        self.finished = True
+
+
+def test_wandb_tracker_logs_steps_in_order_histograms_summaries_and_artifacts(monkeypatch, tmp_path, caplog):
+    wandb = pytest.importorskip("wandb")
+    from levanter_b200.tracker.histogram import Histogram
+    from levanter_b200.tracker.wandb import WandbTracker
+
+    run = _FakeWandbRun()
+    run.summary = {}
+    t = WandbTracker(run)
+    t.log_hyperparameters({"lr": 0.1})
+    t.log({"loss": 1.0}, step=3)
+    t.log({"loss": 0.5, "hist": Histogram.from_array(torch.arange(10.0))}, step=4)
+    t.log({"late": 1.0}, step=2)  # a step the run is already past: refused with a warning, not an error
+    t.log({"auto": 2.0}, step=None)
+    assert run.hparams == {"lr": 0.1} and [s for s, _, _ in run.logged] == [3, 4, 4]
+    assert isinstance(run.logged[1][1]["hist"], wandb.Histogram) and run.logged[2][1] == {"auto": 2.0}
+    assert "Cowardly refusing" in caplog.text
+    t.log_summary({"best": 0.5})
+    (tmp_path / "a.txt").write_text("x")
+    t.log_artifact(str(tmp_path / "a.txt"), name="a", type="text")
+    t.finish()
+    assert run.summary == {"best": 0.5} and run.artifacts == [("a.txt", "a", "text")] and run.finished
+
+
+def test_wandb_config_chooses_the_run_id_mode_and_records_the_commit(monkeypatch):
+    wandb = pytest.importorskip("wandb")
+    from levanter_b200.tracker.wandb import WandbConfig, WandbTracker
+
+    calls = []
+
+    def fake_init(**kw):
+        calls.append(kw)
+        return _FakeWandbRun()
+
+    monkeypatch.setattr(wandb, "init", fake_init)
+    monkeypatch.delenv("WANDB_API_KEY", raising=False)
+    monkeypatch.delenv("WANDB_MODE", raising=False)
+    monkeypatch.setenv("RANK", "0")
+    tracker = WandbConfig(project="proj", tags=["t"], save_code=False).init("run-1")
+    assert isinstance(tracker, WandbTracker)
+    kw = calls[-1]
+    assert kw["id"] == "run-1" and kw["project"] == "proj" and kw["tags"] == ["t"] and kw["resume"] == "allow"
+    assert kw["mode"] == "offline"  # no credentials and no explicit mode: usable without a network
+    assert len(kw["config"]["git_commit"]) == 40
+    WandbConfig(id="mine", mode="online").init("run-1")
+    assert calls[-1]["id"] == "mine" and calls[-1]["mode"] == "online"  # the tracker's own id wins
+    monkeypatch.setenv("WANDB_API_KEY", "k")
+    WandbConfig(save_code=False).init("r")
+    assert calls[-1]["mode"] is None
+    monkeypatch.setenv("RANK", "3")
+    WandbConfig(save_code=False).init("r")
+    assert calls[-1]["mode"] == "offline"  # only process 0 talks to the service
