@@ -162,3 +162,51 @@ def test_exported_names_and_shapes_are_the_ones_transformers_uses(name):
     for k in ours:
         if k in theirs:
             assert ours[k] == theirs[k], k
+
+
+RESIZABLE = FAMILIES + ["gated_deltanet", "gpt2_hyena"]
+
+
+def _any_cfg(name):
+    if name == "gated_deltanet":
+        from levanter_b200.models.gated_deltanet import GatedDeltaNetConfig
+
+        return GatedDeltaNetConfig(seq_len=64, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, head_k_dim=8, head_v_dim=8, chunk_size=16, gradient_checkpointing=False)
+    if name == "gpt2_hyena":
+        from levanter_b200.models.gpt2_hyena import Gpt2HyenaConfig
+        from levanter_b200.models.hyena import HyenaConfig
+
+        return Gpt2HyenaConfig(num_layers=2, gradient_checkpointing=False, hyena=HyenaConfig(seq_len=64, hidden_dim=32, filter_order=8))
+    return _cfg(name)
+
+
+@pytest.mark.parametrize("name", RESIZABLE)
+def test_resizing_the_vocabulary_keeps_the_old_rows_and_the_old_predictions(name):
+    model = _any_cfg(name).build(VOCAB, seed=0).eval()
+    ids = torch.randint(0, VOCAB, (1, 16), generator=torch.Generator().manual_seed(0))
+    with torch.no_grad():
+        before = model(ids, AttentionMask.causal())
+    bigger = model.resize_vocab(VOCAB + 24)
+    assert bigger.vocab_size == VOCAB + 24
+    with torch.no_grad():
+        after = bigger(ids, AttentionMask.causal())
+    assert after.shape == (1, 16, VOCAB + 24)
+    assert torch.allclose(after[..., :VOCAB], before, atol=1e-5)  # logits of the old tokens do not move
+    assert torch.isfinite(after).all() and float(after[..., VOCAB:].abs().sum()) > 0  # the new rows are initialised, not zeros
+    loss = compute_next_token_loss(bigger.train(), LmExample.causal(torch.randint(0, VOCAB + 24, (2, 16)).to(torch.int32)))
+    loss.backward()
+    assert all(p.grad is None or torch.isfinite(p.grad).all() for p in bigger.parameters())
+    smaller = bigger.eval().resize_vocab(VOCAB - 40)
+    with torch.no_grad():
+        cut = smaller(ids.clamp(max=VOCAB - 41), AttentionMask.causal())
+    assert cut.shape[-1] == VOCAB - 40 and smaller.vocab_size == VOCAB - 40
+
+
+def test_prompt_and_completion_examples_mask_the_prompt():
+    tokens = torch.arange(8, dtype=torch.int32)
+    ex = LmExample.from_prompt_and_completion(tokens, prompt_length=3)
+    assert ex.loss_mask.tolist() == [0, 0, 1, 1, 1, 1, 1, 0] and ex.attn_mask.is_causal  # position 2 predicts the first completion token
+    batch = LmExample.from_prompt_and_completion(torch.arange(16, dtype=torch.int32).reshape(2, 8), prompt_length=torch.tensor([1, 6]), ignore_id=15)
+    assert batch.loss_mask.tolist() == [[1, 1, 1, 1, 1, 1, 1, 0], [0, 0, 0, 0, 0, 1, 0, 0]]  # the token before an ignored one is not scored
+    with pytest.raises(NotImplementedError):
+        LmExample.from_prompt_and_completion(tokens, 3, all_causal=False)
