@@ -2,6 +2,8 @@ import datetime
 import json
 import os
 
+import pytest
+
 from levanter_b200.infra import cli_helpers, launch
 from levanter_b200.main.clean_old_checkpoints import checkpoints_to_delete
 
@@ -35,3 +37,22 @@ def test_clean_old_checkpoints_keeps_newest_and_newest_thousand(tmp_path):
     doomed = sorted(os.path.basename(p) for p in checkpoints_to_delete(str(tmp_path), min_age_days=1.0))
     assert doomed == ["step-1000", "step-1500", "step-500"]
     assert checkpoints_to_delete(str(tmp_path), min_age_days=10.0) == []
+
+
+def test_a_command_is_rerun_until_it_succeeds(tmp_path):
+    import sys
+
+    from levanter_b200.infra.resumable import run_command_resumable
+
+    counter = tmp_path / "count"
+    counter.write_text("0")
+    script = f"import sys; p = {str(counter)!r}; n = int(open(p).read()) + 1; open(p, 'w').write(str(n)); sys.exit(0 if n >= 3 else 1)"
+    retries = []
+    rc = run_command_resumable([sys.executable, "-c", script], max_retries_failure=5, backoff_seconds=0, on_retry=lambda kind, n, e: retries.append((kind, n)))
+    assert rc == 0 and counter.read_text() == "3" and [n for _, n in retries] == [1, 2]
+    counter.write_text("-100")
+    import subprocess
+
+    with pytest.raises(subprocess.CalledProcessError):
+        run_command_resumable([sys.executable, "-c", script], max_retries_failure=1, backoff_seconds=0)
+    assert counter.read_text() == "-98"  # the first try and one retry

@@ -113,3 +113,33 @@ def test_the_merged_export_loads_in_transformers_with_the_adapted_logits(tmp_pat
         hf_merged = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "merged")).eval()(ids.long()).logits
     assert torch.allclose(lora_out, hf_merged, atol=1e-4)
     assert any(isinstance(m, LoraLinear) for m in lora.modules())  # exporting did not merge the live model
+
+
+def test_adapter_parameters_partition_and_the_export_hooks(tmp_path):
+    from types import SimpleNamespace
+
+    from levanter_b200.lora import (combine_lora_params, filter_lora_params, partition_lora_params, save_merged_hf_checkpoint_callback,
+                                    save_peft_checkpoint_callback)
+
+    cfg = _llama()
+    lora_cfg = LoraConfig(r=2, target_modules=["q_proj"])
+    model = loraize(cfg.build(VOCAB, seed=0), lora_cfg, seed=1)
+    params = dict(model.named_parameters())
+    adapters, base = partition_lora_params(params)
+    assert adapters and base and set(adapters) | set(base) == set(params) and not set(adapters) & set(base)
+    assert filter_lora_params(params).keys() == adapters.keys() and all("lora" in k for k in adapters)
+    new = {k: torch.zeros_like(v) for k, v in adapters.items()}
+    combined = combine_lora_params(base, new)
+    assert set(combined) == set(params) and all(float(combined[k].abs().sum()) == 0 for k in adapters)
+    wrapped = [m for m in model.modules() if isinstance(m, LoraLinear)]
+    assert wrapped[0].in_features == 32 and wrapped[0].out_features == 32 and wrapped[0].bias is None and wrapped[0].weight.shape == (32, 32)
+
+    conv = cfg.hf_checkpoint_converter()
+    merged_hook = save_merged_hf_checkpoint_callback(str(tmp_path / "merged"), conv, save_tokenizer=False)
+    peft_hook = save_peft_checkpoint_callback(str(tmp_path / "peft"), lora_cfg, "org/base")
+    for hook in (merged_hook, peft_hook):
+        hook(SimpleNamespace(step=0, eval_model=model))  # nothing is exported at step 0
+        hook(SimpleNamespace(step=5, eval_model=model))
+    assert os.listdir(tmp_path / "merged") == ["step-5"] and os.path.exists(tmp_path / "merged" / "step-5" / "config.json")
+    assert os.listdir(tmp_path / "peft") == ["step-5"] and os.path.exists(tmp_path / "peft" / "step-5" / "adapter_config.json")
+    assert any(isinstance(m, LoraLinear) for m in model.modules())
