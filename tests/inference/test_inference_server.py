@@ -146,3 +146,54 @@ def test_weight_reload_during_requests(server):
         assert after["choices"][0]["text"] != before["choices"][0]["text"]
         server.unload()
         assert client.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 2}).status_code == 500
+
+
+def test_server_over_a_real_socket_and_model_loading_from_the_config(tmp_path):
+    """``serve_async`` answers HTTP requests on a port; ``InferenceServer.create`` without a model loads the configured
+    Hugging Face directory."""
+    import asyncio
+    import json
+    import socket
+    import urllib.request
+
+    from levanter_b200.inference.openai import _load_model
+
+    cfg_model = LlamaConfig(seq_len=64, hidden_dim=32, intermediate_dim=64, num_layers=1, num_heads=2, num_kv_heads=2)
+    model = cfg_model.build(256, seed=0).eval()
+    cfg_model.hf_checkpoint_converter().save_pretrained(model, str(tmp_path / "hf"), save_tokenizer=False)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cfg = InferenceServerConfig(model=cfg_model, hf_checkpoint=str(tmp_path / "hf"), host="127.0.0.1", port=port, batch_timeout=0.02,
+                                service=InferenceEngineConfig(max_seqs=2, page_size=8, max_pages_per_seq=8, compute_dtype=torch.float32, max_rounds=2))
+    loaded = _load_model(cfg, CharTokenizer())
+    for (n, p), (_, q) in zip(model.named_parameters(), loaded.named_parameters()):
+        assert torch.equal(p, q.float()), n
+    srv = InferenceServer.create(cfg, model=loaded, tokenizer=CharTokenizer())
+
+    async def scenario():
+        task = asyncio.create_task(srv.serve_async())
+        loop = asyncio.get_running_loop()
+
+        def call():
+            for _ in range(100):
+                try:
+                    with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                        health = json.loads(r.read())
+                    break
+                except OSError:
+                    import time
+
+                    time.sleep(0.05)
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", method="POST", headers={"Content-Type": "application/json"},
+                                         data=json.dumps({"model": "m", "prompt": "hi", "max_tokens": 3, "temperature": 0.0}).encode())
+            with urllib.request.urlopen(req, timeout=30) as r:
+                return health, json.loads(r.read())
+
+        health, body = await loop.run_in_executor(None, call)
+        srv.shutdown()
+        await asyncio.wait_for(task, 30)
+        return health, body
+
+    health, body = asyncio.run(scenario())
+    assert health["status"] == "healthy" and body["object"] == "text_completion" and 1 <= body["usage"]["completion_tokens"] <= 3
