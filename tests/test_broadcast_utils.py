@@ -55,3 +55,45 @@ def test_single_process_paths():
         import ray  # noqa: F401
     except ImportError:
         assert auto_ray_cluster() is False  # nothing here needs Ray: absent means "not started", not an error
+
+
+def _helpers_worker(rank, world, port, out):
+    import json
+
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), CUDA_VISIBLE_DEVICES="")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    res = {}
+    try:
+        from levanter_b200.data.loader import check_sharded_consistency
+        from levanter_b200.distributed import broadcast_one_to_all, is_local_leader, process_count, process_index
+        from levanter_b200.parallel.mesh import DeviceMesh
+        from levanter_b200.utils.torch_utils import multihost_broadcast_sync
+
+        res["index"], res["count"], res["leader"] = process_index(), process_count(), is_local_leader()
+        res["object"] = broadcast_one_to_all({"run": "abc"} if rank == 0 else None)
+        res["synced"] = multihost_broadcast_sync(f"from {rank}")
+        mesh = DeviceMesh(1, 1, 2)  # both ranks on the model axis: they must load identical batches
+        check_sharded_consistency(torch.arange(8).reshape(2, 4), mesh)
+        try:
+            check_sharded_consistency(torch.arange(8).reshape(2, 4) + rank, mesh)
+            res["mismatch"] = "not noticed"
+        except RuntimeError as e:
+            res["mismatch"] = str(e)
+        data_mesh = DeviceMesh(1, 2, 1)  # a data axis only: ranks hold different rows, nothing to compare
+        check_sharded_consistency(torch.arange(8).reshape(2, 4) + rank, data_mesh)
+        json.dump(res, open(os.path.join(out, f"h{rank}.json"), "w"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_process_helpers_and_the_identical_batch_check_on_two_ranks(tmp_path):
+    import json
+
+    mp.spawn(_helpers_worker, args=(2, 29743, str(tmp_path)), nprocs=2, join=True)
+    r = [json.load(open(tmp_path / f"h{i}.json")) for i in range(2)]
+    assert [x["index"] for x in r] == [0, 1] and [x["count"] for x in r] == [2, 2] and [x["leader"] for x in r] == [True, False]
+    assert r[0]["object"] == r[1]["object"] == {"run": "abc"} and r[0]["synced"] == r[1]["synced"] == "from 0"
+    assert all("differs between tensor-parallel ranks" in x["mismatch"] for x in r)
