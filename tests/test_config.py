@@ -215,3 +215,34 @@ data:
     assert mix.train_weights == {"owt": 0.6, "wikitext": 0.4} and mix.tokenizer == "gpt2"
     assert isinstance(mix.configs["owt"], UrlDatasetSourceConfig) and isinstance(mix.configs["wikitext"], HfDatasetSourceConfig)
     assert len(mix.configs["owt"].urls_for_split("validation")) == 1 and mix.configs["wikitext"].id == "dlwh/wikitext_103_detokenized"
+
+
+def test_custom_codecs_and_precision_policy_casts():
+    import dataclasses as dc
+    import fractions
+
+    import torch
+
+    from levanter_b200 import config as C
+
+    C.register_codec(fractions.Fraction, lambda v: fractions.Fraction(str(v)), lambda f: f"{f.numerator}/{f.denominator}")
+
+    @dc.dataclass
+    class Holder:
+        ratio: fractions.Fraction = fractions.Fraction(1, 2)
+        mp: C.Policy = dc.field(default_factory=lambda: C.Policy.parse("f32"))
+
+    h = C.decode(Holder, {"ratio": "3/4", "mp": "p=f32,c=bfloat16,o=f32"})
+    assert h.ratio == fractions.Fraction(3, 4) and C.encode(h)["ratio"] == "3/4"
+    assert C.encode(h)["mp"] == "compute=bfloat16,params=float32,output=float32"
+    assert C.decode(Holder, C.encode(h)) == h  # what is written can be read back
+
+    p = h.mp
+    x = torch.ones(2, dtype=torch.float32)
+    ids = torch.ones(2, dtype=torch.int32)
+    assert p.cast_to_compute(x).dtype == torch.bfloat16 and p.cast_to_param(x.bfloat16()).dtype == torch.float32 and p.cast_to_output(x.bfloat16()).dtype == torch.float32
+    assert p.cast_to_compute(ids).dtype == torch.int32  # integers are left alone
+    assert C.Policy.parse("bfloat16") == C.Policy(torch.bfloat16, torch.bfloat16, torch.bfloat16)
+    assert C.Policy.parse("compute=bfloat16,params=float32").output_dtype == torch.bfloat16  # the output follows the compute dtype
+    with pytest.raises(C.ConfigError):
+        C.Policy.parse("q=f32")
