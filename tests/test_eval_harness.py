@@ -229,3 +229,27 @@ def test_harness_run_reports_results_averages_and_an_artifact(tokenizer, monkeyp
     monkeypatch.setattr(H, "_evaluator", None)
     with pytest.raises(ImportError, match="lm_eval"):
         H.run_lm_eval_harness(cfg, model, tokenizer, 2)
+
+
+def test_harness_entry_point_on_a_hugging_face_directory(tokenizer, tmp_path, monkeypatch, capsys):
+    import levanter_b200.eval_harness as H
+    from levanter_b200 import config as C
+
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    tokenizer.save_pretrained(str(tmp_path / "tok"))
+    cfg_model = LlamaConfig(seq_len=64, hidden_dim=32, intermediate_dim=64, num_layers=1, num_heads=2, num_kv_heads=2)
+    model = cfg_model.build(len(tokenizer), seed=1)
+    cfg_model.hf_checkpoint_converter().save_pretrained(model, str(tmp_path / "hf"), save_tokenizer=False)
+    monkeypatch.setattr(H, "_evaluator", _FakeEvaluator())
+    monkeypatch.setattr(LmEvalHarnessConfig, "to_task_dict", lambda self: {"sayings": PAIRS})
+    cfg = C.decode(H.EvalHarnessMainConfig, {
+        "eval_harness": {"task_spec": ["sayings"], "max_eval_length": 64}, "tokenizer": str(tmp_path / "tok"), "checkpoint_path": str(tmp_path / "hf"),
+        "checkpoint_is_hf": True, "model": {"type": "llama", "seq_len": 64, "hidden_dim": 32, "intermediate_dim": 64, "num_layers": 1, "num_heads": 2, "num_kv_heads": 2},
+        "trainer": {"require_accelerator": False, "tracker": {"type": "noop"}, "log_dir": str(tmp_path / "logs"), "per_device_eval_parallelism": 2}})
+    assert cfg.EvalBatch == 2
+    out = H.run_eval_harness_main(cfg)
+    lm, _ = _lm(tokenizer)
+    lm.leader.scorer.model = model.eval()
+    want = np.mean([l for l, _ in lm.loglikelihood(_requests(PAIRS))])
+    assert out["results"]["sayings"]["ll,none"] == pytest.approx(want, abs=1e-3)  # the weights that were saved are the ones scored
+    assert "macro_avg_ll,none" in capsys.readouterr().out
