@@ -475,3 +475,31 @@ def test_inference_repl_command_line_mode_and_interactive_session(workdir, monke
 
     monkeypatch.setattr("builtins.input", eof)
     R.main(C.decode(R.InferenceReplConfig, base))
+
+
+def test_train_lm_for_a_number_of_epochs_stops_when_the_data_ends(workdir, monkeypatch):
+    """``epoch: 2`` repeats the training windows twice and no more: the run ends there although ``num_train_steps`` is larger,
+    and its last step is checkpointed."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    monkeypatch.chdir(workdir)
+    d = str(workdir)
+    from levanter_b200.checkpoint import _load_metadata, discover_latest_checkpoint
+    from levanter_b200.main import train_lm
+
+    cfg = _base(d, 10_000)
+    cfg["trainer"]["id"] = "epochs"
+    cfg["epoch"] = 2
+    built = C.decode(train_lm.TrainLmConfig, cfg)
+    windows = asyncio_len(built.data.train_set(32, key=0))
+    assert windows >= 8
+    train_lm.main(built)
+    ck = discover_latest_checkpoint(f"{d}/ckpt/epochs")
+    assert ck is not None
+    steps_run = _load_metadata(ck)["step"] + 1
+    assert steps_run == (2 * windows) // 8 or steps_run == -(-(2 * windows) // 8)  # two passes at 8 sequences per step (a short last batch is padded)
+
+
+def asyncio_len(ds):
+    import asyncio
+
+    return asyncio.run(ds.async_len())
