@@ -168,3 +168,33 @@ def test_learning_rate_schedules_from_the_registry():
         AdamConfig(lr_schedule="sawtooth").lr_scheduler(10)
     with pytest.raises(ValueError):
         AdamConfig(warmup=1.5).lr_scheduler(10)
+
+
+def test_hessian_vector_products_noise_trees_block_clipping_and_norm_logging():
+    import levanter_b200.tracker as Tr
+    from levanter_b200.optim.util import hvp, log_norm_passthrough, scan_aware_clip_by_block_rms, tree_gaussian_like
+
+    # f(x, y) = x^T A x + sum(x) * sum(y): Hessian blocks 2A (x, x), ones (x, y), zero (y, y)
+    A = torch.tensor([[2.0, 1.0], [1.0, 3.0]])
+    params = {"x": torch.tensor([1.0, -1.0]), "y": torch.tensor([0.5, 0.25, 2.0]), "ids": None}
+
+    def f(p):
+        return p["x"] @ A @ p["x"] + p["x"].sum() * p["y"].sum()
+
+    v = {"x": torch.tensor([1.0, 2.0]), "y": torch.tensor([1.0, 0.0, -1.0]), "ids": None}
+    hv = hvp(f, params, v)
+    assert torch.allclose(hv["x"], 2 * A @ v["x"] + v["y"].sum()) and torch.allclose(hv["y"], torch.full((3,), v["x"].sum()))
+    assert set(hv) == {"x", "y"} and not params["x"].requires_grad  # the caller's tensors are left as they were
+
+    g = torch.Generator().manual_seed(0)
+    noise = tree_gaussian_like({"w": torch.zeros(200, 200, dtype=torch.bfloat16), "i": torch.zeros(3, dtype=torch.int32), "n": None}, generator=g)
+    assert noise["i"] is None and noise["n"] is None and noise["w"].dtype == torch.bfloat16
+    assert abs(float(noise["w"].float().mean())) < 0.02 and abs(float(noise["w"].float().std()) - 1.0) < 0.02
+
+    clip = scan_aware_clip_by_block_rms(1.0)
+    out, _ = clip.update({"big": torch.full((4,), 3.0), "small": torch.full((4,), 0.5)}, clip.init({}))
+    assert torch.allclose(out["big"], torch.ones(4)) and torch.allclose(out["small"], torch.full((4,), 0.5))  # each tensor by its own RMS
+
+    with Tr.defer_tracker_for_jit() as logged:
+        same, _ = log_norm_passthrough("optim/pre_clip_norm").update({"a": torch.tensor([3.0, 4.0])}, T.EmptyState())
+    assert same["a"].tolist() == [3.0, 4.0] and logged["optim/pre_clip_norm"] == pytest.approx(5.0)
