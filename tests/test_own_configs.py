@@ -42,3 +42,30 @@ def test_flagship_config_is_llama2_7b():
     m = cfg.model
     assert (m.hidden_dim, m.intermediate_dim, m.num_layers, m.num_heads, m.seq_len) == (4096, 11008, 32, 32, 4096)
     assert abs(m.total_trainable_params(32000) - 6.74e9) / 6.74e9 < 0.01
+
+
+def test_packaging_metadata_names_real_packages_scripts_and_sources():
+    """``pyproject.toml`` builds the package that is in the tree: the version attribute, the console scripts' targets and the
+    kernel sources it ships all exist."""
+    import glob
+    import importlib
+    import os
+    import tomllib
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    meta = tomllib.load(open(os.path.join(root, "pyproject.toml"), "rb"))
+    assert meta["project"]["name"] == "levanter_b200"
+    mod, attr = meta["tool"]["setuptools"]["dynamic"]["version"]["attr"].rsplit(".", 1)
+    assert isinstance(getattr(importlib.import_module(mod), attr), str)
+    for target in meta["project"]["scripts"].values():
+        module, func = target.split(":")
+        assert callable(getattr(importlib.import_module(module), func)), target
+    for pkg, patterns in meta["tool"]["setuptools"]["package-data"].items():
+        base = os.path.join(root, *pkg.split("."))
+        for pattern in patterns:
+            assert glob.glob(os.path.join(base, pattern)), (pkg, pattern)
+    from setuptools import find_packages
+
+    found = set(find_packages(root, include=meta["tool"]["setuptools"]["packages"]["find"]["include"]))
+    on_disk = {os.path.relpath(d, root).replace(os.sep, ".") for d, _, files in os.walk(os.path.join(root, "levanter_b200")) if "__init__.py" in files}
+    assert found == on_disk and "levanter_b200.ops" in found and "levanter_b200.main" in found
