@@ -127,3 +127,35 @@ def test_stop_sequence_of_two_tokens():
     stop = full[2:4]
     out = eng.generate([_req(0, prompt, extra=8, stop=stop)])
     assert out.tokens[0] == full[:4]
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_workloads_on_a_small_page_pool_match_plain_greedy_decoding(seed):
+    """Many requests of random prompt lengths, generation lengths, clone counts and stop sequences, served by an engine with
+    few slots, few pages and small prefill batches, so that requests queue, prefill in pieces and reuse freed pages: every
+    generation must equal token-by-token greedy decoding of the full forward pass, and nothing may leak."""
+    rng = np.random.default_rng(seed)
+    model = _tiny_llama()
+    cfg = InferenceEngineConfig(max_seqs=3 + seed, page_size=4, max_pages_per_seq=6, max_pages=14 + 4 * seed, compute_dtype=torch.float32,
+                                max_rounds=int(rng.integers(1, 5)), max_seqs_in_prefill=2, max_prefill_size=16, max_queued_tokens=16)
+    eng = InferenceEngine.from_model_with_config(model, None, cfg)
+    for wave in range(2):  # the second call starts from the state the first one left
+        reqs, want = [], []
+        for i in range(7):
+            prompt = rng.integers(1, 50, size=int(rng.integers(1, 13))).tolist()
+            n_new = int(rng.integers(1, 24 - len(prompt)))
+            n = int(rng.integers(1, 3))
+            full = _greedy_full_forward(model, prompt, n_new)
+            stop = None
+            if n_new >= 3 and rng.random() < 0.4:
+                at = int(rng.integers(1, n_new - 1))
+                stop = full[at:at + 2]
+                first = next(j for j in range(len(full) - 1) if full[j:j + 2] == stop)
+                full = full[:first + 2]  # generation ends with the first occurrence of the stop sequence
+            reqs.append(_req(i, prompt, n=n, extra=n_new, stop=stop))
+            want += [full] * n
+        out = eng.generate(reqs)
+        assert out.tokens == want, (seed, wave)
+        assert out.total_generated == sum(len(w) for w in want)
+        pt = eng.gen_state.decode_state.page_table
+        assert not pt.used_mask.any() and int(pt.page_ref_counts.sum()) == 0 and pt.num_free_pages == pt.num_pages
