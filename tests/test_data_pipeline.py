@@ -290,3 +290,40 @@ def test_supervised_format_packs(tmp_path):
         if lm[t]:
             assert toks[t + 1] >= 100 and seg[t + 1] == seg[t]
     assert lm[seg == -1].sum() == 0
+
+
+def test_any_step_of_a_shuffled_staged_mixture_can_be_reached_directly(tmp_path):
+    """The batch of step k is a function of the configuration and k alone: iterating from 0, resuming at k, and asking a fresh
+    dataset object built from the same config give the same tokens (mixture with stages, per-source shuffle, batch-size schedule)."""
+    from levanter_b200.data.loader import DataLoader
+    from levanter_b200.schedule import BatchSchedule, ScheduleStep
+
+    d = str(tmp_path)
+    rng = np.random.default_rng(0)
+    for name, base in (("a", 100), ("b", 400), ("c", 700)):
+        with open(f"{d}/{name}.jsonl", "w") as f:
+            for _ in range(120):
+                f.write(json.dumps({"text": " ".join(str(base + int(x)) for x in rng.integers(0, 250, size=int(rng.integers(3, 30))))}) + "\n")
+
+    def build():
+        return cfg.decode(LMMixtureDatasetConfig, {
+            "tokenizer": "passthrough", "vocab_size": 1000, "cache_dir": f"{d}/cache", "mixture_block_size": 8, "shuffle": True,
+            "configs": {n: {"train_urls": [f"{d}/{n}.jsonl"]} for n in "abc"},
+            "train_weights": [[0, {"a": 0.75, "b": 0.25, "c": 0.0}], [6, {"a": 0.25, "b": 0.25, "c": 0.5}]]})
+
+    sched = BatchSchedule([ScheduleStep(0, 4), ScheduleStep(4, 8)])
+    ds = build().train_set(16, sched, key=5)
+    loader = DataLoader(ds, sched, max_buffered_batches=0, pin_memory=False)
+    it = iter(loader)
+    straight = [next(it).tokens.clone() for _ in range(10)]
+    assert [b.shape[0] for b in straight] == [4] * 4 + [8] * 6
+    for k in (1, 4, 7, 9):
+        resumed = loader.iter_from_step(k)
+        assert torch.equal(next(resumed).tokens, straight[k]), k
+    fresh = DataLoader(build().train_set(16, sched, key=5), sched, max_buffered_batches=4, pin_memory=False).iter_from_step(6)
+    assert torch.equal(next(fresh).tokens, straight[6]) and torch.equal(next(fresh).tokens, straight[7])
+    other_key = DataLoader(build().train_set(16, sched, key=6), sched, max_buffered_batches=0, pin_memory=False)
+    assert not torch.equal(next(iter(other_key)).tokens, straight[0])
+    # the stage change at step 6 (= sequence 4 * 4 + 2 * 8 = 32, a block boundary) shows in the sources of the tokens
+    share_c = [float(((b >= 700) & (b < 950)).float().mean()) for b in straight]
+    assert max(share_c[:6]) == 0.0 and min(share_c[6:]) > 0.2
