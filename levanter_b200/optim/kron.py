@@ -10,7 +10,6 @@ into ``block_size`` blocks and small dims merged up to ``target_merged_dim_size`
 from __future__ import annotations
 
 import math
-import random
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, NamedTuple, Optional, Tuple, Union
 
@@ -86,9 +85,16 @@ def _solve_Q(Qs, x):
     return x
 
 
-def _update_precond(Qs, g, lr: float):
-    """One PSGD step on every factor: ``A = Q g`` (all modes), ``B = Q^-T v``-style conjugate with the probe folded into g."""
-    v = torch.randn_like(g)
+def _update_precond(Qs, g, lr: float, probe_seed: Optional[int] = None):
+    """One PSGD step on every factor: ``A = Q g`` (all modes), ``B = Q^-T v``-style conjugate with the probe folded into g.
+    The probe is drawn from a generator seeded with ``probe_seed`` (a function of the optimizer's seed, the step and the
+    leaf), so a resumed run and every rank draw the probes an uninterrupted run would."""
+    if probe_seed is None:
+        v = torch.randn_like(g)
+    else:
+        gen = torch.Generator(device=g.device)
+        gen.manual_seed(probe_seed)
+        v = torch.randn(g.shape, generator=gen, device=g.device, dtype=g.dtype)
     gn = g + math.sqrt(torch.finfo(torch.float32).eps) * g.abs().mean() * v
     A = _apply_Q(Qs, gn)
     Bc = _solve_Q(Qs, v)
@@ -112,7 +118,6 @@ def scale_by_kron(b1: float = 0.9, normalize_grads: bool = False,
                   preconditioner_lr: float = 0.1, preconditioner_init_scale: float = 1.0, merge_small_dims: bool = False,
                   target_merged_dim_size: int = 2048, partition_grads_into_blocks: bool = False, block_size: int = 256,
                   seed: int = 0) -> GradientTransformation:
-    rng = random.Random(seed)
 
     def plan(p):
         shape = tuple(p.shape)
@@ -144,7 +149,7 @@ def scale_by_kron(b1: float = 0.9, normalize_grads: bool = False,
         if do_update:
             counter -= 1.0
         out = dict(updates)
-        for k in T.tree_keys(updates):
+        for leaf_index, k in enumerate(T.tree_keys(updates)):
             g = updates[k].float()
             if normalize_grads:
                 g = g / (g.norm() + 1e-16)
@@ -154,10 +159,11 @@ def scale_by_kron(b1: float = 0.9, normalize_grads: bool = False,
             shape = plan(g)
             m2 = mhat.reshape(shape)
             res = torch.empty_like(m2)
-            for bs, Qs in zip(block_slices(shape), state.Qs[k]):
+            for block_index, (bs, Qs) in enumerate(zip(block_slices(shape), state.Qs[k])):
                 blk = m2[bs]
                 if do_update:
-                    _update_precond(Qs, blk, preconditioner_lr)
+                    probe_seed = (seed * 1_000_003 + count * 7_919 + leaf_index * 104_729 + block_index) % (2 ** 63 - 1)
+                    _update_precond(Qs, blk, preconditioner_lr, probe_seed)
                 # P mu = Q^T (Q mu)
                 res[bs] = _apply_Q(Qs, _apply_Q(Qs, blk), transpose_first=True)
             out[k] = res.reshape(updates[k].shape).to(updates[k].dtype)
