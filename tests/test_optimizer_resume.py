@@ -16,7 +16,7 @@ VOCAB = 64
 OPTIMIZERS = ["adam", "adopt", "cautious", "kron", "lion", "mars", "mini", "muon", "rmsprop", "scion", "soap", "sophia-h"]
 
 
-def _run(tmp, steps, opt_name):
+def _run(tmp, steps, opt_name, dropout=False):
     cfg = C.decode(TrainerConfig, {"num_train_steps": steps, "train_batch_size": 8, "require_accelerator": False, "tracker": {"type": "noop"},
                                    "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"}})
     g = torch.Generator().manual_seed(0)
@@ -25,6 +25,10 @@ def _run(tmp, steps, opt_name):
     extra = {"update_interval": 2} if opt_name == "sophia-h" else {"precondition_frequency": 2} if opt_name == "soap" else {}
     opt = C.decode(OptimizerConfig, {"type": opt_name, "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.01, "lr_schedule": "constant", "min_lr_ratio": 1.0, **extra})  # (a schedule that does not depend on the run length)
     mc = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
+    if dropout:
+        from levanter_b200.models.gpt2 import Gpt2Config
+
+        mc = Gpt2Config(seq_len=16, hidden_dim=32, num_layers=2, num_heads=2, gradient_checkpointing=False, resid_pdrop=0.2, embed_pdrop=0.1, attn_pdrop=0.1)
     losses = {}
     with Trainer(cfg, opt, compute_next_token_loss) as trainer:
         state = trainer.initial_state(0, model_init=lambda: mc.build(VOCAB, seed=3))
@@ -45,3 +49,16 @@ def test_an_interrupted_run_continues_as_if_it_had_not_stopped(tmp_path, opt_nam
     assert [losses[i] for i in (3, 4, 5)] == pytest.approx([full_losses[i] for i in (3, 4, 5)], rel=2e-5, abs=2e-5)
     for n in full_params:
         assert torch.allclose(params[n], full_params[n], atol=2e-5), n
+
+
+def test_dropout_masks_are_a_function_of_the_step_so_resuming_does_not_change_them(tmp_path):
+    d = str(tmp_path)
+    _, full_losses, full_params = _run(d + "/full", 6, "adam", dropout=True)
+    _, no_dropout, _ = _run(d + "/plain", 6, "adam", dropout=False)
+    _run(d + "/run", 3, "adam", dropout=True)
+    first, losses, params = _run(d + "/run", 6, "adam", dropout=True)
+    assert first == 3 and [losses[i] for i in (3, 4, 5)] == pytest.approx([full_losses[i] for i in (3, 4, 5)], rel=2e-5, abs=2e-5)
+    for n in full_params:
+        assert torch.allclose(params[n], full_params[n], atol=2e-5), n
+    again = _run(d + "/again", 6, "adam", dropout=True)[1]
+    assert [again[i] for i in range(6)] == pytest.approx([full_losses[i] for i in range(6)], abs=1e-6)  # and the same from run to run
