@@ -394,7 +394,13 @@ def _load_trainer_state(state, checkpoint_path: str, *, allow_partial: bool):
                 lo, fo, n = engine.segments[name]
                 slot = next(s for s in engine.slots if s.name == name)
                 a = fo - slot.offset
-                leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype))
+                leaf.copy_(full.reshape(-1)[a:a + n].to(device=leaf.device, dtype=leaf.dtype).reshape(leaf.shape))
+            if hasattr(state.model_averaging, "tot_weight"):  # the running weight of the decay phase is state too
+                w = tss.read_leaf(checkpoint_path, "model_averaging.tot_weight")
+                if w is not None:
+                    state.model_averaging.tot_weight = float(w.item())
+                else:
+                    missing.append("model_averaging.tot_weight")
     engine.sync_streamed_from_master()  # fully sharded layers: peers gather from the compute-dtype rows, refresh them
     step = tss.read_leaf(checkpoint_path, "step")
     if step is None:

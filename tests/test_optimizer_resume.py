@@ -16,9 +16,10 @@ VOCAB = 64
 OPTIMIZERS = ["adam", "adopt", "cautious", "kron", "lion", "mars", "mini", "muon", "rmsprop", "scion", "soap", "sophia-h"]
 
 
-def _run(tmp, steps, opt_name, dropout=False):
+def _run(tmp, steps, opt_name, dropout=False, averaging=None, return_average=False):
     cfg = C.decode(TrainerConfig, {"num_train_steps": steps, "train_batch_size": 8, "require_accelerator": False, "tracker": {"type": "noop"},
-                                   "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"}})
+                                   "log_dir": f"{tmp}/logs", "id": "t", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"},
+                                   **({"model_averaging": averaging} if averaging else {})})
     g = torch.Generator().manual_seed(0)
     starts = torch.randint(0, VOCAB, (128,), generator=g)
     data = ListAsyncDataset([LmExample.causal(((s + torch.arange(16)) % VOCAB).to(torch.int32)) for s in starts], is_complete=True)
@@ -35,6 +36,8 @@ def _run(tmp, steps, opt_name, dropout=False):
         first = int(state.step)
         trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
         info = trainer.train(state, trainer.data_loader(data).iter_from_step(first))
+        if return_average:
+            return first, losses, {n: p.detach().clone() for n, p in info.state.eval_model.named_parameters()}
     return first, losses, {n: p.detach().clone() for n, p in info.state.model.named_parameters()}
 
 
@@ -62,3 +65,16 @@ def test_dropout_masks_are_a_function_of_the_step_so_resuming_does_not_change_th
         assert torch.allclose(params[n], full_params[n], atol=2e-5), n
     again = _run(d + "/again", 6, "adam", dropout=True)[1]
     assert [again[i] for i in range(6)] == pytest.approx([full_losses[i] for i in range(6)], abs=1e-6)  # and the same from run to run
+
+
+@pytest.mark.parametrize("averaging", [{"type": "ema", "beta": 0.5}, {"type": "ema_decay_sqrt", "beta": 0.5, "switch_step": 2, "decay_steps": 6}])
+def test_the_averaged_weights_resume_too(tmp_path, averaging):
+    d = str(tmp_path)
+    _, _, full_avg = _run(d + "/full", 6, "adam", averaging=averaging, return_average=True)
+    _, _, full_raw = _run(d + "/raw", 6, "adam", averaging=averaging)
+    assert any(not torch.allclose(full_avg[n], full_raw[n], atol=1e-4) for n in full_avg)  # the average lags behind the weights
+    _run(d + "/run", 3, "adam", averaging=averaging)
+    first, _, avg = _run(d + "/run", 6, "adam", averaging=averaging, return_average=True)
+    assert first == 3
+    for n in full_avg:
+        assert torch.allclose(avg[n], full_avg[n], atol=2e-5), n
