@@ -26,7 +26,7 @@ def _init(rank, world, port, timeout_s=60):
     return dist
 
 
-def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None):
+def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, return_average=False):
     from levanter_b200 import config as C
     from levanter_b200.data.dataset import ListAsyncDataset
     from levanter_b200.models.llama import LlamaConfig
@@ -57,6 +57,8 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
         if expect_stage is not None:
             assert state.engine.zero_stage == expect_stage, state.engine.zero_stage
         info = trainer.train(state, trainer.data_loader(data).iter_from_step(int(state.step)))
+        if return_average:  # the averaged weights, whole on every rank
+            return {k: v.detach().clone() for k, v in info.state.eval_model.named_parameters()}, [losses[k] for k in sorted(losses)]
         if expect_stage == 3:
             st = state.engine.stream
             assert st is not None and st.stats["library_weight_grads"] > 0
@@ -202,6 +204,32 @@ def test_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
     assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=3e-5)
     for k, v in full.items():
         assert torch.allclose(v, resumed[k], atol=3e-5), k
+
+
+def _second_half_average_worker(rank, world, port, tmp, extra):
+    dist = _init(rank, world, port)
+    try:
+        avg, tail = _train(tmp, steps=6, trainer_extra=extra, return_average=True)
+        if rank == 0:
+            torch.save({"avg": avg, "tail": tail}, f"{tmp}/avg.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_averaged_weights_written_by_two_ranks_resume_on_one_and_on_two(tmp_path):
+    extra = {"model_averaging": {"type": "ema", "beta": 0.5}}
+    full, losses = _train(str(tmp_path / "full"), steps=6, trainer_extra=extra, return_average=True)
+    for name in ("one", "two"):
+        mp.spawn(_first_half_worker, args=(2, 29717, str(tmp_path / name), 32, extra), nprocs=2, join=True)
+    resumed, tail = _train(str(tmp_path / "one"), steps=6, trainer_extra=extra, return_average=True)
+    assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=3e-5)
+    for k, v in full.items():
+        assert torch.allclose(v, resumed[k], atol=3e-5), k
+    mp.spawn(_second_half_average_worker, args=(2, 29718, str(tmp_path / "two"), extra), nprocs=2, join=True)
+    got = torch.load(tmp_path / "two" / "avg.pt")
+    assert len(got["tail"]) == 3 and got["tail"] == pytest.approx(losses[3:], abs=3e-5)
+    for k, v in full.items():
+        assert torch.allclose(v, got["avg"][k], atol=3e-5), k
 
 
 def _loader_worker(rank, world, port, tmp):
