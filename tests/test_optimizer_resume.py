@@ -13,7 +13,7 @@ from levanter_b200.optim import OptimizerConfig
 from levanter_b200.trainer import Trainer, TrainerConfig
 
 VOCAB = 64
-OPTIMIZERS = ["adam", "adopt", "cautious", "kron", "lion", "mars", "mini", "muon", "rmsprop", "scion", "soap", "sophia-h"]
+OPTIMIZERS = ["adam", "adam+windows", "adopt", "cautious", "kron", "lion", "mars", "mini", "muon", "rmsprop", "scion", "soap", "sophia-h"]
 
 
 def _run(tmp, steps, opt_name, dropout=False, averaging=None, return_average=False):
@@ -24,6 +24,8 @@ def _run(tmp, steps, opt_name, dropout=False, averaging=None, return_average=Fal
     starts = torch.randint(0, VOCAB, (128,), generator=g)
     data = ListAsyncDataset([LmExample.causal(((s + torch.arange(16)) % VOCAB).to(torch.int32)) for s in starts], is_complete=True)
     extra = {"update_interval": 2} if opt_name == "sophia-h" else {"precondition_frequency": 2} if opt_name == "soap" else {}
+    if opt_name == "adam+windows":  # Adam with every stateful wrapper: skip-step window, update-norm window, RMS clipping
+        opt_name, extra = "adam", {"skip_bad_steps": 4, "clip_update_norm": {"rolling_interval_length": 4, "sigma_factor": 2.0}, "update_rms_clipping": 1.0}
     opt = C.decode(OptimizerConfig, {"type": opt_name, "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.01, "lr_schedule": "constant", "min_lr_ratio": 1.0, **extra})  # (a schedule that does not depend on the run length)
     mc = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
     if dropout:
