@@ -121,6 +121,16 @@ def _sophia_gradient_transform(sophia_hess_fn, update_interval: int, b1: float, 
         hessian_count, key = state.hessian_count, state.hess_key
         if count % update_interval == 0:
             new_hess = sophia_hess_fn(obj_fn, params, hess_key=key)
+            groups = T.objective_reduce_group()
+            if groups:
+                # obj_fn is the loss of this rank's part of the batch and the probe is the same on every rank (same key): the
+                # estimate for the whole batch is the mean over the ranks
+                import torch.distributed as dist
+
+                for k in keys:
+                    if k in new_hess:
+                        for group in groups:
+                            dist.all_reduce(new_hess[k], op=dist.ReduceOp.AVG, group=group)
             for k in keys:
                 if k in new_hess:
                     state.h[k].mul_(b2).add_(new_hess[k].to(state.h[k].dtype), alpha=1 - b2)

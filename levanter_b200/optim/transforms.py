@@ -64,6 +64,21 @@ def set_norm_reduce_group(group) -> None:
     _dist_group = group
 
 
+_objective_group = None
+
+
+def set_objective_reduce_group(group) -> None:
+    """Process groups (a list, one per mesh axis) whose ranks each hold a different part of the step's batch.  A transformation that differentiates the
+    batch objective itself (Sophia's Hessian estimate) averages its result over it, so that replicated optimizer state stays
+    the same on every rank.  ``None`` clears."""
+    global _objective_group
+    _objective_group = group
+
+
+def objective_reduce_group():
+    return _objective_group
+
+
 _model_group = None
 _model_sharded: Optional[set] = None
 

@@ -501,6 +501,8 @@ class ShardedEngine:
             # unsharded optimizer on several data ranks: every rank holds the same gradients, so matrix-valued work
             # (Newton-Schulz) is dealt out over them instead of being repeated on each
             set_layer_parallel_group(self.data_group if (self.world > 1 and not self.shard_optimizer) else None)
+            batch_groups = [g for g in (self.data_group if self.world > 1 else None, self.replica_group) if g is not None]
+            T.set_objective_reduce_group(batch_groups or None)
             if self.model_group is not None:
                 # tensor parallelism: norms count a sliced weight's parts on all model ranks and a replicated weight once
                 T.set_model_parallel_norm(self.model_group, [s.name for s in self.slots if getattr(s.param, "tp_dim", None) is not None])
@@ -508,6 +510,7 @@ class ShardedEngine:
                 updates, self.opt_state = self.opt.update(grads, self.opt_state, params, loss=loss, **extra)
             finally:
                 T.set_norm_reduce_group(None)
+                T.set_objective_reduce_group(None)
                 set_layer_parallel_group(None)
                 T.set_model_parallel_norm(None, None)
             T.apply_updates(params, updates)

@@ -576,6 +576,10 @@ class Trainer:
             extra = {}
             if getattr(self.optimizer_config, "needs_objective", False):
                 extra["obj_fn"] = self._batch_objective(model, micro, batch_kwargs)
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                # before the optimizer sees it: a wrapper that judges the step by its loss (skip-step) must reach the same
+                # verdict on every rank, so it gets the loss of the whole batch, not of this rank's part
+                dist.all_reduce(loss_acc, op=dist.ReduceOp.AVG)
             engine.step(loss=loss_acc, **extra)
             if state.model_averaging is not None:
                 state.model_averaging.update(engine.master_tree(), state.step)
@@ -586,8 +590,6 @@ class Trainer:
             if engine.last_grad_norm is not None:
                 trk.jit_log({"grad/norm/total": engine.last_grad_norm})
         state.step += 1
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(loss_acc, op=dist.ReduceOp.AVG)
         return loss_acc, jit_metrics, cb_infos
 
     def _batch_objective(self, model: nn.Module, micro: List[Any], batch_kwargs) -> Callable[[Dict[str, torch.Tensor]], torch.Tensor]:

@@ -84,10 +84,10 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
 
 
-def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None):
+def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, steps=3):
     dist = _init(rank, world, port)
     try:
-        params, losses = _train(tmp, opt_dict=opt_dict, trainer_extra=trainer_extra, hidden=hidden, expect_stage=expect_stage)
+        params, losses = _train(tmp, steps=steps, opt_dict=opt_dict, trainer_extra=trainer_extra, hidden=hidden, expect_stage=expect_stage)
         if rank == 0:
             torch.save({"params": params, "losses": losses}, f"{tmp}/dist.pt")
     finally:
@@ -339,3 +339,35 @@ def test_failure_marker_carries_the_reason_to_the_peers(tmp_path):
         p.join(timeout=5)
     out = json.load(open(tmp_path / "out.json"))
     assert "rank 1 failed" in out["message"] and "loss is NaN" in out["message"] and out["after"] < 5
+
+
+@pytest.mark.parametrize("index,opt", list(enumerate(["lion", "soap", "kron", "mini", "adopt", "cautious", "mars", "rmsprop", "scion", "sophia-h"])))
+def test_every_other_optimizer_on_two_data_ranks_matches_single_process(tmp_path, index, opt):
+    """Whatever the optimizer keeps (moments on slices, whole-matrix preconditioners, per-group scalars, Hessian estimates), two
+    data ranks take the steps one process takes."""
+    extra = {"update_interval": 2} if opt == "sophia-h" else {"precondition_frequency": 2} if opt == "soap" else {}
+    od = {"type": opt, "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0, **extra}
+    single, losses = _train(str(tmp_path / "single"), opt_dict=od)
+    mp.spawn(_sharded_worker, args=(2, 29750 + index, str(tmp_path), od), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=1e-4)
+    for k, v in single.items():
+        if opt == "adopt":
+            # the second step divides by |first gradient| with no clipping: where that is almost zero, the last bit of the gradient
+            # (summed in another order on two ranks) decides the size of the step, so a few elements move apart
+            assert float(((v - got["params"][k]).abs() > 1e-4).float().mean()) < 0.01, k
+        else:
+            assert torch.allclose(v, got["params"][k], atol=1e-4), k
+
+
+def test_skip_step_reaches_the_same_verdicts_on_two_ranks_as_on_one(tmp_path):
+    """The skip-step wrapper judges a step by the loss of the whole batch: with a zero-sigma window (a step is dropped as soon
+    as its loss or gradient norm is above the window's mean) two data ranks drop the same steps as one process."""
+    od = {"type": "adam", "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0,
+          "skip_bad_steps": {"rolling_interval_length": 4, "sigma_factor": 0.0}}
+    single, losses = _train(str(tmp_path / "single"), steps=8, opt_dict=od)
+    mp.spawn(_sharded_worker, args=(2, 29761, str(tmp_path), od, None, 32, None, 8), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=1e-4)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=1e-4), k
