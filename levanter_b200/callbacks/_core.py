@@ -74,6 +74,13 @@ class JitCallback(abc.ABC, Generic[S, M]):
     def inside_step(self, state: S, grads: Any) -> M:
         ...
 
+    # True: the engine keeps the step's parameter change (``engine.last_updates``) and ``after_update`` is called with it
+    wants_updates = False
+
+    def after_update(self, state: S, engine: Any, cb_info: M) -> M:
+        """Called after the optimizer step of a step for which ``inside_step`` ran; returns the (extended) result."""
+        return cb_info
+
     @abc.abstractmethod
     def on_step(self, step_info: StepInfo[S], cb_info: M):
         ...

@@ -27,13 +27,25 @@ class WatchCallback(JitCallback):
         self.include_histogram = config.include_histograms
         self.split_scan_layers = config.split_scan_layers
 
-    def inside_step(self, state, engine) -> Dict[str, Any]:
-        out: Dict[str, Any] = {}
+    @property
+    def wants_updates(self) -> bool:
+        return "updates" in self.watch_targets
+
+    def _stats_kwargs(self, engine) -> Dict[str, Any]:
         group = engine.data_group if (engine.world > 1 and engine.shard_optimizer) else None
         sharded = group is not None
-        kw = dict(split_scan_layers=self.split_scan_layers, include_histogram=self.include_histogram,
-                  include_norms=self.include_norms, include_per_parameter_norms=self.include_per_parameter_norms,
-                  group=group, sharded=sharded, all_names=[s.name for s in engine.slots] if sharded else None)
+        return dict(split_scan_layers=self.split_scan_layers, include_histogram=self.include_histogram,
+                    include_norms=self.include_norms, include_per_parameter_norms=self.include_per_parameter_norms,
+                    group=group, sharded=sharded, all_names=[s.name for s in engine.slots] if sharded else None)
+
+    def after_update(self, state, engine, cb_info: Dict[str, Any]) -> Dict[str, Any]:
+        # the change the optimizer made to the weights in this step: learning rate and weight decay included
+        cb_info.update(summary_statistics_for_tree("updates", engine.last_updates, **self._stats_kwargs(engine)))
+        return cb_info
+
+    def inside_step(self, state, engine) -> Dict[str, Any]:
+        out: Dict[str, Any] = {}
+        kw = self._stats_kwargs(engine)
         if "grads" in self.watch_targets:
             # gradients in the accumulator are not yet reduced over data ranks at this point; use local full grads
             g = {s.name: s.param.main_grad for s in engine.slots if getattr(s.param, "main_grad", None) is not None}

@@ -121,6 +121,8 @@ class ShardedEngine:
         self.opt_state = None
         self.fused_adam: Optional["FusedAdamW"] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self.capture_updates = False  # set by a hook before a step whose parameter change it wants to read
+        self.last_updates: Optional[Dict[str, torch.Tensor]] = None
 
     # ------------------------------------------------------------------------------------------ layout
     def _build_layout(self, is_trainable, bucket_of):
@@ -486,6 +488,7 @@ class ShardedEngine:
     def step(self, *, grad_scale: float = 1.0, loss: Optional[torch.Tensor] = None, **extra) -> None:
         """collect -> reduce -> optimizer update on owned slices -> refresh compute-dtype parameters everywhere."""
         self.collect_grads()
+        before = self.master.clone() if self.capture_updates else None
         if self.stream is not None and self.stream.peer:
             # peers may still be pulling this rank's weight rows for their last layers: nobody overwrites rows before all are done
             self.stream._sym_w.barrier(0)
@@ -514,6 +517,11 @@ class ShardedEngine:
                 set_layer_parallel_group(None)
                 T.set_model_parallel_norm(None, None)
             T.apply_updates(params, updates)
+        if before is not None:
+            # what this step added to the owned master slices (weight decay and learning rate included), for hooks that watch it
+            delta = self.master - before
+            self.last_updates = {name: self._shaped(name, delta[lo:lo + n]) for name, (lo, fo, n) in self.segments.items()}
+            self.capture_updates = False
         self.publish_params()
         if self._sym_grad is not None:
             # peers read this rank's gradients and write this rank's weights: nobody may run ahead into the next step

@@ -573,6 +573,7 @@ class Trainer:
             if self.hooks.stateful_hooks:
                 engine.collect_grads()
                 cb_infos = self.hooks.run_jit_hooks(state, engine, state.step)
+                engine.capture_updates = any(c is not None and h.fn.wants_updates for h, c in zip(self.hooks.stateful_hooks, cb_infos))
             extra = {}
             if getattr(self.optimizer_config, "needs_objective", False):
                 extra["obj_fn"] = self._batch_objective(model, micro, batch_kwargs)
@@ -581,6 +582,10 @@ class Trainer:
                 # verdict on every rank, so it gets the loss of the whole batch, not of this rank's part
                 dist.all_reduce(loss_acc, op=dist.ReduceOp.AVG)
             engine.step(loss=loss_acc, **extra)
+            if cb_infos is not None and engine.last_updates is not None:
+                cb_infos = [h.fn.after_update(state, engine, c) if (c is not None and h.fn.wants_updates) else c
+                            for h, c in zip(self.hooks.stateful_hooks, cb_infos)]
+                engine.last_updates = None
             if state.model_averaging is not None:
                 state.model_averaging.update(engine.master_tree(), state.step)
             if engine.fused_adam is not None:

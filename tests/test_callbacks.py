@@ -65,7 +65,7 @@ def test_watch_hook_and_default_metrics_through_a_trainer(tmp_path):
     cfg = C.decode(TrainerConfig, {"num_train_steps": 4, "train_batch_size": 8, "require_accelerator": False, "tracker": {"type": "noop"},
                                    "log_dir": f"{tmp_path}/logs", "id": "w", "steps_per_eval": 2, "max_eval_batches": 2, "per_device_eval_parallelism": 4,
                                    "checkpointer": {"base_path": f"{tmp_path}/ckpt", "save_interval": "10h"},
-                                   "watch": {"watch_targets": "grads,params,opt_state", "interval": 2, "include_histograms": True}})
+                                   "watch": {"watch_targets": "grads,params,opt_state,updates", "interval": 2, "include_histograms": True}})
     mc = LlamaConfig(seq_len=16, hidden_dim=32, intermediate_dim=64, num_layers=2, num_heads=2, num_kv_heads=2, gradient_checkpointing=False)
     with T.current_tracker(rec):
         with Trainer(cfg, AdamConfig(learning_rate=1e-3, warmup=0.0, max_grad_norm=None), compute_next_token_loss) as trainer:
@@ -79,7 +79,12 @@ def test_watch_hook_and_default_metrics_through_a_trainer(tmp_path):
     assert any(k.startswith("params/norm/transformer/layers/1/") for k in watched)
     assert any(k.startswith("opt_state/") and k.endswith("/norm/total") for k in watched)
     assert isinstance(watched["grad/hist/transformer/layers/0/self_attn/q_proj/weight"], Histogram)
-    assert "grad/norm/total" not in rec.logged[1]  # every second step only
+    # the change of the weights in that step: with Adam and no decay every element moves by about the learning rate
+    upd = float(watched["updates/norm/total"])
+    n_params = sum(p.numel() for p in state.model.parameters())
+    assert 0.2e-3 * n_params ** 0.5 < upd < 1.01e-3 * n_params ** 0.5
+    assert any(k.startswith("updates/norm/transformer/layers/0/") for k in watched)
+    assert "grad/norm/total" not in rec.logged[1] and "updates/norm/total" not in rec.logged[1]  # every second step only
     assert "eval/tiny/loss" in rec.logged[2] and "eval/tiny/loss" not in rec.logged[1] and rec.logged[2]["eval/tiny/loss"] > 0
     for step in (1, 2, 3):
         m = rec.logged[step]
