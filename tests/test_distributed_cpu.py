@@ -371,3 +371,53 @@ def test_skip_step_reaches_the_same_verdicts_on_two_ranks_as_on_one(tmp_path):
     assert got["losses"] == pytest.approx(losses, abs=1e-4)
     for k, v in single.items():
         assert torch.allclose(v, got["params"][k], atol=1e-4), k
+
+
+def _tagged_eval(tmp, trainer_extra=None, hidden=32):
+    from levanter_b200 import config as C
+    from levanter_b200.data.dataset import ListAsyncDataset
+    from levanter_b200.eval import TaggedEvaluator
+    from levanter_b200.models.llama import LlamaConfig
+    from levanter_b200.models.lm_model import LmExample, compute_next_token_loss
+    from levanter_b200.optim import AdamConfig
+    from levanter_b200.trainer import Trainer, TrainerConfig
+
+    cfg = C.decode(TrainerConfig, {"num_train_steps": 1, "train_batch_size": 8, "require_accelerator": False, "tracker": {"type": "noop"},
+                                   "log_dir": f"{tmp}/logs", "id": "e", "seed": 1, "checkpointer": {"base_path": f"{tmp}/ckpt", "save_interval": "10h"},
+                                   **(trainer_extra or {})})
+    g = torch.Generator().manual_seed(5)
+
+    def examples(n):
+        return ListAsyncDataset([LmExample.causal(torch.randint(0, VOCAB, (16,), generator=g, dtype=torch.int32)) for _ in range(n)], is_complete=True)
+
+    sets = [(examples(7), ["web/a"]), (examples(6), ["web/b"]), (examples(1), ["code"])]  # 14 examples: the last batch of 4 is ragged
+    mcfg = LlamaConfig(seq_len=16, hidden_dim=hidden, intermediate_dim=2 * hidden, num_layers=3 if hidden > 32 else 2, num_heads=2, num_kv_heads=2,
+                       gradient_checkpointing=False)
+    with Trainer(cfg, AdamConfig(), compute_next_token_loss) as trainer:
+        state = trainer.initial_state(0, model_init=lambda: mcfg.build(VOCAB, seed=3))
+        ev = TaggedEvaluator(4, sets, device_mesh=trainer.device_mesh if cfg.num_devices > 1 else None)
+        r = ev.evaluate(state.model)
+    return {"micro": r.micro_avg_loss, "macro": r.macro_avg_loss, **{f"tag/{k}": v for k, v in r.tag_micro_losses.items()},
+            **{f"macro/{k}": v for k, v in r.tag_macro_losses.items()}}
+
+
+def _tagged_eval_worker(rank, world, port, tmp, trainer_extra, hidden):
+    dist = _init(rank, world, port)
+    try:
+        torch.save(_tagged_eval(tmp, trainer_extra, hidden), f"{tmp}/eval{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("port,extra,hidden", [(29771, None, 32), (29772, {"zero_stage": 3}, 64)])
+def test_tagged_evaluation_on_two_ranks_equals_one_process(tmp_path, port, extra, hidden):
+    """Every rank scores its part of each evaluation batch (the last one is ragged) and the sums are reduced: overall, per-tag and
+    parent-tag losses equal one process, on every rank, also when the layers are gathered from row slices during the forward pass."""
+    single = _tagged_eval(str(tmp_path / "single"), None, hidden)
+    assert {"tag/web/a", "tag/web/b", "tag/code", "tag/web", "macro/web"} <= set(single)
+    mp.spawn(_tagged_eval_worker, args=(2, port, str(tmp_path), extra, hidden), nprocs=2, join=True)
+    for rank in range(2):
+        got = torch.load(tmp_path / f"eval{rank}.pt")
+        assert set(got) == set(single)
+        for k, v in single.items():
+            assert got[k] == pytest.approx(v, rel=1e-5), (rank, k)
