@@ -26,7 +26,7 @@ def _init(rank, world, port, timeout_s=60):
     return dist
 
 
-def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, return_average=False):
+def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, return_average=False, lora=False):
     from levanter_b200 import config as C
     from levanter_b200.data.dataset import ListAsyncDataset
     from levanter_b200.models.llama import LlamaConfig
@@ -52,7 +52,13 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
         from levanter_b200.parallel.tp import build_sharded_from_seed, gather_full_state
 
         tp = trainer.tensor_parallel
-        state = trainer.initial_state(0, model_init=lambda: build_sharded_from_seed(lambda tp: mcfg.build(VOCAB, seed=3, tp=tp), tp))
+        if lora:  # adapters on the attention projections; only they train
+            from levanter_b200.lora import LoraConfig, lora_trainable_params_filter, loraize
+
+            model = loraize(mcfg.build(VOCAB, seed=3), LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj"]), seed=11)
+            state = trainer.initial_state(0, model=model, is_trainable=lora_trainable_params_filter(model))
+        else:
+            state = trainer.initial_state(0, model_init=lambda: build_sharded_from_seed(lambda tp: mcfg.build(VOCAB, seed=3, tp=tp), tp))
         trainer.add_hook(lambda info: losses.__setitem__(info.step, float(info.loss)), every=1)
         if expect_stage is not None:
             assert state.engine.zero_stage == expect_stage, state.engine.zero_stage
@@ -84,10 +90,10 @@ def _train(tmp, steps=3, batch=8, opt_dict=None, trainer_extra=None, hidden=32, 
     return {k: v.detach().clone() for k, v in info.state.model.named_parameters()}, [losses[k] for k in sorted(losses)]
 
 
-def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, steps=3):
+def _sharded_worker(rank, world, port, tmp, opt_dict=None, trainer_extra=None, hidden=32, expect_stage=None, steps=3, lora=False):
     dist = _init(rank, world, port)
     try:
-        params, losses = _train(tmp, steps=steps, opt_dict=opt_dict, trainer_extra=trainer_extra, hidden=hidden, expect_stage=expect_stage)
+        params, losses = _train(tmp, steps=steps, opt_dict=opt_dict, trainer_extra=trainer_extra, hidden=hidden, expect_stage=expect_stage, lora=lora)
         if rank == 0:
             torch.save({"params": params, "losses": losses}, f"{tmp}/dist.pt")
     finally:
@@ -421,3 +427,15 @@ def test_tagged_evaluation_on_two_ranks_equals_one_process(tmp_path, port, extra
         assert set(got) == set(single)
         for k, v in single.items():
             assert got[k] == pytest.approx(v, rel=1e-5), (rank, k)
+
+
+def test_lora_training_on_two_ranks_matches_single_process(tmp_path):
+    """Only the adapters train: the frozen base weights stay bit-identical, the adapters take the same steps on two data ranks as
+    on one process."""
+    single, losses = _train(str(tmp_path / "single"), steps=4, lora=True)
+    mp.spawn(_sharded_worker, args=(2, 29781, str(tmp_path), None, None, 32, None, 4, True), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5) and losses[-1] < losses[0]
+    assert any("lora" in k.lower() for k in single)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
