@@ -439,3 +439,15 @@ def test_lora_training_on_two_ranks_matches_single_process(tmp_path):
     assert any("lora" in k.lower() for k in single)
     for k, v in single.items():
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+def test_batch_size_schedule_with_accumulation_on_two_ranks_matches_single_process(tmp_path):
+    """The batch grows from 4 to 8 sequences at step 2 and every rank takes two sequences per micro-batch: one process accumulates
+    2 then 4 micro-batches, two ranks 1 then 2 each, and both take the same steps."""
+    extra = {"train_batch_size": [{"start": 0, "value": 4}, {"start": 2, "value": 8}], "per_device_parallelism": 2}
+    single, losses = _train(str(tmp_path / "single"), steps=5, trainer_extra=extra)
+    mp.spawn(_sharded_worker, args=(2, 29783, str(tmp_path), None, extra, 32, None, 5), nprocs=2, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    assert got["losses"] == pytest.approx(losses, abs=2e-5)
+    for k, v in single.items():
+        assert torch.allclose(v, got["params"][k], atol=2e-5), k
