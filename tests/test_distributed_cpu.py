@@ -184,10 +184,10 @@ def test_two_replicas_take_the_same_step_as_one_process(tmp_path):
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
 
 
-def _first_half_worker(rank, world, port, tmp, hidden=32, trainer_extra=None):
+def _first_half_worker(rank, world, port, tmp, hidden=32, trainer_extra=None, opt_dict=None):
     dist = _init(rank, world, port)
     try:
-        _train(tmp, steps=3, hidden=hidden, trainer_extra=trainer_extra)
+        _train(tmp, steps=3, hidden=hidden, trainer_extra=trainer_extra, opt_dict=opt_dict)
     finally:
         dist.destroy_process_group()
 
@@ -451,3 +451,17 @@ def test_batch_size_schedule_with_accumulation_on_two_ranks_matches_single_proce
     assert got["losses"] == pytest.approx(losses, abs=2e-5)
     for k, v in single.items():
         assert torch.allclose(v, got["params"][k], atol=2e-5), k
+
+
+@pytest.mark.parametrize("index,opt", list(enumerate(["muon", "soap", "sophia-h", "lion"])))
+def test_other_optimizers_written_by_two_ranks_resume_on_one(tmp_path, index, opt):
+    """Optimizers whose state is kept whole on every rank (matrix preconditioners, the Hessian estimate) and a sliced one: the
+    checkpoint two ranks wrote continues on one process as the uninterrupted run does."""
+    extra = {"update_interval": 2} if opt == "sophia-h" else {"precondition_frequency": 2} if opt == "soap" else {}
+    od = {"type": opt, "learning_rate": 3e-3, "warmup": 0.0, "weight_decay": 0.0, "lr_schedule": "constant", "min_lr_ratio": 1.0, **extra}
+    full, losses = _train(str(tmp_path / "full"), steps=6, opt_dict=od)
+    mp.spawn(_first_half_worker, args=(2, 29785 + index, str(tmp_path / "res"), 32, None, od), nprocs=2, join=True)
+    resumed, tail = _train(str(tmp_path / "res"), steps=6, opt_dict=od)
+    assert len(tail) == 3 and tail == pytest.approx(losses[3:], abs=1e-4)
+    for k, v in full.items():
+        assert torch.allclose(v, resumed[k], atol=1e-4), k
