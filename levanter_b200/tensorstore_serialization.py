@@ -232,8 +232,9 @@ class AsyncSerializer:
         self._pool = ThreadPoolExecutor(max_workers=max_workers)
         self._lock = threading.Lock()
         self._idle = threading.Condition(self._lock)
-        self._queue: List[Tuple[List[Future], Optional[Callable[[], None]], Optional[str], int, int, str]] = []
+        self._queue: List[Tuple[List[Future], Optional[Callable[[], None]], Optional[str], int, int, str, frozenset]] = []
         self._in_flight = 0
+        self._busy_paths: set = set()  # leaf directories that a queued or running save still writes
         self._errors: List[BaseException] = []
         self._committer: Optional[threading.Thread] = None
 
@@ -242,6 +243,14 @@ class AsyncSerializer:
         rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
         world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
         futures: List[Future] = []
+        leaves = list(leaves)
+        mine = frozenset(str(path) for i, (path, _) in enumerate(leaves) if i % world == rank)
+        with self._lock:
+            # a second save into the same directory (the same step saved again) starts by clearing each leaf's directory:
+            # it must not do that under the first save's writers
+            while self._in_flight > 0 and (mine & self._busy_paths):
+                self._idle.wait(timeout=1.0)
+            self._busy_paths |= mine
         for i, (path, leaf) in enumerate(leaves):
             t = leaf.resolve() if isinstance(leaf, DeferredLeaf) else leaf
             if i % world != rank:
@@ -261,7 +270,7 @@ class AsyncSerializer:
             dist.broadcast_object_list(box, src=0)
             nonce = box[0]
         with self._lock:
-            self._queue.append((futures, on_commit, sync_dir, rank, world, nonce))
+            self._queue.append((futures, on_commit, sync_dir, rank, world, nonce, mine))
             self._in_flight += 1
             if self._committer is None or not self._committer.is_alive():
                 self._committer = threading.Thread(target=self._commit_loop, name="checkpoint-committer", daemon=True)
@@ -277,7 +286,7 @@ class AsyncSerializer:
                         return
                 item = self._queue.pop(0)
             try:
-                self._commit_one(*item)
+                self._commit_one(*item[:6])
             except BaseException as e:  # noqa: BLE001 - reported to the thread that calls wait_until_finished
                 logger.exception("checkpoint commit failed")
                 with self._lock:
@@ -285,6 +294,7 @@ class AsyncSerializer:
             finally:
                 with self._lock:
                     self._in_flight -= 1
+                    self._busy_paths -= item[6]
                     self._idle.notify_all()
 
     def _commit_one(self, futures, cb, sync_dir, rank, world, nonce) -> None:

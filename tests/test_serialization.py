@@ -136,3 +136,19 @@ def test_dataclass_nodes_none_leaves_and_leaves_missing_on_disk(tmp_path):
         tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "m"), wants_a)
     partial = tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "m"), wants_a, allow_missing=True)
     assert torch.equal(partial.a, torch.full((10,), 4.0)) and torch.equal(partial.b, torch.zeros(10))
+
+
+def test_saves_into_the_same_directory_do_not_overlap(tmp_path):
+    """The same step saved again while the first save is still being written: the second waits for the first (it starts by clearing
+    each leaf's directory), saves into other directories go on side by side, and the last values win."""
+    manager = tss.AsyncSerializer(max_workers=8)
+    commits = []
+    for i in range(12):
+        tree = {f"w{j}": torch.full((64, 64), float(i)) for j in range(6)}
+        tss.tree_serialize_leaves_tensorstore(str(tmp_path / "same"), tree, manager, commit_callback=lambda i=i: commits.append(i))
+        tss.tree_serialize_leaves_tensorstore(str(tmp_path / f"other-{i}"), {"w": torch.full((8,), float(i))}, manager)
+    manager.wait_until_finished()
+    assert commits == list(range(12))
+    back = tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "same"), {f"w{j}": torch.zeros(64, 64) for j in range(6)})
+    assert all(float(v.min()) == float(v.max()) == 11.0 for v in back.values())
+    assert float(tss.tree_deserialize_leaves_tensorstore(str(tmp_path / "other-3"), {"w": torch.zeros(8)})["w"][0]) == 3.0
