@@ -170,3 +170,34 @@ def test_decode_state_update_tokens_stop_and_length():
     assert len(set(a.tolist())) == 3 and (a == ds.prng_keys_for(np.array([0, 0, 1]), np.array([3, 4, 3]))).all()
     ds = ds.invalidate_finished()
     assert ds.seq_lens[0] == INVALID and not ds.finished.any()
+
+
+def test_outside_references_keep_pages_alive_and_lengths_round_up_to_a_page(backend):
+    pt = _make_table(pages=8, seqs=4, page_size=4, pages_per_seq=3)
+    assert pt.current_num_seqs == 0
+    pt, a = pt.assign_seq_id_to_seq()
+    pt, b = pt.assign_seq_id_to_seq()
+    assert pt.current_num_seqs == 2 and (a, b) == (0, 1)
+    pt, _ = pt.allocate_for_seq(np.zeros(6, np.int32), np.arange(6, dtype=np.int32))
+    pages = pt.page_indices[0, :2].copy()
+    held = pt.increment_ref_counts_for_pages(pages)  # e.g. a prefix cache that keeps the pages after the sequence is gone
+    assert held.page_ref_counts[pages].tolist() == [2, 2] and pt.page_ref_counts[pages].tolist() == [1, 1]  # tables are values
+    freed = held.free_pages(0)
+    assert freed.page_ref_counts[pages].tolist() == [1, 1] and freed.num_free_pages == 8 - 2 and freed.current_num_seqs == 1
+    assert pt.free_pages(0).num_free_pages == 8
+    assert held.increment_ref_counts_for_pages([INVALID, int(pages[0])], count=2).page_ref_counts[pages].tolist() == [4, 2]  # holes are skipped
+    # 6 tokens on pages of 4: rounding up makes the next token start a fresh page
+    bumped = pt.bump_seq_len_to_next_page(0)
+    assert bumped.seq_lens[0] == 8 and pt.seq_lens[0] == 6
+    assert bumped.bump_seq_len_to_next_page(0).seq_lens[0] == 8  # already on a boundary
+    grown, info = bumped.allocate_for_seq(np.zeros(1, np.int32), np.array([8], np.int32))
+    assert grown.seq_lens[0] == 9 and is_valid_page(grown.page_indices[0, 2]) and grown.page_indices[0, 2] not in pages.tolist()
+
+
+def is_valid_page(p) -> bool:
+    return int(p) != INVALID and int(p) >= 0
+
+
+def test_relative_positions_restart_with_every_run_of_equal_ids():
+    assert PT._relative_positions(np.array([3, 3, 3, 1, 1, 3, 0, 0, 0, 0])).tolist() == [0, 1, 2, 0, 1, 0, 0, 1, 2, 3]
+    assert PT._relative_positions(np.array([7])).tolist() == [0]
