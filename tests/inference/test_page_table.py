@@ -201,3 +201,30 @@ def is_valid_page(p) -> bool:
 def test_relative_positions_restart_with_every_run_of_equal_ids():
     assert PT._relative_positions(np.array([3, 3, 3, 1, 1, 3, 0, 0, 0, 0])).tolist() == [0, 1, 2, 0, 1, 0, 0, 1, 2, 3]
     assert PT._relative_positions(np.array([7])).tolist() == [0]
+
+
+def test_decode_output_buffer_keeps_what_fits_and_accumulates_finished_flags():
+    from levanter_b200.inference.jit_scheduler import _DecodeOutputs
+
+    out = _DecodeOutputs.init(max_tokens=5, max_seqs=3, with_logprobs=True)
+    assert out.max_queued_tokens == 5 and out.empty_queue_space == 5 and out.num_tokens == 0
+    out = out.append(np.array([10, 11, 12, 99]), np.array([0, 1, 0, 2]), np.array([-0.1, -0.2, -0.3, -9.0]), 3, np.array([False, True, False]))
+    assert out.num_tokens == 3 and out.tokens[:3].tolist() == [10, 11, 12] and out.tokens[3] == INVALID  # only the first three count
+    out = out.append(np.array([13, 14, 15]), np.array([2, 2, 2]), None, 3, np.array([False, False, True]))  # room for two more
+    assert out.num_tokens == 5 and out.empty_queue_space == 0 and out.tokens.tolist() == [10, 11, 12, 13, 14]
+    assert out.slot_ids.tolist() == [0, 1, 0, 2, 2] and out.finished.tolist() == [False, True, True]
+    assert out.logprobs[:3].tolist() == pytest.approx([-0.1, -0.2, -0.3]) and np.isnan(out.logprobs[3:]).all()
+    assert _DecodeOutputs.init(4, 2, with_logprobs=False).append([1], [0], [-1.0], 1, [False, False]).logprobs is None
+
+
+def test_queue_clearing_clone_discharge_and_finished_lookup():
+    q = TokenQueue.init(6).enqueue_tokens(np.array([5, 6, 7]), np.array([0, 1, 0]), np.array([0, 0, 1]), 3)
+    assert q.num_queued_tokens == 3
+    empty = q.cleared()
+    assert empty.num_queued_tokens == 0 and empty.max_queued_tokens == 6 and q.num_queued_tokens == 3
+    st = DecodeState.init(_make_table(pages=8, seqs=4, page_size=2, pages_per_seq=2))
+    st.clone_sources[:] = [INVALID, 0, 0, 1]
+    st = st.discharge_clone(np.array([2, INVALID, 3]), 2)  # the first two entries only: slot 2 and a hole
+    assert st.clone_sources.tolist() == [INVALID, 0, INVALID, 1]
+    st.finished[:] = [True, False, False, True]
+    assert st.is_finished(3).tolist() == [True] and st.is_finished(np.array([0, 1])).tolist() == [True, False]
