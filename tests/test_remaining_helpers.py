@@ -193,3 +193,19 @@ def test_converter_reads_the_config_of_a_local_checkpoint_and_merges_overrides(t
     c = a.with_config_overrides({"max_position_embeddings": 64}, merge=False)
     assert b.config_overrides == {"rope_theta": 5.0, "max_position_embeddings": 64} and c.config_overrides == {"max_position_embeddings": 64}
     assert conv.config_overrides in (None, {})  # the original is untouched
+
+
+def test_gemma3_local_rope_and_tied_unembedding():
+    from levanter_b200.models.gemma import Gemma3Config
+    from levanter_b200.models.llama import LlamaConfig
+
+    cfg = Gemma3Config(seq_len=16, hidden_dim=16, intermediate_dim=32, num_layers=1, num_heads=2, num_kv_heads=1, head_dim=8,
+                       rope_local_base_freq=1234.0)
+    assert cfg.local_rope.theta == 1234.0 and cfg.rope.theta != 1234.0 and type(cfg.local_rope) is type(cfg.rope)
+    # the embedding module scores hidden states against its own rows (the head of a model with tied embeddings)
+    model = LlamaConfig(seq_len=8, hidden_dim=16, intermediate_dim=32, num_layers=1, num_heads=2, num_kv_heads=2,
+                        tie_word_embeddings=True).build(20, seed=0)
+    x = torch.randn(2, 3, 16)
+    emb = model.embeddings
+    assert torch.allclose(emb.unembed(x), x @ emb.token_embeddings.weight.t(), atol=1e-5)
+    assert all("lm_head" not in n for n, _ in model.named_parameters())
